@@ -1,0 +1,196 @@
+/*
+ * tsm_b200 — C ABI of the B200-native decode engine for tensomite's quantised token loop.
+ *
+ * Everything here is plain C: opaque handles, 64-bit device addresses, pointers and sizes.
+ * Each entry point names the tensomite interface it stands in for (path within the
+ * tensomite project : lines), so that a Crystal `lib` binding can replace the calls that
+ * `Tensomite::CUDA` makes today (src/tensomite/cuda.cr, src/tensomite/cuda/lib.cr).
+ *
+ * Conventions
+ *  - Every function returns a tsm_status (0 = ok).  The text of the last failure on a
+ *    context is read with tsm_last_error, as CUDA.check builds its DeviceError message
+ *    (cuda.cr:1070-1075).
+ *  - Every function binds its context's device itself and keeps no thread-local state, so
+ *    it may be called from any thread (Crystal fibers migrate: cuda.cr:1118-1125).
+ *  - Kernels never trap on bad data.  An out-of-range row id is recorded in a 3-int error
+ *    record (count, first id, limit) that tsm_sync reads and clears, returning
+ *    TSM_ERR_EXECUTION (kernels.cu:178-183, cuda.cr:967-983).
+ *  - All work of a context runs on one in-order stream (DESIGN.md:570 of the reference).
+ *  - There is no CPU implementation behind any entry point: without a CUDA device every
+ *    compute call fails with TSM_ERR_CUDA.
+ */
+#ifndef TSM_B200_H
+#define TSM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tsm_ctx tsm_ctx;     /* one device: context, stream, pool, scratch (cuda.cr:200-253) */
+typedef struct tsm_model tsm_model; /* a Llama or GPT-2 with its weights resident (models/llama.cr, models/gpt2.cr) */
+typedef struct tsm_cache tsm_cache; /* Generative::BatchCache (models/generative.cr:54-79) */
+typedef uint64_t tsm_dptr;          /* a device address, as cuda/lib.cr passes CUdeviceptr (UInt64) */
+
+typedef enum {
+    TSM_OK = 0,
+    TSM_ERR_CUDA = 1,        /* a CUDA call failed (DeviceError) */
+    TSM_ERR_ARG = 2,         /* a shape, size or pointer the call cannot take (ShapeError / ArgumentError) */
+    TSM_ERR_EXECUTION = 3,   /* a kernel met bad data, e.g. an index out of range (ExecutionError) */
+    TSM_ERR_MEMORY = 4,      /* the device has no room */
+    TSM_ERR_IO = 5,          /* a model file could not be read or is malformed (Tensomite::Error) */
+    TSM_ERR_UNSUPPORTED = 6, /* a dtype or layout this build does not handle (DTypeError) */
+    TSM_ERR_TIMEOUT = 7,     /* a bounded device-side wait ran out */
+    TSM_ERR_COMM = 8         /* the tensor-parallel communicator failed */
+} tsm_status;
+
+/* Block formats, numbered as the reference's kernels number them (kernels.cu:1160-1168). */
+typedef enum { TSM_Q8_0 = 0, TSM_Q4_0 = 1, TSM_Q4_1 = 2, TSM_F32 = -1 } tsm_kind;
+
+/* ---- runtime: Device#alloc/upload/download/sync (device.cr:39-68; cuda.cr:339-428) ---------- */
+
+int tsm_device_count(int* count);
+int tsm_ctx_create(int ordinal, tsm_ctx** out);
+int tsm_ctx_destroy(tsm_ctx* ctx);
+const char* tsm_status_name(int status);
+int tsm_last_error(tsm_ctx* ctx, char* buffer, int capacity);
+void* tsm_ctx_stream(tsm_ctx* ctx); /* the context's cudaStream_t, for callers that share it */
+
+/* Device#alloc: contents undefined; sizes are pooled by exact size (buffer_pool.cr:37-72). */
+int tsm_alloc(tsm_ctx* ctx, int64_t bytes, tsm_dptr* out);
+/* CUDABuffer#give_back -> retire (cuda.cr:439-454): callable from any thread, never waits or raises. */
+int tsm_free(tsm_ctx* ctx, tsm_dptr ptr);
+int tsm_upload(tsm_ctx* ctx, tsm_dptr dst, const void* src, int64_t bytes);   /* Device#upload */
+int tsm_download(tsm_ctx* ctx, void* dst, tsm_dptr src, int64_t bytes);       /* Device#download */
+int tsm_sync(tsm_ctx* ctx);                                                    /* Device#sync, cuda.cr:419-428 */
+
+/* The counters of CUDA::Profile and BufferPool (cuda.cr:215-230, 256-303; buffer_pool.cr:13-34). */
+typedef struct {
+    int64_t launches, uploads, downloads, upload_bytes, download_bytes;
+    int64_t allocs, pool_hits, pool_misses, pool_held_bytes, frees;
+    int64_t host_ops;     /* always 0: no operator has a host fallback (fused_llama_spec.cr:82-90) */
+    int64_t graph_replays;
+} tsm_counters;
+int tsm_counters_read(tsm_ctx* ctx, tsm_counters* out);
+int tsm_counters_reset(tsm_ctx* ctx);
+
+/* How norms and attention add (both modes keep the block products bit-exact):
+ *   TSM_FAST   tree sums and split-K online softmax (within 1e-5 of the host);
+ *   TSM_EXACT  the host's index-order sums and its own exp polynomial (the host's bits). */
+typedef enum { TSM_FAST = 0, TSM_EXACT = 1 } tsm_mode;
+int tsm_set_mode(tsm_ctx* ctx, int mode);
+
+/* ---- operators: one launcher per hot Op (node.cr:3-127; CUDA#launch, cuda.cr:486-502) ------- */
+
+/* Tensor#quantize / Quant.quantize (quant.cr:77-90, 499-535): `count` F32 values -> ggml blocks. */
+int tsm_quantize_blocks(tsm_ctx* ctx, tsm_dptr x, int64_t count, int kind, tsm_dptr out);
+/* Tensor#dequantize / Quant.dequantize (quant.cr:93-105, 537-556). */
+int tsm_dequantize_blocks(tsm_ctx* ctx, tsm_dptr blocks, int64_t count, int kind, tsm_dptr out);
+
+/* quantize_rows_q8_f32 (kernels.cu:1190-1207; Quant.quantize_activations, quant.cr:428-442):
+ * x [rows,k] F32 (row stride x_stride floats) -> scales, sums F32 [rows,k/32], qs I8 [rows,k]. */
+int tsm_quantize_rows_q8(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride, tsm_dptr scales, tsm_dptr sums,
+                         tsm_dptr qs);
+
+/* Op::BlockMatMul (Tensor#linear, tensor/structural.cr:165-172; CUDA#launch_blocks, cuda.cr:736-769;
+ * Quant.matmul_reference, quant.cr:122-142): out[rows,n] = x[rows,k] . w[n,k]^T (+ bias[n]) with the
+ * host's bits.  w holds n rows of k/32 ggml blocks of `kind`, starting at an even address. */
+int tsm_block_matmul(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride, tsm_dptr w, int kind, int n,
+                     tsm_dptr bias, tsm_dptr out);
+/* The product alone, on activations already quantised by tsm_quantize_rows_q8 (block_matmul_f32 /
+ * block_matmul_lanes_f32, kernels.cu:1233-1328). */
+int tsm_block_matmul_quantized(tsm_ctx* ctx, tsm_dptr scales, tsm_dptr sums, tsm_dptr qs, int rows, int k, tsm_dptr w,
+                               int kind, int n, tsm_dptr bias, tsm_dptr out);
+
+/* Op::Gather on a block table (gather_blocks_f32, kernels.cu:1172-1185; Quant.gather, quant.cr:417-422):
+ * out[count,width] = dequantised rows ids[i] of table[table_rows,width]; a bad id is recorded, its row zeroed. */
+int tsm_gather_blocks(tsm_ctx* ctx, tsm_dptr table, int kind, int table_rows, int width, tsm_dptr ids, int count,
+                      tsm_dptr out);
+/* Op::Gather on an F32 table (gather_f32, kernels.cu:186-197). */
+int tsm_gather_f32(tsm_ctx* ctx, tsm_dptr table, int table_rows, int width, tsm_dptr ids, int count, tsm_dptr out);
+
+/* Op::RMSNorm (Tensor#rmsnorm, tensor/composite.cr:153-159; rmsnorm_f32, kernels.cu:930-956). w may be 0. */
+int tsm_rmsnorm(tsm_ctx* ctx, tsm_dptr x, tsm_dptr w, int rows, int n, float eps, tsm_dptr out);
+/* Op::LayerNorm (Tensor#layernorm, tensor/composite.cr:89-98; layernorm_f32, kernels.cu:904-923). */
+int tsm_layernorm(tsm_ctx* ctx, tsm_dptr x, tsm_dptr w, tsm_dptr b, int rows, int n, float eps, tsm_dptr out);
+
+/* Op::Rope (Tensor#rope, tensor/composite.cr:254-261; rope_f32, kernels.cu:1102-1112) in its packed form
+ * (RotaryEmbedding#angles + #call, modules.cr:355-368): x [tokens,heads,width] with token stride x_stride,
+ * rotated by rows positions[token] of the cos/sin tables [context,width]. out is dense [tokens,heads,width]. */
+int tsm_rope(tsm_ctx* ctx, tsm_dptr x, int tokens, int heads, int width, int64_t x_stride, tsm_dptr cos_table,
+             tsm_dptr sin_table, int context, tsm_dptr positions, tsm_dptr out);
+
+/* Op::WriteRows (Tensor#write_rows, tensor/structural.cr:82-92; write_rows_f32, kernels.cu:68-76):
+ * token t of values [tokens,heads,width] (token stride v_stride) -> cache[row,head,position,:],
+ * slots[t] = row * capacity + position; cache is [rows,heads,capacity,width]. */
+int tsm_write_rows(tsm_ctx* ctx, tsm_dptr cache, int rows, int heads, int capacity, int width, tsm_dptr values,
+                   int64_t v_stride, int tokens, tsm_dptr slots);
+
+/* Op::RaggedAttention (Tensor.ragged_attention, tensor/composite.cr:210-227; attention_ragged_f32,
+ * kernels.cu:1081-1097) and, with one row, Op::Attention (attention_f32, kernels.cu:1058-1073):
+ * q [tokens,heads,width] (token stride q_stride); k, v [rows,kv_heads,capacity,width];
+ * table I32 [tokens,3] = (row, last visible position, positions held); out dense [tokens,heads,width].
+ * No limit on positions (the reference stops at 4096). */
+int tsm_ragged_attention(tsm_ctx* ctx, tsm_dptr q, int64_t q_stride, int tokens, int heads, int width, tsm_dptr k,
+                         tsm_dptr v, int rows, int kv_heads, int capacity, tsm_dptr table, float scale, tsm_dptr out);
+
+/* Tensor#swiglu / #gelu (kernels.cr:4,18): elementwise over [rows,n]; strides in floats. */
+int tsm_swiglu(tsm_ctx* ctx, tsm_dptr gate, tsm_dptr up, int rows, int n, int64_t in_stride, tsm_dptr out);
+int tsm_gelu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out);
+/* Op::Add (tensor/elementwise.cr:4-6). */
+int tsm_add(tsm_ctx* ctx, tsm_dptr a, tsm_dptr b, int64_t count, tsm_dptr out);
+
+/* Sampler#pick, greedy (sampler.cr:36): first index of each row's maximum -> I32 [rows]. */
+int tsm_argmax(tsm_ctx* ctx, tsm_dptr logits, int rows, int n, tsm_dptr out);
+/* Sampler#top (sampler.cr:77-96): each row's `count` highest, highest first, ties to the lower index. */
+int tsm_topk(tsm_ctx* ctx, tsm_dptr logits, int rows, int n, int count, tsm_dptr out_ids, tsm_dptr out_values);
+
+/* ---- engine: the token loop (models/generative.cr, models/llama.cr, models/gpt2.cr) --------- */
+
+typedef struct {
+    int arch;                 /* 0 Llama, 1 GPT-2 */
+    int layers, width, heads, kv_heads, head_width, hidden, vocab, context;
+    float eps;
+    double rope_theta;
+    int tied;                 /* the head reuses the token table (llama.cr:294-303; always for GPT-2) */
+} tsm_model_config;
+
+/* Llama.load / GPT2.load of a .gguf file (llama.cr:165-206, gpt2.cr:75-89): reads the configuration
+ * from the metadata, uploads every tensor, un-permutes q/k rows, joins [q;k;v] and [gate;up]. */
+int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out);
+/* Llama.new(config) / GPT2.new(config) with Init.normal(0.02) then Module#quantize(kind, embeddings: true)
+ * (module.cr, builder.cr): weights drawn on the device from `seed`, quantised on the device. */
+int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uint64_t seed, tsm_model** out);
+int tsm_model_config_get(tsm_model* model, tsm_model_config* out);
+int tsm_model_free(tsm_model* model);
+/* The weight behind a parameter ("embed", "head", "final_w", "final_b", "wpe", "<layer>.qkv", ".o", ".up",
+ * ".down", ".norm1_w", ... and their "_b" biases): device address, kind, rows and columns. */
+int tsm_model_tensor(tsm_model* model, const char* name, tsm_dptr* ptr, int* kind, int* n, int* k);
+
+/* Generative#new_batch_cache (generative.cr:89-91): rows x capacity positions per layer, in place. */
+int tsm_cache_create(tsm_model* model, int rows, int capacity, tsm_cache** out);
+int tsm_cache_free(tsm_cache* cache);
+int tsm_cache_length(tsm_cache* cache, int row, int* length);
+int tsm_cache_reset(tsm_cache* cache, int row);                       /* BatchCache#reset */
+/* Fills row `row` with `length` positions of seeded N(0,1) keys and values (a stand-in for a prefill
+ * whose cost is out of reach; the bytes can be read back with tsm_cache_layer). */
+int tsm_cache_fill(tsm_cache* cache, int row, int length, uint64_t seed);
+int tsm_cache_layer(tsm_cache* cache, int layer, tsm_dptr* keys, tsm_dptr* values);
+
+/* Generative#forward / #forward_last over a BatchCache (generative.cr:101-125): counts[row] new tokens
+ * per row (0 = idle), ids packed row after row.  Writes logits of each row's last new token (last = 1)
+ * or of every new token to the host array `logits` [outputs, vocab], and advances the cache. */
+int tsm_forward(tsm_model* model, tsm_cache* cache, const int32_t* counts, const int32_t* ids, int last,
+                float* logits);
+/* One decode step for every row: ids[row] is the row's next token; picks each row's next token greedily
+ * on the device (Sampler.greedy) and writes it to tokens[row].  The step is captured once as a CUDA
+ * graph and replayed.  logits (may be NULL) receives [rows, vocab] on the host. */
+int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* tokens, float* logits);
+/* Generative#generate with Sampler.greedy (generative.cr:177-190): `count` tokens after `prompt`. */
+int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TSM_B200_H */

@@ -1,0 +1,341 @@
+// Decode attention over the in-place KV cache [rows, kv_heads, capacity, width] (F32), one query per
+// token, ragged lengths (Tensor.ragged_attention, tensor/composite.cr:210-227; the host composite of
+// devices/host.cr:368-387, 700-721 is the arithmetic being matched).
+//
+// fast path (mode TSM_FAST, head width 64 or 128): split-K with online softmax.  Positions are cut
+//   into chunks of 256 at fixed absolute offsets; one CTA takes (chunk, kv head, token), scores all the
+//   query heads that share the kv head while the keys pass through registers once, and writes the
+//   chunk's (max, sum, unnormalised output).  A second kernel merges a token's chunks in chunk order,
+//   so a stream's bits depend neither on the batch around it nor on other streams' lengths.
+//
+// ordered path (mode TSM_EXACT, or any other head width): the host's order of arithmetic — each score
+//   a dot product folded over the width from 0f, the host's own exp polynomial, the denominator
+//   folded over positions in order, each output column folded over positions in order — run as many
+//   independent chains in parallel (positions for scores, columns for outputs), which gives the host's
+//   bits.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace tsm {
+
+constexpr int kChunk = 256;
+
+struct QuantOutA {
+    float* scales;
+    float* sums;
+    int* totals;
+    int8_t* qs;
+};
+
+// ---- fast path --------------------------------------------------------------------------------------
+
+template <int WIDTH, int GROUP>
+__global__ void __launch_bounds__(256) attention_chunk_kernel(const float* __restrict__ q, int64_t q_stride, int heads,
+                                                              const float* __restrict__ k, const float* __restrict__ v,
+                                                              int rows, int kv_heads, int capacity,
+                                                              const int* __restrict__ table, float scale, int chunks,
+                                                              float* part_o, float* part_ml, ErrorRecord* errors) {
+    constexpr int LPP = WIDTH / 16;  // lanes per position in the score phase (16 values each)
+    constexpr int PPW = 32 / LPP;    // positions per warp iteration
+    constexpr int TPR = WIDTH / 4;   // threads per value row in the output phase
+    constexpr int PG = 256 / TPR;    // position groups in the output phase
+    __shared__ float scores[GROUP][kChunk];
+    __shared__ __align__(16) float red[PG][GROUP][WIDTH];
+    __shared__ float stat[GROUP][2];
+    __shared__ float wred[8][GROUP];
+
+    const int chunk = blockIdx.x, token = blockIdx.z;
+    const int groups_per_kv = (heads / kv_heads) / GROUP;
+    const int kvh = blockIdx.y / groups_per_kv;
+    const int head0 = kvh * (heads / kv_heads) + (blockIdx.y % groups_per_kv) * GROUP;
+    const int row = table[3 * token], limit = table[3 * token + 1];
+    if (row < 0 || row >= rows || limit < 0 || limit >= capacity) {
+        if (threadIdx.x == 0 && chunk == 0 && blockIdx.y == 0) report_bad_index(errors, limit, capacity);
+        return;
+    }
+    const int len = limit + 1;
+    const int c0 = chunk * kChunk;
+    if (c0 >= len) return;
+    const int cnt = min(kChunk, len - c0);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* kbase = k + (((int64_t)row * kv_heads + kvh) * capacity + c0) * WIDTH;
+    const float* vbase = v + (((int64_t)row * kv_heads + kvh) * capacity + c0) * WIDTH;
+
+    // queries: lane holds values d = 4*(lane % LPP) + 4*LPP*i + {0..3}, i < 4, of each head
+    float4 qr[GROUP][4];
+    {
+        const float* qt = q + (int64_t)token * q_stride + (int64_t)head0 * WIDTH;
+#pragma unroll
+        for (int h = 0; h < GROUP; h++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) qr[h][i] = *(const float4*)(qt + h * WIDTH + 4 * (lane % LPP) + 4 * LPP * i);
+    }
+    // scores
+    for (int base = warp * PPW; base < kChunk; base += 8 * PPW) {
+        int p = base + lane / LPP;
+        float dot[GROUP];
+#pragma unroll
+        for (int h = 0; h < GROUP; h++) dot[h] = 0.0f;
+        if (p < cnt) {
+            const float* kp = kbase + (int64_t)p * WIDTH + 4 * (lane % LPP);
+            float4 kv4[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) kv4[i] = *(const float4*)(kp + 4 * LPP * i);
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int h = 0; h < GROUP; h++)
+                    dot[h] += qr[h][i].x * kv4[i].x + qr[h][i].y * kv4[i].y + qr[h][i].z * kv4[i].z + qr[h][i].w * kv4[i].w;
+        }
+#pragma unroll
+        for (int off = LPP / 2; off > 0; off >>= 1)
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) dot[h] += __shfl_xor_sync(0xffffffffu, dot[h], off);
+        if (lane % LPP == 0) {
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) scores[h][p] = p < cnt ? dot[h] * scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    // chunk maximum and exponentials (each thread owns one position)
+    float sv[GROUP], mx[GROUP];
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) {
+        sv[h] = scores[h][tid];
+        mx[h] = sv[h];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], off));
+        if (lane == 0) wred[warp][h] = mx[h];
+    }
+    __syncthreads();
+    float ev[GROUP], sm[GROUP];
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) {
+        float m = wred[0][h];
+#pragma unroll
+        for (int w2 = 1; w2 < 8; w2++) m = fmaxf(m, wred[w2][h]);
+        mx[h] = m;
+        ev[h] = expf(sv[h] - m);  // -inf beyond the chunk's end gives 0
+        sm[h] = ev[h];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sm[h] += __shfl_xor_sync(0xffffffffu, sm[h], off);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) {
+        scores[h][tid] = ev[h];
+        if (lane == 0) wred[warp][h] = sm[h];
+    }
+    __syncthreads();
+    if (tid < GROUP) {
+        float l = 0.0f;
+        for (int w2 = 0; w2 < 8; w2++) l += wred[w2][tid];
+        stat[tid][0] = mx[tid];
+        stat[tid][1] = l;
+    }
+    // weighted values: thread (pg, cg) folds positions pg, pg + PG, ... for 4 columns of every head
+    const int pg = tid / TPR, cg = tid % TPR;
+    float4 acc[GROUP];
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int p = pg;
+    for (; p + 3 * PG < cnt; p += 4 * PG) {
+        float4 vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) vv[u] = *(const float4*)(vbase + (int64_t)(p + u * PG) * WIDTH + 4 * cg);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int h = 0; h < GROUP; h++) {
+                float w = scores[h][p + u * PG];
+                acc[h].x += w * vv[u].x, acc[h].y += w * vv[u].y, acc[h].z += w * vv[u].z, acc[h].w += w * vv[u].w;
+            }
+    }
+    for (; p < cnt; p += PG) {
+        float4 vv = *(const float4*)(vbase + (int64_t)p * WIDTH + 4 * cg);
+#pragma unroll
+        for (int h = 0; h < GROUP; h++) {
+            float w = scores[h][p];
+            acc[h].x += w * vv.x, acc[h].y += w * vv.y, acc[h].z += w * vv.z, acc[h].w += w * vv.w;
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < GROUP; h++) *(float4*)&red[pg][h][4 * cg] = acc[h];
+    __syncthreads();
+    for (int i = tid; i < GROUP * WIDTH; i += 256) {
+        int h = i / WIDTH, c = i % WIDTH;
+        float total = 0.0f;
+#pragma unroll 4
+        for (int g = 0; g < PG; g++) total += red[g][h][c];
+        part_o[(((int64_t)token * heads + head0 + h) * chunks + chunk) * WIDTH + c] = total;
+    }
+    if (tid < GROUP) {
+        float* ml = part_ml + (((int64_t)token * heads + head0 + tid) * chunks + chunk) * 2;
+        ml[0] = stat[tid][0];
+        ml[1] = stat[tid][1];
+    }
+}
+
+// Merges a token's chunks in chunk order; one warp per 32 output columns so that the block quantiser
+// for the product that follows can run in registers.
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int heads,
+                                       int width, int chunks, const int* __restrict__ table, int capacity, float* out,
+                                       QuantOutA qo) {
+    int token = blockIdx.y;
+    int lane = threadIdx.x & 31;
+    int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // 32-column block of the token's [heads*width]
+    int total = heads * width;
+    if (item * 32 >= total) return;
+    int col = item * 32 + lane;
+    int limit = table[3 * token + 1];
+    float y = 0.0f;
+    if (col < total && limit >= 0 && limit < capacity) {
+        int head = col / width, c = col % width;
+        int used = limit / kChunk + 1;
+        const float* ml = part_ml + ((int64_t)token * heads + head) * chunks * 2;
+        const float* po = part_o + ((int64_t)token * heads + head) * chunks * width + c;
+        float m = ml[0];
+        for (int i = 1; i < used; i++) m = fmaxf(m, ml[2 * i]);
+        float l = 0.0f, o = 0.0f;
+        for (int i = 0; i < used; i++) {
+            float f = expf(ml[2 * i] - m);
+            l += ml[2 * i + 1] * f;
+            o += po[(int64_t)i * width] * f;
+        }
+        y = o / l;
+        if (out) out[(int64_t)token * total + col] = y;
+    }
+    if (qo.qs) {
+        int64_t at = (int64_t)token * (total >> 5) + item;
+        quantize_block_q8(y, lane, qo.scales + at, qo.sums + at, qo.totals + at, qo.qs + (int64_t)token * total + col);
+    }
+}
+
+// ---- ordered path ----------------------------------------------------------------------------------
+
+// One CTA per (query head, token).  Shared memory holds the row's scores (len floats).
+__global__ void attention_ordered_kernel(const float* __restrict__ q, int64_t q_stride, int heads, int width,
+                                         const float* __restrict__ k, const float* __restrict__ v, int rows, int kv_heads,
+                                         int capacity, const int* __restrict__ table, float scale, float* out,
+                                         ErrorRecord* errors) {
+    extern __shared__ float sh[];
+    float* qs = sh;              // width
+    float* scores = sh + width;  // len
+    __shared__ float wmax[32];
+    __shared__ float total_s;
+    const int head = blockIdx.x, token = blockIdx.y;
+    const int row = table[3 * token], limit = table[3 * token + 1];
+    if (row < 0 || row >= rows || limit < 0 || limit >= capacity) {
+        if (threadIdx.x == 0 && head == 0) report_bad_index(errors, limit, capacity);
+        return;
+    }
+    const int len = limit + 1;
+    const int kvh = head / (heads / kv_heads);
+    const float* kb = k + ((int64_t)row * kv_heads + kvh) * capacity * width;
+    const float* vb = v + ((int64_t)row * kv_heads + kvh) * capacity * width;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = blockDim.x >> 5;
+    for (int d = tid; d < width; d += blockDim.x) qs[d] = q[(int64_t)token * q_stride + (int64_t)head * width + d];
+    __syncthreads();
+    float top = -INFINITY;
+    for (int p = tid; p < len; p += blockDim.x) {
+        const float* kp = kb + (int64_t)p * width;
+        float dot = 0.0f;
+        for (int d = 0; d < width; d++) dot = __fadd_rn(dot, __fmul_rn(qs[d], kp[d]));
+        float s = __fadd_rn(__fmul_rn(dot, scale), 0.0f);
+        scores[p] = s;
+        top = fmaxf(top, s);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    if (lane == 0) wmax[warp] = top;
+    __syncthreads();
+    top = wmax[0];
+    for (int w2 = 1; w2 < warps; w2++) top = fmaxf(top, wmax[w2]);
+    for (int p = tid; p < len; p += blockDim.x) scores[p] = exact_exp(__fsub_rn(scores[p], top));
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.0f;
+        for (int p = 0; p < len; p++) total = __fadd_rn(total, scores[p]);
+        total_s = total;
+    }
+    __syncthreads();
+    float total = total_s;
+    for (int p = tid; p < len; p += blockDim.x) scores[p] = __fdiv_rn(scores[p], total);
+    __syncthreads();
+    for (int c = tid; c < width; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int p = 0; p < len; p++) acc = __fadd_rn(acc, __fmul_rn(scores[p], vb[(int64_t)p * width + c]));
+        out[((int64_t)token * heads + head) * width + c] = acc;
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity) {
+    int chunks = (capacity + kChunk - 1) / kChunk;
+    return (int64_t)tokens * heads * chunks * (width + 2) * 4 + 256;
+}
+
+template <int WIDTH>
+static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
+                       int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
+                       const QuantizedActs* quantized) {
+    int chunks = (capacity + kChunk - 1) / kChunk;
+    int64_t need = attention_scratch_bytes(tokens, heads, WIDTH, capacity);
+    TSM_TRY(ensure_scratch(ctx, ctx->attn, need));
+    float* part_o = (float*)ctx->attn.ptr;
+    float* part_ml = part_o + (int64_t)tokens * heads * chunks * WIDTH;
+    int per_kv = heads / kv_heads;
+    int group = per_kv <= 4 ? per_kv : (per_kv % 4 == 0 ? 4 : (per_kv % 2 == 0 ? 2 : 1));
+    dim3 grid(chunks, kv_heads * (per_kv / group), tokens);
+#define TSM_ATTN(G)                                                                                                     \
+    attention_chunk_kernel<WIDTH, G><<<grid, 256, 0, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, \
+                                                                    table, scale, chunks, part_o, part_ml, ctx->errors)
+    if (group == 1) TSM_ATTN(1);
+    else if (group == 2) TSM_ATTN(2);
+    else if (group == 3) TSM_ATTN(3);
+    else TSM_ATTN(4);
+#undef TSM_ATTN
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    QuantOutA qo{nullptr, nullptr, nullptr, nullptr};
+    if (quantized) qo = QuantOutA{(float*)quantized->scales, (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs};
+    int items = (heads * WIDTH + 31) / 32;
+    dim3 mgrid((items + 3) / 4, tokens);
+    attention_merge_kernel<<<mgrid, 128, 0, ctx->stream>>>(part_o, part_ml, heads, WIDTH, chunks, table, capacity, out, qo);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
+                     const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
+                     const QuantizedActs* quantized) {
+    if (kv_heads <= 0 || heads % kv_heads != 0)
+        return fail(ctx, TSM_ERR_ARG, std::to_string(heads) + " query heads do not group into " + std::to_string(kv_heads) + " key and value heads");
+    if (tokens == 0) return TSM_OK;
+    bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
+    if (ctx->mode == TSM_FAST && aligned && width == 64)
+        return launch_fast<64>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
+    if (ctx->mode == TSM_FAST && aligned && width == 128)
+        return launch_fast<128>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
+    size_t smem = (size_t)(width + capacity) * 4;
+    if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "ordered attention over more than 51000 positions");
+    if (!out) return fail(ctx, TSM_ERR_ARG, "ordered attention needs an F32 output");
+    if (smem > 48 * 1024)
+        TSM_CUDA(ctx, cudaFuncSetAttribute(attention_ordered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    dim3 grid(heads, tokens);
+    int threads = capacity >= 1024 ? 256 : 128;
+    attention_ordered_kernel<<<grid, threads, smem, ctx->stream>>>(q, q_stride, heads, width, k, v, rows, kv_heads, capacity,
+                                                                   table, scale, out, ctx->errors);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    if (quantized) {
+        TSM_TRY(launch_quantize_rows(ctx, out, tokens, heads * width, (int64_t)heads * width, (float*)quantized->scales,
+                                     (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs));
+    }
+    return TSM_OK;
+}
+
+}  // namespace tsm

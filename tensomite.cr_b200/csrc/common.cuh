@@ -1,0 +1,225 @@
+// Shared declarations of the library: the context, status plumbing and small device helpers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/tsm_b200.h"
+
+namespace tsm {
+
+constexpr int kBlockBytes[3] = {34, 18, 20};  // Q8_0, Q4_0, Q4_1 (dtype.cr:38-45 of the reference)
+inline int block_bytes(int kind) { return kBlockBytes[kind]; }
+
+// The 3-int record kernels write for bad data (count, first id, limit), as the reference's
+// kernels do (kernels.cu:178-183), plus a fourth word for bounded waits that ran out.
+struct ErrorRecord {
+    int count, first, limit, timeout;
+};
+
+// Exact-size free lists, as the reference's BufferPool keeps them (buffer_pool.cr:37-72).
+struct Pool {
+    std::mutex lock;
+    std::unordered_map<int64_t, std::vector<void*>> free_lists;
+    std::unordered_map<void*, int64_t> sizes;  // every live or pooled allocation
+    int64_t held_bytes = 0, limit_bytes = 0;
+};
+
+struct Scratch {
+    void* ptr = nullptr;
+    int64_t bytes = 0;
+};
+
+}  // namespace tsm
+
+struct tsm_ctx {
+    int ordinal = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 148;
+    int mode = TSM_FAST;
+    tsm::Pool pool;
+    tsm::ErrorRecord* errors = nullptr;       // device
+    tsm::ErrorRecord* errors_host = nullptr;  // pinned
+    tsm::Scratch quant;                       // activation quantiser output for tsm_block_matmul
+    tsm::Scratch attn;                        // split-K partials
+    uint64_t scratch_generation = 1;          // bumped whenever a scratch buffer moves
+    std::mutex message_lock;
+    std::string message;
+    tsm_counters counters{};
+    std::mutex counter_lock;
+};
+
+namespace tsm {
+
+void set_message(tsm_ctx* ctx, const std::string& text);
+int fail(tsm_ctx* ctx, int status, const std::string& text);
+int cuda_fail(tsm_ctx* ctx, cudaError_t err, const char* what);
+int ensure_scratch(tsm_ctx* ctx, Scratch& s, int64_t bytes);
+int check_error_record(tsm_ctx* ctx);  // inspects the host copy of the record; clears the device's when set
+int pool_alloc(tsm_ctx* ctx, int64_t bytes, void** out);
+void pool_release(tsm_ctx* ctx, void* p);
+inline void count_launch(tsm_ctx* ctx, int n = 1) { ctx->counters.launches += n; }
+
+#define TSM_CUDA(ctx, call)                                              \
+    do {                                                                 \
+        cudaError_t err__ = (call);                                      \
+        if (err__ != cudaSuccess) return tsm::cuda_fail(ctx, err__, #call); \
+    } while (0)
+
+#define TSM_TRY(call)              \
+    do {                           \
+        int rc__ = (call);         \
+        if (rc__ != TSM_OK) return rc__; \
+    } while (0)
+
+#define TSM_LAUNCH_CHECK(ctx) TSM_CUDA(ctx, cudaGetLastError())
+
+struct DeviceGuard {
+    int previous = -1;
+    explicit DeviceGuard(int ordinal) {
+        cudaGetDevice(&previous);
+        if (previous != ordinal) cudaSetDevice(ordinal);
+        else previous = -1;
+    }
+    ~DeviceGuard() {
+        if (previous >= 0) cudaSetDevice(previous);
+    }
+};
+
+// ---- launch declarations (each in its own .cu) -------------------------------------------------
+
+struct QuantizedActs {
+    const float* scales;  // [rows, k/32]  f32(f16(d))
+    const float* sums;    // [rows, k/32]  f32(f16(total * d))
+    const int* totals;    // [rows, k/32]  integer sum of the block's quantised values
+    const int8_t* qs;     // [rows, k]
+};
+
+int64_t quant_scratch_bytes(int rows, int k);
+QuantizedActs quant_scratch_layout(void* base, int rows, int k);
+
+int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t x_stride, float* scales, float* sums,
+                         int* totals, int8_t* qs);
+int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                        const float* bias, const float* residual, float* out);
+int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind, uint8_t* out);
+int launch_dequantize_blocks(tsm_ctx* ctx, const uint8_t* blocks, int64_t count, int kind, float* out);
+int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table_rows, int width, const int* ids,
+                         int count, float* out, const uint8_t* table2, const int* ids2, int ids2_stride);
+int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out);
+int launch_rmsnorm(tsm_ctx* ctx, const float* x, const float* w, int rows, int n, float eps, float* out,
+                   const QuantizedActs* quantized);
+int launch_layernorm(tsm_ctx* ctx, const float* x, const float* w, const float* b, int rows, int n, float eps, float* out,
+                     const QuantizedActs* quantized);
+int launch_rope(tsm_ctx* ctx, const float* x, int tokens, int heads, int width, int64_t x_stride, const float* cos_table,
+                const float* sin_table, int context, const int* positions, float* out);
+int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capacity, int width, const float* values,
+                      int64_t v_stride, int tokens, const int* slots);
+// Rotates q and k in place inside qkv [tokens, (heads + 2 kv_heads) * width] (when cos_table is not null) and
+// writes k and v to their cache slots (table[t] = row, position, ...): one launch per layer.
+int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_heads, int width, const float* cos_table,
+                       const float* sin_table, int context, const int* table, float* keys, float* values, int rows,
+                       int capacity);
+int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
+                     const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
+                     const QuantizedActs* quantized);
+int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity);
+int launch_swiglu(tsm_ctx* ctx, const float* gate, const float* up, int rows, int n, int64_t in_stride, float* out,
+                  const QuantizedActs* quantized);
+int launch_gelu(tsm_ctx* ctx, const float* x, int rows, int n, float* out, const QuantizedActs* quantized);
+int launch_add(tsm_ctx* ctx, const float* a, const float* b, int64_t count, float* out);
+int launch_argmax(tsm_ctx* ctx, const float* logits, int rows, int n, int* out);
+int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, int* out_ids, float* out_values);
+int launch_normal_fill(tsm_ctx* ctx, float* out, int64_t count, float mean, float stddev, uint64_t seed);
+int launch_fill(tsm_ctx* ctx, float* out, int64_t count, float value);
+
+}  // namespace tsm
+
+// ---- device helpers ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+namespace tsm {
+
+// f32(f16(x)) with round-to-nearest-even, as the reference's F16.new(...).to_f32 (f16.cr:29-59).
+__device__ __forceinline__ float round_to_half(float x) { return __half2float(__float2half_rn(x)); }
+__device__ __forceinline__ float half_bits_to_float(unsigned int bits) {
+    return __half2float(__ushort_as_half((unsigned short)bits));
+}
+
+// The reference's own exp (maths.cr:36-54), operation for operation; no contraction.
+__device__ __forceinline__ float exact_exp(float x) {
+    const float LOG2E = 1.44269504088896341f, LN2_HI = 0.693359375f, LN2_LO = -2.12194440e-4f;
+    const float EXP_HI = 88.72283905f, EXP_LO = -87.3365447f, ROUNDER = 12582912.0f;
+    float clamped = (x > EXP_HI || x < EXP_LO) ? 0.0f : x;
+    float n = __fsub_rn(__fadd_rn(__fmul_rn(clamped, LOG2E), ROUNDER), ROUNDER);
+    float r = __fsub_rn(__fsub_rn(clamped, __fmul_rn(n, LN2_HI)), __fmul_rn(n, LN2_LO));
+    float z = __fmul_rn(r, r);
+    float p = 1.9875691500e-4f;
+    p = __fadd_rn(__fmul_rn(p, r), 1.3981999507e-3f);
+    p = __fadd_rn(__fmul_rn(p, r), 8.3334519073e-3f);
+    p = __fadd_rn(__fmul_rn(p, r), 4.1665795894e-2f);
+    p = __fadd_rn(__fmul_rn(p, r), 1.6666665459e-1f);
+    p = __fadd_rn(__fmul_rn(p, r), 5.0000001201e-1f);
+    p = __fadd_rn(__fadd_rn(__fmul_rn(p, z), r), 1.0f);
+    int whole = (int)n;
+    int half = whole >> 1;
+    float result = __fmul_rn(__fmul_rn(p, __int_as_float((half + 127) << 23)), __int_as_float((whole - half + 127) << 23));
+    result = x > EXP_HI ? __int_as_float(0x7f800000) : result;
+    result = x < EXP_LO ? 0.0f : result;
+    return x != x ? x : result;
+}
+
+// The reference's own tanh (maths.cr:99-114).
+__device__ __forceinline__ float exact_tanh(float x) {
+    float a = fabsf(x);
+    float z = __fmul_rn(x, x);
+    float p = -5.70498872745e-3f;
+    p = __fadd_rn(__fmul_rn(p, z), 2.06390887954e-2f);
+    p = __fsub_rn(__fmul_rn(p, z), 5.37397155531e-2f);
+    p = __fadd_rn(__fmul_rn(p, z), 1.33314422036e-1f);
+    p = __fsub_rn(__fmul_rn(p, z), 3.33332819422e-1f);
+    float near = __fadd_rn(__fmul_rn(__fmul_rn(p, z), x), x);
+    float far = __fsub_rn(1.0f, __fdiv_rn(2.0f, __fadd_rn(exact_exp(__fadd_rn(a, a)), 1.0f)));
+    far = a > 9.01f ? 1.0f : far;
+    far = x < 0.0f ? -far : far;
+    float result = a < 0.625f ? near : far;
+    result = x == 0.0f ? x : result;
+    return x != x ? x : result;
+}
+
+// One warp quantises one block of 32 activations, lane j holding element j, with the arithmetic of
+// the reference's Quant.quantize_activations (quant.cr:428-442): d = amax / 127, id = 1 / d (IEEE
+// division), q = round-half-away(x * id), scale = f32(f16(d)), sum = f32(f16(float(total) * d)).
+__device__ __forceinline__ void quantize_block_q8(float x, int lane, float* scale, float* sum, int* total, int8_t* q_out) {
+    float amax = fabsf(x);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float d = __fdiv_rn(amax, 127.0f);
+    float id = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+    int q = (int)(signed char)(int)roundf(__fmul_rn(x, id));
+    int t = q;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    *q_out = (int8_t)q;
+    if (lane == 0) {
+        *scale = round_to_half(d);
+        *sum = round_to_half(__fmul_rn((float)t, d));
+        *total = t;
+    }
+}
+
+__device__ __forceinline__ void report_bad_index(ErrorRecord* errors, int id, int limit) {
+    if (atomicAdd(&errors->count, 1) == 0) {
+        errors->first = id;
+        errors->limit = limit;
+    }
+}
+
+}  // namespace tsm
+#endif

@@ -1,0 +1,926 @@
+// The token loop: models with resident weights, the batch cache, one packed forward step, its CUDA-graph
+// replay for decoding, and the GGUF loader.  Host-side counterpart of the reference's
+// models/{generative,llama,gpt2}.cr and modules.cr; the op order of one step is theirs.
+#include <fcntl.h>
+#include <math.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <memory>
+
+#include "common.cuh"
+
+namespace tsm {
+
+struct Linear {
+    int kind = TSM_F32;
+    int n = 0, k = 0;
+    uint8_t* w = nullptr;
+    float* bias = nullptr;
+};
+
+struct Layer {
+    float *norm1_w = nullptr, *norm1_b = nullptr, *norm2_w = nullptr, *norm2_b = nullptr;
+    Linear qkv, o, up, down;
+};
+
+struct Named {
+    void* ptr;
+    int kind, n, k;
+};
+
+// Buffers of one packed step over up to `tokens` new tokens.
+struct Workspace {
+    int tokens = 0;
+    int* ids = nullptr;      // [T]
+    int* table = nullptr;    // [T,3] row, position, positions held
+    int* last = nullptr;     // [T] indices of the rows whose logits are wanted
+    float* x = nullptr;      // [T, width]
+    float* xl = nullptr;     // [T, width] gathered last rows
+    float* qkv = nullptr;    // [T, (heads + 2 kv) * hw]
+    float* att = nullptr;    // [T, heads * hw] (ordered attention writes F32 first)
+    float* up = nullptr;     // [T, 2*hidden | hidden]
+    float* logits = nullptr; // [T, vocab]
+    int* picks = nullptr;    // [T]
+    void* qa = nullptr;      // quantised activations, K = width
+    void* qb = nullptr;      // K = heads * hw
+    void* qc = nullptr;      // K = hidden
+    int32_t* host = nullptr; // pinned: ids [T] + table [3T] + picks [T]
+};
+
+}  // namespace tsm
+
+using namespace tsm;
+
+struct tsm_model {
+    tsm_ctx* ctx = nullptr;
+    tsm_model_config cfg{};
+    Linear embed, wpe, head;
+    float *final_w = nullptr, *final_b = nullptr;
+    std::vector<Layer> layers;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    std::vector<void*> owned;
+    std::map<std::string, Named> named;
+    Workspace ws;
+    uint64_t ws_generation = 1;
+};
+
+struct tsm_cache {
+    tsm_model* model = nullptr;
+    int rows = 0, capacity = 0;
+    std::vector<float*> keys, values;
+    std::vector<int> lengths;
+    cudaGraphExec_t graph = nullptr;  // one decode step over all rows
+    uint64_t graph_stamp = 0;         // what the captured step depends on (buffers, mode)
+};
+
+namespace tsm {
+
+static int dev_alloc(tsm_model* m, int64_t bytes, void** out) {
+    TSM_TRY(pool_alloc(m->ctx, bytes, out));
+    m->owned.push_back(*out);
+    return TSM_OK;
+}
+
+static void name_tensor(tsm_model* m, const std::string& name, void* ptr, int kind, int n, int k) {
+    m->named[name] = Named{ptr, kind, n, k};
+}
+
+static void name_linear(tsm_model* m, const std::string& name, const Linear& l) {
+    name_tensor(m, name, l.w, l.kind, l.n, l.k);
+    if (l.bias) name_tensor(m, name + "_b", l.bias, TSM_F32, 1, l.n);
+}
+
+static int64_t weight_bytes(int kind, int64_t n, int64_t k) { return kind == TSM_F32 ? n * k * 4 : n * (k / 32) * block_bytes(kind); }
+
+// cos/sin of every position, in F32 through the host's libm, as RotaryEmbedding computes them
+// (modules.cr:343-351): freq_i = 1f / powf(theta_f32, f32(2i) / width).
+static int make_rope_tables(tsm_model* m) {
+    const tsm_model_config& c = m->cfg;
+    int hw = c.head_width, half = hw / 2;
+    std::vector<float> freq(half), cosv((size_t)c.context * hw), sinv((size_t)c.context * hw);
+    for (int i = 0; i < half; i++) freq[i] = 1.0f / powf((float)c.rope_theta, (float)(2 * i) / (float)hw);
+    for (int p = 0; p < c.context; p++)
+        for (int i = 0; i < hw; i++) {
+            float angle = (float)p * freq[i % half];
+            cosv[(size_t)p * hw + i] = cosf(angle);
+            sinv[(size_t)p * hw + i] = sinf(angle);
+        }
+    int64_t bytes = (int64_t)c.context * hw * 4;
+    TSM_TRY(dev_alloc(m, bytes, (void**)&m->rope_cos));
+    TSM_TRY(dev_alloc(m, bytes, (void**)&m->rope_sin));
+    TSM_TRY(tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)m->rope_cos, cosv.data(), bytes));
+    TSM_TRY(tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)m->rope_sin, sinv.data(), bytes));
+    return TSM_OK;
+}
+
+static int check_config(tsm_ctx* ctx, const tsm_model_config& c) {
+    if (c.arch != 0 && c.arch != 1) return fail(ctx, TSM_ERR_ARG, "unknown architecture");
+    if (c.layers < 1 || c.width < 32 || c.heads < 1 || c.kv_heads < 1 || c.head_width < 2 || c.hidden < 32 || c.vocab < 1 || c.context < 1)
+        return fail(ctx, TSM_ERR_ARG, "a model size is not positive");
+    if (c.heads % c.kv_heads != 0)
+        return fail(ctx, TSM_ERR_ARG, std::to_string(c.heads) + " query heads do not group into " + std::to_string(c.kv_heads) + " key and value heads");
+    if (c.width % 32 != 0 || c.hidden % 32 != 0 || (c.heads * c.head_width) % 32 != 0)
+        return fail(ctx, TSM_ERR_ARG, "quantised products need widths that split into blocks of 32");
+    if (c.arch == 1 && (c.kv_heads != c.heads || c.heads * c.head_width != c.width))
+        return fail(ctx, TSM_ERR_ARG, "width " + std::to_string(c.width) + " does not divide into " + std::to_string(c.heads) + " heads");
+    return TSM_OK;
+}
+
+static void register_names(tsm_model* m) {
+    name_linear(m, "embed", m->embed);
+    if (m->wpe.w) name_linear(m, "wpe", m->wpe);
+    name_linear(m, "head", m->head);
+    name_tensor(m, "final_w", m->final_w, TSM_F32, 1, m->cfg.width);
+    if (m->final_b) name_tensor(m, "final_b", m->final_b, TSM_F32, 1, m->cfg.width);
+    for (size_t i = 0; i < m->layers.size(); i++) {
+        std::string p = std::to_string(i) + ".";
+        Layer& l = m->layers[i];
+        name_tensor(m, p + "norm1_w", l.norm1_w, TSM_F32, 1, m->cfg.width);
+        name_tensor(m, p + "norm2_w", l.norm2_w, TSM_F32, 1, m->cfg.width);
+        if (l.norm1_b) name_tensor(m, p + "norm1_b", l.norm1_b, TSM_F32, 1, m->cfg.width);
+        if (l.norm2_b) name_tensor(m, p + "norm2_b", l.norm2_b, TSM_F32, 1, m->cfg.width);
+        name_linear(m, p + "qkv", l.qkv);
+        name_linear(m, p + "o", l.o);
+        name_linear(m, p + "up", l.up);
+        name_linear(m, p + "down", l.down);
+    }
+}
+
+// ---- GGUF (gguf.cr:297-381) ------------------------------------------------------------------------
+
+struct GgufEntry {
+    uint32_t kind;
+    std::vector<int64_t> shape;  // outermost first
+    int64_t offset;              // absolute
+    int64_t bytes;
+};
+
+struct GgufFile {
+    const uint8_t* data = nullptr;
+    int64_t size = 0, pos = 0;
+    bool bad = false;
+    std::map<std::string, double> numbers;
+    std::map<std::string, std::string> strings;
+    std::map<std::string, GgufEntry> entries;
+    std::vector<std::string> order;
+    ~GgufFile() {
+        if (data) munmap((void*)data, (size_t)size);
+    }
+    const uint8_t* take(int64_t n) {
+        if (n < 0 || pos + n > size) {
+            bad = true;
+            static uint8_t zeros[16] = {0};
+            return zeros;
+        }
+        const uint8_t* p = data + pos;
+        pos += n;
+        return p;
+    }
+    template <class T> T read() {
+        T v;
+        memcpy(&v, take(sizeof(T)), sizeof(T));
+        return v;
+    }
+    std::string str() {
+        uint64_t n = read<uint64_t>();
+        if (n > (uint64_t)(size - pos)) {
+            bad = true;
+            return "";
+        }
+        return std::string((const char*)take((int64_t)n), (size_t)n);
+    }
+    // reads a value of GGUF type t; numbers and strings are kept under `key`, arrays skipped
+    void value(uint32_t t, const std::string& key, int depth = 0) {
+        switch (t) {
+            case 0: numbers[key] = read<uint8_t>(); break;
+            case 1: numbers[key] = read<int8_t>(); break;
+            case 2: numbers[key] = read<uint16_t>(); break;
+            case 3: numbers[key] = read<int16_t>(); break;
+            case 4: numbers[key] = read<uint32_t>(); break;
+            case 5: numbers[key] = read<int32_t>(); break;
+            case 6: numbers[key] = read<float>(); break;
+            case 7: numbers[key] = read<uint8_t>() != 0; break;
+            case 8: strings[key] = str(); break;
+            case 9: {
+                uint32_t element = read<uint32_t>();
+                uint64_t count = read<uint64_t>();
+                for (uint64_t i = 0; i < count && !bad; i++) value(element, "", depth + 1);
+                break;
+            }
+            case 10: numbers[key] = (double)read<uint64_t>(); break;
+            case 11: numbers[key] = (double)read<int64_t>(); break;
+            case 12: numbers[key] = read<double>(); break;
+            default: bad = true;
+        }
+    }
+};
+
+static int64_t gguf_bytes(uint32_t kind, int64_t count) {
+    switch (kind) {
+        case 0: return count * 4;
+        case 1: case 30: return count * 2;
+        case 2: return count / 32 * 18;
+        case 3: return count / 32 * 20;
+        case 8: return count / 32 * 34;
+    }
+    return -1;
+}
+
+static int gguf_kind_to_tsm(uint32_t kind) { return kind == 8 ? TSM_Q8_0 : kind == 2 ? TSM_Q4_0 : kind == 3 ? TSM_Q4_1 : TSM_F32; }
+
+static int gguf_open(tsm_ctx* ctx, const char* path, GgufFile& f) {
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return fail(ctx, TSM_ERR_IO, std::string(path) + " cannot be opened");
+    struct stat st;
+    if (fstat(fd, &st) != 0 || st.st_size < 24) {
+        close(fd);
+        return fail(ctx, TSM_ERR_IO, std::string(path) + " is not a GGUF file");
+    }
+    f.size = st.st_size;
+    void* map = mmap(nullptr, (size_t)f.size, PROT_READ, MAP_PRIVATE, fd, 0);
+    close(fd);
+    if (map == MAP_FAILED) return fail(ctx, TSM_ERR_IO, std::string(path) + " cannot be mapped");
+    f.data = (const uint8_t*)map;
+    if (f.read<uint32_t>() != 0x46554747u) return fail(ctx, TSM_ERR_IO, std::string(path) + " is not a GGUF file");
+    uint32_t version = f.read<uint32_t>();
+    if (version != 2 && version != 3) return fail(ctx, TSM_ERR_IO, std::string(path) + ": GGUF version " + std::to_string(version) + " is not supported");
+    uint64_t tensors = f.read<uint64_t>(), keys = f.read<uint64_t>();
+    for (uint64_t i = 0; i < keys && !f.bad; i++) {
+        std::string key = f.str();
+        f.value(f.read<uint32_t>(), key);
+    }
+    struct Info { std::string name; std::vector<int64_t> shape; uint32_t kind; int64_t offset; };
+    std::vector<Info> infos;
+    for (uint64_t i = 0; i < tensors && !f.bad; i++) {
+        Info info;
+        info.name = f.str();
+        uint32_t nd = f.read<uint32_t>();
+        if (nd > 8) { f.bad = true; break; }
+        std::vector<int64_t> dims(nd);
+        for (uint32_t d = 0; d < nd; d++) dims[d] = (int64_t)f.read<uint64_t>();
+        info.shape.assign(dims.rbegin(), dims.rend());
+        info.kind = f.read<uint32_t>();
+        info.offset = (int64_t)f.read<uint64_t>();
+        infos.push_back(info);
+    }
+    if (f.bad) return fail(ctx, TSM_ERR_IO, std::string(path) + " is malformed");
+    int64_t alignment = f.numbers.count("general.alignment") ? (int64_t)f.numbers["general.alignment"] : 32;
+    if (alignment < 1) alignment = 32;
+    int64_t start = (f.pos + alignment - 1) / alignment * alignment;
+    for (auto& info : infos) {
+        int64_t count = 1;
+        for (int64_t d : info.shape) count *= d;
+        int64_t bytes = gguf_bytes(info.kind, count);
+        if (bytes < 0) return fail(ctx, TSM_ERR_UNSUPPORTED, info.name + ": GGUF tensor type " + std::to_string(info.kind) + " is not supported yet");
+        if ((info.kind == 2 || info.kind == 3 || info.kind == 8) && (info.shape.empty() || info.shape.back() % 32 != 0))
+            return fail(ctx, TSM_ERR_IO, info.name + ": rows of " + std::to_string(info.shape.empty() ? 0 : info.shape.back()) + " do not split into blocks of 32");
+        if (info.offset % alignment != 0 || start + info.offset + bytes > f.size)
+            return fail(ctx, TSM_ERR_IO, info.name + ": " + std::to_string(bytes) + " bytes at " + std::to_string(info.offset) + " do not fit " + path);
+        f.entries[info.name] = GgufEntry{info.kind, info.shape, start + info.offset, bytes};
+        f.order.push_back(info.name);
+    }
+    return TSM_OK;
+}
+
+// Uploads an F32 / F16 / BF16 vector or matrix as F32.
+static int upload_f32(tsm_model* m, GgufFile& f, const std::string& name, int64_t expect, float** out) {
+    auto found = f.entries.find(name);
+    if (found == f.entries.end()) return fail(m->ctx, TSM_ERR_IO, "the file lacks " + name);
+    const GgufEntry& e = found->second;
+    int64_t count = 1;
+    for (int64_t d : e.shape) count *= d;
+    if (count != expect) return fail(m->ctx, TSM_ERR_ARG, name + ": the file holds " + std::to_string(count) + " values, the model " + std::to_string(expect));
+    std::vector<float> wide;
+    const void* src = f.data + e.offset;
+    if (e.kind == 1 || e.kind == 30) {
+        wide.resize((size_t)count);
+        const uint16_t* h = (const uint16_t*)src;
+        for (int64_t i = 0; i < count; i++) {
+            if (e.kind == 30) {
+                uint32_t u = (uint32_t)h[i] << 16;
+                memcpy(&wide[i], &u, 4);
+            } else {
+                wide[i] = __half2float(__ushort_as_half(h[i]));
+            }
+        }
+        src = wide.data();
+    } else if (e.kind != 0) {
+        return fail(m->ctx, TSM_ERR_UNSUPPORTED, name + " is a block format where F32 is expected");
+    }
+    TSM_TRY(dev_alloc(m, count * 4, (void**)out));
+    return tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)*out, src, count * 4);
+}
+
+struct RowSource {
+    std::string name;
+    int heads;  // > 0: undo llama.cpp's rotary row order for this many heads (llama.cr:226-235)
+};
+
+// Uploads one or several [n_i, k] block tensors as one row-joined weight (Linear.merge, modules.cr:36-54).
+static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& parts, int k, int expect_n, Linear* out) {
+    int kind = -2;
+    int64_t total_rows = 0;
+    for (auto& part : parts) {
+        auto found = f.entries.find(part.name);
+        if (found == f.entries.end()) return fail(m->ctx, TSM_ERR_IO, "the file lacks " + part.name);
+        const GgufEntry& e = found->second;
+        if (e.shape.size() != 2 || e.shape[1] != k)
+            return fail(m->ctx, TSM_ERR_ARG, part.name + ": the file's shape does not match the model's [" + std::to_string(expect_n) + ", " + std::to_string(k) + "]");
+        int this_kind = gguf_kind_to_tsm(e.kind);
+        if (e.kind == 1 || e.kind == 30) return fail(m->ctx, TSM_ERR_UNSUPPORTED, part.name + ": F16 matrices are not supported; quantise or store F32");
+        if (kind != -2 && kind != this_kind) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "joined projections must share a format");
+        kind = this_kind;
+        total_rows += e.shape[0];
+    }
+    if (total_rows != expect_n) return fail(m->ctx, TSM_ERR_ARG, parts[0].name + ": the file holds " + std::to_string(total_rows) + " rows, the model " + std::to_string(expect_n));
+    int64_t row_bytes = weight_bytes(kind, 1, k);
+    std::vector<uint8_t> staging((size_t)(total_rows * row_bytes));
+    int64_t at = 0;
+    for (auto& part : parts) {
+        const GgufEntry& e = f.entries[part.name];
+        const uint8_t* src = f.data + e.offset;
+        int64_t rows = e.shape[0];
+        if (part.heads > 0) {
+            int64_t half = rows / part.heads / 2;
+            int64_t dst_row = 0;
+            for (int head = 0; head < part.heads; head++)
+                for (int pair = 0; pair < 2; pair++)
+                    for (int64_t i = 0; i < half; i++, dst_row++)
+                        memcpy(&staging[(size_t)((at + dst_row) * row_bytes)], src + (head * 2 * half + 2 * i + pair) * row_bytes, (size_t)row_bytes);
+        } else {
+            memcpy(&staging[(size_t)(at * row_bytes)], src, (size_t)(rows * row_bytes));
+        }
+        at += rows;
+    }
+    out->kind = kind, out->n = expect_n, out->k = k;
+    TSM_TRY(dev_alloc(m, (int64_t)staging.size(), (void**)&out->w));
+    return tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)out->w, staging.data(), (int64_t)staging.size());
+}
+
+static int load_llama(tsm_model* m, GgufFile& f) {
+    auto num = [&](const std::string& key, double fallback, bool required, bool* missing) {
+        auto found = f.numbers.find("llama." + key);
+        if (found != f.numbers.end()) return found->second;
+        if (required) *missing = true;
+        return fallback;
+    };
+    bool missing = false;
+    tsm_model_config& c = m->cfg;
+    c.arch = 0;
+    c.width = (int)num("embedding_length", 0, true, &missing);
+    c.heads = (int)num("attention.head_count", 0, true, &missing);
+    c.layers = (int)num("block_count", 0, true, &missing);
+    c.hidden = (int)num("feed_forward_length", 0, true, &missing);
+    c.context = (int)num("context_length", 0, true, &missing);
+    c.eps = (float)num("attention.layer_norm_rms_epsilon", 0, true, &missing);
+    if (missing) return fail(m->ctx, TSM_ERR_IO, "the file lacks a llama.* key the model needs");
+    c.kv_heads = (int)num("attention.head_count_kv", c.heads, false, &missing);
+    c.head_width = (int)num("rope.dimension_count", c.heads ? c.width / c.heads : 0, false, &missing);
+    c.rope_theta = num("rope.freq_base", 10000.0, false, &missing);
+    if (f.strings.count("llama.rope.scaling.type") && f.strings["llama.rope.scaling.type"] != "none")
+        return fail(m->ctx, TSM_ERR_UNSUPPORTED, "rope scaling " + f.strings["llama.rope.scaling.type"] + " is not supported");
+    if (!f.entries.count("token_embd.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks token_embd.weight");
+    c.vocab = (int)num("vocab_size", (double)f.entries["token_embd.weight"].shape[0], false, &missing);
+    c.tied = f.entries.count("output.weight") ? 0 : 1;
+    TSM_TRY(check_config(m->ctx, c));
+    std::vector<std::string> used;
+    auto use = [&](const std::string& name) { used.push_back(name); return name; };
+    TSM_TRY(upload_rows(m, f, {{use("token_embd.weight"), 0}}, c.width, c.vocab, &m->embed));
+    if (!c.tied) TSM_TRY(upload_rows(m, f, {{use("output.weight"), 0}}, c.width, c.vocab, &m->head));
+    else m->head = m->embed;
+    TSM_TRY(upload_f32(m, f, use("output_norm.weight"), c.width, &m->final_w));
+    int qn = c.heads * c.head_width, kvn = c.kv_heads * c.head_width;
+    m->layers.resize(c.layers);
+    for (int i = 0; i < c.layers; i++) {
+        std::string p = "blk." + std::to_string(i) + ".";
+        Layer& l = m->layers[i];
+        TSM_TRY(upload_f32(m, f, use(p + "attn_norm.weight"), c.width, &l.norm1_w));
+        TSM_TRY(upload_f32(m, f, use(p + "ffn_norm.weight"), c.width, &l.norm2_w));
+        TSM_TRY(upload_rows(m, f, {{use(p + "attn_q.weight"), c.heads}, {use(p + "attn_k.weight"), c.kv_heads}, {use(p + "attn_v.weight"), 0}},
+                            c.width, qn + 2 * kvn, &l.qkv));
+        TSM_TRY(upload_rows(m, f, {{use(p + "attn_output.weight"), 0}}, qn, c.width, &l.o));
+        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_gate.weight"), 0}, {use(p + "ffn_up.weight"), 0}}, c.width, 2 * c.hidden, &l.up));
+        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_down.weight"), 0}}, c.hidden, c.width, &l.down));
+    }
+    // any tensor left over is an error, as the reference's loader raises (llama.cr:202-203)
+    for (auto& name : f.order) {
+        bool seen = false;
+        for (auto& u : used) seen = seen || u == name;
+        if (!seen) return fail(m->ctx, TSM_ERR_IO, "the file has " + name + ", which the model lacks");
+    }
+    return make_rope_tables(m);
+}
+
+static int upload_bias(tsm_model* m, GgufFile& f, const std::string& name, int n, float** out) {
+    if (!f.entries.count(name)) {
+        *out = nullptr;
+        return TSM_OK;
+    }
+    return upload_f32(m, f, name, n, out);
+}
+
+// GPT-2 in tensomite's own names (gpt2.cr:75-89; module.cr:200-213): wte, wpe, h.N.*, ln_f.
+static int load_gpt2(tsm_model* m, GgufFile& f) {
+    tsm_model_config& c = m->cfg;
+    c.arch = 1;
+    if (!f.strings.count("gpt2.heads")) return fail(m->ctx, TSM_ERR_IO, "the file lacks gpt2.heads");
+    c.heads = atoi(f.strings["gpt2.heads"].c_str());
+    if (!f.entries.count("wte.weight") || !f.entries.count("wpe.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks wte.weight or wpe.weight");
+    c.vocab = (int)f.entries["wte.weight"].shape[0];
+    c.width = (int)f.entries["wte.weight"].shape[1];
+    c.context = (int)f.entries["wpe.weight"].shape[0];
+    c.layers = 0;
+    while (f.entries.count("h." + std::to_string(c.layers) + ".ln_1.weight")) c.layers++;
+    c.kv_heads = c.heads;
+    c.head_width = c.heads > 0 ? c.width / c.heads : 0;
+    c.hidden = 4 * c.width;
+    c.eps = 1e-5f;
+    c.rope_theta = 0;
+    c.tied = 1;
+    TSM_TRY(check_config(m->ctx, c));
+    TSM_TRY(upload_rows(m, f, {{"wte.weight", 0}}, c.width, c.vocab, &m->embed));
+    TSM_TRY(upload_rows(m, f, {{"wpe.weight", 0}}, c.width, c.context, &m->wpe));
+    m->head = m->embed;
+    TSM_TRY(upload_f32(m, f, "ln_f.weight", c.width, &m->final_w));
+    TSM_TRY(upload_f32(m, f, "ln_f.bias", c.width, &m->final_b));
+    m->layers.resize(c.layers);
+    for (int i = 0; i < c.layers; i++) {
+        std::string p = "h." + std::to_string(i) + ".";
+        Layer& l = m->layers[i];
+        TSM_TRY(upload_f32(m, f, p + "ln_1.weight", c.width, &l.norm1_w));
+        TSM_TRY(upload_f32(m, f, p + "ln_1.bias", c.width, &l.norm1_b));
+        TSM_TRY(upload_f32(m, f, p + "ln_2.weight", c.width, &l.norm2_w));
+        TSM_TRY(upload_f32(m, f, p + "ln_2.bias", c.width, &l.norm2_b));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_attn.weight", 0}}, c.width, 3 * c.width, &l.qkv));
+        TSM_TRY(upload_bias(m, f, p + "attn.c_attn.bias", 3 * c.width, &l.qkv.bias));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_proj.weight", 0}}, c.width, c.width, &l.o));
+        TSM_TRY(upload_bias(m, f, p + "attn.c_proj.bias", c.width, &l.o.bias));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_fc.weight", 0}}, c.width, c.hidden, &l.up));
+        TSM_TRY(upload_bias(m, f, p + "mlp.c_fc.bias", c.hidden, &l.up.bias));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0}}, c.hidden, c.width, &l.down));
+        TSM_TRY(upload_bias(m, f, p + "mlp.c_proj.bias", c.width, &l.down.bias));
+    }
+    return TSM_OK;
+}
+
+// ---- random models (Llama.new / GPT2.new with Init.normal(0.02), then Module#quantize) ---------------
+
+static int random_linear(tsm_model* m, int kind, int n, int k, uint64_t seed, bool with_bias, float* scratch, Linear* out) {
+    out->kind = kind, out->n = n, out->k = k;
+    int64_t count = (int64_t)n * k;
+    TSM_TRY(launch_normal_fill(m->ctx, scratch, count, 0.0f, 0.02f, seed));
+    TSM_TRY(dev_alloc(m, weight_bytes(kind, n, k), (void**)&out->w));
+    TSM_TRY(launch_quantize_blocks(m->ctx, scratch, count, kind, out->w));
+    if (with_bias) {
+        TSM_TRY(dev_alloc(m, (int64_t)n * 4, (void**)&out->bias));
+        TSM_TRY(launch_fill(m->ctx, out->bias, n, 0.0f));
+    }
+    return TSM_OK;
+}
+
+static int constant_vector(tsm_model* m, int n, float value, float** out) {
+    TSM_TRY(dev_alloc(m, (int64_t)n * 4, (void**)out));
+    return launch_fill(m->ctx, *out, n, value);
+}
+
+static int build_random(tsm_model* m, int kind, uint64_t seed) {
+    const tsm_model_config& c = m->cfg;
+    int qn = c.heads * c.head_width, kvn = c.kv_heads * c.head_width;
+    int upn = c.arch == 0 ? 2 * c.hidden : c.hidden;
+    int64_t biggest = (int64_t)c.vocab * c.width;
+    int64_t others[] = {(int64_t)(qn + 2 * kvn) * c.width, (int64_t)upn * c.width, (int64_t)c.context * c.width};
+    for (int64_t o : others) biggest = o > biggest ? o : biggest;
+    float* scratch = nullptr;
+    TSM_TRY(pool_alloc(m->ctx, biggest * 4, (void**)&scratch));
+    bool gpt = c.arch == 1;
+    uint64_t t = seed * 1000003ull;
+    int rc = TSM_OK;
+    do {
+        if ((rc = random_linear(m, kind, c.vocab, c.width, t++, false, scratch, &m->embed))) break;
+        if (gpt && (rc = random_linear(m, kind, c.context, c.width, t++, false, scratch, &m->wpe))) break;
+        if (!c.tied) {
+            if ((rc = random_linear(m, kind, c.vocab, c.width, t++, false, scratch, &m->head))) break;
+        } else {
+            m->head = m->embed;
+        }
+        if ((rc = constant_vector(m, c.width, 1.0f, &m->final_w))) break;
+        if (gpt && (rc = constant_vector(m, c.width, 0.0f, &m->final_b))) break;
+        m->layers.resize(c.layers);
+        for (int i = 0; i < c.layers && rc == TSM_OK; i++) {
+            Layer& l = m->layers[i];
+            if ((rc = constant_vector(m, c.width, 1.0f, &l.norm1_w))) break;
+            if ((rc = constant_vector(m, c.width, 1.0f, &l.norm2_w))) break;
+            if (gpt && ((rc = constant_vector(m, c.width, 0.0f, &l.norm1_b)) || (rc = constant_vector(m, c.width, 0.0f, &l.norm2_b)))) break;
+            if ((rc = random_linear(m, kind, qn + 2 * kvn, c.width, t++, gpt, scratch, &l.qkv))) break;
+            if ((rc = random_linear(m, kind, c.width, qn, t++, gpt, scratch, &l.o))) break;
+            if ((rc = random_linear(m, kind, upn, c.width, t++, gpt, scratch, &l.up))) break;
+            if ((rc = random_linear(m, kind, c.width, c.hidden, t++, gpt, scratch, &l.down))) break;
+        }
+    } while (0);
+    cudaStreamSynchronize(m->ctx->stream);
+    pool_release(m->ctx, scratch);
+    if (rc != TSM_OK) return rc;
+    if (!gpt) TSM_TRY(make_rope_tables(m));
+    return TSM_OK;
+}
+
+// ---- one packed step -----------------------------------------------------------------------------
+
+static void free_workspace(tsm_model* m) {
+    Workspace& w = m->ws;
+    void* bufs[] = {w.ids, w.table, w.last, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc};
+    for (void* b : bufs) pool_release(m->ctx, b);
+    if (w.host) cudaFreeHost(w.host);
+    w = Workspace{};
+}
+
+static int ensure_workspace(tsm_model* m, int tokens) {
+    if (m->ws.tokens >= tokens) return TSM_OK;
+    cudaStreamSynchronize(m->ctx->stream);
+    free_workspace(m);
+    const tsm_model_config& c = m->cfg;
+    Workspace& w = m->ws;
+    int64_t T = tokens;
+    int qn = c.heads * c.head_width, kvn = c.kv_heads * c.head_width;
+    int upn = c.arch == 0 ? 2 * c.hidden : c.hidden;
+    tsm_ctx* ctx = m->ctx;
+    TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.ids));
+    TSM_TRY(pool_alloc(ctx, T * 12, (void**)&w.table));
+    TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.last));
+    TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.x));
+    TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.xl));
+    TSM_TRY(pool_alloc(ctx, T * (qn + 2 * kvn) * 4, (void**)&w.qkv));
+    TSM_TRY(pool_alloc(ctx, T * qn * 4, (void**)&w.att));
+    TSM_TRY(pool_alloc(ctx, T * upn * 4, (void**)&w.up));
+    TSM_TRY(pool_alloc(ctx, T * c.vocab * 4, (void**)&w.logits));
+    TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.picks));
+    TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.width), &w.qa));
+    TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, qn), &w.qb));
+    TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.hidden), &w.qc));
+    TSM_CUDA(ctx, cudaMallocHost((void**)&w.host, (size_t)T * 5 * 4));
+    w.tokens = tokens;
+    m->ws_generation++;
+    return TSM_OK;
+}
+
+static int product(tsm_model* m, const QuantizedActs& a, int rows, const Linear& l, const float* residual, float* out) {
+    if (l.kind == TSM_F32) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "F32 matrices are not supported by this engine; quantise the model");
+    return launch_block_matmul(m->ctx, a, rows, l.k, l.w, l.kind, l.n, l.bias, residual, out);
+}
+
+// Launches one step over `total` packed tokens whose ids and table are already in the workspace.
+// `outputs` rows (indices in ws.last when fewer than total) go through the final norm and the head.
+static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, bool pick) {
+    const tsm_model_config& c = m->cfg;
+    tsm_ctx* ctx = m->ctx;
+    Workspace& w = m->ws;
+    int hw = c.head_width, qn = c.heads * hw, kvn = c.kv_heads * hw, qkvn = qn + 2 * kvn;
+    QuantizedActs qa = quant_scratch_layout(w.qa, total, c.width);
+    QuantizedActs qb = quant_scratch_layout(w.qb, total, qn);
+    QuantizedActs qc = quant_scratch_layout(w.qc, total, c.hidden);
+    float scale = (float)(1.0 / sqrt((double)hw));
+    bool ordered = ctx->mode == TSM_EXACT || !(hw == 64 || hw == 128);
+
+    if (m->embed.kind == TSM_F32) return fail(ctx, TSM_ERR_UNSUPPORTED, "F32 embedding tables are not supported by this engine; quantise the model with its embeddings");
+    if (c.arch == 0) {
+        TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, nullptr, nullptr, 0));
+    } else {
+        if (m->wpe.kind != m->embed.kind) return fail(ctx, TSM_ERR_UNSUPPORTED, "token and position tables must share a format");
+        TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, m->wpe.w, w.table + 1, 3));
+    }
+    for (int i = 0; i < c.layers; i++) {
+        Layer& l = m->layers[i];
+        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
+        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
+        TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+        TSM_TRY(launch_rope_append(ctx, w.qkv, total, c.heads, c.kv_heads, hw, c.arch == 0 ? m->rope_cos : nullptr,
+                                   c.arch == 0 ? m->rope_sin : nullptr, c.context, w.table, cache->keys[i], cache->values[i],
+                                   cache->rows, cache->capacity));
+        TSM_TRY(launch_attention(ctx, w.qkv, qkvn, total, c.heads, hw, cache->keys[i], cache->values[i], cache->rows, c.kv_heads,
+                                 cache->capacity, w.table, scale, ordered ? w.att : nullptr, &qb));
+        TSM_TRY(product(m, qb, total, l.o, w.x, w.x));
+        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
+        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
+        TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
+        if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + c.hidden, total, c.hidden, 2 * (int64_t)c.hidden, nullptr, &qc));
+        else TSM_TRY(launch_gelu(ctx, w.up, total, c.hidden, nullptr, &qc));
+        TSM_TRY(product(m, qc, total, l.down, w.x, w.x));
+    }
+    const float* xl = w.x;
+    if (outputs < total) {
+        TSM_TRY(launch_gather_f32(ctx, w.x, total, c.width, w.last, outputs, w.xl));
+        xl = w.xl;
+    }
+    QuantizedActs qh = quant_scratch_layout(w.qa, outputs, c.width);
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, xl, m->final_w, outputs, c.width, c.eps, nullptr, &qh));
+    else TSM_TRY(launch_layernorm(ctx, xl, m->final_w, m->final_b, outputs, c.width, c.eps, nullptr, &qh));
+    Linear head = m->head;
+    head.bias = nullptr;
+    TSM_TRY(product(m, qh, outputs, head, nullptr, w.logits));
+    if (pick) TSM_TRY(launch_argmax(ctx, w.logits, outputs, c.vocab, w.picks));
+    return TSM_OK;
+}
+
+static int prepare_scratch(tsm_model* m, tsm_cache* cache, int tokens) {
+    const tsm_model_config& c = m->cfg;
+    TSM_TRY(ensure_workspace(m, tokens));
+    if (m->ctx->mode == TSM_FAST && (c.head_width == 64 || c.head_width == 128))
+        TSM_TRY(ensure_scratch(m->ctx, m->ctx->attn, attention_scratch_bytes(tokens, c.heads, c.head_width, cache->capacity)));
+    return TSM_OK;
+}
+
+static void drop_graph(tsm_cache* cache) {
+    if (cache->graph) cudaGraphExecDestroy(cache->graph);
+    cache->graph = nullptr;
+}
+
+}  // namespace tsm
+
+#define MODEL_GUARD(m)                                \
+    if (!(m) || !(m)->ctx) return TSM_ERR_ARG;        \
+    tsm::DeviceGuard device_guard__((m)->ctx->ordinal)
+
+extern "C" {
+
+int tsm_model_free(tsm_model* model) {
+    if (!model) return TSM_OK;
+    MODEL_GUARD(model);
+    cudaStreamSynchronize(model->ctx->stream);
+    free_workspace(model);
+    for (void* p : model->owned) pool_release(model->ctx, p);
+    delete model;
+    return TSM_OK;
+}
+
+int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
+    if (!ctx || !path || !out) return TSM_ERR_ARG;
+    tsm::DeviceGuard guard(ctx->ordinal);
+    *out = nullptr;
+    GgufFile f;
+    TSM_TRY(gguf_open(ctx, path, f));
+    std::unique_ptr<tsm_model> m(new tsm_model());
+    m->ctx = ctx;
+    std::string arch = f.strings.count("general.architecture") ? f.strings["general.architecture"] : "";
+    int rc;
+    if (arch == "llama") rc = load_llama(m.get(), f);
+    else if (f.strings.count("gpt2.heads")) rc = load_gpt2(m.get(), f);
+    else rc = fail(ctx, TSM_ERR_IO, std::string(path) + " holds a " + arch + " model, not a Llama or GPT-2");
+    if (rc != TSM_OK) {
+        tsm_model_free(m.release());
+        return rc;
+    }
+    register_names(m.get());
+    *out = m.release();
+    return TSM_OK;
+}
+
+int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uint64_t seed, tsm_model** out) {
+    if (!ctx || !config || !out) return TSM_ERR_ARG;
+    tsm::DeviceGuard guard(ctx->ordinal);
+    *out = nullptr;
+    if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
+    TSM_TRY(check_config(ctx, *config));
+    std::unique_ptr<tsm_model> m(new tsm_model());
+    m->ctx = ctx;
+    m->cfg = *config;
+    if (m->cfg.arch == 1) m->cfg.tied = 1;
+    int rc = build_random(m.get(), kind, seed);
+    if (rc != TSM_OK) {
+        tsm_model_free(m.release());
+        return rc;
+    }
+    register_names(m.get());
+    *out = m.release();
+    return TSM_OK;
+}
+
+int tsm_model_config_get(tsm_model* model, tsm_model_config* out) {
+    if (!model || !out) return TSM_ERR_ARG;
+    *out = model->cfg;
+    return TSM_OK;
+}
+
+int tsm_model_tensor(tsm_model* model, const char* name, tsm_dptr* ptr, int* kind, int* n, int* k) {
+    if (!model || !name) return TSM_ERR_ARG;
+    auto found = model->named.find(name);
+    if (found == model->named.end()) return fail(model->ctx, TSM_ERR_ARG, std::string("the model has no parameter ") + name);
+    if (ptr) *ptr = (tsm_dptr)(uintptr_t)found->second.ptr;
+    if (kind) *kind = found->second.kind;
+    if (n) *n = found->second.n;
+    if (k) *k = found->second.k;
+    return TSM_OK;
+}
+
+int tsm_cache_create(tsm_model* model, int rows, int capacity, tsm_cache** out) {
+    MODEL_GUARD(model);
+    if (!out) return TSM_ERR_ARG;
+    *out = nullptr;
+    if (rows < 1 || capacity < 1) return fail(model->ctx, TSM_ERR_ARG, "a cache needs rows and positions");
+    const tsm_model_config& c = model->cfg;
+    std::unique_ptr<tsm_cache> cache(new tsm_cache());
+    cache->model = model, cache->rows = rows, cache->capacity = capacity;
+    cache->lengths.assign(rows, 0);
+    int64_t bytes = (int64_t)rows * c.kv_heads * capacity * c.head_width * 4;
+    for (int i = 0; i < c.layers; i++) {
+        void *kp = nullptr, *vp = nullptr;
+        int rc = pool_alloc(model->ctx, bytes, &kp);
+        if (rc == TSM_OK) cache->keys.push_back((float*)kp), rc = pool_alloc(model->ctx, bytes, &vp);
+        if (rc == TSM_OK) cache->values.push_back((float*)vp);
+        if (rc != TSM_OK) {
+            tsm_cache_free(cache.release());
+            return rc;
+        }
+    }
+    *out = cache.release();
+    return TSM_OK;
+}
+
+int tsm_cache_free(tsm_cache* cache) {
+    if (!cache) return TSM_OK;
+    MODEL_GUARD(cache->model);
+    cudaStreamSynchronize(cache->model->ctx->stream);
+    drop_graph(cache);
+    for (float* p : cache->keys) pool_release(cache->model->ctx, p);
+    for (float* p : cache->values) pool_release(cache->model->ctx, p);
+    delete cache;
+    return TSM_OK;
+}
+
+int tsm_cache_length(tsm_cache* cache, int row, int* length) {
+    if (!cache || !length || row < 0 || row >= cache->rows) return TSM_ERR_ARG;
+    *length = cache->lengths[row];
+    return TSM_OK;
+}
+
+int tsm_cache_reset(tsm_cache* cache, int row) {
+    if (!cache || row < 0 || row >= cache->rows) return TSM_ERR_ARG;
+    cache->lengths[row] = 0;
+    return TSM_OK;
+}
+
+int tsm_cache_layer(tsm_cache* cache, int layer, tsm_dptr* keys, tsm_dptr* values) {
+    if (!cache || layer < 0 || layer >= (int)cache->keys.size()) return TSM_ERR_ARG;
+    if (keys) *keys = (tsm_dptr)(uintptr_t)cache->keys[layer];
+    if (values) *values = (tsm_dptr)(uintptr_t)cache->values[layer];
+    return TSM_OK;
+}
+
+int tsm_cache_fill(tsm_cache* cache, int row, int length, uint64_t seed) {
+    if (!cache) return TSM_ERR_ARG;
+    MODEL_GUARD(cache->model);
+    tsm_model* m = cache->model;
+    if (row < 0 || row >= cache->rows || length < 0 || length > cache->capacity || length > m->cfg.context)
+        return fail(m->ctx, TSM_ERR_ARG, std::to_string(length) + " positions exceed the " + std::to_string(cache->capacity) + " a row holds");
+    const tsm_model_config& c = m->cfg;
+    for (int i = 0; i < c.layers; i++)
+        for (int kh = 0; kh < c.kv_heads; kh++) {
+            int64_t at = ((int64_t)row * c.kv_heads + kh) * cache->capacity * c.head_width;
+            uint64_t s = seed * 7919ull + (uint64_t)((i * c.kv_heads + kh) * 2 + 1) * 1000003ull + (uint64_t)row;
+            TSM_TRY(launch_normal_fill(m->ctx, cache->keys[i] + at, (int64_t)length * c.head_width, 0.0f, 1.0f, s));
+            TSM_TRY(launch_normal_fill(m->ctx, cache->values[i] + at, (int64_t)length * c.head_width, 0.0f, 1.0f, s + 1));
+        }
+    cache->lengths[row] = length;
+    return TSM_OK;
+}
+
+// Generative#packed (generative.cr:112-125) with optional greedy picks of each output row.
+static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* counts, const int32_t* ids, int last, float* logits,
+                        int32_t* picks) {
+    if (!cache || cache->model != model || !counts || !ids || (!logits && !picks)) return fail(model->ctx, TSM_ERR_ARG, "forward needs a cache of this model, counts, ids and a place for logits");
+    tsm_ctx* ctx = model->ctx;
+    const tsm_model_config& c = model->cfg;
+    int total = 0, active = 0;
+    int limit = cache->capacity < c.context ? cache->capacity : c.context;
+    for (int row = 0; row < cache->rows; row++) {
+        if (counts[row] < 0) return fail(ctx, TSM_ERR_ARG, "a negative token count");
+        if (counts[row] == 0) continue;
+        if (cache->lengths[row] + counts[row] > limit)
+            return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + counts[row]) + " positions exceed the " + std::to_string(limit) + " a row holds");
+        total += counts[row];
+        active++;
+    }
+    if (total == 0) return fail(ctx, TSM_ERR_ARG, "forward of no tokens");
+    TSM_TRY(prepare_scratch(model, cache, total));
+    Workspace& w = model->ws;
+    int32_t* h_ids = w.host;
+    int32_t* h_table = w.host + w.tokens;
+    int32_t* h_last = w.host + 4 * (int64_t)w.tokens;
+    int t = 0, outputs = 0;
+    for (int row = 0; row < cache->rows; row++) {
+        int past = cache->lengths[row];
+        for (int j = 0; j < counts[row]; j++, t++) {
+            h_ids[t] = ids[t];
+            h_table[3 * t] = row, h_table[3 * t + 1] = past + j, h_table[3 * t + 2] = past + counts[row];
+            if (!last || j == counts[row] - 1) h_last[outputs++] = t;
+        }
+    }
+    TSM_CUDA(ctx, cudaMemcpyAsync(w.ids, h_ids, (size_t)total * 4, cudaMemcpyHostToDevice, ctx->stream));
+    TSM_CUDA(ctx, cudaMemcpyAsync(w.table, h_table, (size_t)total * 12, cudaMemcpyHostToDevice, ctx->stream));
+    TSM_CUDA(ctx, cudaMemcpyAsync(w.last, h_last, (size_t)outputs * 4, cudaMemcpyHostToDevice, ctx->stream));
+    ctx->counters.uploads += 3;
+    ctx->counters.upload_bytes += (int64_t)total * 16 + (int64_t)outputs * 4;
+    TSM_TRY(launch_step(model, cache, total, outputs, picks != nullptr));
+    if (logits) {
+        TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)outputs * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->counters.downloads++;
+        ctx->counters.download_bytes += (int64_t)outputs * c.vocab * 4;
+    }
+    if (picks) {
+        TSM_CUDA(ctx, cudaMemcpyAsync(picks, w.picks, (size_t)outputs * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->counters.downloads++;
+        ctx->counters.download_bytes += (int64_t)outputs * 4;
+    }
+    TSM_TRY(tsm_sync(ctx));
+    for (int row = 0; row < cache->rows; row++) cache->lengths[row] += counts[row];
+    return TSM_OK;
+}
+
+int tsm_forward(tsm_model* model, tsm_cache* cache, const int32_t* counts, const int32_t* ids, int last, float* logits) {
+    MODEL_GUARD(model);
+    if (!logits) return fail(model->ctx, TSM_ERR_ARG, "forward needs a place for logits");
+    return forward_impl(model, cache, counts, ids, last, logits, nullptr);
+}
+
+int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* tokens, float* logits) {
+    MODEL_GUARD(model);
+    if (!cache || cache->model != model || !ids || !tokens) return fail(model->ctx, TSM_ERR_ARG, "decode needs a cache of this model, ids and a place for tokens");
+    tsm_ctx* ctx = model->ctx;
+    const tsm_model_config& c = model->cfg;
+    int rows = cache->rows;
+    int limit = cache->capacity < c.context ? cache->capacity : c.context;
+    for (int row = 0; row < rows; row++)
+        if (cache->lengths[row] + 1 > limit)
+            return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + 1) + " positions exceed the " + std::to_string(limit) + " a row holds");
+    TSM_TRY(prepare_scratch(model, cache, rows));
+    // a captured step holds the addresses of the workspace and of the scratch memory, and the mode's kernels
+    uint64_t stamp = model->ws_generation * 1000003ull + ctx->scratch_generation * 10ull + (uint64_t)ctx->mode;
+    if (cache->graph && cache->graph_stamp != stamp) drop_graph(cache);
+    cache->graph_stamp = stamp;
+    Workspace& w = model->ws;
+    int32_t* h_ids = w.host;
+    int32_t* h_table = w.host + w.tokens;
+    int32_t* h_picks = w.host + 4 * (int64_t)w.tokens;
+    for (int row = 0; row < rows; row++) {
+        h_ids[row] = ids[row];
+        h_table[3 * row] = row, h_table[3 * row + 1] = cache->lengths[row], h_table[3 * row + 2] = cache->lengths[row] + 1;
+    }
+    if (!cache->graph) {
+        // the step reads ids and positions from device memory, so one capture serves every later step
+        cudaGraph_t graph = nullptr;
+        TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        int rc = TSM_OK;
+        cudaError_t e1 = cudaMemcpyAsync(w.ids, h_ids, (size_t)rows * 4, cudaMemcpyHostToDevice, ctx->stream);
+        cudaError_t e2 = cudaMemcpyAsync(w.table, h_table, (size_t)rows * 12, cudaMemcpyHostToDevice, ctx->stream);
+        if (e1 != cudaSuccess || e2 != cudaSuccess) rc = cuda_fail(ctx, e1 != cudaSuccess ? e1 : e2, "cudaMemcpyAsync");
+        if (rc == TSM_OK) rc = launch_step(model, cache, rows, rows, true);
+        cudaError_t e3 = cudaMemcpyAsync(h_picks, w.picks, (size_t)rows * 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e3 == cudaSuccess) e3 = cudaMemcpyAsync(ctx->errors_host, ctx->errors, sizeof(ErrorRecord), cudaMemcpyDeviceToHost, ctx->stream);
+        cudaError_t e4 = cudaStreamEndCapture(ctx->stream, &graph);
+        if (rc == TSM_OK && (e3 != cudaSuccess || e4 != cudaSuccess)) rc = cuda_fail(ctx, e3 != cudaSuccess ? e3 : e4, "capture of a decode step");
+        if (rc == TSM_OK) {
+            cudaError_t e5 = cudaGraphInstantiate(&cache->graph, graph, 0);
+            if (e5 != cudaSuccess) rc = cuda_fail(ctx, e5, "cudaGraphInstantiate");
+        }
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != TSM_OK) {
+            cudaGetLastError();
+            return rc;
+        }
+    }
+    TSM_CUDA(ctx, cudaGraphLaunch(cache->graph, ctx->stream));
+    ctx->counters.graph_replays++;
+    ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
+    ctx->counters.downloads += 1, ctx->counters.download_bytes += (int64_t)rows * 4;
+    if (logits) {
+        TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)rows * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->counters.downloads++, ctx->counters.download_bytes += (int64_t)rows * c.vocab * 4;
+    }
+    TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TSM_TRY(check_error_record(ctx));  // the replayed step copied the record to the host
+    for (int row = 0; row < rows; row++) {
+        tokens[row] = h_picks[row];
+        cache->lengths[row] += 1;
+    }
+    return TSM_OK;
+}
+
+int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens) {
+    MODEL_GUARD(model);
+    if (!prompt || prompt_size < 1 || count < 0 || (count > 0 && !tokens)) return fail(model->ctx, TSM_ERR_ARG, "generate needs a prompt and a place for tokens");
+    const tsm_model_config& c = model->cfg;
+    if (count == 0) return TSM_OK;
+    int capacity = prompt_size + count < c.context ? prompt_size + count : c.context;
+    tsm_cache* cache = nullptr;
+    TSM_TRY(tsm_cache_create(model, 1, capacity, &cache));
+    int32_t counts[1] = {prompt_size};
+    // Sampler.greedy picks on the device: the first index of the maximum (sampler.cr:36)
+    int rc = forward_impl(model, cache, counts, prompt, 1, nullptr, &tokens[0]);
+    for (int i = 1; i < count && rc == TSM_OK; i++) rc = tsm_decode(model, cache, &tokens[i - 1], &tokens[i], nullptr);
+    tsm_cache_free(cache);
+    return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,427 @@
+// The quantised product x . w^T over ggml block weights, with the reference's bits
+// (Quant.matmul_reference, quant.cr:122-142; block_matmul_lanes_f32, kernels.cu:1286-1328).
+//
+// Each output is the sum, IN BLOCK ORDER from 0f, of one float contribution per 32-element block;
+// a block's integer dot product may be taken in any order (it is exact), the float sum may not.
+//
+// streamed kernel (rows of activations <= 4, the decode case)
+//   The weight matrix is one contiguous run of blocks.  It is cut into tiles of whole rows; a tile's
+//   bytes, widened to whole groups of 8 blocks (4 for Q4_1) so that both ends fall on 16-byte
+//   boundaries, arrive in shared memory through one bulk asynchronous copy (cp.async.bulk, completion
+//   counted on an mbarrier) into a ring of stages, so HBM sees long sequential reads and no thread
+//   spends instructions on loads.  Each compute thread takes one group: 9 / 17 / 5 aligned 16-byte
+//   shared loads (group sizes 144 / 272 / 80 bytes are odd multiples of 16, so a quarter-warp's loads
+//   fall in distinct banks), unpacks scales and quants with byte permutes, multiplies with __dp4a
+//   against the quantised activations held in shared memory, and writes the group's float
+//   contributions to a staging array.  A fifth warp folds each row's contributions in block order
+//   (one lane per row) while the compute warps work on the next tile, and issues the copies.
+//
+// generic kernel (any row count, any alignment down to 2 bytes)
+//   One warp per output; lane l takes blocks l, l+32, ...; contributions are folded in block order
+//   through shuffles.  It is the fallback for shapes the streamed kernel does not take.
+#include "common.cuh"
+
+namespace tsm {
+
+template <int KIND> struct Fmt;
+template <> struct Fmt<TSM_Q8_0> { static constexpr int B = 34, G = 8, GB = 272, WORDS = 68, CAP = 128; };
+template <> struct Fmt<TSM_Q4_0> { static constexpr int B = 18, G = 8, GB = 144, WORDS = 36, CAP = 128; };
+template <> struct Fmt<TSM_Q4_1> { static constexpr int B = 20, G = 4, GB = 80, WORDS = 20, CAP = 256; };
+
+constexpr int kComputeThreads = 128;
+constexpr int kThreads = 160;  // 4 compute warps + 1 fold/producer warp
+constexpr int kStages = 3;
+constexpr unsigned kWaitSpins = 4u << 20;
+
+struct MatvecParams {
+    const uint8_t* w;
+    int n, nb;
+    QuantizedActs acts;
+    const float* bias;
+    const float* residual;
+    float* out;
+    int rows_per_tile, num_tiles;
+    ErrorRecord* errors;
+};
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Waits for the phase with a bounded number of tries; false when it ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+    for (unsigned spin = 0; spin < kWaitSpins; spin++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (spin > 4096) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Staging index of a tile-relative block: one pad word per 32, so that lanes folding different rows
+// (a whole number of blocks apart) read different banks.
+__host__ __device__ __forceinline__ int part_index(int p) { return p + (p >> 5); }
+// Byte offset of activation block kb in shared memory: 16 pad bytes per 8 blocks, so that lanes on
+// consecutive groups (256 bytes apart) read different banks.
+__host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (kb >> 3) * 16; }
+
+template <int KIND, int C>
+__global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
+    using F = Fmt<KIND>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int nb = p.nb;
+    const int act_bytes = (act_offset(nb) + 15) & ~15;
+    const int pcap = part_index(F::CAP * F::G) + 1;
+    uint64_t* full = (uint64_t*)smem;                        // kStages barriers
+    int* abort_flag = (int*)(smem + 64);
+    unsigned char* acts_q = smem + 128;                      // C x act_bytes
+    float* acts_scale = (float*)(acts_q + C * act_bytes);    // C x nb
+    float* acts_aux = acts_scale + C * nb;                   // C x nb (Q4_0: totals as int; Q4_1: sums)
+    float* parts = acts_aux + C * nb;                        // 2 x C x pcap
+    size_t stage_off = (size_t)((unsigned char*)(parts + 2 * C * pcap) - smem);
+    stage_off = (stage_off + 127) & ~(size_t)127;
+    unsigned char* stages = smem + stage_off;                // kStages x CAP x GB
+    constexpr int kStageBytes = F::CAP * F::GB;
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const bool producer = (tid == kComputeThreads);
+
+    auto tile_span = [&](int tile, int& r0, int& r1, int64_t& g0, int& groups) {
+        r0 = tile * p.rows_per_tile;
+        r1 = min(p.n, r0 + p.rows_per_tile);
+        int64_t fb0 = (int64_t)r0 * nb, fb1 = (int64_t)r1 * nb;
+        g0 = fb0 / F::G;
+        groups = (int)((fb1 + F::G - 1) / F::G - g0);
+    };
+    auto issue = [&](int it) {
+        int tile = blockIdx.x + it * gridDim.x;
+        if (tile >= p.num_tiles) return;
+        int r0, r1, groups;
+        int64_t g0;
+        tile_span(tile, r0, r1, g0, groups);
+        int s = it % kStages;
+        unsigned bytes = (unsigned)groups * F::GB;
+        mbar_expect_tx(&full[s], bytes);
+        bulk_load(stages + (size_t)s * kStageBytes, p.w + g0 * F::GB, bytes, &full[s]);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; s++) mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (producer)
+        for (int it = 0; it < kStages; it++) issue(it);
+
+    // quantised activations -> shared memory (every CTA reads them once; they stay in L2)
+    for (int c = 0; c < C; c++) {
+        const int4* src = (const int4*)(p.acts.qs + (int64_t)c * nb * 32);
+        for (int i = tid; i < nb * 2; i += kThreads) {
+            int kb = i >> 1;
+            *(int4*)(acts_q + c * act_bytes + act_offset(kb) + (i & 1) * 16) = src[i];
+        }
+        for (int i = tid; i < nb; i += kThreads) {
+            acts_scale[c * nb + i] = p.acts.scales[(int64_t)c * nb + i];
+            if (KIND == TSM_Q4_0) ((int*)acts_aux)[c * nb + i] = p.acts.totals[(int64_t)c * nb + i];
+            if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = p.acts.sums[(int64_t)c * nb + i];
+        }
+    }
+    __syncthreads();
+
+    int prev_r0 = 0, prev_r1 = 0, prev_base = 0;  // the tile whose contributions wait to be folded
+    bool have_prev = false;
+    for (int it = 0;; it++) {
+        int tile = blockIdx.x + it * gridDim.x;
+        bool valid = tile < p.num_tiles;
+        int r0 = 0, r1 = 0, groups = 0;
+        int64_t g0 = 0;
+        if (valid) tile_span(tile, r0, r1, g0, groups);
+        float* cur = parts + (it & 1) * C * pcap;
+        if (warp < 4) {
+            if (valid) {
+                int s = it % kStages;
+                bool arrived = mbar_wait(&full[s], (unsigned)((it / kStages) & 1));
+                if (!arrived) *abort_flag = 1;
+                const unsigned char* stage = stages + (size_t)s * kStageBytes;
+                int kb_first = (int)((g0 * F::G) % nb);
+                for (int gi = tid; gi < groups && arrived; gi += kComputeThreads) {
+                    unsigned W[F::WORDS];
+                    const uint4* gp = (const uint4*)(stage + (size_t)gi * F::GB);
+#pragma unroll
+                    for (int i = 0; i < F::WORDS / 4; i++) {
+                        uint4 v = gp[i];
+                        W[4 * i] = v.x, W[4 * i + 1] = v.y, W[4 * i + 2] = v.z, W[4 * i + 3] = v.w;
+                    }
+                    int kb = (kb_first + gi * F::G) % nb;
+#pragma unroll
+                    for (int j = 0; j < F::G; j++) {
+                        int kbj = kb + j;
+                        if (kbj >= nb) kbj -= nb;
+                        float dw, mw = 0.0f;
+                        unsigned q[8];
+                        if (KIND == TSM_Q8_0) {
+                            const int base = 17 * (j >> 1);
+                            if ((j & 1) == 0) {
+                                dw = half_bits_to_float(W[base] & 0xffffu);
+#pragma unroll
+                                for (int i = 0; i < 8; i++) q[i] = __byte_perm(W[base + i], W[base + i + 1], 0x5432);
+                            } else {
+                                dw = half_bits_to_float(W[base + 8] >> 16);
+#pragma unroll
+                                for (int i = 0; i < 8; i++) q[i] = W[base + 9 + i];
+                            }
+                        } else if (KIND == TSM_Q4_0) {
+                            const int base = 9 * (j >> 1);
+                            unsigned nib[4];
+                            if ((j & 1) == 0) {
+                                dw = half_bits_to_float(W[base] & 0xffffu);
+#pragma unroll
+                                for (int i = 0; i < 4; i++) nib[i] = __byte_perm(W[base + i], W[base + i + 1], 0x5432);
+                            } else {
+                                dw = half_bits_to_float(W[base + 4] >> 16);
+#pragma unroll
+                                for (int i = 0; i < 4; i++) nib[i] = W[base + 5 + i];
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; i++) q[i] = nib[i] & 0x0f0f0f0fu, q[4 + i] = (nib[i] >> 4) & 0x0f0f0f0fu;
+                        } else {
+                            const int base = 5 * j;
+                            dw = half_bits_to_float(W[base] & 0xffffu);
+                            mw = half_bits_to_float(W[base] >> 16);
+#pragma unroll
+                            for (int i = 0; i < 4; i++)
+                                q[i] = W[base + 1 + i] & 0x0f0f0f0fu, q[4 + i] = (W[base + 1 + i] >> 4) & 0x0f0f0f0fu;
+                        }
+#pragma unroll
+                        for (int c = 0; c < C; c++) {
+                            const uint4* ap = (const uint4*)(acts_q + c * act_bytes + act_offset(kbj));
+                            uint4 a0 = ap[0], a1 = ap[1];
+                            int total = __dp4a((int)q[0], (int)a0.x, 0);
+                            total = __dp4a((int)q[1], (int)a0.y, total);
+                            total = __dp4a((int)q[2], (int)a0.z, total);
+                            total = __dp4a((int)q[3], (int)a0.w, total);
+                            total = __dp4a((int)q[4], (int)a1.x, total);
+                            total = __dp4a((int)q[5], (int)a1.y, total);
+                            total = __dp4a((int)q[6], (int)a1.z, total);
+                            total = __dp4a((int)q[7], (int)a1.w, total);
+                            float dx = acts_scale[c * nb + kbj];
+                            float contribution;
+                            if (KIND == TSM_Q8_0) {
+                                contribution = __fmul_rn((float)total, __fmul_rn(dw, dx));
+                            } else if (KIND == TSM_Q4_0) {
+                                int xt = ((const int*)acts_aux)[c * nb + kbj];
+                                contribution = __fmul_rn(__fmul_rn((float)(total - 8 * xt), dw), dx);
+                            } else {
+                                float sx = acts_aux[c * nb + kbj];
+                                contribution = __fadd_rn(__fmul_rn(__fmul_rn(dw, dx), (float)total), __fmul_rn(mw, sx));
+                            }
+                            cur[c * pcap + part_index(gi * F::G + j)] = contribution;
+                        }
+                    }
+                }
+            }
+        } else if (have_prev) {
+            // fold the previous tile: lane per row, each row's blocks in order from 0f
+            const float* old = parts + ((it - 1) & 1) * C * pcap;
+            for (int r = prev_r0 + lane; r < prev_r1; r += 32) {
+                int at = prev_base + (r - prev_r0) * nb;
+                float sum[C];
+#pragma unroll
+                for (int c = 0; c < C; c++) sum[c] = 0.0f;
+                for (int b = 0; b < nb; b++) {
+                    int idx = part_index(at + b);
+#pragma unroll
+                    for (int c = 0; c < C; c++) sum[c] = __fadd_rn(sum[c], old[c * pcap + idx]);
+                }
+#pragma unroll
+                for (int c = 0; c < C; c++) {
+                    float v = sum[c];
+                    if (p.bias) v = __fadd_rn(v, p.bias[r]);
+                    if (p.residual) v = __fadd_rn(p.residual[(int64_t)c * p.n + r], v);
+                    p.out[(int64_t)c * p.n + r] = v;
+                }
+            }
+        }
+        __syncthreads();
+        if (*abort_flag) break;
+        if (!valid) break;
+        have_prev = true;
+        prev_r0 = r0, prev_r1 = r1;
+        prev_base = (int)((int64_t)r0 * nb - g0 * F::G);
+        if (producer) issue(it + kStages);
+    }
+    if (*abort_flag && tid == 0) {
+        atomicExch(&p.errors->timeout, 1);
+        // give copies still in flight a bounded chance to land before the shared memory is released
+        for (int s = 0; s < kStages; s++) mbar_wait(&full[s], 0), mbar_wait(&full[s], 1);
+    }
+}
+
+// ---- generic kernel ------------------------------------------------------------------------------
+
+__device__ __forceinline__ unsigned load_u32_2(const uint8_t* p) {  // p is 2-byte aligned
+    const unsigned short* h = (const unsigned short*)p;
+    return (unsigned)h[0] | ((unsigned)h[1] << 16);
+}
+
+template <int KIND>
+__global__ void matvec_generic_kernel(const uint8_t* __restrict__ w, int n, int nb, QuantizedActs acts, int rows,
+                                      const float* __restrict__ bias, const float* __restrict__ residual, float* out) {
+    constexpr int B = Fmt<KIND>::B;
+    int lane = threadIdx.x & 31;
+    int64_t col = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (col >= n) return;
+    const uint8_t* wrow = w + col * (int64_t)nb * B;
+    for (int row = 0; row < rows; row++) {
+        const int8_t* qs = acts.qs + (int64_t)row * nb * 32;
+        float sum = 0.0f;
+        for (int start = 0; start < nb; start += 32) {
+            int block = start + lane;
+            float contribution = 0.0f;
+            if (block < nb) {
+                const uint8_t* blk = wrow + (int64_t)block * B;
+                const int* a = (const int*)(qs + block * 32);
+                float dw = half_bits_to_float(*(const unsigned short*)blk);
+                float dx = acts.scales[(int64_t)row * nb + block];
+                int total = 0;
+                if (KIND == TSM_Q8_0) {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) total = __dp4a((int)load_u32_2(blk + 2 + 4 * i), a[i], total);
+                    contribution = __fmul_rn((float)total, __fmul_rn(dw, dx));
+                } else {
+                    const uint8_t* packed = blk + (KIND == TSM_Q4_0 ? 2 : 4);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        unsigned word = load_u32_2(packed + 4 * i);
+                        total = __dp4a((int)(word & 0x0f0f0f0fu), a[i], total);
+                        total = __dp4a((int)((word >> 4) & 0x0f0f0f0fu), a[4 + i], total);
+                    }
+                    if (KIND == TSM_Q4_0) {
+                        int xt = acts.totals[(int64_t)row * nb + block];
+                        contribution = __fmul_rn(__fmul_rn((float)(total - 8 * xt), dw), dx);
+                    } else {
+                        float mw = half_bits_to_float(*(const unsigned short*)(blk + 2));
+                        float sx = acts.sums[(int64_t)row * nb + block];
+                        contribution = __fadd_rn(__fmul_rn(__fmul_rn(dw, dx), (float)total), __fmul_rn(mw, sx));
+                    }
+                }
+            }
+            int run = min(32, nb - start);
+            for (int j = 0; j < run; j++) sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, contribution, j));
+        }
+        if (lane == 0) {
+            float v = sum;
+            if (bias) v = __fadd_rn(v, bias[col]);
+            if (residual) v = __fadd_rn(residual[(int64_t)row * n + col], v);
+            out[(int64_t)row * n + col] = v;
+        }
+    }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+
+template <int KIND, int C>
+static size_t stream_smem_bytes(int nb) {
+    using F = Fmt<KIND>;
+    size_t act_bytes = (size_t)((act_offset(nb) + 15) & ~15);
+    size_t pcap = (size_t)(F::CAP * F::G + (F::CAP * F::G >> 5) + 1);
+    size_t bytes = 128 + C * act_bytes + (size_t)2 * C * nb * 4 + 2 * C * pcap * 4;
+    bytes = (bytes + 127) & ~(size_t)127;
+    return bytes + (size_t)kStages * F::CAP * F::GB;
+}
+
+template <int KIND, int C>
+static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint8_t* w, int n, const float* bias,
+                         const float* residual, float* out, bool* taken) {
+    using F = Fmt<KIND>;
+    *taken = false;
+    int nb = k / 32;
+    if (((uintptr_t)w & 15) != 0 || ((int64_t)n * nb) % F::G != 0 || ((uintptr_t)a.qs & 15) != 0) return TSM_OK;
+    int max_rows = ((F::CAP - 2) * F::G) / nb;
+    if (max_rows < 1) return TSM_OK;
+    size_t smem = stream_smem_bytes<KIND, C>(nb);
+    if (smem > 200 * 1024) return TSM_OK;
+    auto kernel = matvec_stream_kernel<KIND, C>;
+    static std::mutex attr_lock;  // the attribute is per device and per function
+    static std::map<std::pair<int, const void*>, size_t> attr_set;
+    {
+        std::lock_guard<std::mutex> guard(attr_lock);
+        auto key = std::make_pair(ctx->ordinal, (const void*)kernel);
+        auto found = attr_set.find(key);
+        if (found == attr_set.end() || found->second < smem) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            attr_set[key] = 200 * 1024;
+        }
+    }
+    int per_sm = 0;
+    TSM_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem));
+    if (per_sm < 1) return TSM_OK;
+    int slots = per_sm * ctx->sm_count;
+    int tiles = (n + max_rows - 1) / max_rows;
+    int grid = tiles < slots ? tiles : slots;
+    int per_cta = (tiles + grid - 1) / grid;
+    int rows_per_tile = (n + grid * per_cta - 1) / (grid * per_cta);
+    if (rows_per_tile > max_rows) rows_per_tile = max_rows;
+    if (rows_per_tile < 1) rows_per_tile = 1;
+    tiles = (n + rows_per_tile - 1) / rows_per_tile;
+    if (grid > tiles) grid = tiles;
+    MatvecParams p;
+    p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
+    p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
+    kernel<<<grid, kThreads, smem, ctx->stream>>>(p);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    *taken = true;
+    return TSM_OK;
+}
+
+template <int KIND>
+static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int n, const float* bias,
+                       const float* residual, float* out) {
+    bool taken = false;
+    if (rows == 1) TSM_TRY((launch_stream<KIND, 1>(ctx, a, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 2) TSM_TRY((launch_stream<KIND, 2>(ctx, a, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, k, w, n, bias, residual, out, &taken)));
+    if (taken) return TSM_OK;
+    int nb = k / 32;
+    int64_t grid = ((int64_t)n + 3) / 4;
+    matvec_generic_kernel<KIND><<<(unsigned)grid, 128, 0, ctx->stream>>>(w, n, nb, a, rows, bias, residual, out);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                        const float* bias, const float* residual, float* out) {
+    if (k <= 0 || k % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
+    if (((uintptr_t)w & 1) != 0) return fail(ctx, TSM_ERR_ARG, "block weights must start at an even address");
+    if (rows == 0 || n == 0) return TSM_OK;
+    switch (kind) {
+        case TSM_Q8_0: return launch_kind<TSM_Q8_0>(ctx, a, rows, k, w, n, bias, residual, out);
+        case TSM_Q4_0: return launch_kind<TSM_Q4_0>(ctx, a, rows, k, w, n, bias, residual, out);
+        case TSM_Q4_1: return launch_kind<TSM_Q4_1>(ctx, a, rows, k, w, n, bias, residual, out);
+    }
+    return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
+}
+
+}  // namespace tsm

@@ -1,0 +1,394 @@
+// Row-wise and elementwise kernels of the decode step: RMSNorm, LayerNorm, RoPE, cache writes,
+// SwiGLU, GELU, residual add, greedy argmax and top-k.  Norms and activations can also write their
+// output already quantised for the product that follows (the quantiser of quant.cr:428-442), which
+// removes the separate quantising launch the reference pays before every product.
+#include "common.cuh"
+
+namespace tsm {
+
+struct QuantOut {
+    float* scales;
+    float* sums;
+    int* totals;
+    int8_t* qs;
+};
+
+static QuantOut quant_out(const QuantizedActs* q) {
+    QuantOut o{nullptr, nullptr, nullptr, nullptr};
+    if (q) o = QuantOut{(float*)q->scales, (float*)q->sums, (int*)q->totals, (int8_t*)q->qs};
+    return o;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int i = 0; i < warps; i++) total += scratch[i];
+    return total;
+}
+
+// Σ f(row[j]) in index order from 0f, each step rounded (the host's fold, devices/host.cr:391-403,
+// 348-361), by one thread; every thread receives the result.
+template <bool SQUARE>
+__device__ __forceinline__ float ordered_sum(const float* row, int n, float shift, float* scratch) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float acc = 0.0f;
+        for (int j = 0; j < n; j++) {
+            float v = SQUARE ? __fsub_rn(row[j], shift) : row[j];
+            acc = SQUARE ? __fadd_rn(acc, __fmul_rn(v, v)) : __fadd_rn(acc, v);
+        }
+        scratch[0] = acc;
+    }
+    __syncthreads();
+    return scratch[0];
+}
+
+// One CTA per row.  LAYER = false: x / sqrt(Σx²/n + eps) * w (rmsnorm_row, host.cr:391-403).
+// LAYER = true: mean, centred, variance, c / std * w + b (host.cr:348-361).
+template <bool LAYER>
+__global__ void norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int n,
+                            float eps, float* out, QuantOut q, int exact) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    int r = blockIdx.x;
+    const float* xr = x + (int64_t)r * n;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) row[j] = xr[j];
+    __syncthreads();
+    float count = (float)n;
+    float mean = 0.0f, denom;
+    if (LAYER) {
+        float total;
+        if (exact) {
+            total = ordered_sum<false>(row, n, 0.0f, scratch);
+        } else {
+            float part = 0.0f;
+            for (int j = threadIdx.x; j < n; j += blockDim.x) part += row[j];
+            total = block_sum(part, scratch);
+        }
+        mean = __fdiv_rn(total, count);
+    }
+    float squares;
+    if (exact) {
+        squares = ordered_sum<true>(row, n, mean, scratch);
+    } else {
+        float part = 0.0f;
+        for (int j = threadIdx.x; j < n; j += blockDim.x) {
+            float c = __fsub_rn(row[j], mean);
+            part += c * c;
+        }
+        squares = block_sum(part, scratch);
+    }
+    denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, count), eps));
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    int blocks = (n + 31) >> 5;
+    for (int blk = warp; blk < blocks; blk += warps) {
+        int j = blk * 32 + lane;
+        float y = 0.0f;
+        if (j < n) {
+            float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
+            y = __fdiv_rn(c, denom);
+            if (w) y = __fmul_rn(y, w[j]);
+            if (LAYER) y = __fadd_rn(y, b[j]);
+            if (out) out[(int64_t)r * n + j] = y;
+        }
+        if (q.qs) {
+            int64_t at = (int64_t)r * (n >> 5) + blk;
+            quantize_block_q8(y, lane, q.scales + at, q.sums + at, q.totals + at, q.qs + (int64_t)r * n + j);
+        }
+    }
+}
+
+static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w, const float* b, int rows, int n, float eps,
+                       float* out, const QuantizedActs* quantized) {
+    if (rows == 0 || n == 0) return TSM_OK;
+    if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
+    if ((size_t)n * 4 > 160 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "norm rows over 40960 values");
+    int threads = n >= 2048 ? 512 : n >= 512 ? 256 : 128;
+    size_t smem = (size_t)n * 4;
+    QuantOut q = quant_out(quantized);
+    int exact = ctx->mode == TSM_EXACT;
+    if (layer) {
+        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        norm_kernel<true><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
+    } else {
+        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        norm_kernel<false><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
+    }
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+int launch_rmsnorm(tsm_ctx* ctx, const float* x, const float* w, int rows, int n, float eps, float* out,
+                   const QuantizedActs* quantized) {
+    return launch_norm(ctx, false, x, w, nullptr, rows, n, eps, out, quantized);
+}
+
+int launch_layernorm(tsm_ctx* ctx, const float* x, const float* w, const float* b, int rows, int n, float eps, float* out,
+                     const QuantizedActs* quantized) {
+    if (!w || !b) return fail(ctx, TSM_ERR_ARG, "layernorm needs a weight and a bias");
+    return launch_norm(ctx, true, x, w, b, rows, n, eps, out, quantized);
+}
+
+// ---- RoPE (host.cr:448-466): x*cos + rotate_half(x)*sin, three roundings per element ------------
+
+__device__ __forceinline__ void rotate_pair(float a, float b, const float* c, const float* s, int i, int half, float* oa,
+                                            float* ob) {
+    // a = x[i] (first half), b = x[i + half]
+    *oa = __fadd_rn(__fmul_rn(a, c[i]), __fmul_rn(__fmul_rn(b, -1.0f), s[i]));
+    *ob = __fadd_rn(__fmul_rn(b, c[i + half]), __fmul_rn(a, s[i + half]));
+}
+
+__global__ void rope_kernel(const float* __restrict__ x, int tokens, int heads, int width, int64_t x_stride,
+                            const float* __restrict__ cos_table, const float* __restrict__ sin_table, int context,
+                            const int* __restrict__ positions, float* out, ErrorRecord* errors) {
+    int half = width >> 1;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t total = (int64_t)tokens * heads * half;
+    if (i >= total) return;
+    int col = (int)(i % half);
+    int head = (int)((i / half) % heads);
+    int token = (int)(i / ((int64_t)half * heads));
+    int pos = positions[token];
+    float* o = out + ((int64_t)token * heads + head) * width;
+    if (pos < 0 || pos >= context) {
+        if (col == 0 && head == 0) report_bad_index(errors, pos, context);
+        o[col] = 0.0f, o[col + half] = 0.0f;
+        return;
+    }
+    const float* xr = x + (int64_t)token * x_stride + (int64_t)head * width;
+    rotate_pair(xr[col], xr[col + half], cos_table + (int64_t)pos * width, sin_table + (int64_t)pos * width, col, half,
+                &o[col], &o[col + half]);
+}
+
+int launch_rope(tsm_ctx* ctx, const float* x, int tokens, int heads, int width, int64_t x_stride, const float* cos_table,
+                const float* sin_table, int context, const int* positions, float* out) {
+    if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "rotary embeddings need an even width, not " + std::to_string(width));
+    int64_t total = (int64_t)tokens * heads * (width / 2);
+    if (total == 0) return TSM_OK;
+    rope_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(x, tokens, heads, width, x_stride, cos_table,
+                                                                         sin_table, context, positions, out, ctx->errors);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+// ---- cache writes (write_rows, host.cr:587-597) ---------------------------------------------------
+
+__global__ void write_rows_kernel(float* cache, int rows, int heads, int capacity, int width, const float* __restrict__ values,
+                                  int64_t v_stride, int64_t total, const int* __restrict__ slots, ErrorRecord* errors) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    int column = (int)(i % width);
+    int head = (int)((i / width) % heads);
+    int token = (int)(i / ((int64_t)width * heads));
+    int slot = slots[token];
+    if (slot < 0 || slot >= rows * capacity) {
+        if (column == 0 && head == 0) report_bad_index(errors, slot, rows * capacity);
+        return;
+    }
+    int row = slot / capacity, position = slot % capacity;
+    cache[(((int64_t)row * heads + head) * capacity + position) * width + column] =
+        values[(int64_t)token * v_stride + (int64_t)head * width + column];
+}
+
+int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capacity, int width, const float* values,
+                      int64_t v_stride, int tokens, const int* slots) {
+    int64_t total = (int64_t)tokens * heads * width;
+    if (total == 0) return TSM_OK;
+    write_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(cache, rows, heads, capacity, width, values,
+                                                                               v_stride, total, slots, ctx->errors);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+// Rotates the q and k heads of each token's joined qkv row in place (Llama) and appends k and v to
+// the token's cache row at its position: the RoPE x2 + WriteRows x2 of modules.cr:434-452 as one launch.
+__global__ void rope_append_kernel(float* qkv, int tokens, int heads, int kv_heads, int width, const float* __restrict__ cos_table,
+                                   const float* __restrict__ sin_table, int context, const int* __restrict__ table,
+                                   float* keys, float* values, int rows, int capacity, ErrorRecord* errors) {
+    int half = width >> 1;
+    int all = heads + 2 * kv_heads;
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t total = (int64_t)tokens * all * half;
+    if (i >= total) return;
+    int col = (int)(i % half);
+    int head = (int)((i / half) % all);
+    int token = (int)(i / ((int64_t)half * all));
+    int row = table[3 * token], pos = table[3 * token + 1];
+    if (row < 0 || row >= rows || pos < 0 || pos >= capacity || (cos_table && pos >= context)) {
+        if (col == 0 && head == 0) report_bad_index(errors, pos, capacity);
+        return;
+    }
+    float* xr = qkv + (int64_t)token * all * width + (int64_t)head * width;
+    float a = xr[col], b = xr[col + half];
+    if (head < heads + kv_heads && cos_table) {
+        float ra, rb;
+        rotate_pair(a, b, cos_table + (int64_t)pos * width, sin_table + (int64_t)pos * width, col, half, &ra, &rb);
+        a = ra, b = rb;
+        xr[col] = a, xr[col + half] = b;
+    }
+    if (head >= heads) {
+        bool is_key = head < heads + kv_heads;
+        int kh = is_key ? head - heads : head - heads - kv_heads;
+        float* dst = (is_key ? keys : values) + (((int64_t)row * kv_heads + kh) * capacity + pos) * width;
+        dst[col] = a, dst[col + half] = b;
+    }
+}
+
+int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_heads, int width, const float* cos_table,
+                       const float* sin_table, int context, const int* table, float* keys, float* values, int rows,
+                       int capacity) {
+    if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "head width must be even, not " + std::to_string(width));
+    int64_t total = (int64_t)tokens * (heads + 2 * kv_heads) * (width / 2);
+    if (total == 0) return TSM_OK;
+    rope_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
+        qkv, tokens, heads, kv_heads, width, cos_table, sin_table, context, table, keys, values, rows, capacity, ctx->errors);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+// ---- activations (kernels.cr:4,18 through the tape of kernel.cr:259-300) --------------------------
+
+__device__ __forceinline__ float swiglu_value(float gate, float up) {
+    float t1 = exact_exp(-gate);
+    float t2 = __fadd_rn(t1, 1.0f);
+    float t3 = __fdiv_rn(gate, t2);
+    return __fmul_rn(t3, up);
+}
+
+__device__ __forceinline__ float gelu_value(float x) {
+    const float c = 0.7978845608028654f;  // f32(sqrt(2 / pi))
+    float t0 = __fmul_rn(x, 0.5f);
+    float t1 = __fmul_rn(x, x);
+    float t2 = __fmul_rn(t1, x);
+    float t3 = __fmul_rn(t2, 0.044715f);
+    float t4 = __fadd_rn(x, t3);
+    float t5 = __fmul_rn(t4, c);
+    float t6 = exact_tanh(t5);
+    float t7 = __fadd_rn(t6, 1.0f);
+    return __fmul_rn(t0, t7);
+}
+
+// One warp per 32 consecutive outputs of a row, so that the block quantiser can follow in registers.
+template <bool GELU>
+__global__ void activation_kernel(const float* __restrict__ a, const float* __restrict__ b, int rows, int n, int64_t in_stride,
+                                  float* out, QuantOut q) {
+    int lane = threadIdx.x & 31;
+    int blocks = (n + 31) >> 5;
+    int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)rows * blocks) return;
+    int r = (int)(item / blocks), blk = (int)(item % blocks);
+    int j = blk * 32 + lane;
+    float y = 0.0f;
+    if (j < n) {
+        y = GELU ? gelu_value(a[(int64_t)r * in_stride + j]) : swiglu_value(a[(int64_t)r * in_stride + j], b[(int64_t)r * in_stride + j]);
+        if (out) out[(int64_t)r * n + j] = y;
+    }
+    if (q.qs) {
+        int64_t at = (int64_t)r * (n >> 5) + blk;
+        quantize_block_q8(y, lane, q.scales + at, q.sums + at, q.totals + at, q.qs + (int64_t)r * n + j);
+    }
+}
+
+static int launch_activation(tsm_ctx* ctx, bool gelu, const float* a, const float* b, int rows, int n, int64_t in_stride,
+                             float* out, const QuantizedActs* quantized) {
+    if (rows == 0 || n == 0) return TSM_OK;
+    if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
+    int64_t items = (int64_t)rows * ((n + 31) / 32);
+    unsigned grid = (unsigned)((items + 7) / 8);
+    QuantOut q = quant_out(quantized);
+    if (gelu) activation_kernel<true><<<grid, 256, 0, ctx->stream>>>(a, b, rows, n, in_stride, out, q);
+    else activation_kernel<false><<<grid, 256, 0, ctx->stream>>>(a, b, rows, n, in_stride, out, q);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+int launch_swiglu(tsm_ctx* ctx, const float* gate, const float* up, int rows, int n, int64_t in_stride, float* out,
+                  const QuantizedActs* quantized) {
+    return launch_activation(ctx, false, gate, up, rows, n, in_stride, out, quantized);
+}
+
+int launch_gelu(tsm_ctx* ctx, const float* x, int rows, int n, float* out, const QuantizedActs* quantized) {
+    return launch_activation(ctx, true, x, nullptr, rows, n, n, out, quantized);
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t count, float* out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = __fadd_rn(a[i], b[i]);
+}
+
+int launch_add(tsm_ctx* ctx, const float* a, const float* b, int64_t count, float* out) {
+    if (count == 0) return TSM_OK;
+    add_kernel<<<(unsigned)((count + 255) / 256), 256, 0, ctx->stream>>>(a, b, count, out);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+// ---- sampling (sampler.cr:36, 77-96) -----------------------------------------------------------------
+
+// Is (va, ia) ahead of (vb, ib) in the sampler's order: higher logit first, equal logits by lower index.
+__device__ __forceinline__ bool ahead(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); }
+
+// One CTA per row.  Round r picks the best candidate that comes after round r-1's pick, so no row
+// is modified and ties keep index order.  count = 1 is the greedy pick.
+__global__ void topk_kernel(const float* __restrict__ logits, int n, int count, int* out_ids, float* out_values) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    __shared__ float last_v;
+    __shared__ int last_i;
+    const float* row = logits + (int64_t)blockIdx.x * n;
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int round = 0; round < count; round++) {
+        float lv = last_v;
+        int li = last_i;
+        float v = 0.0f;
+        int at = -1;
+        for (int j = threadIdx.x; j < n; j += blockDim.x) {
+            float x = row[j];
+            if (round > 0 && !ahead(lv, li, x, j)) continue;  // not after the last pick
+            if (at < 0 || ahead(x, j, v, at)) v = x, at = j;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, v, off);
+            int oi = __shfl_xor_sync(0xffffffffu, at, off);
+            if (oi >= 0 && (at < 0 || ahead(ov, oi, v, at))) v = ov, at = oi;
+        }
+        if (lane == 0) best_v[warp] = v, best_i[warp] = at;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w2 = 1; w2 < warps; w2++)
+                if (best_i[w2] >= 0 && (at < 0 || ahead(best_v[w2], best_i[w2], v, at))) v = best_v[w2], at = best_i[w2];
+            last_v = v, last_i = at;
+            out_ids[(int64_t)blockIdx.x * count + round] = at;
+            if (out_values) out_values[(int64_t)blockIdx.x * count + round] = v;
+        }
+        __syncthreads();
+    }
+}
+
+int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, int* out_ids, float* out_values) {
+    if (count < 1 || count > n) return fail(ctx, TSM_ERR_ARG, "top " + std::to_string(count) + " of " + std::to_string(n));
+    if (rows == 0) return TSM_OK;
+    topk_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, n, count, out_ids, out_values);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+int launch_argmax(tsm_ctx* ctx, const float* logits, int rows, int n, int* out) {
+    if (n < 1) return fail(ctx, TSM_ERR_ARG, "argmax of an empty row");
+    return launch_topk(ctx, logits, rows, n, 1, out, nullptr);
+}
+
+}  // namespace tsm
