@@ -76,8 +76,11 @@ int tsm_counters_read(tsm_ctx* ctx, tsm_counters* out);
 int tsm_counters_reset(tsm_ctx* ctx);
 
 /* How norms and attention add (both modes keep the block products bit-exact):
- *   TSM_FAST   tree sums and split-K online softmax (within 1e-5 of the host);
- *   TSM_EXACT  the host's index-order sums and its own exp polynomial (the host's bits). */
+ *   TSM_EXACT  (default) the host's index-order sums and its own exp polynomial: the host's bits, so
+ *              whole-model logits and greedy tokens equal the CPU device's;
+ *   TSM_FAST   tree sums and split-K online softmax: each op within 1e-5 of the host, but a last-bit
+ *              difference can flip an 8-bit activation, so logits follow the host only statistically
+ *              (the reference's own GPU budget: 0.001 nats of KL per token). */
 typedef enum { TSM_FAST = 0, TSM_EXACT = 1 } tsm_mode;
 int tsm_set_mode(tsm_ctx* ctx, int mode);
 
@@ -141,6 +144,10 @@ int tsm_gelu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out);
 /* Op::Add (tensor/elementwise.cr:4-6). */
 int tsm_add(tsm_ctx* ctx, tsm_dptr a, tsm_dptr b, int64_t count, tsm_dptr out);
 
+/* Init.normal (module.cr; builder.cr:43-45): `count` F32 values drawn N(mean, stddev) on the device by a
+ * counter-based generator, element i depending only on (seed, i). */
+int tsm_fill_normal(tsm_ctx* ctx, tsm_dptr out, int64_t count, float mean, float stddev, uint64_t seed);
+
 /* Sampler#pick, greedy (sampler.cr:36): first index of each row's maximum -> I32 [rows]. */
 int tsm_argmax(tsm_ctx* ctx, tsm_dptr logits, int rows, int n, tsm_dptr out);
 /* Sampler#top (sampler.cr:77-96): each row's `count` highest, highest first, ties to the lower index. */
@@ -187,6 +194,10 @@ int tsm_forward(tsm_model* model, tsm_cache* cache, const int32_t* counts, const
  * on the device (Sampler.greedy) and writes it to tokens[row].  The step is captured once as a CUDA
  * graph and replayed.  logits (may be NULL) receives [rows, vocab] on the host. */
 int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* tokens, float* logits);
+/* `steps` greedy decode steps for every row without returning to the host in between: each row's pick
+ * feeds its next step on the device (the loop of Generative#generate, generative.cr:181-188, for all rows
+ * at once).  ids[row] is each row's first token; tokens receives [steps, rows] on the host. */
+int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int steps, int32_t* tokens);
 /* Generative#generate with Sampler.greedy (generative.cr:177-190): `count` tokens after `prompt`. */
 int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens);
 

@@ -490,6 +490,16 @@ class Model:
                                                      _ptr(out) if logits else None), "tsm_decode")
         return (tokens, out) if logits else tokens
 
+    def decode_run(self, cache, ids, steps):
+        """`steps` greedy steps for every row, fed on the device; returns tokens [steps, rows]."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        if ids.size != cache.size:
+            raise ShapeError(f"{ids.size} tokens for {cache.size} rows")
+        tokens = np.empty((steps, cache.size), dtype=np.int32)
+        self.device.check(self.device.lib.tsm_decode_run(self.handle, cache.handle, _ptr(ids), C.c_int(steps), _ptr(tokens)),
+                          "tsm_decode_run")
+        return tokens
+
     def generate(self, prompt, count):
         """Generative#generate with Sampler.greedy."""
         prompt = np.ascontiguousarray(prompt, dtype=np.int32)

@@ -270,6 +270,164 @@ __global__ void attention_ordered_kernel(const float* __restrict__ q, int64_t q_
     }
 }
 
+// The ordered path for head widths 64 and 128, built for throughput: one CTA per (token, group of G
+// query heads that share a kv head).
+//  1. scores: keys arrive in tiles of 4096 / width positions through cp.async into shared memory rows padded by
+//     16 bytes (so that threads walking different rows hit different banks); thread (position, head)
+//     folds its dot product over the width in index order.
+//  2. the maximum, the host's exp of each score, then one thread per head folds the denominator over
+//     positions in order (loads run ahead of the adds), then every weight is divided by it.
+//  3. outputs: thread (column, heads) folds weight * value over positions in order, values read
+//     coalesced from the cache.
+// Scores live in shared memory interleaved by head: sc[p * GS + h], GS = 1, 2 or 4.
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <int WIDTH, int G>
+__global__ void __launch_bounds__(256) attention_exact_kernel(const float* __restrict__ q, int64_t q_stride, int heads,
+                                                              const float* __restrict__ k, const float* __restrict__ v,
+                                                              int rows, int kv_heads, int capacity,
+                                                              const int* __restrict__ table, float scale, float* out,
+                                                              ErrorRecord* errors) {
+    constexpr int kTilePositions = 4096 / WIDTH;  // 16 KB of keys per tile
+    constexpr int GS = G == 3 ? 4 : G;        // interleave stride of the scores
+    constexpr int PITCH = WIDTH + 4;          // floats per staged key row
+    constexpr int CHUNKS = WIDTH / 4;         // 16-byte pieces per key row
+    constexpr int COLS = 256 / WIDTH;         // column groups in the output phase (2 or 4)
+    constexpr int HPT = (G + COLS - 1) / COLS;  // heads per thread in the output phase
+    extern __shared__ __align__(16) float sh[];
+    float* qs = sh;                                   // [GS][PITCH]
+    float* kt = qs + GS * PITCH;                      // [2][tile][PITCH]
+    float* sc = kt + 2 * kTilePositions * PITCH;      // [capacity * GS]
+    __shared__ float wred[8][4];
+    __shared__ float totals[4];
+
+    const int token = blockIdx.y;
+    const int per_kv = heads / kv_heads, groups_per_kv = per_kv / G;
+    const int kvh = blockIdx.x / groups_per_kv;
+    const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
+    const int row = table[3 * token], limit = table[3 * token + 1];
+    if (row < 0 || row >= rows || limit < 0 || limit >= capacity) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) report_bad_index(errors, limit, capacity);
+        return;
+    }
+    const int len = limit + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* kb = k + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
+    const float* vb = v + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
+
+    for (int i = tid; i < G * WIDTH; i += 256)
+        qs[(i / WIDTH) * PITCH + i % WIDTH] = q[(int64_t)token * q_stride + (int64_t)head0 * WIDTH + i];
+
+    auto load_tile = [&](int tile, int buffer) {
+        int p0 = tile * kTilePositions;
+        int count = min(kTilePositions, len - p0);
+        float* dst = kt + buffer * kTilePositions * PITCH;
+        for (int i = tid; i < count * CHUNKS; i += 256) {
+            int p = i / CHUNKS, c = i % CHUNKS;
+            cp_async16(dst + p * PITCH + 4 * c, kb + (int64_t)(p0 + p) * WIDTH + 4 * c);
+        }
+        cp_async_commit();
+    };
+
+    // ---- 1. scores ----
+    const int tiles = (len + kTilePositions - 1) / kTilePositions;
+    const int sp = tid / GS, shd = tid % GS;  // this thread's position within a tile and its head
+    float top = -INFINITY;
+    load_tile(0, 0);
+    for (int tile = 0; tile < tiles; tile++) {
+        if (tile + 1 < tiles) load_tile(tile + 1, (tile + 1) & 1);
+        else cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        int p = tile * kTilePositions + sp;
+        if (sp < kTilePositions && shd < G && p < len) {
+            const float4* kr = (const float4*)(kt + ((tile & 1) * kTilePositions + sp) * PITCH);
+            const float4* qr = (const float4*)(qs + shd * PITCH);
+            float dot = 0.0f;
+#pragma unroll 8
+            for (int c = 0; c < CHUNKS; c++) {
+                float4 kv4 = kr[c], qv = qr[c];
+                dot = __fadd_rn(dot, __fmul_rn(qv.x, kv4.x));
+                dot = __fadd_rn(dot, __fmul_rn(qv.y, kv4.y));
+                dot = __fadd_rn(dot, __fmul_rn(qv.z, kv4.z));
+                dot = __fadd_rn(dot, __fmul_rn(qv.w, kv4.w));
+            }
+            float s = __fadd_rn(__fmul_rn(dot, scale), 0.0f);
+            sc[p * GS + shd] = s;
+            top = fmaxf(top, s);
+        }
+        __syncthreads();
+    }
+    // ---- 2. softmax weights ----
+    // threads of one head are GS apart, so a butterfly over offsets >= GS keeps heads separate
+#pragma unroll
+    for (int off = 16; off >= GS; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    if (lane < GS) wred[warp][lane] = top;
+    __syncthreads();
+    {
+        // 256 % GS == 0, so in the flat walk below a thread always meets its own head: index % GS == tid % GS
+        float m = wred[0][shd];
+#pragma unroll
+        for (int w2 = 1; w2 < 8; w2++) m = fmaxf(m, wred[w2][shd]);
+        if (shd < G)
+            for (int i = tid; i < len * GS; i += 256) sc[i] = exact_exp(__fsub_rn(sc[i], m));
+    }
+    __syncthreads();
+    if (tid < G) {
+        float total = 0.0f;
+        int p = 0;
+        for (; p + 8 <= len; p += 8) {
+            float e[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) e[u] = sc[(p + u) * GS + tid];
+#pragma unroll
+            for (int u = 0; u < 8; u++) total = __fadd_rn(total, e[u]);
+        }
+        for (; p < len; p++) total = __fadd_rn(total, sc[p * GS + tid]);
+        totals[tid] = total;
+    }
+    __syncthreads();
+    if (shd < G) {
+        float total = totals[shd];
+        for (int i = tid; i < len * GS; i += 256) sc[i] = __fdiv_rn(sc[i], total);
+    }
+    __syncthreads();
+    // ---- 3. outputs ----
+    const int col = tid % WIDTH, hg = tid / WIDTH;
+    const int h0 = hg * HPT;
+    if (h0 < G) {
+        float acc[HPT];
+#pragma unroll
+        for (int i = 0; i < HPT; i++) acc[i] = 0.0f;
+        const float* vp = vb + col;
+        int p = 0;
+        for (; p + 8 <= len; p += 8) {
+            float vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) vv[u] = vp[(int64_t)(p + u) * WIDTH];
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+#pragma unroll
+                for (int i = 0; i < HPT; i++)
+                    if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(sc[(p + u) * GS + h0 + i], vv[u]));
+        }
+        for (; p < len; p++) {
+            float vv = vp[(int64_t)p * WIDTH];
+#pragma unroll
+            for (int i = 0; i < HPT; i++)
+                if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(sc[p * GS + h0 + i], vv));
+        }
+#pragma unroll
+        for (int i = 0; i < HPT; i++)
+            if (h0 + i < G) out[((int64_t)token * heads + head0 + h0 + i) * WIDTH + col] = acc[i];
+    }
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 
 int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity) {
@@ -320,15 +478,49 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         return launch_fast<64>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
     if (ctx->mode == TSM_FAST && aligned && width == 128)
         return launch_fast<128>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
-    size_t smem = (size_t)(width + capacity) * 4;
-    if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "ordered attention over more than 51000 positions");
     if (!out) return fail(ctx, TSM_ERR_ARG, "ordered attention needs an F32 output");
-    if (smem > 48 * 1024)
-        TSM_CUDA(ctx, cudaFuncSetAttribute(attention_ordered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    dim3 grid(heads, tokens);
-    int threads = capacity >= 1024 ? 256 : 128;
-    attention_ordered_kernel<<<grid, threads, smem, ctx->stream>>>(q, q_stride, heads, width, k, v, rows, kv_heads, capacity,
-                                                                   table, scale, out, ctx->errors);
+    bool launched = false;
+    if (aligned && (width == 64 || width == 128)) {
+        int per_kv = heads / kv_heads;
+        int tile = 4096 / width, pitch = width + 4;
+        for (int g = 4; g >= 1 && !launched; g--) {
+            if (per_kv % g != 0) continue;
+            int gs = g == 3 ? 4 : g;
+            size_t smem = ((size_t)gs * pitch + 2 * (size_t)tile * pitch + (size_t)capacity * gs) * 4;
+            if (smem > 200 * 1024) continue;
+            dim3 grid(kv_heads * (per_kv / g), tokens);
+#define TSM_EXACT_ATTN(W, G)                                                                                              \
+    do {                                                                                                                  \
+        auto kernel = attention_exact_kernel<W, G>;                                                                       \
+        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+        kernel<<<grid, 256, smem, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, out,    \
+                                                 ctx->errors);                                                            \
+    } while (0)
+            if (width == 64) {
+                if (g == 4) TSM_EXACT_ATTN(64, 4);
+                else if (g == 3) TSM_EXACT_ATTN(64, 3);
+                else if (g == 2) TSM_EXACT_ATTN(64, 2);
+                else TSM_EXACT_ATTN(64, 1);
+            } else {
+                if (g == 4) TSM_EXACT_ATTN(128, 4);
+                else if (g == 3) TSM_EXACT_ATTN(128, 3);
+                else if (g == 2) TSM_EXACT_ATTN(128, 2);
+                else TSM_EXACT_ATTN(128, 1);
+            }
+#undef TSM_EXACT_ATTN
+            launched = true;
+        }
+    }
+    if (!launched) {
+        size_t smem = (size_t)(width + capacity) * 4;
+        if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "ordered attention over more than 51000 positions");
+        if (smem > 48 * 1024)
+            TSM_CUDA(ctx, cudaFuncSetAttribute(attention_ordered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        dim3 grid(heads, tokens);
+        int threads = capacity >= 1024 ? 256 : 128;
+        attention_ordered_kernel<<<grid, threads, smem, ctx->stream>>>(q, q_stride, heads, width, k, v, rows, kv_heads, capacity,
+                                                                       table, scale, out, ctx->errors);
+    }
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     if (quantized) {

@@ -43,7 +43,7 @@ struct tsm_ctx {
     int ordinal = 0;
     cudaStream_t stream = nullptr;
     int sm_count = 148;
-    int mode = TSM_FAST;
+    int mode = TSM_EXACT;
     tsm::Pool pool;
     tsm::ErrorRecord* errors = nullptr;       // device
     tsm::ErrorRecord* errors_host = nullptr;  // pinned
@@ -109,6 +109,9 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
                          int* totals, int8_t* qs);
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out);
+bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+int launch_block_matmul_mma(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                            const float* bias, const float* residual, float* out);
 int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind, uint8_t* out);
 int launch_dequantize_blocks(tsm_ctx* ctx, const uint8_t* blocks, int64_t count, int kind, float* out);
 int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table_rows, int width, const int* ids,

@@ -74,6 +74,11 @@ struct tsm_cache {
     std::vector<int> lengths;
     cudaGraphExec_t graph = nullptr;  // one decode step over all rows
     uint64_t graph_stamp = 0;         // what the captured step depends on (buffers, mode)
+    cudaGraphExec_t run_graph = nullptr;  // one step of a device-resident run (tsm_decode_run)
+    uint64_t run_stamp = 0;
+    int* run_state = nullptr;         // device: [0] steps done, then tokens [steps, rows]
+    int64_t run_capacity = 0;         // ints in run_state
+    int graph_kernels = 0, run_kernels = 0;  // kernel nodes per replay, for the launch counter
 };
 
 namespace tsm {
@@ -637,6 +642,43 @@ static void drop_graph(tsm_cache* cache) {
     cache->graph = nullptr;
 }
 
+// Kernel nodes of a captured step: what one replay launches.
+static int kernel_nodes(cudaGraph_t graph) {
+    size_t count = 0;
+    if (cudaGraphGetNodes(graph, nullptr, &count) != cudaSuccess || count == 0) return 0;
+    std::vector<cudaGraphNode_t> nodes(count);
+    if (cudaGraphGetNodes(graph, nodes.data(), &count) != cudaSuccess) return 0;
+    int kernels = 0;
+    for (size_t i = 0; i < count; i++) {
+        cudaGraphNodeType type;
+        if (cudaGraphNodeGetType(nodes[i], &type) == cudaSuccess && type == cudaGraphNodeTypeKernel) kernels++;
+    }
+    return kernels;
+}
+
+static void drop_run_graph(tsm_cache* cache) {
+    if (cache->run_graph) cudaGraphExecDestroy(cache->run_graph);
+    cache->run_graph = nullptr;
+}
+
+// Between the steps of a device-resident run: each row's pick becomes its next token and its
+// position moves on, so that no step waits for the host.
+__global__ void run_advance_kernel(int* ids, int* table, const int* picks, int rows, const int* state) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows || state[0] == 0) return;
+    ids[r] = picks[r];
+    table[3 * r + 1] += 1;
+    table[3 * r + 2] += 1;
+}
+
+__global__ void run_record_kernel(const int* picks, int rows, int* state) {
+    int r = blockIdx.x * blockDim.x + threadIdx.x;
+    int step = state[0];
+    if (r < rows) state[1 + (int64_t)step * rows + r] = picks[r];
+    __syncthreads();
+    if (r == 0) state[0] = step + 1;
+}
+
 }  // namespace tsm
 
 #define MODEL_GUARD(m)                                \
@@ -743,6 +785,8 @@ int tsm_cache_free(tsm_cache* cache) {
     MODEL_GUARD(cache->model);
     cudaStreamSynchronize(cache->model->ctx->stream);
     drop_graph(cache);
+    drop_run_graph(cache);
+    pool_release(cache->model->ctx, cache->run_state);
     for (float* p : cache->keys) pool_release(cache->model->ctx, p);
     for (float* p : cache->values) pool_release(cache->model->ctx, p);
     delete cache;
@@ -883,6 +927,8 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
         if (rc == TSM_OK) {
             cudaError_t e5 = cudaGraphInstantiate(&cache->graph, graph, 0);
             if (e5 != cudaSuccess) rc = cuda_fail(ctx, e5, "cudaGraphInstantiate");
+            cache->graph_kernels = kernel_nodes(graph);
+            ctx->counters.launches -= cache->graph_kernels;  // captured, not launched; replays count below
         }
         if (graph) cudaGraphDestroy(graph);
         if (rc != TSM_OK) {
@@ -892,6 +938,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     }
     TSM_CUDA(ctx, cudaGraphLaunch(cache->graph, ctx->stream));
     ctx->counters.graph_replays++;
+    ctx->counters.launches += cache->graph_kernels;
     ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
     ctx->counters.downloads += 1, ctx->counters.download_bytes += (int64_t)rows * 4;
     if (logits) {
@@ -907,6 +954,74 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     return TSM_OK;
 }
 
+int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int steps, int32_t* tokens) {
+    MODEL_GUARD(model);
+    if (!cache || cache->model != model || !ids || !tokens || steps < 1) return fail(model->ctx, TSM_ERR_ARG, "a run needs a cache of this model, ids, steps and a place for tokens");
+    tsm_ctx* ctx = model->ctx;
+    const tsm_model_config& c = model->cfg;
+    int rows = cache->rows;
+    if (rows > 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "a device-resident run takes at most 1024 rows");
+    int limit = cache->capacity < c.context ? cache->capacity : c.context;
+    for (int row = 0; row < rows; row++)
+        if (cache->lengths[row] + steps > limit)
+            return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + steps) + " positions exceed the " + std::to_string(limit) + " a row holds");
+    TSM_TRY(prepare_scratch(model, cache, rows));
+    int64_t need = 1 + (int64_t)steps * rows;
+    if (cache->run_capacity < need) {
+        TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        pool_release(ctx, cache->run_state);
+        cache->run_state = nullptr, cache->run_capacity = 0;
+        drop_run_graph(cache);
+        TSM_TRY(pool_alloc(ctx, need * 4, (void**)&cache->run_state));
+        cache->run_capacity = need;
+    }
+    uint64_t stamp = model->ws_generation * 1000003ull + ctx->scratch_generation * 10ull + (uint64_t)ctx->mode;
+    if (cache->run_graph && cache->run_stamp != stamp) drop_run_graph(cache);
+    cache->run_stamp = stamp;
+    Workspace& w = model->ws;
+    int32_t* h_ids = w.host;
+    int32_t* h_table = w.host + w.tokens;
+    for (int row = 0; row < rows; row++) {
+        h_ids[row] = ids[row];
+        h_table[3 * row] = row, h_table[3 * row + 1] = cache->lengths[row], h_table[3 * row + 2] = cache->lengths[row] + 1;
+    }
+    TSM_CUDA(ctx, cudaMemcpyAsync(w.ids, h_ids, (size_t)rows * 4, cudaMemcpyHostToDevice, ctx->stream));
+    TSM_CUDA(ctx, cudaMemcpyAsync(w.table, h_table, (size_t)rows * 12, cudaMemcpyHostToDevice, ctx->stream));
+    TSM_CUDA(ctx, cudaMemsetAsync(cache->run_state, 0, 4, ctx->stream));
+    ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
+    if (!cache->run_graph) {
+        cudaGraph_t graph = nullptr;
+        TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        run_advance_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(w.ids, w.table, w.picks, rows, cache->run_state);
+        count_launch(ctx);
+        int rc = launch_step(model, cache, rows, rows, true);
+        run_record_kernel<<<1, 1024, 0, ctx->stream>>>(w.picks, rows, cache->run_state);
+        count_launch(ctx);
+        cudaError_t e1 = cudaGetLastError();
+        cudaError_t e2 = cudaStreamEndCapture(ctx->stream, &graph);
+        if (rc == TSM_OK && (e1 != cudaSuccess || e2 != cudaSuccess)) rc = cuda_fail(ctx, e1 != cudaSuccess ? e1 : e2, "capture of a decode step");
+        if (rc == TSM_OK) {
+            cudaError_t e3 = cudaGraphInstantiate(&cache->run_graph, graph, 0);
+            if (e3 != cudaSuccess) rc = cuda_fail(ctx, e3, "cudaGraphInstantiate");
+            cache->run_kernels = kernel_nodes(graph);
+            ctx->counters.launches -= cache->run_kernels;
+        }
+        if (graph) cudaGraphDestroy(graph);
+        if (rc != TSM_OK) {
+            cudaGetLastError();
+            return rc;
+        }
+    }
+    for (int s = 0; s < steps; s++) TSM_CUDA(ctx, cudaGraphLaunch(cache->run_graph, ctx->stream));
+    ctx->counters.graph_replays += steps;
+    ctx->counters.launches += (int64_t)steps * cache->run_kernels;
+    TSM_CUDA(ctx, cudaMemcpyAsync(tokens, cache->run_state + 1, (size_t)steps * rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->counters.downloads++, ctx->counters.download_bytes += (int64_t)steps * rows * 4;
+    TSM_TRY(tsm_sync(ctx));
+    for (int row = 0; row < rows; row++) cache->lengths[row] += steps;
+    return TSM_OK;
+}
+
 int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens) {
     MODEL_GUARD(model);
     if (!prompt || prompt_size < 1 || count < 0 || (count > 0 && !tokens)) return fail(model->ctx, TSM_ERR_ARG, "generate needs a prompt and a place for tokens");
@@ -918,7 +1033,7 @@ int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int c
     int32_t counts[1] = {prompt_size};
     // Sampler.greedy picks on the device: the first index of the maximum (sampler.cr:36)
     int rc = forward_impl(model, cache, counts, prompt, 1, nullptr, &tokens[0]);
-    for (int i = 1; i < count && rc == TSM_OK; i++) rc = tsm_decode(model, cache, &tokens[i - 1], &tokens[i], nullptr);
+    if (rc == TSM_OK && count > 1) rc = tsm_decode_run(model, cache, &tokens[0], count - 1, &tokens[1]);
     tsm_cache_free(cache);
     return rc;
 }

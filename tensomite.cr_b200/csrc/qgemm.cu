@@ -1,0 +1,301 @@
+// The quantised product for several rows of activations (batched decode, prefill), with the reference's
+// bits (Quant.matmul_reference, quant.cr:122-142): out[m, n] = sum over blocks, in block order, of the
+// block's contribution.
+//
+// A block is 32 elements, which is exactly the K of one int8 tensor-core instruction
+// (mma.sync m16n8k32, s8 x s8 -> s32).  One instruction therefore gives the exact integer dot products
+// of 16 weight rows with 8 activation rows for ONE block, into a fresh accumulator; the float work that
+// must stay ordered (scale, scale, add to the running sum) then happens in the thread that holds each
+// (weight row, activation row) pair, block after block, so the sum is folded in block order without
+// any exchange between threads.  ggml's nibble layout (low nibble = element j, high = element j + 16)
+// matches the instruction's fragment layout: one 32-bit word of packed nibbles yields both of a
+// thread's A registers.  The accumulator is started at the bit pattern of 1.5 * 2^23, so the integer
+// result read back as a float is 12582912 + dot and one subtraction converts it exactly.
+//
+// Weights stream through shared memory in chunks of 8 to 32 blocks per weight row.  Each row's chunk is one
+// bulk asynchronous copy (cp.async.bulk) whose start is rounded down and end rounded up to 16 bytes,
+// so rows of any even pitch (612-byte rows of 18 Q8_0 blocks included) are handled; the reader adds the
+// row's shift back.  Activations (int8) and their scales come from L2 through L1: they are shared by
+// every CTA and small.
+#include "common.cuh"
+
+namespace tsm {
+
+namespace {
+
+constexpr int kGemmStages = 4;
+constexpr unsigned kGemmSpins = 4u << 20;
+
+template <int KIND> struct GFmt;
+template <> struct GFmt<TSM_Q8_0> { static constexpr int B = 34; };
+template <> struct GFmt<TSM_Q4_0> { static constexpr int B = 18; };
+template <> struct GFmt<TSM_Q4_1> { static constexpr int B = 20; };
+
+struct GemmParams {
+    const uint8_t* w;
+    int n, nb, m;          // weight rows, blocks per row, activation rows
+    QuantizedActs acts;
+    const float* bias;
+    const float* residual;
+    float* out;            // [m, n]
+    ErrorRecord* errors;
+};
+
+__device__ __forceinline__ unsigned g_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void g_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(g_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void g_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(g_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool g_mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(g_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool g_mbar_wait(uint64_t* bar, unsigned parity) {
+    for (unsigned spin = 0; spin < kGemmSpins; spin++) {
+        if (g_mbar_try_wait(bar, parity)) return true;
+        if (spin > 4096) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void g_bulk_load(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(g_smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(g_smem_u32(bar))
+                 : "memory");
+}
+
+// The 4 bytes at p (2-byte aligned, in shared memory) as a little-endian word.
+__device__ __forceinline__ unsigned lds_u32_at2(const unsigned char* p) {
+    uintptr_t a = (uintptr_t)p;
+    const unsigned* q = (const unsigned*)(a & ~(uintptr_t)3);
+    return __funnelshift_r(q[0], q[1], (unsigned)(a & 3) * 8);
+}
+__device__ __forceinline__ unsigned lds_u16_at2(const unsigned char* p) { return *(const unsigned short*)p; }
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    const int bias = 0x4b400000;  // 1.5 * 2^23 as a float: the result reads back as 12582912 + dot
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(bias));
+}
+
+// WR x WC warps: warp (wr, wc) owns weight rows [16 wr, 16 wr + 16) of the CTA's slab and NT tiles of
+// 8 activation rows starting at tile wc * NT.
+template <int KIND, int NT, int WR, int WC>
+__global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) {
+    constexpr int B = GFmt<KIND>::B;
+    constexpr int ROWS = 16 * WR;
+    constexpr int kChunkBlocks = 32 / WR;         // blocks of a row per stage: a stage is about 18 KB whatever WR is
+    constexpr int PITCH = kChunkBlocks * B + 32;  // a chunk plus the slack of rounding both ends to 16 bytes
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full = (uint64_t*)smem;
+    int* abort_flag = (int*)(smem + 64);
+    unsigned char* stages = smem + 128;  // kGemmStages x ROWS x PITCH
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wr = warp / WC, wc = warp % WC;
+    const int g = lane >> 2, t = lane & 3;
+    const int nb = p.nb;
+    const int64_t rb = (int64_t)nb * B;
+    const int row0 = blockIdx.x * ROWS;
+    const int col0 = blockIdx.y * (8 * NT * WC) + wc * 8 * NT;
+    const int chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;
+
+    // producer (warp 0): thread 0 announces the bytes, then the lanes issue one row's copy each
+    auto issue = [&](int chunk) {
+        if (chunk >= chunks) return;
+        int s = chunk % kGemmStages;
+        int len = min(kChunkBlocks, nb - chunk * kChunkBlocks) * B;
+        if (tid == 0) {
+            unsigned total = 0;
+            for (int r = 0; r < ROWS; r++) {
+                int row = row0 + r;
+                if (row >= p.n) break;
+                int64_t o = (int64_t)row * rb + (int64_t)chunk * kChunkBlocks * B;
+                int64_t a0 = o & ~(int64_t)15;
+                total += (unsigned)(((o + len + 15) & ~(int64_t)15) - a0);
+            }
+            g_mbar_expect_tx(&full[s], total);
+        }
+        __syncwarp();
+        for (int r = lane; r < ROWS && row0 + r < p.n; r += 32) {
+            int64_t o = (int64_t)(row0 + r) * rb + (int64_t)chunk * kChunkBlocks * B;
+            int64_t a0 = o & ~(int64_t)15;
+            unsigned bytes = (unsigned)(((o + len + 15) & ~(int64_t)15) - a0);
+            g_bulk_load(stages + ((size_t)s * ROWS + r) * PITCH, p.w + a0, bytes, &full[s]);
+        }
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < kGemmStages; s++) g_mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0)
+        for (int c = 0; c < kGemmStages; c++) issue(c);
+
+    // this thread's two weight rows and their shifts inside the staged slots
+    const int ra = 16 * wr + g, rbw = ra + 8;
+    const int shift_a = (int)(((int64_t)(row0 + ra) * rb) & 15), shift_b = (int)(((int64_t)(row0 + rbw) * rb) & 15);
+    // a chunk is 8, 16 or 32 blocks, whose bytes are a multiple of 16 in every format (8 * 34, 8 * 18, 8 * 20),
+    // so a row's shift is the same in every chunk.
+
+    float acc[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+
+    // activation rows of this thread: B fragments come from row col0 + 8 i + g, the epilogue needs the
+    // scales of rows col0 + 8 i + 2 t and + 1; rows beyond m are clamped (their results are dropped)
+    int brow[NT], erow[NT][2];
+#pragma unroll
+    for (int i = 0; i < NT; i++) {
+        brow[i] = min(col0 + 8 * i + g, p.m - 1);
+        erow[i][0] = min(col0 + 8 * i + 2 * t, p.m - 1);
+        erow[i][1] = min(col0 + 8 * i + 2 * t + 1, p.m - 1);
+    }
+    const int8_t* qs = p.acts.qs;
+    const int64_t k = (int64_t)nb * 32;
+
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        int s = chunk % kGemmStages;
+        bool arrived = g_mbar_wait(&full[s], (unsigned)((chunk / kGemmStages) & 1));
+        if (!arrived) *abort_flag = 1;
+        const unsigned char* slot_a = stages + ((size_t)s * ROWS + ra) * PITCH + shift_a;
+        const unsigned char* slot_b = stages + ((size_t)s * ROWS + rbw) * PITCH + shift_b;
+        int count = min(kChunkBlocks, nb - chunk * kChunkBlocks);
+        if (arrived) {
+#pragma unroll 2
+            for (int j = 0; j < count; j++) {
+                int b = chunk * kChunkBlocks + j;
+                const unsigned char* pa = slot_a + j * B;
+                const unsigned char* pb = slot_b + j * B;
+                unsigned a0, a1, a2, a3;
+                float dwa = half_bits_to_float(lds_u16_at2(pa)), dwb = half_bits_to_float(lds_u16_at2(pb));
+                float mwa = 0.0f, mwb = 0.0f;
+                if (KIND == TSM_Q8_0) {
+                    a0 = lds_u32_at2(pa + 2 + 4 * t), a2 = lds_u32_at2(pa + 18 + 4 * t);
+                    a1 = lds_u32_at2(pb + 2 + 4 * t), a3 = lds_u32_at2(pb + 18 + 4 * t);
+                } else {
+                    constexpr int HEAD = KIND == TSM_Q4_0 ? 2 : 4;
+                    unsigned na = lds_u32_at2(pa + HEAD + 4 * t), nbw = lds_u32_at2(pb + HEAD + 4 * t);
+                    a0 = na & 0x0f0f0f0fu, a2 = (na >> 4) & 0x0f0f0f0fu;
+                    a1 = nbw & 0x0f0f0f0fu, a3 = (nbw >> 4) & 0x0f0f0f0fu;
+                    if (KIND == TSM_Q4_1) mwa = half_bits_to_float(lds_u16_at2(pa + 2)), mwb = half_bits_to_float(lds_u16_at2(pb + 2));
+                }
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    const int* xq = (const int*)(qs + (int64_t)brow[i] * k + (int64_t)b * 32);
+                    unsigned b0 = (unsigned)__ldg(xq + t), b1 = (unsigned)__ldg(xq + 4 + t);
+                    int d[4];
+                    mma_s8(d, a0, a1, a2, a3, b0, b1);
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        int64_t at = (int64_t)erow[i][e] * nb + b;
+                        float dx = __ldg(p.acts.scales + at);
+                        if (KIND == TSM_Q8_0) {
+                            float fa = __fsub_rn(__int_as_float(d[e]), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e]), 12582912.0f);
+                            acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(fa, __fmul_rn(dwa, dx)));
+                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(fb, __fmul_rn(dwb, dx)));
+                        } else if (KIND == TSM_Q4_0) {
+                            int xt8 = 8 * __ldg(p.acts.totals + at);
+                            float fa = __fsub_rn(__int_as_float(d[e] - xt8), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e] - xt8), 12582912.0f);
+                            acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(__fmul_rn(fa, dwa), dx));
+                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(__fmul_rn(fb, dwb), dx));
+                        } else {
+                            float sx = __ldg(p.acts.sums + at);
+                            float fa = __fsub_rn(__int_as_float(d[e]), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e]), 12582912.0f);
+                            acc[i][e] = __fadd_rn(acc[i][e], __fadd_rn(__fmul_rn(__fmul_rn(dwa, dx), fa), __fmul_rn(mwa, sx)));
+                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fadd_rn(__fmul_rn(__fmul_rn(dwb, dx), fb), __fmul_rn(mwb, sx)));
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (*abort_flag) break;
+        if (warp == 0) issue(chunk + kGemmStages);
+    }
+    if (*abort_flag) {
+        if (tid == 0) {
+            atomicExch(&p.errors->timeout, 1);
+            for (int s = 0; s < kGemmStages; s++) g_mbar_wait(&full[s], 0), g_mbar_wait(&full[s], 1);
+        }
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < NT; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            int row = row0 + (e < 2 ? ra : rbw);
+            int col = col0 + 8 * i + 2 * t + (e & 1);
+            if (row < p.n && col < p.m) {
+                float v = acc[i][e];
+                if (p.bias) v = __fadd_rn(v, p.bias[row]);
+                if (p.residual) v = __fadd_rn(p.residual[(int64_t)col * p.n + row], v);
+                p.out[(int64_t)col * p.n + row] = v;
+            }
+        }
+}
+
+template <int KIND, int NT, int WR, int WC>
+int launch_shape(tsm_ctx* ctx, const GemmParams& p) {
+    constexpr int ROWS = 16 * WR, PITCH = (32 / WR) * GFmt<KIND>::B + 32, THREADS = 32 * WR * WC;
+    size_t smem = 128 + (size_t)kGemmStages * ROWS * PITCH;
+    auto kernel = matmul_mma_kernel<KIND, NT, WR, WC>;
+    if (smem > 48 * 1024) {
+        static std::mutex lock;
+        static std::map<std::pair<int, const void*>, bool> done;
+        std::lock_guard<std::mutex> guard(lock);
+        auto key = std::make_pair(ctx->ordinal, (const void*)kernel);
+        if (!done.count(key)) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done[key] = true;
+        }
+    }
+    dim3 grid((p.n + ROWS - 1) / ROWS, (p.m + 8 * NT * WC - 1) / (8 * NT * WC));
+    kernel<<<grid, THREADS, smem, ctx->stream>>>(p);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+template <int KIND>
+int launch_kind(tsm_ctx* ctx, const GemmParams& p) {
+    if (p.m <= 8) return launch_shape<KIND, 1, 4, 1>(ctx, p);
+    if (p.m <= 16) return launch_shape<KIND, 1, 2, 2>(ctx, p);
+    if (p.m <= 32) return launch_shape<KIND, 1, 1, 4>(ctx, p);
+    return launch_shape<KIND, 2, 1, 4>(ctx, p);
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this product: 16-byte aligned weights whose total size is a
+// multiple of 16 bytes (so that no rounded-up copy reads past the matrix), 4-byte aligned activations.
+bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n) {
+    int64_t total = (int64_t)n * (k / 32) * block_bytes(kind);
+    return rows >= 1 && ((uintptr_t)w & 15) == 0 && total % 16 == 0 && ((uintptr_t)a.qs & 3) == 0;
+}
+
+int launch_block_matmul_mma(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                            const float* bias, const float* residual, float* out) {
+    GemmParams p;
+    p.w = w, p.n = n, p.nb = k / 32, p.m = rows, p.acts = a, p.bias = bias, p.residual = residual, p.out = out, p.errors = ctx->errors;
+    switch (kind) {
+        case TSM_Q8_0: return launch_kind<TSM_Q8_0>(ctx, p);
+        case TSM_Q4_0: return launch_kind<TSM_Q4_0>(ctx, p);
+        case TSM_Q4_1: return launch_kind<TSM_Q4_1>(ctx, p);
+    }
+    return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
+}
+
+}  // namespace tsm

@@ -41,6 +41,7 @@ struct MatvecParams {
     const float* residual;
     float* out;
     int rows_per_tile, num_tiles;
+    unsigned nb_magic;  // floor(2^32 / nb) + 1: x / nb = umulhi(x, nb_magic) for the small x used here
     ErrorRecord* errors;
 };
 
@@ -69,6 +70,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
     }
     return false;
 }
+// Dot product of four unsigned bytes of a with four signed bytes of b, plus c.
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, unsigned bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
@@ -82,7 +89,7 @@ __host__ __device__ __forceinline__ int part_index(int p) { return p + (p >> 5);
 // consecutive groups (256 bytes apart) read different banks.
 __host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (kb >> 3) * 16; }
 
-template <int KIND, int C>
+template <int KIND, int C, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
     using F = Fmt<KIND>;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -171,13 +178,16 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                         uint4 v = gp[i];
                         W[4 * i] = v.x, W[4 * i + 1] = v.y, W[4 * i + 2] = v.z, W[4 * i + 3] = v.w;
                     }
-                    int kb = (kb_first + gi * F::G) % nb;
+                    // first activation block of the group: (kb_first + gi * G) mod nb by a reciprocal multiply
+                    unsigned x = (unsigned)(kb_first + gi * F::G);
+                    int kb = (int)(x - __umulhi(x, p.nb_magic) * (unsigned)nb);
+                    float* dst = cur + gi * F::G + ((gi * F::G) >> 5);  // part_index(gi * G), then + j within the same 32
 #pragma unroll
                     for (int j = 0; j < F::G; j++) {
                         int kbj = kb + j;
-                        if (kbj >= nb) kbj -= nb;
+                        if (!ALIGNED && kbj >= nb) kbj -= nb;  // a group may run over the end of a row (rows hold >= G blocks)
                         float dw, mw = 0.0f;
-                        unsigned q[8];
+                        unsigned q[8];  // Q8_0: 8 words of int8; Q4: q[0..3] low nibbles, q[4..7] high nibbles still times 16
                         if (KIND == TSM_Q8_0) {
                             const int base = 17 * (j >> 1);
                             if ((j & 1) == 0) {
@@ -202,27 +212,41 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                                 for (int i = 0; i < 4; i++) nib[i] = W[base + 5 + i];
                             }
 #pragma unroll
-                            for (int i = 0; i < 4; i++) q[i] = nib[i] & 0x0f0f0f0fu, q[4 + i] = (nib[i] >> 4) & 0x0f0f0f0fu;
+                            for (int i = 0; i < 4; i++) q[i] = nib[i] & 0x0f0f0f0fu, q[4 + i] = nib[i] & 0xf0f0f0f0u;
                         } else {
                             const int base = 5 * j;
                             dw = half_bits_to_float(W[base] & 0xffffu);
                             mw = half_bits_to_float(W[base] >> 16);
 #pragma unroll
-                            for (int i = 0; i < 4; i++)
-                                q[i] = W[base + 1 + i] & 0x0f0f0f0fu, q[4 + i] = (W[base + 1 + i] >> 4) & 0x0f0f0f0fu;
+                            for (int i = 0; i < 4; i++) q[i] = W[base + 1 + i] & 0x0f0f0f0fu, q[4 + i] = W[base + 1 + i] & 0xf0f0f0f0u;
                         }
 #pragma unroll
                         for (int c = 0; c < C; c++) {
-                            const uint4* ap = (const uint4*)(acts_q + c * act_bytes + act_offset(kbj));
+                            const uint4* ap = ALIGNED ? (const uint4*)(acts_q + c * act_bytes + act_offset(kb)) + 2 * j
+                                                      : (const uint4*)(acts_q + c * act_bytes + act_offset(kbj));
                             uint4 a0 = ap[0], a1 = ap[1];
-                            int total = __dp4a((int)q[0], (int)a0.x, 0);
-                            total = __dp4a((int)q[1], (int)a0.y, total);
-                            total = __dp4a((int)q[2], (int)a0.z, total);
-                            total = __dp4a((int)q[3], (int)a0.w, total);
-                            total = __dp4a((int)q[4], (int)a1.x, total);
-                            total = __dp4a((int)q[5], (int)a1.y, total);
-                            total = __dp4a((int)q[6], (int)a1.z, total);
-                            total = __dp4a((int)q[7], (int)a1.w, total);
+                            int total;
+                            if (KIND == TSM_Q8_0) {
+                                total = __dp4a((int)q[0], (int)a0.x, 0);
+                                total = __dp4a((int)q[1], (int)a0.y, total);
+                                total = __dp4a((int)q[2], (int)a0.z, total);
+                                total = __dp4a((int)q[3], (int)a0.w, total);
+                                total = __dp4a((int)q[4], (int)a1.x, total);
+                                total = __dp4a((int)q[5], (int)a1.y, total);
+                                total = __dp4a((int)q[6], (int)a1.z, total);
+                                total = __dp4a((int)q[7], (int)a1.w, total);
+                            } else {
+                                // low nibbles as they are; high nibbles as unsigned bytes worth 16 each, divided out after
+                                int low = __dp4a((int)q[0], (int)a0.x, 0);
+                                low = __dp4a((int)q[1], (int)a0.y, low);
+                                low = __dp4a((int)q[2], (int)a0.z, low);
+                                low = __dp4a((int)q[3], (int)a0.w, low);
+                                int high = dp4a_us(q[4], (int)a1.x, 0);
+                                high = dp4a_us(q[5], (int)a1.y, high);
+                                high = dp4a_us(q[6], (int)a1.z, high);
+                                high = dp4a_us(q[7], (int)a1.w, high);
+                                total = low + (high >> 4);
+                            }
                             float dx = acts_scale[c * nb + kbj];
                             float contribution;
                             if (KIND == TSM_Q8_0) {
@@ -234,7 +258,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                                 float sx = acts_aux[c * nb + kbj];
                                 contribution = __fadd_rn(__fmul_rn(__fmul_rn(dw, dx), (float)total), __fmul_rn(mw, sx));
                             }
-                            cur[c * pcap + part_index(gi * F::G + j)] = contribution;
+                            dst[c * pcap + j] = contribution;
                         }
                     }
                 }
@@ -247,7 +271,22 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                 float sum[C];
 #pragma unroll
                 for (int c = 0; c < C; c++) sum[c] = 0.0f;
-                for (int b = 0; b < nb; b++) {
+                // loads run ahead of the adds: 8 contributions are fetched, then folded in order
+                int b = 0;
+                for (; b + 8 <= nb; b += 8) {
+                    float v[C][8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        int idx = part_index(at + b + u);
+#pragma unroll
+                        for (int c = 0; c < C; c++) v[c][u] = old[c * pcap + idx];
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+#pragma unroll
+                        for (int c = 0; c < C; c++) sum[c] = __fadd_rn(sum[c], v[c][u]);
+                }
+                for (; b < nb; b++) {
                     int idx = part_index(at + b);
 #pragma unroll
                     for (int c = 0; c < C; c++) sum[c] = __fadd_rn(sum[c], old[c * pcap + idx]);
@@ -360,7 +399,9 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     if (max_rows < 1) return TSM_OK;
     size_t smem = stream_smem_bytes<KIND, C>(nb);
     if (smem > 200 * 1024) return TSM_OK;
-    auto kernel = matvec_stream_kernel<KIND, C>;
+    if (nb < F::G) return TSM_OK;  // rows shorter than a group: the generic kernel takes them
+    bool aligned = nb % F::G == 0;
+    auto kernel = aligned ? matvec_stream_kernel<KIND, C, true> : matvec_stream_kernel<KIND, C, false>;
     static std::mutex attr_lock;  // the attribute is per device and per function
     static std::map<std::pair<int, const void*>, size_t> attr_set;
     {
@@ -387,6 +428,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     MatvecParams p;
     p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
+    p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
     kernel<<<grid, kThreads, smem, ctx->stream>>>(p);
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
@@ -403,6 +445,7 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
     else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, k, w, n, bias, residual, out, &taken)));
     else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, k, w, n, bias, residual, out, &taken)));
     if (taken) return TSM_OK;
+    if (rows > 4 && mma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_mma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     int nb = k / 32;
     int64_t grid = ((int64_t)n + 3) / 4;
     matvec_generic_kernel<KIND><<<(unsigned)grid, 128, 0, ctx->stream>>>(w, n, nb, a, rows, bias, residual, out);

@@ -382,6 +382,11 @@ int tsm_add(tsm_ctx* ctx, tsm_dptr a, tsm_dptr b, int64_t count, tsm_dptr out) {
     return launch_add(ctx, PCF(a), PCF(b), count, PF(out));
 }
 
+int tsm_fill_normal(tsm_ctx* ctx, tsm_dptr out, int64_t count, float mean, float stddev, uint64_t seed) {
+    CTX_GUARD(ctx);
+    return launch_normal_fill(ctx, PF(out), count, mean, stddev, seed);
+}
+
 int tsm_argmax(tsm_ctx* ctx, tsm_dptr logits, int rows, int n, tsm_dptr out) {
     CTX_GUARD(ctx);
     return launch_argmax(ctx, PCF(logits), rows, n, (int*)(uintptr_t)out);

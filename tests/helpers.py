@@ -142,3 +142,47 @@ def gpt2_tensors_from_hf(st, layers, quantize_kind=None, embeddings=False):
             t[f"{i}.{ours}"] = lin(st[h + theirs + ".weight"])
             t[f"{i}.{ours}_b"] = (-1, st[h + theirs + ".bias"])
     return t
+
+
+def oracle_from_device_model(model, threads=1):
+    """An oracle model over the very weights a device model holds (downloaded through the C ABI)."""
+    c = dict(model.config)
+    names = ["embed", "final_w"] + (["wpe", "final_b"] if c["arch"] == "gpt2" else [])
+    if not c["tied"]:
+        names.append("head")
+    for i in range(c["layers"]):
+        names += [f"{i}.{p}" for p in ("norm1_w", "norm2_w", "qkv", "o", "up", "down")]
+        if c["arch"] == "gpt2":
+            names += [f"{i}.{p}" for p in ("norm1_b", "norm2_b", "qkv_b", "o_b", "up_b", "down_b")]
+    t = {}
+    for name in names:
+        buf, kind, n, k = model.tensor(name)
+        if kind < 0:
+            t[name] = (-1, buf.numpy(np.float32).reshape(-1) if n == 1 else buf.numpy(np.float32).reshape(n, k))
+        else:
+            t[name] = (kind, buf.numpy(np.uint8).reshape(n, -1))
+    return oracle.Model(c, t, threads=threads)
+
+
+def write_gpt2_gguf(path, st, layers, heads, kind):
+    """A GPT-2 in tensomite's own GGUF names (gpt2.cr:75-89), Linear weights and both tables quantised."""
+    t = gpt2_tensors_from_hf(st, layers, quantize_kind=kind, embeddings=True)
+    gk = GGUF_OF_KIND[kind]
+    d = st["transformer.wte.weight"].shape[1]
+    tensors = [("wte.weight", gk, list(st["transformer.wte.weight"].shape), t["embed"][1]),
+               ("wpe.weight", gk, list(st["transformer.wpe.weight"].shape), t["wpe"][1]),
+               ("ln_f.weight", gguf.F32, [d], t["final_w"][1]), ("ln_f.bias", gguf.F32, [d], t["final_b"][1])]
+    for i in range(layers):
+        for ours, theirs in (("norm1", "ln_1"), ("norm2", "ln_2")):
+            tensors.append((f"h.{i}.{theirs}.weight", gguf.F32, [d], t[f"{i}.{ours}_w"][1]))
+            tensors.append((f"h.{i}.{theirs}.bias", gguf.F32, [d], t[f"{i}.{ours}_b"][1]))
+        for ours, theirs in (("qkv", "attn.c_attn"), ("o", "attn.c_proj"), ("up", "mlp.c_fc"), ("down", "mlp.c_proj")):
+            w = st[f"transformer.h.{i}.{theirs}.weight"]
+            tensors.append((f"h.{i}.{theirs}.weight", gk, [w.shape[1], w.shape[0]], t[f"{i}.{ours}"][1]))
+            tensors.append((f"h.{i}.{theirs}.bias", gguf.F32, [w.shape[1]], t[f"{i}.{ours}_b"][1]))
+    gguf.write(path, {"general.architecture": "gpt2", "gpt2.heads": str(heads)}, tensors)
+    return t
+
+
+def rel_max(a, b):
+    return float(np.max(np.abs(a - b)) / max(float(np.max(np.abs(b))), 1e-30))

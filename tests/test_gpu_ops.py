@@ -1,0 +1,221 @@
+"""CUDA operators against the CPU oracle, through the C ABI (needs a B200).
+
+Mirrors spec/quant_spec.cr, spec/block_matmul_spec.cr, spec/fused_llama_spec.cr, spec/llama_ops_spec.cr,
+spec/attention_spec.cr, spec/batched_decode_spec.cr, spec/sampler_spec.cr and spec/buffer_pool_spec.cr.
+Block products, gathers, RoPE, activations and cache writes are held to the oracle's bits; norms and
+attention to 1e-5 relative in the fast mode and to the oracle's bits in the exact mode.
+"""
+import numpy as np
+import pytest
+
+import helpers
+from helpers import bits, golden, oracle, pkg, rel_max
+
+pytestmark = pytest.mark.gpu
+KINDS = {"Q8_0": oracle.Q8_0, "Q4_0": oracle.Q4_0, "Q4_1": oracle.Q4_1}
+
+
+@pytest.fixture(scope="module")
+def dev():
+    d = pkg.B200(0)
+    yield d
+    d.close()
+
+
+@pytest.mark.parametrize("name", list(KINDS))
+def test_weight_quantiser_gives_ggmls_bytes(dev, name):
+    g = golden()
+    for i in range(7):
+        row = g[f"quant/rows/{i}"]
+        buf = dev.quantize(row, KINDS[name])
+        assert buf.numpy(np.uint8).tobytes() == g[f"quant/{name}/bytes/{i}"].tobytes(), (name, i)
+        back = dev.dequantize(buf, row.size, KINDS[name])
+        assert np.array_equal(bits(back.numpy(np.float32)), bits(g[f"quant/{name}/values/{i}"]))
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 0.02, 64 * 1024).astype(np.float32)
+    x[:32] = 0
+    assert dev.quantize(x, KINDS[name]).numpy(np.uint8).tobytes() == oracle.quantize(KINDS[name], x).tobytes()
+
+
+def test_activation_quantiser_has_the_hosts_bits(dev):
+    rng = np.random.default_rng(2)
+    x = rng.uniform(-3, 3, (5, 1280)).astype(np.float32)
+    x[1, :32] = 0
+    x[2, :32] = [127.0 if j == 0 else j - 15.5 for j in range(32)]
+    x[3, 64:96] *= 1e-20
+    scales, sums, qs = dev.quantize_rows(x)
+    ws, wm, wq = oracle.quantize_activations(x)
+    assert np.array_equal(bits(scales), bits(ws)) and np.array_equal(bits(sums), bits(wm)) and np.array_equal(qs, wq)
+
+
+def product_case(rng, count, n, k):
+    values = rng.uniform(-2, 2, n * k).astype(np.float32)
+    values[:32] = 0
+    values[96] = 50
+    x = rng.uniform(-3, 3, (count, k)).astype(np.float32)
+    if count > 1:
+        x[1, :32] = 0
+    if count > 2:
+        x[2, :32] = [127.0 if j == 0 else j - 15.5 for j in range(32)]
+    return values, x
+
+
+SHAPES = [(1, 37, 64), (3, 5, 1280), (2, 9, 4096),            # the reference's spec shapes (generic kernel)
+          (1, 64, 576), (1, 960, 576), (4, 576, 1536),        # rows of 18 and 48 blocks (SmolLM2-135M's)
+          (1, 1600, 1600), (2, 200, 6400),                    # 50 and 200 blocks (GPT-2 XL's)
+          (1, 2048, 2048), (3, 1024, 4096), (1, 256, 14336),  # aligned rows, long rows
+          (8, 128, 2048), (16, 64, 576), (1, 7, 4096), (1, 4097, 256),
+          (5, 40, 1536), (33, 48, 4096), (64, 200, 1600), (100, 96, 576), (64, 1024, 2048), (17, 72, 14336)]  # tensor-core kernel
+
+
+@pytest.mark.parametrize("name", list(KINDS))
+def test_block_product_is_bit_exact(dev, name):
+    rng = np.random.default_rng(11)
+    kind = KINDS[name]
+    for count, n, k in SHAPES:
+        values, x = product_case(rng, count, n, k)
+        bias = rng.normal(0, 1, n).astype(np.float32) if n % 2 else None
+        w = oracle.quantize(kind, values)
+        wb = dev.tensor(w)
+        got = dev.block_matmul(x, wb, kind, n, bias=bias)
+        want = oracle.matmul_reference(kind, x, w, n, bias=bias)
+        wb.free()
+        assert np.array_equal(bits(got), bits(want)), (name, count, n, k)
+
+
+def test_a_row_alone_equals_the_row_in_a_batch(dev):
+    rng = np.random.default_rng(4)
+    n, k = 512, 2048
+    w = oracle.quantize(oracle.Q4_0, rng.normal(0, 0.02, n * k).astype(np.float32))
+    wb = dev.tensor(w)
+    x = rng.normal(0, 1, (9, k)).astype(np.float32)
+    batch = dev.block_matmul(x, wb, oracle.Q4_0, n)
+    for r in (0, 4, 8):
+        assert np.array_equal(bits(dev.block_matmul(x[r:r + 1], wb, oracle.Q4_0, n)[0]), bits(batch[r]))
+
+
+@pytest.mark.parametrize("name", list(KINDS))
+def test_block_gather(dev, name):
+    rng = np.random.default_rng(5)
+    kind = KINDS[name]
+    table = oracle.quantize(kind, rng.normal(0, 1, (50, 96)).astype(np.float32))
+    tb = dev.tensor(table)
+    ids = np.array([3, 0, 49, 7, 7], dtype=np.int32)
+    assert np.array_equal(bits(dev.gather_blocks(tb, kind, 50, 96, ids)), bits(oracle.gather_blocks(kind, table, 50, 96, ids)))
+    with pytest.raises(pkg.ExecutionError, match="index 50 out of range for 50 rows"):
+        dev.gather_blocks(tb, kind, 50, 96, np.array([1, 50], dtype=np.int32))
+    # the record is cleared: the next call succeeds
+    dev.gather_blocks(tb, kind, 50, 96, ids)
+
+
+@pytest.mark.parametrize("n", [32, 576, 1600, 2048, 4096])
+def test_norms(dev, n):
+    rng = np.random.default_rng(6)
+    x = rng.normal(0, 2, (3, n)).astype(np.float32)
+    w = rng.normal(1, 0.2, n).astype(np.float32)
+    b = rng.normal(0, 0.2, n).astype(np.float32)
+    dev.set_mode(pkg.FAST)
+    assert rel_max(dev.rmsnorm(x, w), oracle.rmsnorm(x, w)) <= 1e-5
+    assert rel_max(dev.layernorm(x, w, b), oracle.layernorm(x, w, b)) <= 1e-5
+    dev.set_mode(pkg.EXACT)
+    assert np.array_equal(bits(dev.rmsnorm(x, w)), bits(oracle.rmsnorm(x, w)))
+    assert np.array_equal(bits(dev.rmsnorm(x, None)), bits(oracle.rmsnorm(x, None)))
+    assert np.array_equal(bits(dev.layernorm(x, w, b)), bits(oracle.layernorm(x, w, b)))
+
+
+def test_rope_is_bit_exact(dev):
+    rng = np.random.default_rng(7)
+    cos, sin = oracle.rope_tables(64, 300, 10000.0)
+    x = rng.normal(0, 1, (6, 5, 64)).astype(np.float32)
+    positions = np.array([0, 1, 17, 299, 128, 5], dtype=np.int32)
+    got = dev.rope(x, cos, sin, positions)
+    for t in range(6):
+        want = oracle.rope(x[t], np.repeat(cos[positions[t]][None], 5, 0), np.repeat(sin[positions[t]][None], 5, 0))
+        assert np.array_equal(bits(got[t]), bits(want))
+
+
+def test_write_rows_places_tokens(dev):
+    rng = np.random.default_rng(8)
+    cache = rng.normal(0, 1, (3, 2, 10, 8)).astype(np.float32)
+    values = rng.normal(0, 1, (4, 2, 8)).astype(np.float32)
+    slots = np.array([0 * 10 + 3, 2 * 10 + 0, 2 * 10 + 1, 1 * 10 + 9], dtype=np.int32)
+    got = dev.write_rows(cache, values, slots)
+    want = cache.copy()
+    for t, slot in enumerate(slots):
+        want[slot // 10, :, slot % 10, :] = values[t]
+    assert np.array_equal(got, want)
+
+
+def test_activations_are_bit_exact(dev):
+    rng = np.random.default_rng(9)
+    gate = np.concatenate([rng.normal(0, 3, 4000), [0.0, -0.0, 100.0, -100.0, 88.8, -88.0]]).astype(np.float32).reshape(2, -1)
+    up = rng.normal(0, 1, gate.shape).astype(np.float32)
+    assert np.array_equal(bits(dev.swiglu(gate, up)), bits(oracle.swiglu(gate, up)))
+    assert np.array_equal(bits(dev.gelu(gate)), bits(oracle.gelu(gate)))
+    assert np.array_equal(bits(dev.add(gate, up)), bits(gate + up))
+
+
+def attention_case(rng, rows, kv_heads, group, capacity, width, lengths):
+    heads = kv_heads * group
+    k = rng.normal(0, 1, (rows, kv_heads, capacity, width)).astype(np.float32)
+    v = rng.normal(0, 1, (rows, kv_heads, capacity, width)).astype(np.float32)
+    q = rng.normal(0, 1, (len(lengths), heads, width)).astype(np.float32)
+    table = np.array([[row, length - 1, length] for row, length in lengths], dtype=np.int32)
+    return q, k, v, table, heads
+
+
+def oracle_attention(q, k, v, table, scale):
+    tokens, heads, width = q.shape
+    group = heads // k.shape[1]
+    out = np.empty_like(q)
+    for t in range(tokens):
+        row, limit = table[t, 0], table[t, 1]
+        for h in range(heads):
+            out[t, h] = oracle.attend(q[t, h], k[row, h // group, :limit + 1], v[row, h // group, :limit + 1], scale)
+    return out
+
+
+@pytest.mark.parametrize("width,group", [(64, 1), (64, 3), (128, 4), (64, 2), (8, 2), (128, 8)])
+def test_ragged_attention(dev, width, group):
+    rng = np.random.default_rng(10)
+    lengths = [(0, 1), (1, 300), (2, 256), (3, 257), (1, 77), (0, 700)]
+    q, k, v, table, heads = attention_case(rng, 4, 2, group, 700, width, lengths)
+    scale = np.float32(1.0 / np.sqrt(width))
+    want = oracle_attention(q, k, v, table, scale)
+    dev.set_mode(pkg.FAST)
+    fast = dev.ragged_attention(q, k, v, table, scale)
+    assert rel_max(fast, want) <= 1e-5
+    # each token's bits do not depend on its neighbours in the batch
+    alone = dev.ragged_attention(q[1:2], k, v, table[1:2], scale)
+    assert np.array_equal(bits(alone[0]), bits(fast[1]))
+    dev.set_mode(pkg.EXACT)
+    exact = dev.ragged_attention(q, k, v, table, scale)
+    assert np.array_equal(bits(exact), bits(want))
+    assert np.array_equal(bits(dev.ragged_attention(q[1:2], k, v, table[1:2], scale)[0]), bits(exact[1]))
+
+
+def test_sampler_picks(dev):
+    logits = np.array([[0.5, 2.0, 2.0, -1.0, 2.0, 1.5], [3.0, 1.0, 3.0, 0.0, 0.0, 0.0]], dtype=np.float32)
+    assert dev.argmax(logits).tolist() == [1, 0]
+    ids, values = dev.topk(logits, 4)
+    assert ids.tolist() == [[1, 2, 4, 5], [0, 2, 1, 3]]
+    assert values[0].tolist() == [2.0, 2.0, 2.0, 1.5]
+    rng = np.random.default_rng(3)
+    big = rng.normal(0, 1, (3, 50257)).astype(np.float32)
+    assert dev.argmax(big).tolist() == [oracle.argmax_first(r) for r in big]
+    assert dev.topk(big, 40)[0].tolist() == [oracle.topk(r, 40).tolist() for r in big]
+
+
+def test_pool_reuses_exact_sizes(dev):
+    dev.sync()
+    a = dev.alloc(123456)
+    ptr = a.ptr
+    a.free()
+    before = dev.counters()
+    b = dev.alloc(123456)
+    after = dev.counters()
+    assert b.ptr == ptr and after["pool_hits"] == before["pool_hits"] + 1 and after["pool_misses"] == before["pool_misses"]
+    c = dev.alloc(123457)
+    assert c.ptr != ptr
+    b.free(), c.free()
+    assert dev.counters()["host_ops"] == 0
