@@ -272,7 +272,7 @@ __global__ void attention_ordered_kernel(const float* __restrict__ q, int64_t q_
 
 // The ordered path for head widths 64 and 128, built for throughput: one CTA per (token, group of G
 // query heads that share a kv head).
-//  1. scores: keys arrive in tiles of 4096 / width positions through cp.async into shared memory rows padded by
+//  1. scores: keys arrive in tiles of 64 or 128 positions through a ring of cp.async stages into shared memory rows padded by
 //     16 bytes (so that threads walking different rows hit different banks); thread (position, head)
 //     folds its dot product over the width in index order.
 //  2. the maximum, the host's exp of each score, then one thread per head folds the denominator over
@@ -287,23 +287,24 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <int WIDTH, int G>
-__global__ void __launch_bounds__(256) attention_exact_kernel(const float* __restrict__ q, int64_t q_stride, int heads,
-                                                              const float* __restrict__ k, const float* __restrict__ v,
-                                                              int rows, int kv_heads, int capacity,
-                                                              const int* __restrict__ table, float scale, float* out,
-                                                              ErrorRecord* errors) {
-    constexpr int kTilePositions = 4096 / WIDTH;  // 16 KB of keys per tile
-    constexpr int GS = G == 3 ? 4 : G;        // interleave stride of the scores
-    constexpr int PITCH = WIDTH + 4;          // floats per staged key row
-    constexpr int CHUNKS = WIDTH / 4;         // 16-byte pieces per key row
-    constexpr int COLS = 256 / WIDTH;         // column groups in the output phase (2 or 4)
+template <int WIDTH, int G, int THREADS, int TP, int STAGES, int UNROLL>
+__global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* __restrict__ q, int64_t q_stride, int heads,
+                                                                  const float* __restrict__ k, const float* __restrict__ v,
+                                                                  int rows, int kv_heads, int capacity,
+                                                                  const int* __restrict__ table, float scale, float* out,
+                                                                  ErrorRecord* errors) {
+    constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
+    constexpr int PITCH = WIDTH + 4;            // floats per staged key row
+    constexpr int CHUNKS = WIDTH / 4;           // 16-byte pieces per key row
+    constexpr int COLS = THREADS / WIDTH;       // column groups in the output phase
     constexpr int HPT = (G + COLS - 1) / COLS;  // heads per thread in the output phase
+    constexpr int WARPS = THREADS / 32;
+    static_assert(THREADS / GS >= TP && THREADS % GS == 0 && THREADS % WIDTH == 0, "thread mapping");
     extern __shared__ __align__(16) float sh[];
-    float* qs = sh;                                   // [GS][PITCH]
-    float* kt = qs + GS * PITCH;                      // [2][tile][PITCH]
-    float* sc = kt + 2 * kTilePositions * PITCH;      // [capacity * GS]
-    __shared__ float wred[8][4];
+    float* qs = sh;                         // [GS][PITCH]
+    float* kt = qs + GS * PITCH;            // [STAGES][TP][PITCH]
+    float* sc = kt + STAGES * TP * PITCH;   // [capacity * GS]
+    __shared__ float wred[WARPS][4];
     __shared__ float totals[4];
 
     const int token = blockIdx.y;
@@ -320,33 +321,35 @@ __global__ void __launch_bounds__(256) attention_exact_kernel(const float* __res
     const float* kb = k + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
     const float* vb = v + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
 
-    for (int i = tid; i < G * WIDTH; i += 256)
+    for (int i = tid; i < G * WIDTH; i += THREADS)
         qs[(i / WIDTH) * PITCH + i % WIDTH] = q[(int64_t)token * q_stride + (int64_t)head0 * WIDTH + i];
 
-    auto load_tile = [&](int tile, int buffer) {
-        int p0 = tile * kTilePositions;
-        int count = min(kTilePositions, len - p0);
-        float* dst = kt + buffer * kTilePositions * PITCH;
-        for (int i = tid; i < count * CHUNKS; i += 256) {
-            int p = i / CHUNKS, c = i % CHUNKS;
-            cp_async16(dst + p * PITCH + 4 * c, kb + (int64_t)(p0 + p) * WIDTH + 4 * c);
+    const int tiles = (len + TP - 1) / TP;
+    auto load_tile = [&](int tile) {  // always commits a group, so that group t is tile t
+        if (tile < tiles) {
+            int p0 = tile * TP;
+            int count = min(TP, len - p0);
+            float* dst = kt + (tile % STAGES) * TP * PITCH;
+            for (int i = tid; i < count * CHUNKS; i += THREADS) {
+                int p = i / CHUNKS, c = i % CHUNKS;
+                cp_async16(dst + p * PITCH + 4 * c, kb + (int64_t)(p0 + p) * WIDTH + 4 * c);
+            }
         }
         cp_async_commit();
     };
 
     // ---- 1. scores ----
-    const int tiles = (len + kTilePositions - 1) / kTilePositions;
     const int sp = tid / GS, shd = tid % GS;  // this thread's position within a tile and its head
     float top = -INFINITY;
-    load_tile(0, 0);
+#pragma unroll
+    for (int t = 0; t < STAGES - 1; t++) load_tile(t);
     for (int tile = 0; tile < tiles; tile++) {
-        if (tile + 1 < tiles) load_tile(tile + 1, (tile + 1) & 1);
-        else cp_async_commit();
-        cp_async_wait<1>();
+        load_tile(tile + STAGES - 1);  // into the stage read in the previous iteration (a barrier ended it)
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
-        int p = tile * kTilePositions + sp;
-        if (sp < kTilePositions && shd < G && p < len) {
-            const float4* kr = (const float4*)(kt + ((tile & 1) * kTilePositions + sp) * PITCH);
+        int p = tile * TP + sp;
+        if (sp < TP && shd < G && p < len) {
+            const float4* kr = (const float4*)(kt + ((tile % STAGES) * TP + sp) * PITCH);
             const float4* qr = (const float4*)(qs + shd * PITCH);
             float dot = 0.0f;
 #pragma unroll 8
@@ -370,12 +373,12 @@ __global__ void __launch_bounds__(256) attention_exact_kernel(const float* __res
     if (lane < GS) wred[warp][lane] = top;
     __syncthreads();
     {
-        // 256 % GS == 0, so in the flat walk below a thread always meets its own head: index % GS == tid % GS
+        // THREADS % GS == 0, so in the flat walk below a thread always meets its own head
         float m = wred[0][shd];
 #pragma unroll
-        for (int w2 = 1; w2 < 8; w2++) m = fmaxf(m, wred[w2][shd]);
+        for (int w2 = 1; w2 < WARPS; w2++) m = fmaxf(m, wred[w2][shd]);
         if (shd < G)
-            for (int i = tid; i < len * GS; i += 256) sc[i] = exact_exp(__fsub_rn(sc[i], m));
+            for (int i = tid; i < len * GS; i += THREADS) sc[i] = exact_exp(__fsub_rn(sc[i], m));
     }
     __syncthreads();
     if (tid < G) {
@@ -394,34 +397,59 @@ __global__ void __launch_bounds__(256) attention_exact_kernel(const float* __res
     __syncthreads();
     if (shd < G) {
         float total = totals[shd];
-        for (int i = tid; i < len * GS; i += 256) sc[i] = __fdiv_rn(sc[i], total);
+        for (int i = tid; i < len * GS; i += THREADS) sc[i] = __fdiv_rn(sc[i], total);
     }
     __syncthreads();
-    // ---- 3. outputs ----
+    // ---- 3. outputs: values pass through the same ring of stages (rows unpadded reads are conflict-free:
+    //         consecutive threads read consecutive columns) ----
     const int col = tid % WIDTH, hg = tid / WIDTH;
     const int h0 = hg * HPT;
-    if (h0 < G) {
-        float acc[HPT];
+    auto load_values = [&](int tile) {
+        if (tile < tiles) {
+            int p0 = tile * TP;
+            int count = min(TP, len - p0);
+            float* dst = kt + (tile % STAGES) * TP * PITCH;
+            for (int i = tid; i < count * CHUNKS; i += THREADS) {
+                int p = i / CHUNKS, c = i % CHUNKS;
+                cp_async16(dst + p * PITCH + 4 * c, vb + (int64_t)(p0 + p) * WIDTH + 4 * c);
+            }
+        }
+        cp_async_commit();
+    };
+    float acc[HPT];
 #pragma unroll
-        for (int i = 0; i < HPT; i++) acc[i] = 0.0f;
-        const float* vp = vb + col;
-        int p = 0;
-        for (; p + 8 <= len; p += 8) {
-            float vv[8];
+    for (int i = 0; i < HPT; i++) acc[i] = 0.0f;
 #pragma unroll
-            for (int u = 0; u < 8; u++) vv[u] = vp[(int64_t)(p + u) * WIDTH];
+    for (int t = 0; t < STAGES - 1; t++) load_values(t);
+    for (int tile = 0; tile < tiles; tile++) {
+        load_values(tile + STAGES - 1);
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        if (h0 < G) {
+            const float* vt = kt + (tile % STAGES) * TP * PITCH + col;
+            const float* wt = sc + (int64_t)tile * TP * GS + h0;
+            int count = min(TP, len - tile * TP);
+            int p = 0;
+            for (; p + UNROLL <= count; p += UNROLL) {
+                float vv[UNROLL];
 #pragma unroll
-            for (int u = 0; u < 8; u++)
+                for (int u = 0; u < UNROLL; u++) vv[u] = vt[(p + u) * PITCH];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+                    for (int i = 0; i < HPT; i++)
+                        if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(wt[(p + u) * GS + i], vv[u]));
+            }
+            for (; p < count; p++) {
+                float vv = vt[p * PITCH];
 #pragma unroll
                 for (int i = 0; i < HPT; i++)
-                    if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(sc[(p + u) * GS + h0 + i], vv[u]));
+                    if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(wt[p * GS + i], vv));
+            }
         }
-        for (; p < len; p++) {
-            float vv = vp[(int64_t)p * WIDTH];
-#pragma unroll
-            for (int i = 0; i < HPT; i++)
-                if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(sc[p * GS + h0 + i], vv));
-        }
+        __syncthreads();
+    }
+    if (h0 < G) {
 #pragma unroll
         for (int i = 0; i < HPT; i++)
             if (h0 + i < G) out[((int64_t)token * heads + head0 + h0 + i) * WIDTH + col] = acc[i];
@@ -482,33 +510,43 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     bool launched = false;
     if (aligned && (width == 64 || width == 128)) {
         int per_kv = heads / kv_heads;
-        int tile = 4096 / width, pitch = width + 4;
+        int pitch = width + 4;
         for (int g = 4; g >= 1 && !launched; g--) {
             if (per_kv % g != 0) continue;
             int gs = g == 3 ? 4 : g;
-            size_t smem = ((size_t)gs * pitch + 2 * (size_t)tile * pitch + (size_t)capacity * gs) * 4;
-            if (smem > 200 * 1024) continue;
-            dim3 grid(kv_heads * (per_kv / g), tokens);
-#define TSM_EXACT_ATTN(W, G)                                                                                              \
+            bool small = width == 64 && g == 1;  // few chains per CTA: smaller CTAs, more of them per SM
+            int tp = width == 128 ? 64 : (small ? 64 : 128);
+            for (int stages = 3; stages >= 2 && !launched; stages--) {
+                size_t smem = ((size_t)gs * pitch + (size_t)stages * tp * pitch + (size_t)capacity * gs) * 4;
+                if (smem > 200 * 1024) continue;
+                dim3 grid(kv_heads * (per_kv / g), tokens);
+#define TSM_EXACT_ATTN(W, G, T, TP, S, U)                                                                                 \
     do {                                                                                                                  \
-        auto kernel = attention_exact_kernel<W, G>;                                                                       \
+        auto kernel = attention_exact_kernel<W, G, T, TP, S, U>;                                                          \
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-        kernel<<<grid, 256, smem, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, out,    \
-                                                 ctx->errors);                                                            \
+        kernel<<<grid, T, smem, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, out,      \
+                                               ctx->errors);                                                              \
     } while (0)
-            if (width == 64) {
-                if (g == 4) TSM_EXACT_ATTN(64, 4);
-                else if (g == 3) TSM_EXACT_ATTN(64, 3);
-                else if (g == 2) TSM_EXACT_ATTN(64, 2);
-                else TSM_EXACT_ATTN(64, 1);
-            } else {
-                if (g == 4) TSM_EXACT_ATTN(128, 4);
-                else if (g == 3) TSM_EXACT_ATTN(128, 3);
-                else if (g == 2) TSM_EXACT_ATTN(128, 2);
-                else TSM_EXACT_ATTN(128, 1);
-            }
+#define TSM_EXACT_STAGES(W, G, T, TP, U)          \
+    do {                                          \
+        if (stages == 3) TSM_EXACT_ATTN(W, G, T, TP, 3, U); \
+        else TSM_EXACT_ATTN(W, G, T, TP, 2, U);   \
+    } while (0)
+                if (width == 64) {
+                    if (g == 4) TSM_EXACT_STAGES(64, 4, 512, 128, 16);
+                    else if (g == 3) TSM_EXACT_STAGES(64, 3, 512, 128, 16);
+                    else if (g == 2) TSM_EXACT_STAGES(64, 2, 512, 128, 16);
+                    else TSM_EXACT_STAGES(64, 1, 128, 64, 32);
+                } else {
+                    if (g == 4) TSM_EXACT_STAGES(128, 4, 512, 64, 16);
+                    else if (g == 3) TSM_EXACT_STAGES(128, 3, 512, 64, 16);
+                    else if (g == 2) TSM_EXACT_STAGES(128, 2, 512, 64, 16);
+                    else TSM_EXACT_STAGES(128, 1, 512, 64, 16);
+                }
+#undef TSM_EXACT_STAGES
 #undef TSM_EXACT_ATTN
-            launched = true;
+                launched = true;
+            }
         }
     }
     if (!launched) {

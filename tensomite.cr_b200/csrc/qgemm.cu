@@ -12,18 +12,19 @@
 // thread's A registers.  The accumulator is started at the bit pattern of 1.5 * 2^23, so the integer
 // result read back as a float is 12582912 + dot and one subtraction converts it exactly.
 //
-// Weights stream through shared memory in chunks of 8 to 32 blocks per weight row.  Each row's chunk is one
+// Weights stream through shared memory in chunks of 8 blocks per weight row.  Each row's chunk is one
 // bulk asynchronous copy (cp.async.bulk) whose start is rounded down and end rounded up to 16 bytes,
 // so rows of any even pitch (612-byte rows of 18 Q8_0 blocks included) are handled; the reader adds the
-// row's shift back.  Activations (int8) and their scales come from L2 through L1: they are shared by
-// every CTA and small.
+// row's shift back.  The quantised activations and their scales for the same 8 blocks are staged beside
+// them with cp.async, so the inner loop reads shared memory only.  For Q4_0 the nibbles are turned into
+// signed bytes (nibble - 8) before the multiply, which removes the -8 * sum(q) correction.
 #include "common.cuh"
 
 namespace tsm {
 
 namespace {
 
-constexpr int kGemmStages = 4;
+constexpr int kGemmStages = 3;
 constexpr unsigned kGemmSpins = 4u << 20;
 
 template <int KIND> struct GFmt;
@@ -86,18 +87,35 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], unsigned a0, unsigned a1, un
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(bias));
 }
 
-// WR x WC warps: warp (wr, wc) owns weight rows [16 wr, 16 wr + 16) of the CTA's slab and NT tiles of
-// 8 activation rows starting at tile wc * NT.
+__device__ __forceinline__ void g_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(g_smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void g_cp_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(g_smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void g_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void g_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Nibbles 0..15 in the low half of each byte of x -> signed bytes nibble - 8, without touching neighbours:
+// (b | 128) - 8 never borrows, and flipping bit 7 afterwards leaves b - 8 in two's complement.
+__device__ __forceinline__ unsigned nibbles_minus_8(unsigned x) { return (((x & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
+
+constexpr int kChunkBlocks = 8;  // blocks of K per stage
+
+// A CTA takes 16 WR weight rows and 8 NT WC activation rows; warp (wr, wc) owns weight rows
+// [16 wr, 16 wr + 16) and NT tiles of 8 activation rows from tile wc * NT.  Per stage of 8 blocks the
+// weights arrive by one bulk copy per row, the quantised activations and their scales by cp.async.
 template <int KIND, int NT, int WR, int WC>
 __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) {
     constexpr int B = GFmt<KIND>::B;
-    constexpr int ROWS = 16 * WR;
-    constexpr int kChunkBlocks = 32 / WR;         // blocks of a row per stage: a stage is about 18 KB whatever WR is
-    constexpr int PITCH = kChunkBlocks * B + 32;  // a chunk plus the slack of rounding both ends to 16 bytes
+    constexpr int ROWS = 16 * WR, COLS = 8 * NT * WC, THREADS = 32 * WR * WC;
+    constexpr int WP = kChunkBlocks * B + (KIND == TSM_Q4_1 ? 48 : 32);  // weight row pitch: a chunk + rounding slack, bank-friendly
+    constexpr int AP = kChunkBlocks * 32 + 16;                            // activation row pitch
+    constexpr int STAGE = ROWS * WP + COLS * AP + 2 * COLS * kChunkBlocks * 4;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = (uint64_t*)smem;
     int* abort_flag = (int*)(smem + 64);
-    unsigned char* stages = smem + 128;  // kGemmStages x ROWS x PITCH
+    unsigned char* stages = smem + 128;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wr = warp / WC, wc = warp % WC;
@@ -105,32 +123,49 @@ __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) 
     const int nb = p.nb;
     const int64_t rb = (int64_t)nb * B;
     const int row0 = blockIdx.x * ROWS;
-    const int col0 = blockIdx.y * (8 * NT * WC) + wc * 8 * NT;
+    const int cta_col0 = blockIdx.y * COLS;
     const int chunks = (nb + kChunkBlocks - 1) / kChunkBlocks;
+    const int64_t k = (int64_t)nb * 32;
 
-    // producer (warp 0): thread 0 announces the bytes, then the lanes issue one row's copy each
-    auto issue = [&](int chunk) {
-        if (chunk >= chunks) return;
-        int s = chunk % kGemmStages;
-        int len = min(kChunkBlocks, nb - chunk * kChunkBlocks) * B;
-        if (tid == 0) {
-            unsigned total = 0;
-            for (int r = 0; r < ROWS; r++) {
-                int row = row0 + r;
-                if (row >= p.n) break;
-                int64_t o = (int64_t)row * rb + (int64_t)chunk * kChunkBlocks * B;
-                int64_t a0 = o & ~(int64_t)15;
-                total += (unsigned)(((o + len + 15) & ~(int64_t)15) - a0);
+    auto issue = [&](int chunk) {  // every thread commits one cp.async group per call, so group c is chunk c
+        if (chunk < chunks) {
+            int s = chunk % kGemmStages;
+            int count = min(kChunkBlocks, nb - chunk * kChunkBlocks);
+            int len = count * B;
+            unsigned char* base = stages + (size_t)s * STAGE;
+            if (warp == 0) {
+                if (lane == 0) {
+                    unsigned total = 0;
+                    for (int r = 0; r < ROWS && row0 + r < p.n; r++) {
+                        int64_t o = (int64_t)(row0 + r) * rb + (int64_t)chunk * kChunkBlocks * B;
+                        total += (unsigned)(((o + len + 15) & ~(int64_t)15) - (o & ~(int64_t)15));
+                    }
+                    g_mbar_expect_tx(&full[s], total);
+                }
+                __syncwarp();
+                for (int r = lane; r < ROWS && row0 + r < p.n; r += 32) {
+                    int64_t o = (int64_t)(row0 + r) * rb + (int64_t)chunk * kChunkBlocks * B;
+                    int64_t a0 = o & ~(int64_t)15;
+                    g_bulk_load(base + (size_t)r * WP, p.w + a0, (unsigned)(((o + len + 15) & ~(int64_t)15) - a0), &full[s]);
+                }
             }
-            g_mbar_expect_tx(&full[s], total);
+            unsigned char* acts = base + ROWS * WP;
+            float* sc = (float*)(acts + COLS * AP);
+            float* aux = sc + COLS * kChunkBlocks;
+            for (int i = tid; i < COLS * count * 2; i += THREADS) {
+                int c = i / (count * 2), piece = i % (count * 2);
+                int col = min(cta_col0 + c, p.m - 1);
+                g_cp_async16(acts + c * AP + piece * 16, p.acts.qs + (int64_t)col * k + (int64_t)chunk * kChunkBlocks * 32 + piece * 16);
+            }
+            for (int i = tid; i < COLS * count; i += THREADS) {
+                int c = i / count, j = i % count;
+                int col = min(cta_col0 + c, p.m - 1);
+                int64_t at = (int64_t)col * nb + chunk * kChunkBlocks + j;
+                g_cp_async4(sc + c * kChunkBlocks + j, p.acts.scales + at);
+                if (KIND == TSM_Q4_1) g_cp_async4(aux + c * kChunkBlocks + j, p.acts.sums + at);
+            }
         }
-        __syncwarp();
-        for (int r = lane; r < ROWS && row0 + r < p.n; r += 32) {
-            int64_t o = (int64_t)(row0 + r) * rb + (int64_t)chunk * kChunkBlocks * B;
-            int64_t a0 = o & ~(int64_t)15;
-            unsigned bytes = (unsigned)(((o + len + 15) & ~(int64_t)15) - a0);
-            g_bulk_load(stages + ((size_t)s * ROWS + r) * PITCH, p.w + a0, bytes, &full[s]);
-        }
+        g_cp_async_commit();
     };
 
     if (tid == 0) {
@@ -139,14 +174,14 @@ __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) 
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 0)
-        for (int c = 0; c < kGemmStages; c++) issue(c);
+#pragma unroll
+    for (int c = 0; c < kGemmStages - 1; c++) issue(c);
 
-    // this thread's two weight rows and their shifts inside the staged slots
+    // this thread's two weight rows and their shifts inside the staged slots (a chunk is 8 blocks, whose
+    // bytes are a multiple of 16 in every format, so a row's shift is the same in every chunk)
     const int ra = 16 * wr + g, rbw = ra + 8;
     const int shift_a = (int)(((int64_t)(row0 + ra) * rb) & 15), shift_b = (int)(((int64_t)(row0 + rbw) * rb) & 15);
-    // a chunk is 8, 16 or 32 blocks, whose bytes are a multiple of 16 in every format (8 * 34, 8 * 18, 8 * 20),
-    // so a row's shift is the same in every chunk.
+    const int lcol0 = wc * 8 * NT;  // first activation row of this warp within the CTA's slab
 
     float acc[NT][4];
 #pragma unroll
@@ -154,90 +189,82 @@ __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) 
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
 
-    // activation rows of this thread: B fragments come from row col0 + 8 i + g, the epilogue needs the
-    // scales of rows col0 + 8 i + 2 t and + 1; rows beyond m are clamped (their results are dropped)
-    int brow[NT], erow[NT][2];
-#pragma unroll
-    for (int i = 0; i < NT; i++) {
-        brow[i] = min(col0 + 8 * i + g, p.m - 1);
-        erow[i][0] = min(col0 + 8 * i + 2 * t, p.m - 1);
-        erow[i][1] = min(col0 + 8 * i + 2 * t + 1, p.m - 1);
-    }
-    const int8_t* qs = p.acts.qs;
-    const int64_t k = (int64_t)nb * 32;
-
     for (int chunk = 0; chunk < chunks; chunk++) {
+        issue(chunk + kGemmStages - 1);  // into the stage read in the previous iteration (a barrier ended it)
         int s = chunk % kGemmStages;
+        g_cp_async_wait<kGemmStages - 1>();
         bool arrived = g_mbar_wait(&full[s], (unsigned)((chunk / kGemmStages) & 1));
         if (!arrived) *abort_flag = 1;
-        const unsigned char* slot_a = stages + ((size_t)s * ROWS + ra) * PITCH + shift_a;
-        const unsigned char* slot_b = stages + ((size_t)s * ROWS + rbw) * PITCH + shift_b;
+        __syncthreads();
+        if (*abort_flag) break;
+        const unsigned char* base = stages + (size_t)s * STAGE;
+        const unsigned char* slot_a = base + (size_t)ra * WP + shift_a;
+        const unsigned char* slot_b = base + (size_t)rbw * WP + shift_b;
+        const unsigned char* acts = base + ROWS * WP;
+        const float* sc = (const float*)(acts + COLS * AP);
+        const float* aux = sc + COLS * kChunkBlocks;
         int count = min(kChunkBlocks, nb - chunk * kChunkBlocks);
-        if (arrived) {
 #pragma unroll 2
-            for (int j = 0; j < count; j++) {
-                int b = chunk * kChunkBlocks + j;
-                const unsigned char* pa = slot_a + j * B;
-                const unsigned char* pb = slot_b + j * B;
-                unsigned a0, a1, a2, a3;
-                float dwa = half_bits_to_float(lds_u16_at2(pa)), dwb = half_bits_to_float(lds_u16_at2(pb));
-                float mwa = 0.0f, mwb = 0.0f;
-                if (KIND == TSM_Q8_0) {
-                    a0 = lds_u32_at2(pa + 2 + 4 * t), a2 = lds_u32_at2(pa + 18 + 4 * t);
-                    a1 = lds_u32_at2(pb + 2 + 4 * t), a3 = lds_u32_at2(pb + 18 + 4 * t);
-                } else {
-                    constexpr int HEAD = KIND == TSM_Q4_0 ? 2 : 4;
-                    unsigned na = lds_u32_at2(pa + HEAD + 4 * t), nbw = lds_u32_at2(pb + HEAD + 4 * t);
-                    a0 = na & 0x0f0f0f0fu, a2 = (na >> 4) & 0x0f0f0f0fu;
-                    a1 = nbw & 0x0f0f0f0fu, a3 = (nbw >> 4) & 0x0f0f0f0fu;
-                    if (KIND == TSM_Q4_1) mwa = half_bits_to_float(lds_u16_at2(pa + 2)), mwb = half_bits_to_float(lds_u16_at2(pb + 2));
-                }
+        for (int j = 0; j < count; j++) {
+            const unsigned char* pa = slot_a + j * B;
+            const unsigned char* pb = slot_b + j * B;
+            unsigned a0, a1, a2, a3;
+            float dwa = half_bits_to_float(lds_u16_at2(pa)), dwb = half_bits_to_float(lds_u16_at2(pb));
+            float mwa = 0.0f, mwb = 0.0f;
+            if (KIND == TSM_Q8_0) {
+                a0 = lds_u32_at2(pa + 2 + 4 * t), a2 = lds_u32_at2(pa + 18 + 4 * t);
+                a1 = lds_u32_at2(pb + 2 + 4 * t), a3 = lds_u32_at2(pb + 18 + 4 * t);
+            } else if (KIND == TSM_Q4_0) {
+                unsigned na = lds_u32_at2(pa + 2 + 4 * t), nbw = lds_u32_at2(pb + 2 + 4 * t);
+                a0 = nibbles_minus_8(na), a2 = nibbles_minus_8(na >> 4);
+                a1 = nibbles_minus_8(nbw), a3 = nibbles_minus_8(nbw >> 4);
+            } else {
+                unsigned na = lds_u32_at2(pa + 4 + 4 * t), nbw = lds_u32_at2(pb + 4 + 4 * t);
+                a0 = na & 0x0f0f0f0fu, a2 = (na >> 4) & 0x0f0f0f0fu;
+                a1 = nbw & 0x0f0f0f0fu, a3 = (nbw >> 4) & 0x0f0f0f0fu;
+                mwa = half_bits_to_float(lds_u16_at2(pa + 2)), mwb = half_bits_to_float(lds_u16_at2(pb + 2));
+            }
 #pragma unroll
-                for (int i = 0; i < NT; i++) {
-                    const int* xq = (const int*)(qs + (int64_t)brow[i] * k + (int64_t)b * 32);
-                    unsigned b0 = (unsigned)__ldg(xq + t), b1 = (unsigned)__ldg(xq + 4 + t);
-                    int d[4];
-                    mma_s8(d, a0, a1, a2, a3, b0, b1);
+            for (int i = 0; i < NT; i++) {
+                const unsigned* xq = (const unsigned*)(acts + (lcol0 + 8 * i + g) * AP + j * 32);
+                int d[4];
+                mma_s8(d, a0, a1, a2, a3, xq[t], xq[4 + t]);
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        int64_t at = (int64_t)erow[i][e] * nb + b;
-                        float dx = __ldg(p.acts.scales + at);
-                        if (KIND == TSM_Q8_0) {
-                            float fa = __fsub_rn(__int_as_float(d[e]), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e]), 12582912.0f);
-                            acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(fa, __fmul_rn(dwa, dx)));
-                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(fb, __fmul_rn(dwb, dx)));
-                        } else if (KIND == TSM_Q4_0) {
-                            int xt8 = 8 * __ldg(p.acts.totals + at);
-                            float fa = __fsub_rn(__int_as_float(d[e] - xt8), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e] - xt8), 12582912.0f);
-                            acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(__fmul_rn(fa, dwa), dx));
-                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(__fmul_rn(fb, dwb), dx));
-                        } else {
-                            float sx = __ldg(p.acts.sums + at);
-                            float fa = __fsub_rn(__int_as_float(d[e]), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e]), 12582912.0f);
-                            acc[i][e] = __fadd_rn(acc[i][e], __fadd_rn(__fmul_rn(__fmul_rn(dwa, dx), fa), __fmul_rn(mwa, sx)));
-                            acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fadd_rn(__fmul_rn(__fmul_rn(dwb, dx), fb), __fmul_rn(mwb, sx)));
-                        }
+                for (int e = 0; e < 2; e++) {
+                    int c = lcol0 + 8 * i + 2 * t + e;
+                    float dx = sc[c * kChunkBlocks + j];
+                    float fa = __fsub_rn(__int_as_float(d[e]), 12582912.0f), fb = __fsub_rn(__int_as_float(d[2 + e]), 12582912.0f);
+                    if (KIND == TSM_Q8_0) {
+                        acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(fa, __fmul_rn(dwa, dx)));
+                        acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(fb, __fmul_rn(dwb, dx)));
+                    } else if (KIND == TSM_Q4_0) {
+                        acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(__fmul_rn(fa, dwa), dx));
+                        acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(__fmul_rn(fb, dwb), dx));
+                    } else {
+                        float sx = aux[c * kChunkBlocks + j];
+                        acc[i][e] = __fadd_rn(acc[i][e], __fadd_rn(__fmul_rn(__fmul_rn(dwa, dx), fa), __fmul_rn(mwa, sx)));
+                        acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fadd_rn(__fmul_rn(__fmul_rn(dwb, dx), fb), __fmul_rn(mwb, sx)));
                     }
                 }
             }
         }
         __syncthreads();
-        if (*abort_flag) break;
-        if (warp == 0) issue(chunk + kGemmStages);
     }
     if (*abort_flag) {
+        g_cp_async_wait<0>();
         if (tid == 0) {
             atomicExch(&p.errors->timeout, 1);
             for (int s = 0; s < kGemmStages; s++) g_mbar_wait(&full[s], 0), g_mbar_wait(&full[s], 1);
         }
         return;
     }
+    g_cp_async_wait<0>();
 #pragma unroll
     for (int i = 0; i < NT; i++)
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             int row = row0 + (e < 2 ? ra : rbw);
-            int col = col0 + 8 * i + 2 * t + (e & 1);
+            int col = cta_col0 + lcol0 + 8 * i + 2 * t + (e & 1);
             if (row < p.n && col < p.m) {
                 float v = acc[i][e];
                 if (p.bias) v = __fadd_rn(v, p.bias[row]);
@@ -249,8 +276,10 @@ __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) 
 
 template <int KIND, int NT, int WR, int WC>
 int launch_shape(tsm_ctx* ctx, const GemmParams& p) {
-    constexpr int ROWS = 16 * WR, PITCH = (32 / WR) * GFmt<KIND>::B + 32, THREADS = 32 * WR * WC;
-    size_t smem = 128 + (size_t)kGemmStages * ROWS * PITCH;
+    constexpr int B = GFmt<KIND>::B;
+    constexpr int ROWS = 16 * WR, COLS = 8 * NT * WC, THREADS = 32 * WR * WC;
+    constexpr int WP = kChunkBlocks * B + (KIND == TSM_Q4_1 ? 48 : 32), AP = kChunkBlocks * 32 + 16;
+    size_t smem = 128 + (size_t)kGemmStages * (ROWS * WP + COLS * AP + 2 * COLS * kChunkBlocks * 4);
     auto kernel = matmul_mma_kernel<KIND, NT, WR, WC>;
     if (smem > 48 * 1024) {
         static std::mutex lock;
@@ -262,19 +291,26 @@ int launch_shape(tsm_ctx* ctx, const GemmParams& p) {
             done[key] = true;
         }
     }
-    dim3 grid((p.n + ROWS - 1) / ROWS, (p.m + 8 * NT * WC - 1) / (8 * NT * WC));
+    dim3 grid((p.n + ROWS - 1) / ROWS, (p.m + COLS - 1) / COLS);
     kernel<<<grid, THREADS, smem, ctx->stream>>>(p);
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
 }
 
+template <int KIND, int NT>
+int launch_rows(tsm_ctx* ctx, const GemmParams& p) {
+    // taller CTAs re-read the activations less often; shorter ones keep every SM busy when n is small
+    if (p.n / 64 >= ctx->sm_count) return launch_shape<KIND, NT, 4, 2>(ctx, p);
+    if (p.n / 32 >= (ctx->sm_count * 2) / 3) return launch_shape<KIND, NT, 2, 2>(ctx, p);
+    return launch_shape<KIND, NT, 1, 2>(ctx, p);
+}
+
 template <int KIND>
 int launch_kind(tsm_ctx* ctx, const GemmParams& p) {
-    if (p.m <= 8) return launch_shape<KIND, 1, 4, 1>(ctx, p);
-    if (p.m <= 16) return launch_shape<KIND, 1, 2, 2>(ctx, p);
-    if (p.m <= 32) return launch_shape<KIND, 1, 1, 4>(ctx, p);
-    return launch_shape<KIND, 2, 1, 4>(ctx, p);
+    if (p.m <= 16) return launch_rows<KIND, 1>(ctx, p);
+    if (p.m <= 32) return launch_rows<KIND, 2>(ctx, p);
+    return launch_rows<KIND, 4>(ctx, p);
 }
 
 }  // namespace

@@ -30,7 +30,6 @@ template <> struct Fmt<TSM_Q4_1> { static constexpr int B = 20, G = 4, GB = 80, 
 
 constexpr int kComputeThreads = 128;
 constexpr int kThreads = 160;  // 4 compute warps + 1 fold/producer warp
-constexpr int kStages = 3;
 constexpr unsigned kWaitSpins = 4u << 20;
 
 struct MatvecParams {
@@ -41,6 +40,7 @@ struct MatvecParams {
     const float* residual;
     float* out;
     int rows_per_tile, num_tiles;
+    int cap, stages;    // groups a stage holds, stages in the ring
     unsigned nb_magic;  // floor(2^32 / nb) + 1: x / nb = umulhi(x, nb_magic) for the small x used here
     ErrorRecord* errors;
 };
@@ -95,8 +95,9 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = p.nb;
     const int act_bytes = (act_offset(nb) + 15) & ~15;
-    const int pcap = part_index(F::CAP * F::G) + 1;
-    uint64_t* full = (uint64_t*)smem;                        // kStages barriers
+    const int pcap = part_index(p.cap * F::G) + 1;
+    const int kStages = p.stages;
+    uint64_t* full = (uint64_t*)smem;                        // one barrier per stage
     int* abort_flag = (int*)(smem + 64);
     unsigned char* acts_q = smem + 128;                      // C x act_bytes
     float* acts_scale = (float*)(acts_q + C * act_bytes);    // C x nb
@@ -104,8 +105,8 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     float* parts = acts_aux + C * nb;                        // 2 x C x pcap
     size_t stage_off = (size_t)((unsigned char*)(parts + 2 * C * pcap) - smem);
     stage_off = (stage_off + 127) & ~(size_t)127;
-    unsigned char* stages = smem + stage_off;                // kStages x CAP x GB
-    constexpr int kStageBytes = F::CAP * F::GB;
+    unsigned char* stages = smem + stage_off;                // stages x cap x GB
+    const int kStageBytes = p.cap * F::GB;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -182,6 +183,21 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                     unsigned x = (unsigned)(kb_first + gi * F::G);
                     int kb = (int)(x - __umulhi(x, p.nb_magic) * (unsigned)nb);
                     float* dst = cur + gi * F::G + ((gi * F::G) >> 5);  // part_index(gi * G), then + j within the same 32
+                    // the group's activation scales (and totals or sums) in 16-byte loads when the group lies in one row
+                    float dxs[C][F::G], auxs[C][F::G];
+                    if (ALIGNED) {
+#pragma unroll
+                        for (int c = 0; c < C; c++)
+#pragma unroll
+                            for (int v4 = 0; v4 < F::G / 4; v4++) {
+                                float4 d4 = *(const float4*)(acts_scale + c * nb + kb + 4 * v4);
+                                dxs[c][4 * v4] = d4.x, dxs[c][4 * v4 + 1] = d4.y, dxs[c][4 * v4 + 2] = d4.z, dxs[c][4 * v4 + 3] = d4.w;
+                                if (KIND != TSM_Q8_0) {
+                                    float4 a4 = *(const float4*)(acts_aux + c * nb + kb + 4 * v4);
+                                    auxs[c][4 * v4] = a4.x, auxs[c][4 * v4 + 1] = a4.y, auxs[c][4 * v4 + 2] = a4.z, auxs[c][4 * v4 + 3] = a4.w;
+                                }
+                            }
+                    }
 #pragma unroll
                     for (int j = 0; j < F::G; j++) {
                         int kbj = kb + j;
@@ -247,15 +263,15 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                                 high = dp4a_us(q[7], (int)a1.w, high);
                                 total = low + (high >> 4);
                             }
-                            float dx = acts_scale[c * nb + kbj];
+                            float dx = ALIGNED ? dxs[c][j] : acts_scale[c * nb + kbj];
                             float contribution;
                             if (KIND == TSM_Q8_0) {
                                 contribution = __fmul_rn((float)total, __fmul_rn(dw, dx));
                             } else if (KIND == TSM_Q4_0) {
-                                int xt = ((const int*)acts_aux)[c * nb + kbj];
+                                int xt = ALIGNED ? __float_as_int(auxs[c][j]) : ((const int*)acts_aux)[c * nb + kbj];
                                 contribution = __fmul_rn(__fmul_rn((float)(total - 8 * xt), dw), dx);
                             } else {
-                                float sx = acts_aux[c * nb + kbj];
+                                float sx = ALIGNED ? auxs[c][j] : acts_aux[c * nb + kbj];
                                 contribution = __fadd_rn(__fmul_rn(__fmul_rn(dw, dx), (float)total), __fmul_rn(mw, sx));
                             }
                             dst[c * pcap + j] = contribution;
@@ -275,11 +291,13 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                 int b = 0;
                 for (; b + 8 <= nb; b += 8) {
                     float v[C][8];
+                    // when rows hold a multiple of 8 blocks, 8 consecutive blocks never straddle a pad word
+                    const float* src = old + part_index(at + b);
 #pragma unroll
                     for (int u = 0; u < 8; u++) {
                         int idx = part_index(at + b + u);
 #pragma unroll
-                        for (int c = 0; c < C; c++) v[c][u] = old[c * pcap + idx];
+                        for (int c = 0; c < C; c++) v[c][u] = ALIGNED ? src[c * pcap + u] : old[c * pcap + idx];
                     }
 #pragma unroll
                     for (int u = 0; u < 8; u++)
@@ -379,13 +397,13 @@ __global__ void matvec_generic_kernel(const uint8_t* __restrict__ w, int n, int 
 // ---- host side -----------------------------------------------------------------------------------
 
 template <int KIND, int C>
-static size_t stream_smem_bytes(int nb) {
+static size_t stream_smem_bytes(int nb, int cap, int stages) {
     using F = Fmt<KIND>;
     size_t act_bytes = (size_t)((act_offset(nb) + 15) & ~15);
-    size_t pcap = (size_t)(F::CAP * F::G + (F::CAP * F::G >> 5) + 1);
+    size_t pcap = (size_t)(part_index(cap * F::G) + 1);
     size_t bytes = 128 + C * act_bytes + (size_t)2 * C * nb * 4 + 2 * C * pcap * 4;
     bytes = (bytes + 127) & ~(size_t)127;
-    return bytes + (size_t)kStages * F::CAP * F::GB;
+    return bytes + (size_t)stages * cap * F::GB;
 }
 
 template <int KIND, int C>
@@ -395,11 +413,16 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     *taken = false;
     int nb = k / 32;
     if (((uintptr_t)w & 15) != 0 || ((int64_t)n * nb) % F::G != 0 || ((uintptr_t)a.qs & 15) != 0) return TSM_OK;
-    int max_rows = ((F::CAP - 2) * F::G) / nb;
-    if (max_rows < 1) return TSM_OK;
-    size_t smem = stream_smem_bytes<KIND, C>(nb);
-    if (smem > 200 * 1024) return TSM_OK;
     if (nb < F::G) return TSM_OK;  // rows shorter than a group: the generic kernel takes them
+    // A stage holds `cap` groups.  Short rows: 128 groups (one per compute thread) in a ring of 3.  Long rows:
+    // 256 groups in a ring of 2, so that a tile still holds several rows for the fold warp to fold side by side.
+    int per_thread = F::CAP / 128;  // groups per thread of the small configuration (Q4_1's groups are half as large)
+    bool long_rows = nb / F::G > 32 * per_thread;
+    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = long_rows ? 2 : 3;
+    int max_rows = ((cap - 2) * F::G) / nb;
+    if (max_rows < 1) return TSM_OK;
+    size_t smem = stream_smem_bytes<KIND, C>(nb, cap, stages);
+    if (smem > 200 * 1024) return TSM_OK;
     bool aligned = nb % F::G == 0;
     auto kernel = aligned ? matvec_stream_kernel<KIND, C, true> : matvec_stream_kernel<KIND, C, false>;
     static std::mutex attr_lock;  // the attribute is per device and per function
@@ -408,7 +431,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
         std::lock_guard<std::mutex> guard(attr_lock);
         auto key = std::make_pair(ctx->ordinal, (const void*)kernel);
         auto found = attr_set.find(key);
-        if (found == attr_set.end() || found->second < smem) {
+        if (found == attr_set.end()) {
             TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             attr_set[key] = 200 * 1024;
         }
@@ -428,6 +451,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     MatvecParams p;
     p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
+    p.cap = cap, p.stages = stages;
     p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
     kernel<<<grid, kThreads, smem, ctx->stream>>>(p);
     count_launch(ctx);
