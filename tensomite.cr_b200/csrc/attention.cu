@@ -14,6 +14,7 @@
 //   independent chains in parallel (positions for scores, columns for outputs), which gives the host's
 //   bits.
 #include <math.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -296,10 +297,8 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
     constexpr int PITCH = WIDTH + 4;            // floats per staged key row
     constexpr int CHUNKS = WIDTH / 4;           // 16-byte pieces per key row
-    constexpr int COLS = THREADS / WIDTH;       // column groups in the output phase
-    constexpr int HPT = (G + COLS - 1) / COLS;  // heads per thread in the output phase
     constexpr int WARPS = THREADS / 32;
-    static_assert(THREADS / GS >= TP && THREADS % GS == 0 && THREADS % WIDTH == 0, "thread mapping");
+    static_assert(THREADS / GS >= TP && THREADS % GS == 0 && THREADS >= WIDTH, "thread mapping");
     extern __shared__ __align__(16) float sh[];
     float* qs = sh;                         // [GS][PITCH]
     float* kt = qs + GS * PITCH;            // [STAGES][TP][PITCH]
@@ -325,18 +324,24 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
         qs[(i / WIDTH) * PITCH + i % WIDTH] = q[(int64_t)token * q_stride + (int64_t)head0 * WIDTH + i];
 
     const int tiles = (len + TP - 1) / TP;
-    auto load_tile = [&](int tile) {  // always commits a group, so that group t is tile t
+    // Tile loads: thread tid always copies 16-byte piece (tid % CHUNKS) of rows (tid / CHUNKS) + n * (THREADS / CHUNKS),
+    // so the addresses are a fixed base plus a constant stride.
+    constexpr int RPP = THREADS / CHUNKS;  // rows covered by one pass of all threads
+    static_assert(THREADS % CHUNKS == 0 && TP % RPP == 0, "tile load mapping");
+    const int lrow = tid / CHUNKS, lpiece = tid % CHUNKS;
+    auto load_rows = [&](const float* src, int tile) {  // always commits a group, so that group t is tile t
         if (tile < tiles) {
             int p0 = tile * TP;
             int count = min(TP, len - p0);
-            float* dst = kt + (tile % STAGES) * TP * PITCH;
-            for (int i = tid; i < count * CHUNKS; i += THREADS) {
-                int p = i / CHUNKS, c = i % CHUNKS;
-                cp_async16(dst + p * PITCH + 4 * c, kb + (int64_t)(p0 + p) * WIDTH + 4 * c);
-            }
+            float* dst = kt + (tile % STAGES) * TP * PITCH + lrow * PITCH + 4 * lpiece;
+            const float* from = src + (int64_t)(p0 + lrow) * WIDTH + 4 * lpiece;
+#pragma unroll
+            for (int n = 0; n < TP / RPP; n++)
+                if (lrow + n * RPP < count) cp_async16(dst + n * RPP * PITCH, from + (int64_t)n * RPP * WIDTH);
         }
         cp_async_commit();
     };
+    auto load_tile = [&](int tile) { load_rows(kb, tile); };
 
     // ---- 1. scores ----
     const int sp = tid / GS, shd = tid % GS;  // this thread's position within a tile and its head
@@ -402,57 +407,56 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     __syncthreads();
     // ---- 3. outputs: values pass through the same ring of stages (rows unpadded reads are conflict-free:
     //         consecutive threads read consecutive columns) ----
-    const int col = tid % WIDTH, hg = tid / WIDTH;
-    const int h0 = hg * HPT;
-    auto load_values = [&](int tile) {
-        if (tile < tiles) {
-            int p0 = tile * TP;
-            int count = min(TP, len - p0);
-            float* dst = kt + (tile % STAGES) * TP * PITCH;
-            for (int i = tid; i < count * CHUNKS; i += THREADS) {
-                int p = i / CHUNKS, c = i % CHUNKS;
-                cp_async16(dst + p * PITCH + 4 * c, vb + (int64_t)(p0 + p) * WIDTH + 4 * c);
-            }
-        }
-        cp_async_commit();
-    };
-    float acc[HPT];
+    // One thread per column folds all G heads' chains (the weights of a position are one 16-byte broadcast
+    // load); the other threads only help to fetch.
+    const int col = tid;
+    const bool folds = tid < WIDTH;
+    auto load_values = [&](int tile) { load_rows(vb, tile); };
+    float acc[G];
 #pragma unroll
-    for (int i = 0; i < HPT; i++) acc[i] = 0.0f;
+    for (int i = 0; i < G; i++) acc[i] = 0.0f;
 #pragma unroll
     for (int t = 0; t < STAGES - 1; t++) load_values(t);
     for (int tile = 0; tile < tiles; tile++) {
         load_values(tile + STAGES - 1);
         cp_async_wait<STAGES - 1>();
         __syncthreads();
-        if (h0 < G) {
+        if (folds) {
             const float* vt = kt + (tile % STAGES) * TP * PITCH + col;
-            const float* wt = sc + (int64_t)tile * TP * GS + h0;
+            const float* wt = sc + (int64_t)tile * TP * GS;
             int count = min(TP, len - tile * TP);
             int p = 0;
-            for (; p + UNROLL <= count; p += UNROLL) {
-                float vv[UNROLL];
+            for (; p + 8 <= count; p += 8) {
+                float vv[8];
 #pragma unroll
-                for (int u = 0; u < UNROLL; u++) vv[u] = vt[(p + u) * PITCH];
+                for (int u = 0; u < 8; u++) vv[u] = vt[(p + u) * PITCH];
 #pragma unroll
-                for (int u = 0; u < UNROLL; u++)
+                for (int u = 0; u < 8; u++) {
+                    float w[GS];
+                    if (GS == 4) {
+                        float4 w4 = *(const float4*)(wt + (p + u) * 4);
+                        w[0] = w4.x, w[1] = w4.y, w[2] = w4.z, w[3] = w4.w;
+                    } else if (GS == 2) {
+                        float2 w2 = *(const float2*)(wt + (p + u) * 2);
+                        w[0] = w2.x, w[1] = w2.y;
+                    } else {
+                        w[0] = wt[p + u];
+                    }
 #pragma unroll
-                    for (int i = 0; i < HPT; i++)
-                        if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(wt[(p + u) * GS + i], vv[u]));
+                    for (int i = 0; i < G; i++) acc[i] = __fadd_rn(acc[i], __fmul_rn(w[i], vv[u]));
+                }
             }
             for (; p < count; p++) {
                 float vv = vt[p * PITCH];
 #pragma unroll
-                for (int i = 0; i < HPT; i++)
-                    if (h0 + i < G) acc[i] = __fadd_rn(acc[i], __fmul_rn(wt[p * GS + i], vv));
+                for (int i = 0; i < G; i++) acc[i] = __fadd_rn(acc[i], __fmul_rn(wt[p * GS + i], vv));
             }
         }
         __syncthreads();
     }
-    if (h0 < G) {
+    if (folds) {
 #pragma unroll
-        for (int i = 0; i < HPT; i++)
-            if (h0 + i < G) out[((int64_t)token * heads + head0 + h0 + i) * WIDTH + col] = acc[i];
+        for (int i = 0; i < G; i++) out[((int64_t)token * heads + head0 + i) * WIDTH + col] = acc[i];
     }
 }
 
@@ -532,11 +536,15 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         if (stages == 3) TSM_EXACT_ATTN(W, G, T, TP, 3, U); \
         else TSM_EXACT_ATTN(W, G, T, TP, 2, U);   \
     } while (0)
+                static const int alt = getenv("TSM_ATTN_CONFIG") ? atoi(getenv("TSM_ATTN_CONFIG")) : 0;  // 1: smaller CTAs, for timing variants
                 if (width == 64) {
                     if (g == 4) TSM_EXACT_STAGES(64, 4, 512, 128, 16);
                     else if (g == 3) TSM_EXACT_STAGES(64, 3, 512, 128, 16);
                     else if (g == 2) TSM_EXACT_STAGES(64, 2, 512, 128, 16);
                     else TSM_EXACT_STAGES(64, 1, 128, 64, 32);
+                } else if (alt == 1 && g == 4) {
+                    smem = ((size_t)gs * pitch + 2 * (size_t)32 * pitch + (size_t)capacity * gs) * 4;
+                    TSM_EXACT_ATTN(128, 4, 256, 32, 2, 16);
                 } else {
                     if (g == 4) TSM_EXACT_STAGES(128, 4, 512, 64, 16);
                     else if (g == 3) TSM_EXACT_STAGES(128, 3, 512, 64, 16);

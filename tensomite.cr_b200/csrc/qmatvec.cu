@@ -19,6 +19,8 @@
 // generic kernel (any row count, any alignment down to 2 bytes)
 //   One warp per output; lane l takes blocks l, l+32, ...; contributions are folded in block order
 //   through shuffles.  It is the fallback for shapes the streamed kernel does not take.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace tsm {
@@ -170,7 +172,10 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                 bool arrived = mbar_wait(&full[s], (unsigned)((it / kStages) & 1));
                 if (!arrived) *abort_flag = 1;
                 const unsigned char* stage = stages + (size_t)s * kStageBytes;
-                int kb_first = (int)((g0 * F::G) % nb);
+                // first activation block of the tile's first group: tiles start on a row, so the group that holds
+                // the row's block 0 starts (r0 * nb) mod G blocks earlier, i.e. inside the previous row
+                int lead = (int)(((int64_t)r0 * nb) & (F::G - 1));
+                int kb_first = ALIGNED || lead == 0 ? 0 : nb - lead;
                 for (int gi = tid; gi < groups && arrived; gi += kComputeThreads) {
                     unsigned W[F::WORDS];
                     const uint4* gp = (const uint4*)(stage + (size_t)gi * F::GB);
@@ -414,11 +419,17 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     int nb = k / 32;
     if (((uintptr_t)w & 15) != 0 || ((int64_t)n * nb) % F::G != 0 || ((uintptr_t)a.qs & 15) != 0) return TSM_OK;
     if (nb < F::G) return TSM_OK;  // rows shorter than a group: the generic kernel takes them
-    // A stage holds `cap` groups.  Short rows: 128 groups (one per compute thread) in a ring of 3.  Long rows:
-    // 256 groups in a ring of 2, so that a tile still holds several rows for the fold warp to fold side by side.
+    // A stage holds `cap` groups.  Short rows: 128 groups (one per compute thread).  Long rows: 256 groups, so
+    // that a tile still holds several rows for the fold warp to fold side by side.
     int per_thread = F::CAP / 128;  // groups per thread of the small configuration (Q4_1's groups are half as large)
     bool long_rows = nb / F::G > 32 * per_thread;
-    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = long_rows ? 2 : 3;
+    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = 2;  // two stages measured faster than three: more CTAs fit an SM
+    // TSM_MATVEC_CAP / TSM_MATVEC_STAGES override the tile size (in units of the format's default) and ring depth, so
+    // that variants can be timed without rebuilding (as TENSOMITE_BLOCK_MATMUL does in the reference, quant.cr:36-41)
+    static const int env_cap = getenv("TSM_MATVEC_CAP") ? atoi(getenv("TSM_MATVEC_CAP")) : 0;
+    static const int env_stages = getenv("TSM_MATVEC_STAGES") ? atoi(getenv("TSM_MATVEC_STAGES")) : 0;
+    if (env_cap > 0 && !long_rows) cap = F::CAP * env_cap / 4;  // quarters of the default
+    if (env_stages >= 1 && env_stages <= 4) stages = env_stages;
     int max_rows = ((cap - 2) * F::G) / nb;
     if (max_rows < 1) return TSM_OK;
     size_t smem = stream_smem_bytes<KIND, C>(nb, cap, stages);
