@@ -106,6 +106,17 @@ int tsm_block_matmul(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride
 int tsm_block_matmul_quantized(tsm_ctx* ctx, tsm_dptr scales, tsm_dptr sums, tsm_dptr qs, int rows, int k, tsm_dptr w,
                                int kind, int n, tsm_dptr bias, tsm_dptr out);
 
+/* tsm_block_matmul without any allocation (no counterpart in the reference, whose CUDA device allocates its
+ * scratch from a pool on demand, cuda.cr:791-798).  For callers that cannot allocate device memory while they
+ * run: latency-bound serving threads (cudaMalloc can take milliseconds and synchronise the device) and processes
+ * whose device memory is handed out once at start-up.  The 8-bit activations are quantised into a fixed array inside the library
+ * (1.5 MB per GPU that loads it, held until the process ends), so rows * k may be at most 1,048,576; larger
+ * products are refused with TSM_ERR_ARG.  The first call on a device looks the array's address up, so make that
+ * call before starting any stream capture.  Every call uses the same array, which keeps whatever the last call
+ * left there: two calls whose kernels overlap on the GPU (different contexts or streams of one device) race. */
+int tsm_block_matmul_static(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride, tsm_dptr w, int kind, int n,
+                            tsm_dptr bias, tsm_dptr out);
+
 /* Op::Gather on a block table (gather_blocks_f32, kernels.cu:1172-1185; Quant.gather, quant.cr:417-422):
  * out[count,width] = dequantised rows ids[i] of table[table_rows,width]; a bad id is recorded, its row zeroed. */
 int tsm_gather_blocks(tsm_ctx* ctx, tsm_dptr table, int kind, int table_rows, int width, tsm_dptr ids, int count,

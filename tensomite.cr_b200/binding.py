@@ -233,6 +233,25 @@ class B200:
                 b.free()
         return result
 
+    def block_matmul_static(self, x, w, kind, n, bias=None):
+        """As block_matmul, through tsm_block_matmul_static: the product's scratch is a fixed array in the library."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, k = x.shape
+        xb = self.tensor(x)
+        bb = self.tensor(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+        out = self.alloc(max(rows * n * 4, 1))
+        try:
+            self.check(self.lib.tsm_block_matmul_static(self.ctx, C.c_uint64(xb.ptr), C.c_int(rows), C.c_int(k), C.c_int64(k),
+                                                        C.c_uint64(w.ptr), C.c_int(kind), C.c_int(n),
+                                                        C.c_uint64(bb.ptr if bb else 0), C.c_uint64(out.ptr)),
+                       "tsm_block_matmul_static")
+            self.sync()
+            return out.numpy(np.float32)[:rows * n].reshape(rows, n)
+        finally:
+            for b in (xb, bb, out):
+                if b:
+                    b.free()
+
     def gather_blocks(self, table, kind, table_rows, width, ids):
         ids = np.ascontiguousarray(ids, dtype=np.int32)
         idb = self.tensor(ids)
