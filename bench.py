@@ -201,35 +201,102 @@ def matvec_sweep(pkg, dev, torch, stream, peak):
     return out
 
 
+def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
+    """One kernel on a small case, a few launches, for a profiler capture or a timing alone:
+         matvec,<kind>,<n>,<k>             batch-1 product over already-quantised activations
+         product,<kind>,<n>,<k>,<rows>     quantiser + batched product
+         attention,<tokens>,<heads>,<kv_heads>,<width>,<capacity>   ragged lengths 128..capacity-128 (seed 11)
+       Returns the JSON record (microseconds per launch, GB/s of algorithmic bytes)."""
+    import ctypes as C
+    parts = spec.split(",")
+    what = parts[0]
+    if what in ("matvec", "product"):
+        kind = KIND[parts[1].upper()]
+        n, k = int(parts[2]), int(parts[3])
+        rows = int(parts[4]) if what == "product" else 1
+        blocks = n * (k // 32)
+        wbuf = dev.alloc(blocks * BLOCK[kind])
+        src = dev.alloc(min(n, 4096) * k * 4)
+        for r0 in range(0, n, 4096):
+            r = min(4096, n - r0)
+            dev.check(dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(src.ptr), C.c_int64(r * k), C.c_float(0.0), C.c_float(0.02),
+                                              C.c_uint64(n * 31 + r0)), "tsm_fill_normal")
+            dev.check(dev.lib.tsm_quantize_blocks(dev.ctx, C.c_uint64(src.ptr), C.c_int64(r * k), C.c_int(kind),
+                                                  C.c_uint64(wbuf.ptr + r0 * (k // 32) * BLOCK[kind])), "tsm_quantize_blocks")
+        x = dev.tensor(np.random.default_rng(5).normal(0, 1, (rows, k)).astype(np.float32))
+        y = dev.alloc(rows * n * 4)
+        algorithmic = blocks * BLOCK[kind] + rows * k * 4 + rows * n * 4
+        if what == "matvec":
+            scales, sums, qs = dev.alloc(k // 32 * 4), dev.alloc(k // 32 * 4), dev.alloc(k)
+            dev.check(dev.lib.tsm_quantize_rows_q8(dev.ctx, C.c_uint64(x.ptr), 1, k, C.c_int64(k), C.c_uint64(scales.ptr),
+                                                   C.c_uint64(sums.ptr), C.c_uint64(qs.ptr)), "tsm_quantize_rows_q8")
+
+            def run():
+                dev.lib.tsm_block_matmul_quantized(dev.ctx, C.c_uint64(scales.ptr), C.c_uint64(sums.ptr), C.c_uint64(qs.ptr), 1, k,
+                                                   C.c_uint64(wbuf.ptr), kind, n, C.c_uint64(0), C.c_uint64(y.ptr))
+        else:
+            def run():
+                dev.lib.tsm_block_matmul(dev.ctx, C.c_uint64(x.ptr), rows, k, C.c_int64(k), C.c_uint64(wbuf.ptr), kind, n,
+                                         C.c_uint64(0), C.c_uint64(y.ptr))
+    elif what == "attention":
+        tokens, H, KV, W, cap = (int(v) for v in parts[1:6])
+        count = tokens * KV * cap * W
+        kb, vb = dev.alloc(count * 4), dev.alloc(count * 4)
+        for b, seed in ((kb, 1), (vb, 2)):
+            dev.check(dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(b.ptr), C.c_int64(count), C.c_float(0.0), C.c_float(1.0),
+                                              C.c_uint64(seed)), "tsm_fill_normal")
+        lengths = np.random.default_rng(11).integers(128, cap - 127, size=tokens)
+        table = dev.tensor(np.stack([np.arange(tokens), lengths, lengths + 1], 1).astype(np.int32))
+        q = dev.tensor(np.random.default_rng(3).normal(0, 1, (tokens, H * W)).astype(np.float32))
+        o = dev.alloc(tokens * H * W * 4)
+        algorithmic = int(sum(2 * KV * W * 4 * (int(n) + 1) for n in lengths)) + 2 * tokens * H * W * 4
+
+        def run():
+            dev.lib.tsm_ragged_attention(dev.ctx, C.c_uint64(q.ptr), C.c_int64(H * W), tokens, H, W, C.c_uint64(kb.ptr),
+                                         C.c_uint64(vb.ptr), tokens, KV, cap, C.c_uint64(table.ptr), C.c_float(1.0 / np.sqrt(W)),
+                                         C.c_uint64(o.ptr))
+    else:
+        raise SystemExit(f"unknown case {spec!r}")
+    dev.sync()
+    seconds = time_kernel(torch, stream, run, repeats)
+    dev.sync()
+    return dict(case=spec, launches=repeats + 1, us=seconds * 1e6, algorithmic_bytes=algorithmic, gbs=algorithmic / seconds / 1e9,
+                frac=algorithmic / seconds / 1e9 / peak)
+
+
 def oracle_model_from_device(model, threads):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from tests import helpers
     return helpers.oracle_from_device_model(model, threads=threads)
 
 
-def cpu_sample(pkg, model, cache, w, lengths, ids, threads, sample_rows, sample_steps):
-    """Times the CPU oracle's threaded decode on the first `sample_rows` streams for `sample_steps` steps."""
-    ref = oracle_model_from_device(model, threads)
-    rcache = ref.new_cache(sample_rows, int(max(lengths[:sample_rows])) + sample_steps + 1)
-    c = model.config
-    for layer in range(c["layers"]):
-        kb, vb = cache.layer(layer)
+class CpuArm:
+    """The CPU oracle's threaded decode over the first `sample_rows` streams of the device workload: same
+    weights (downloaded once through the C ABI), same KV contents, same first tokens."""
+
+    def __init__(self, pkg, model, cache, lengths, ids, threads, sample_rows, budget_steps):
+        self.ref = oracle_model_from_device(model, threads)
+        self.rows = sample_rows
+        self.rcache = self.ref.new_cache(sample_rows, int(max(lengths[:sample_rows])) + budget_steps + 2)
+        c = model.config
         row_floats = c["kv_heads"] * cache.capacity * c["head_width"]
+        for layer in range(c["layers"]):
+            kb, vb = cache.layer(layer)
+            for row in range(sample_rows):
+                n = int(lengths[row])
+                for src, dst in ((kb, self.rcache.keys[layer]), (vb, self.rcache.values[layer])):
+                    part = pkg.Buffer(model.device, src.ptr + row * row_floats * 4, row_floats * 4).numpy(np.float32)
+                    dst[row, :, :n, :] = part.reshape(c["kv_heads"], cache.capacity, c["head_width"])[:, :n, :]
         for row in range(sample_rows):
-            n = int(lengths[row])
-            for src, dst in ((kb, rcache.keys[layer]), (vb, rcache.values[layer])):
-                part = pkg.Buffer(model.device, src.ptr + row * row_floats * 4, row_floats * 4).numpy(np.float32)
-                dst[row, :, :n, :] = part.reshape(c["kv_heads"], cache.capacity, c["head_width"])[:, :n, :]
-    for row in range(sample_rows):
-        rcache.lengths[row] = int(lengths[row])
-    tokens = [int(t) for t in ids[:sample_rows]]
-    ref.forward(rcache, [[t] for t in tokens])  # warm-up (threads start, pages touched)
-    start = time.perf_counter()
-    for _ in range(sample_steps):
-        logits = ref.forward(rcache, [[t] for t in tokens])
-        tokens = [int(np.argmax(r)) for r in logits]
-    seconds = time.perf_counter() - start
-    return sample_rows * sample_steps / seconds, seconds
+            self.rcache.lengths[row] = int(lengths[row])
+        self.tokens = [int(t) for t in ids[:sample_rows]]
+
+    def step(self):
+        """One greedy decode step of the sample's streams; returns seconds."""
+        start = time.perf_counter()
+        logits = self.ref.forward(self.rcache, [[t] for t in self.tokens])
+        self.tokens = [int(np.argmax(r)) for r in logits]
+        return time.perf_counter() - start
 
 
 def main():
@@ -241,6 +308,8 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 model and the matvec sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--case", default=None, help="time one kernel on a small case instead (see kernel_case), e.g. matvec,q4_0,128256,4096")
+    ap.add_argument("--repeats", type=int, default=3, help="timed launches of --case")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -261,6 +330,10 @@ def main():
     dev = pkg.B200(local)
     stream = torch.cuda.ExternalStream(dev.stream, device=local)
     peak, peak_kind = peaks()
+    if args.case:
+        print(json.dumps(kernel_case(pkg, dev, torch, stream, args.case, args.repeats, peak["hbm_gbs"])))
+        dev.close()
+        return
     lengths = draw_lengths(w, rank)
     model = pkg.Model.random(dev, model_config(w), KIND[w["kind"]], seed=20260101)
     dev.sync()
@@ -273,13 +346,10 @@ def main():
         sample_rows, sample_steps = min(rows, 2), 1
         cache, ids = make_streams(pkg, dev, model, w, lengths, 8 + K + W, rank)
         dev.sync()
-        rates = []
-        for i in range(W + K):
-            rate, seconds = cpu_sample(pkg, model, cache, w, lengths, ids, threads, sample_rows, sample_steps)
-            if i >= W:
-                rates.append((rate, seconds))
-        value = float(np.mean([r for r, _ in rates]))
-        ms = float(np.mean([s for _, s in rates])) * 1e3
+        arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, W + K)
+        times = [arm.step() for _ in range(W + K)][W:]
+        value = sample_rows * len(times) / float(np.sum(times))
+        ms = float(np.mean(times)) * 1e3
         sample = f"{sample_rows} of {rows} streams x {sample_steps} decode step per bench step, all {threads} host threads"
         print(json.dumps(dict(metric="decode_tokens_per_second", value=value, unit="tokens/s", n_gpus=args.gpus, steps=K, warmup=W,
                               ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8 x int8 -> int32 blocks, f32 accumulate",
@@ -375,7 +445,7 @@ def main():
         up_bytes = n * (k // 32) * BLOCK[kind] + rows * k * 4 + rows * n * 4
         L = c["layers"]
         attn_share, up_share = attn_s * L, up_s * L
-        kernels = [dict(kernel="attention_chunk_kernel+merge (one layer)", bytes=attn_bytes, us=attn_s * 1e6, gbs=attn_bytes / attn_s / 1e9,
+        kernels = [dict(kernel="attention_exact_kernel (one layer, 64 ragged streams)", bytes=attn_bytes, us=attn_s * 1e6, gbs=attn_bytes / attn_s / 1e9,
                         share_of_step=attn_share / (seconds / K)),
                    dict(kernel=f"block product {n}x{k} {w['kind']} rows={rows} (+quantiser)", bytes=up_bytes, us=up_s * 1e6,
                         gbs=up_bytes / up_s / 1e9, share_of_step=up_share / (seconds / K))]
@@ -391,7 +461,10 @@ def main():
             refill(cache, lengths, rank)
             dev.sync()
             sample_rows, sample_steps = min(rows, 4), 2
-            rate, cpu_seconds = cpu_sample(pkg, model, cache, w, lengths, ids, threads, sample_rows, sample_steps)
+            arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, sample_steps + 1)
+            arm.step()  # warm-up: threads start, pages are touched
+            cpu_seconds = sum(arm.step() for _ in range(sample_steps))
+            rate = sample_rows * sample_steps / cpu_seconds
             line["cpu_baseline"] = dict(value=rate, unit="tokens/s", cores=threads, kind="port",
                                         sample=f"{sample_rows} of {rows} streams x {sample_steps} decode steps, {cpu_seconds:.1f} s, "
                                                f"oracle's threaded product on {threads} threads, other host ops on one thread")

@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
                                                                   const float* __restrict__ k, const float* __restrict__ v,
                                                                   int rows, int kv_heads, int capacity,
                                                                   const int* __restrict__ table, float scale, float* out,
-                                                                  ErrorRecord* errors) {
+                                                                  ErrorRecord* errors, const int* __restrict__ order) {
     constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
     constexpr int PITCH = WIDTH + 4;            // floats per staged key row
     constexpr int CHUNKS = WIDTH / 4;           // 16-byte pieces per key row
@@ -306,7 +306,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     __shared__ float wred[WARPS][4];
     __shared__ float totals[4];
 
-    const int token = blockIdx.y;
+    const int token = order ? order[blockIdx.y] : blockIdx.y;  // longest tokens first when an order is given
     const int per_kv = heads / kv_heads, groups_per_kv = per_kv / G;
     const int kvh = blockIdx.x / groups_per_kv;
     const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
@@ -460,6 +460,27 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     }
 }
 
+// Ranks tokens by visible positions, most first: with one long-running CTA per (token, kv group) and ragged
+// lengths, starting the longest first keeps the last wave short.
+__global__ void length_order_kernel(const int* __restrict__ table, int tokens, int* order) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= tokens) return;
+    int mine = table[3 * t + 1], rank = 0;
+    for (int u = 0; u < tokens; u++) {
+        int other = table[3 * u + 1];
+        rank += (other > mine || (other == mine && u < t)) ? 1 : 0;
+    }
+    order[rank] = t;
+}
+
+int launch_length_order(tsm_ctx* ctx, const int* table, int tokens, int* order) {
+    if (tokens == 0) return TSM_OK;
+    length_order_kernel<<<(tokens + 255) / 256, 256, 0, ctx->stream>>>(table, tokens, order);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
 // ---- host side -----------------------------------------------------------------------------------
 
 int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity) {
@@ -501,7 +522,7 @@ static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int token
 
 int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
                      const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
-                     const QuantizedActs* quantized) {
+                     const QuantizedActs* quantized, const int* order) {
     if (kv_heads <= 0 || heads % kv_heads != 0)
         return fail(ctx, TSM_ERR_ARG, std::to_string(heads) + " query heads do not group into " + std::to_string(kv_heads) + " key and value heads");
     if (tokens == 0) return TSM_OK;
@@ -529,20 +550,22 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         auto kernel = attention_exact_kernel<W, G, T, TP, S, U>;                                                          \
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
         kernel<<<grid, T, smem, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, out,      \
-                                               ctx->errors);                                                              \
+                                               ctx->errors, order);                                                       \
     } while (0)
 #define TSM_EXACT_STAGES(W, G, T, TP, U)          \
     do {                                          \
         if (stages == 3) TSM_EXACT_ATTN(W, G, T, TP, 3, U); \
         else TSM_EXACT_ATTN(W, G, T, TP, 2, U);   \
     } while (0)
-                static const int alt = getenv("TSM_ATTN_CONFIG") ? atoi(getenv("TSM_ATTN_CONFIG")) : 0;  // 1: smaller CTAs, for timing variants
+                static const bool one_cta = getenv("TSM_ATTN_ONE_CTA") != nullptr;  // the 512-thread shape everywhere, for timing it
                 if (width == 64) {
                     if (g == 4) TSM_EXACT_STAGES(64, 4, 512, 128, 16);
                     else if (g == 3) TSM_EXACT_STAGES(64, 3, 512, 128, 16);
                     else if (g == 2) TSM_EXACT_STAGES(64, 2, 512, 128, 16);
                     else TSM_EXACT_STAGES(64, 1, 128, 64, 32);
-                } else if (alt == 1 && g == 4) {
+                } else if (!one_cta && g == 4 && ((size_t)gs * pitch + 2 * (size_t)32 * pitch + (size_t)capacity * gs) * 4 <= 110 * 1024) {
+                    // two CTAs of 256 threads per SM overlap one's serial phases with the other's streaming: measured
+                    // faster than one CTA of 512 threads with a deeper ring
                     smem = ((size_t)gs * pitch + 2 * (size_t)32 * pitch + (size_t)capacity * gs) * 4;
                     TSM_EXACT_ATTN(128, 4, 256, 32, 2, 16);
                 } else {

@@ -49,6 +49,7 @@ struct tsm_ctx {
     tsm::ErrorRecord* errors_host = nullptr;  // pinned
     tsm::Scratch quant;                       // activation quantiser output for tsm_block_matmul
     tsm::Scratch attn;                        // split-K partials
+    tsm::Scratch order;                       // attention's longest-first token order (operator-level calls)
     uint64_t scratch_generation = 1;          // bumped whenever a scratch buffer moves
     std::mutex message_lock;
     std::string message;
@@ -132,7 +133,10 @@ int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_h
                        int capacity);
 int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
                      const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
-                     const QuantizedActs* quantized);
+                     const QuantizedActs* quantized, const int* order = nullptr);
+// order[r] = the token with the r-th most visible positions (ties by index), so that attention can start its
+// longest tokens first; null means token order.
+int launch_length_order(tsm_ctx* ctx, const int* table, int tokens, int* order);
 int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity);
 int launch_swiglu(tsm_ctx* ctx, const float* gate, const float* up, int rows, int n, int64_t in_stride, float* out,
                   const QuantizedActs* quantized);

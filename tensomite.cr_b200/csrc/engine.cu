@@ -37,6 +37,7 @@ struct Workspace {
     int* ids = nullptr;      // [T]
     int* table = nullptr;    // [T,3] row, position, positions held
     int* last = nullptr;     // [T] indices of the rows whose logits are wanted
+    int* order = nullptr;    // [T] tokens by visible positions, most first (attention's launch order)
     float* x = nullptr;      // [T, width]
     float* xl = nullptr;     // [T, width] gathered last rows
     float* qkv = nullptr;    // [T, (heads + 2 kv) * hw]
@@ -536,7 +537,7 @@ static int build_random(tsm_model* m, int kind, uint64_t seed) {
 
 static void free_workspace(tsm_model* m) {
     Workspace& w = m->ws;
-    void* bufs[] = {w.ids, w.table, w.last, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc};
+    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc};
     for (void* b : bufs) pool_release(m->ctx, b);
     if (w.host) cudaFreeHost(w.host);
     w = Workspace{};
@@ -555,6 +556,7 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.ids));
     TSM_TRY(pool_alloc(ctx, T * 12, (void**)&w.table));
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.last));
+    TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.order));
     TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.x));
     TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.xl));
     TSM_TRY(pool_alloc(ctx, T * (qn + 2 * kvn) * 4, (void**)&w.qkv));
@@ -596,6 +598,11 @@ static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, b
         if (m->wpe.kind != m->embed.kind) return fail(ctx, TSM_ERR_UNSUPPORTED, "token and position tables must share a format");
         TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, m->wpe.w, w.table + 1, 3));
     }
+    const int* order = nullptr;
+    if (total > 1 && total <= 4096) {  // the same order serves every layer of the step
+        TSM_TRY(launch_length_order(ctx, w.table, total, w.order));
+        order = w.order;
+    }
     for (int i = 0; i < c.layers; i++) {
         Layer& l = m->layers[i];
         if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
@@ -605,7 +612,7 @@ static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, b
                                    c.arch == 0 ? m->rope_sin : nullptr, c.context, w.table, cache->keys[i], cache->values[i],
                                    cache->rows, cache->capacity));
         TSM_TRY(launch_attention(ctx, w.qkv, qkvn, total, c.heads, hw, cache->keys[i], cache->values[i], cache->rows, c.kv_heads,
-                                 cache->capacity, w.table, scale, ordered ? w.att : nullptr, &qb));
+                                 cache->capacity, w.table, scale, ordered ? w.att : nullptr, &qb, order));
         TSM_TRY(product(m, qb, total, l.o, w.x, w.x));
         if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
         else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));

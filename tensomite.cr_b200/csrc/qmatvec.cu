@@ -151,7 +151,14 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
         }
         for (int i = tid; i < nb; i += kThreads) {
             acts_scale[c * nb + i] = p.acts.scales[(int64_t)c * nb + i];
-            if (KIND == TSM_Q4_0) ((int*)acts_aux)[c * nb + i] = p.acts.totals[(int64_t)c * nb + i];
+            if (KIND == TSM_Q4_0) {
+                // the block's integer sum of quantised activations, for the -8 offset of Q4_0's nibbles
+                const int* words = (const int*)(p.acts.qs + ((int64_t)c * nb + i) * 32);
+                int total = 0;
+#pragma unroll
+                for (int u = 0; u < 8; u++) total = __dp4a(0x01010101, words[u], total);
+                ((int*)acts_aux)[c * nb + i] = total;
+            }
             if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = p.acts.sums[(int64_t)c * nb + i];
         }
     }
@@ -378,7 +385,9 @@ __global__ void matvec_generic_kernel(const uint8_t* __restrict__ w, int n, int 
                         total = __dp4a((int)((word >> 4) & 0x0f0f0f0fu), a[4 + i], total);
                     }
                     if (KIND == TSM_Q4_0) {
-                        int xt = acts.totals[(int64_t)row * nb + block];
+                        int xt = 0;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) xt = __dp4a(0x01010101, a[i], xt);
                         contribution = __fmul_rn(__fmul_rn((float)(total - 8 * xt), dw), dx);
                     } else {
                         float mw = half_bits_to_float(*(const unsigned short*)(blk + 2));

@@ -172,6 +172,7 @@ int tsm_ctx_destroy(tsm_ctx* ctx) {
     for (auto& entry : ctx->pool.sizes) cudaFree(entry.first);
     if (ctx->quant.ptr) cudaFree(ctx->quant.ptr);
     if (ctx->attn.ptr) cudaFree(ctx->attn.ptr);
+    if (ctx->order.ptr) cudaFree(ctx->order.ptr);
     cudaFree(ctx->errors);
     cudaFreeHost(ctx->errors_host);
     cudaStreamDestroy(ctx->stream);
@@ -301,29 +302,14 @@ int tsm_block_matmul(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride
     return launch_block_matmul(ctx, a, rows, k, PCB(w), kind, n, PCF(bias), nullptr, PF(out));
 }
 
-// Integer totals of already-quantised rows, for callers that quantised through tsm_quantize_rows_q8.
-__global__ void block_totals_kernel(const int8_t* __restrict__ qs, int64_t blocks, int* totals) {
-    int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= blocks) return;
-    const int* words = (const int*)(qs + b * 32);
-    int total = 0;
-#pragma unroll
-    for (int i = 0; i < 8; i++) total = __dp4a(0x01010101, words[i], total);
-    totals[b] = total;
-}
-
 int tsm_block_matmul_quantized(tsm_ctx* ctx, tsm_dptr scales, tsm_dptr sums, tsm_dptr qs, int rows, int k, tsm_dptr w, int kind,
                                int n, tsm_dptr bias, tsm_dptr out) {
     CTX_GUARD(ctx);
     if (k <= 0 || k % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
     if (rows == 0 || n == 0) return TSM_OK;
     if ((qs & 3) != 0) return fail(ctx, TSM_ERR_ARG, "quantised activations must be 4-byte aligned");
-    int64_t blocks = (int64_t)rows * (k / 32);
-    TSM_TRY(ensure_scratch(ctx, ctx->quant, blocks * 4 + 256));
-    block_totals_kernel<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>((const int8_t*)(uintptr_t)qs, blocks, (int*)ctx->quant.ptr);
-    count_launch(ctx);
-    TSM_LAUNCH_CHECK(ctx);
-    QuantizedActs a{PCF(scales), PCF(sums), (const int*)ctx->quant.ptr, (const int8_t*)(uintptr_t)qs};
+    // the products take the blocks' integer sums from the quantised values themselves, so none are passed
+    QuantizedActs a{PCF(scales), PCF(sums), nullptr, (const int8_t*)(uintptr_t)qs};
     return launch_block_matmul(ctx, a, rows, k, PCB(w), kind, n, PCF(bias), nullptr, PF(out));
 }
 
@@ -362,8 +348,14 @@ int tsm_write_rows(tsm_ctx* ctx, tsm_dptr cache, int rows, int heads, int capaci
 int tsm_ragged_attention(tsm_ctx* ctx, tsm_dptr q, int64_t q_stride, int tokens, int heads, int width, tsm_dptr k, tsm_dptr v,
                          int rows, int kv_heads, int capacity, tsm_dptr table, float scale, tsm_dptr out) {
     CTX_GUARD(ctx);
+    const int* order = nullptr;
+    if (tokens > 1 && tokens <= 4096) {
+        TSM_TRY(ensure_scratch(ctx, ctx->order, (int64_t)tokens * 4));
+        TSM_TRY(launch_length_order(ctx, PCI(table), tokens, (int*)ctx->order.ptr));
+        order = (const int*)ctx->order.ptr;
+    }
     return launch_attention(ctx, PCF(q), q_stride, tokens, heads, width, PCF(k), PCF(v), rows, kv_heads, capacity, PCI(table), scale,
-                            PF(out), nullptr);
+                            PF(out), nullptr, order);
 }
 
 int tsm_swiglu(tsm_ctx* ctx, tsm_dptr gate, tsm_dptr up, int rows, int n, int64_t in_stride, tsm_dptr out) {
