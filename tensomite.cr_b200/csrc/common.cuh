@@ -111,6 +111,9 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out);
 bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                             const float* bias, const float* residual, float* out);
 int launch_block_matmul_mma(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                             const float* bias, const float* residual, float* out);
 int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind, uint8_t* out);

@@ -1,0 +1,467 @@
+// The quantised product for several rows of activations, as a producer / consumer pipeline.
+//
+// Same arithmetic and same bits as matmul_mma_kernel (qgemm.cu): one int8 tensor-core instruction
+// (mma.sync m16n8k32) gives the exact integer dot products of 16 weight rows with 8 activation rows for one
+// 32-element block, and the thread that holds a (weight row, activation row) pair folds the block's float
+// contribution into its running sum, block after block (Quant.matmul_reference, quant.cr:122-142).
+//
+// What differs is how the operands reach the multiply:
+//   * one producer thread per CTA moves a whole stage (8 blocks of K) with four or five tiled tensor copies
+//     (cp.async.bulk.tensor.2d through tensor maps): the CTA's weight rows as one box of the block matrix, the
+//     quantised activations as two boxes of 128 bytes x 64 rows written with the 128-byte swizzle, their scales as
+//     one box.  Copies complete on a "full" mbarrier per stage; consumer warps release a stage through an "empty"
+//     mbarrier.  The main loop has no CTA-wide barrier and the consumer warps issue no copies.  (One copy per
+//     weight row and chunk, as matmul_mma_kernel does, is bounded by the rate at which an SM issues small bulk
+//     copies: about one per 30 ns measured.)
+//   * a CTA takes ALL activation rows (up to 64) and as many groups of 16 weight rows as keep every SM equally
+//     loaded, so a stage of activations is staged once per SM and used by every consumer warp;
+//   * a consumer warp prepares the weight fragments of 4 blocks, then walks its tiles of 8 activation rows with
+//     the 4 blocks innermost: the activation scales of a tile arrive as one 16-byte load per column, and the
+//     int -> float conversion of the dot product is folded into the first multiply (Q4_0).
+//
+// Shapes this kernel does not take (blocks per row not a multiple of 8, unaligned operands) stay with
+// matmul_mma_kernel.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include "common.cuh"
+
+namespace tsm {
+
+namespace {
+
+constexpr int kPipeStages = 4;
+constexpr unsigned kPipeSpins = 4u << 20;
+constexpr int kSub = 4;  // blocks whose weight fragments a warp holds at once
+
+template <int KIND> struct PFmt;
+template <> struct PFmt<TSM_Q8_0> { static constexpr int B = 34; };
+template <> struct PFmt<TSM_Q4_0> { static constexpr int B = 18; };
+template <> struct PFmt<TSM_Q4_1> { static constexpr int B = 20; };
+
+struct PipeParams {
+    const uint8_t* w;
+    int n, nb, m;          // weight rows, blocks per row, activation rows
+    int groups;            // ceil(n / 16)
+    QuantizedActs acts;
+    const float* bias;
+    const float* residual;
+    float* out;            // [m, n]
+    ErrorRecord* errors;
+};
+
+__device__ __forceinline__ unsigned p_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void p_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(p_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void p_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(p_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void p_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool p_mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(p_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after kPipeSpins polls, or as soon as another warp has raised the CTA's abort flag.
+__device__ __forceinline__ bool p_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
+    for (unsigned spin = 0; spin < kPipeSpins; spin++) {
+        if (p_mbar_try_wait(bar, parity)) return true;
+        if (spin > 1024) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    return false;
+}
+__device__ __forceinline__ void p_tensor_load(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     p_smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(p_smem_u32(bar))
+                 : "memory");
+}
+
+// The 4 bytes at p (2-byte aligned, in shared memory) as a little-endian word.
+__device__ __forceinline__ unsigned p_lds_u32_at2(const unsigned char* p) {
+    uintptr_t a = (uintptr_t)p;
+    const unsigned* q = (const unsigned*)(a & ~(uintptr_t)3);
+    return __funnelshift_r(q[0], q[1], (unsigned)(a & 3) * 8);
+}
+__device__ __forceinline__ unsigned p_lds_u16(const unsigned char* p) { return *(const unsigned short*)p; }
+
+// Nibbles 0..15 in the low half of each byte of x -> signed bytes nibble - 8, without touching neighbours.
+__device__ __forceinline__ unsigned p_nibbles_minus_8(unsigned x) { return (((x & 0x0f0f0f0fu) | 0x80808080u) - 0x08080808u) ^ 0x80808080u; }
+
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23: an int32 accumulator started at this float's bits reads back as kMagic + dot
+
+// d = C + A * B with the accumulator input C given as four registers that the caller keeps alive across calls.
+__device__ __forceinline__ void p_mma_s8(int (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1, const int (&c)[4]) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+constexpr int kCB = 8;  // blocks of K per stage
+
+template <int KIND, int COLS>
+struct PipeLayout {
+    static constexpr int B = PFmt<KIND>::B;
+    static constexpr int WP = kCB * B;                       // a weight row's chunk, dense: 144, 272 or 160 bytes
+    static constexpr int ABOX = COLS * 128;                  // one swizzled box of activations: 4 blocks x COLS rows
+    static constexpr int SP = kCB * 4;                       // scales of one activation row
+    static constexpr int SCALE_BYTES = COLS * SP * (KIND == TSM_Q4_1 ? 2 : 1);
+    __host__ __device__ static constexpr int weights_at() { return 2 * ABOX; }
+    __host__ __device__ static constexpr int scales_at(int row_groups) { return 2 * ABOX + row_groups * 16 * WP; }
+    __host__ __device__ static constexpr int stage_bytes(int row_groups) { return (scales_at(row_groups) + SCALE_BYTES + 1023) / 1024 * 1024; }
+};
+
+struct PipeMaps {
+    CUtensorMap weights;  // u16 [n, nb * B / 2], box (kCB * B / 2) x (16 * groups per CTA)
+    CUtensorMap acts;     // u8 [m, k], box 128 x COLS, 128-byte swizzle
+    CUtensorMap scales;   // f32 [m, nb], box kCB x COLS
+    CUtensorMap sums;     // the same over the block sums (Q4_1)
+};
+
+// A consumer warp owns one group of 16 weight rows and NT tiles of 8 activation rows (from tile wc * NT); the
+// CTA has `wr_max` groups x WC such warps plus one producer warp (the last).  CTA b takes the groups
+// [b * groups / gridDim.x, (b + 1) * groups / gridDim.x): at most wr_max of them by the host's choice of grid.
+template <int KIND, int NT, int WC>
+__global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int wr_max, const __grid_constant__ PipeMaps maps) {
+    constexpr int COLS = 8 * NT * WC;
+    using L = PipeLayout<KIND, COLS>;
+    constexpr int B = L::B, WP = L::WP;
+    extern __shared__ unsigned char smem_raw[];
+    // the swizzled boxes need 1024-byte alignment: barriers sit in the first 128 bytes, stages start at the next 1024
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)smem;                 // [kPipeStages]
+    uint64_t* empty = full + kPipeStages;             // [kPipeStages]
+    volatile int* abort_flag = (volatile int*)(smem + 96);
+    unsigned char* stages = smem + 1024;
+    const int stage_bytes = L::stage_bytes(wr_max);
+    const int scales_at = L::scales_at(wr_max);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nb = p.nb;
+    const int group0 = (int)((int64_t)blockIdx.x * p.groups / gridDim.x);
+    const int group_count = (int)((int64_t)(blockIdx.x + 1) * p.groups / gridDim.x) - group0;
+    const int col0 = blockIdx.y * COLS;
+    const int valid = min(COLS, p.m - col0);          // activation rows this CTA really has
+    const int active_wc = min(WC, (valid + 8 * NT - 1) / (8 * NT));
+    const int chunks = nb / kCB;
+    const int producer_warp = wr_max * WC;
+
+    if (tid == 0) {
+        for (int s = 0; s < kPipeStages; s++) {
+            p_mbar_init(&full[s], 1);
+            p_mbar_init(&empty[s], group_count * active_wc);
+        }
+        abort_flag[0] = 0, abort_flag[1] = 0;  // [1] stays 0: a wait that must not be cut short polls it
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == producer_warp) {
+        // ---------------------------------------------------------------- producer: one thread
+        if (lane != 0) return;
+        // a box that reaches past the matrix is filled with zeros and still counts in full
+        const unsigned tx = (unsigned)(2 * L::ABOX + wr_max * 16 * WP + L::SCALE_BYTES);
+        int issued = 0;
+        bool ok = true;
+        for (int chunk = 0; chunk < chunks; chunk++) {
+            int s = chunk % kPipeStages;
+            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag);
+            if (!ok) break;
+            unsigned char* base = stages + (size_t)s * stage_bytes;
+            p_mbar_expect_tx(&full[s], tx);
+            p_tensor_load(base, &maps.acts, chunk * kCB * 32, col0, &full[s]);
+            p_tensor_load(base + L::ABOX, &maps.acts, chunk * kCB * 32 + 128, col0, &full[s]);
+            p_tensor_load(base + L::weights_at(), &maps.weights, chunk * (kCB * B / 2), group0 * 16, &full[s]);
+            p_tensor_load(base + scales_at, &maps.scales, chunk * kCB, col0, &full[s]);
+            if (KIND == TSM_Q4_1) p_tensor_load(base + scales_at + COLS * L::SP, &maps.sums, chunk * kCB, col0, &full[s]);
+            issued = chunk + 1;
+        }
+        if (!ok) {
+            // a consumer stopped arriving: say so, then see the copies already issued land before leaving
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int chunk = max(0, issued - kPipeStages); chunk < issued; chunk++)
+                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1);
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    const int wr = warp / WC, wc = warp % WC;
+    if (wr >= group_count || wc >= active_wc) return;
+    const int g = lane >> 2, t = lane & 3;
+    const int lcol0 = wc * 8 * NT;
+    const int my_tiles = min(NT, (valid - lcol0 + 7) / 8);
+    const int row0 = (group0 + wr) * 16;
+    const int ra = wr * 16 + g, rbw = ra + 8;         // this thread's two weight rows within the CTA's box
+    // a fragment word of activation row 8 i + g, block u: 16-byte piece 2u (elements 4t..) or 2u + 1 (elements 16 + 4t..)
+    // of the row's 128 bytes, stored at piece ^ (row & 7) = piece ^ g
+    int frag_at[kSub];
+#pragma unroll
+    for (int u = 0; u < kSub; u++) frag_at[u] = (lcol0 + g) * 128 + (((2 * u) ^ g) << 4) + 4 * t;
+
+    int cq[4];  // the accumulator input of every multiply: four registers holding kMagic's bits, set once
+#pragma unroll
+    for (int e = 0; e < 4; e++) asm volatile("mov.b32 %0, 0x4b400000;" : "=r"(cq[e]));
+
+    float acc[NT][4];  // [tile][(row a, col 2t), (row a, col 2t+1), (row b, col 2t), (row b, col 2t+1)]
+#pragma unroll
+    for (int i = 0; i < NT; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[i][e] = 0.0f;
+
+    bool ok = true;
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        int s = chunk % kPipeStages;
+        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag);
+        if (!ok) break;
+        const unsigned char* base = stages + (size_t)s * stage_bytes;
+        const unsigned char* slot_a = base + L::weights_at() + (size_t)ra * WP;
+        const unsigned char* slot_b = base + L::weights_at() + (size_t)rbw * WP;
+        const float* sc = (const float*)(base + scales_at);
+        const float* aux = sc + COLS * kCB;
+#pragma unroll
+        for (int sub = 0; sub < kCB / kSub; sub++) {
+            const unsigned char* abox = base + sub * L::ABOX;
+            unsigned a[kSub][4];
+            float dwa[kSub], dwb[kSub], xa[kSub], xb[kSub];  // xa/xb: Q4_0 -kMagic * dw; Q4_1 the block minimum
+            bool plain = true;
+#pragma unroll
+            for (int u = 0; u < kSub; u++) {
+                const unsigned char* pa = slot_a + (sub * kSub + u) * B;
+                const unsigned char* pb = slot_b + (sub * kSub + u) * B;
+                dwa[u] = half_bits_to_float(p_lds_u16(pa)), dwb[u] = half_bits_to_float(p_lds_u16(pb));
+                if (KIND == TSM_Q8_0) {
+                    a[u][0] = p_lds_u32_at2(pa + 2 + 4 * t), a[u][2] = p_lds_u32_at2(pa + 18 + 4 * t);
+                    a[u][1] = p_lds_u32_at2(pb + 2 + 4 * t), a[u][3] = p_lds_u32_at2(pb + 18 + 4 * t);
+                    xa[u] = xb[u] = 0.0f;
+                } else if (KIND == TSM_Q4_0) {
+                    unsigned na = p_lds_u32_at2(pa + 2 + 4 * t), nbw = p_lds_u32_at2(pb + 2 + 4 * t);
+                    a[u][0] = p_nibbles_minus_8(na), a[u][2] = p_nibbles_minus_8(na >> 4);
+                    a[u][1] = p_nibbles_minus_8(nbw), a[u][3] = p_nibbles_minus_8(nbw >> 4);
+                    xa[u] = __fmul_rn(-kMagic, dwa[u]), xb[u] = __fmul_rn(-kMagic, dwb[u]);
+                    plain = plain && fabsf(dwa[u]) <= 65504.0f && fabsf(dwb[u]) <= 65504.0f;
+                } else {
+                    unsigned na = p_lds_u32_at2(pa + 4 + 4 * t), nbw = p_lds_u32_at2(pb + 4 + 4 * t);
+                    a[u][0] = na & 0x0f0f0f0fu, a[u][2] = (na >> 4) & 0x0f0f0f0fu;
+                    a[u][1] = nbw & 0x0f0f0f0fu, a[u][3] = (nbw >> 4) & 0x0f0f0f0fu;
+                    xa[u] = half_bits_to_float(p_lds_u16(pa + 2)), xb[u] = half_bits_to_float(p_lds_u16(pb + 2));
+                }
+            }
+            // Q4_0: (float(dot) * dw) * dx with float(dot) * dw taken as fma(kMagic + dot, dw, -kMagic * dw): both
+            // products are exact (dw has 11 significant bits), so the one rounding is that of dot * dw.  With a
+            // scale that is not finite the fused form would give NaN where the reference gives an infinity, so
+            // such a group of blocks takes the subtract-then-multiply form instead.
+            const bool fused = KIND == TSM_Q4_0 && __all_sync(0xffffffffu, plain);
+#pragma unroll
+            for (int i = 0; i < NT; i++) {
+                if (i < my_tiles) {
+                    const int c = lcol0 + 8 * i + 2 * t;
+                    const float4 s0 = *(const float4*)(sc + c * kCB + sub * kSub);
+                    const float4 s1 = *(const float4*)(sc + (c + 1) * kCB + sub * kSub);
+                    float4 m0 = make_float4(0.f, 0.f, 0.f, 0.f), m1 = m0;
+                    if (KIND == TSM_Q4_1) {
+                        m0 = *(const float4*)(aux + c * kCB + sub * kSub);
+                        m1 = *(const float4*)(aux + (c + 1) * kCB + sub * kSub);
+                    }
+                    const unsigned char* tile = abox + i * 1024;
+#pragma unroll
+                    for (int u = 0; u < kSub; u++) {
+                        int d[4];
+                        p_mma_s8(d, a[u], *(const unsigned*)(tile + frag_at[u]), *(const unsigned*)(tile + (frag_at[u] ^ 16)), cq);
+                        const float dx0 = u == 0 ? s0.x : u == 1 ? s0.y : u == 2 ? s0.z : s0.w;
+                        const float dx1 = u == 0 ? s1.x : u == 1 ? s1.y : u == 2 ? s1.z : s1.w;
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const float dx = e == 0 ? dx0 : dx1;
+                            const float fa_bits = __int_as_float(d[e]), fb_bits = __int_as_float(d[2 + e]);
+                            if (KIND == TSM_Q8_0) {
+                                float fa = __fsub_rn(fa_bits, kMagic), fb = __fsub_rn(fb_bits, kMagic);
+                                acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(fa, __fmul_rn(dwa[u], dx)));
+                                acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(fb, __fmul_rn(dwb[u], dx)));
+                            } else if (KIND == TSM_Q4_0) {
+                                float pa, pb;
+                                if (fused) {
+                                    pa = __fmaf_rn(fa_bits, dwa[u], xa[u]), pb = __fmaf_rn(fb_bits, dwb[u], xb[u]);
+                                } else {
+                                    pa = __fmul_rn(__fsub_rn(fa_bits, kMagic), dwa[u]), pb = __fmul_rn(__fsub_rn(fb_bits, kMagic), dwb[u]);
+                                }
+                                acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(pa, dx));
+                                acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fmul_rn(pb, dx));
+                            } else {
+                                const float sx = e == 0 ? (u == 0 ? m0.x : u == 1 ? m0.y : u == 2 ? m0.z : m0.w)
+                                                        : (u == 0 ? m1.x : u == 1 ? m1.y : u == 2 ? m1.z : m1.w);
+                                float fa = __fsub_rn(fa_bits, kMagic), fb = __fsub_rn(fb_bits, kMagic);
+                                acc[i][e] = __fadd_rn(acc[i][e], __fadd_rn(__fmul_rn(__fmul_rn(dwa[u], dx), fa), __fmul_rn(xa[u], sx)));
+                                acc[i][2 + e] = __fadd_rn(acc[i][2 + e], __fadd_rn(__fmul_rn(__fmul_rn(dwb[u], dx), fb), __fmul_rn(xb[u], sx)));
+                            }
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) p_mbar_arrive(&empty[s]);
+    }
+    if (!ok) {
+        *abort_flag = 1;
+        if (lane == 0) atomicExch(&p.errors->timeout, 1);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < NT; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            int row = row0 + g + (e < 2 ? 0 : 8);
+            int col = col0 + lcol0 + 8 * i + 2 * t + (e & 1);
+            if (row < p.n && col < p.m) {
+                float v = acc[i][e];
+                if (p.bias) v = __fadd_rn(v, p.bias[row]);
+                if (p.residual) v = __fadd_rn(p.residual[(int64_t)col * p.n + row], v);
+                p.out[(int64_t)col * p.n + row] = v;
+            }
+        }
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled from the driver that is already loaded (the library links the runtime only).
+EncodeTiled encode_tiled() {
+    static EncodeTiled fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return (EncodeTiled)ptr;
+    }();
+    return fn;
+}
+
+// A rank-2 map over `rows` rows of `width` elements (pitch `pitch_bytes`), copied in boxes of box_w x box_h elements.
+int make_map(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows, uint64_t pitch_bytes,
+             uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle swizzle) {
+    EncodeTiled encode = encode_tiled();
+    if (!encode) return fail(ctx, TSM_ERR_UNSUPPORTED, "the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {width, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_w, box_h};
+    cuuint32_t steps[2] = {1, 1};
+    CUresult rc = encode(map, type, 2, const_cast<void*>(base), dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return fail(ctx, TSM_ERR_ARG, "cuTensorMapEncodeTiled refused a map (code " + std::to_string((int)rc) + ")");
+    return TSM_OK;
+}
+
+template <int KIND, int NT, int WC>
+int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
+    constexpr int COLS = 8 * NT * WC;
+    using L = PipeLayout<KIND, COLS>;
+    constexpr int B = L::B;
+    constexpr size_t kSmemBudget = 224 * 1024;
+    auto smem_for = [](int groups) { return (size_t)2048 + (size_t)kPipeStages * L::stage_bytes(groups); };
+    const int wr_cap = 15 / WC;  // 15 consumer warps and the producer: 512 threads
+    int wr_max = 0, grid_x = 0;
+    // the fewest CTAs per SM whose share of the weight-row groups fits a CTA; every SM then gets the same share
+    for (int c = 1; c <= 4 && !wr_max; c++) {
+        if (ctas_per_sm_forced && c != ctas_per_sm_forced) continue;
+        int gx = std::min(p.groups, ctx->sm_count * c);
+        int need = (p.groups + gx - 1) / gx;
+        if (need <= wr_cap && smem_for(need) * c <= kSmemBudget && 32 * (need * WC + 1) * c <= 512) wr_max = need, grid_x = gx;
+    }
+    if (!wr_max) {
+        wr_max = wr_cap;
+        while (wr_max > 1 && smem_for(wr_max) > kSmemBudget) wr_max--;
+        grid_x = (p.groups + wr_max - 1) / wr_max;
+    }
+    size_t smem = smem_for(wr_max);
+    auto kernel = matmul_pipe_kernel<KIND, NT, WC>;
+    {
+        static std::mutex lock;
+        static std::map<std::pair<int, const void*>, bool> done;
+        std::lock_guard<std::mutex> guard(lock);
+        auto key = std::make_pair(ctx->ordinal, (const void*)kernel);
+        if (!done.count(key)) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            done[key] = true;
+        }
+    }
+    PipeMaps maps;
+    const uint64_t nb = (uint64_t)p.nb;
+    TSM_TRY(make_map(ctx, &maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT16, p.w, nb * B / 2, (uint64_t)p.n, nb * B, kCB * B / 2, 16 * wr_max,
+                     CU_TENSOR_MAP_SWIZZLE_NONE));
+    TSM_TRY(make_map(ctx, &maps.acts, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.acts.qs, nb * 32, (uint64_t)p.m, nb * 32, 128, COLS,
+                     CU_TENSOR_MAP_SWIZZLE_128B));
+    TSM_TRY(make_map(ctx, &maps.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.acts.scales, nb, (uint64_t)p.m, nb * 4, kCB, COLS,
+                     CU_TENSOR_MAP_SWIZZLE_NONE));
+    TSM_TRY(make_map(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m, nb * 4,
+                     kCB, COLS, CU_TENSOR_MAP_SWIZZLE_NONE));
+    dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
+    kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+template <int KIND>
+int launch_pipe_kind(tsm_ctx* ctx, const PipeParams& p) {
+    // TSM_PIPE_CONFIG = WC * 10 + CTAs per SM picks a split for timing variants without rebuilding
+    static const int forced = getenv("TSM_PIPE_CONFIG") ? atoi(getenv("TSM_PIPE_CONFIG")) : 0;
+    const int tiles = (std::min(p.m, 64) + 7) / 8;
+    // few weight rows: split the activation rows over 2 or 4 warps per group so that every SM still has warps to run
+    int wc = p.groups >= 8 * ctx->sm_count ? 1 : p.groups >= 4 * ctx->sm_count ? 2 : 4;
+    if (forced) wc = forced / 10;
+    const int c = forced % 10;
+    if (tiles > 4) {
+        if (wc >= 4) return launch_pipe_shape<KIND, 2, 4>(ctx, p, c);
+        if (wc == 2) return launch_pipe_shape<KIND, 4, 2>(ctx, p, c);
+        return launch_pipe_shape<KIND, 8, 1>(ctx, p, c);
+    }
+    if (tiles > 2) {
+        if (wc >= 2) return launch_pipe_shape<KIND, 2, 2>(ctx, p, c);
+        return launch_pipe_shape<KIND, 4, 1>(ctx, p, c);
+    }
+    if (tiles > 1) {
+        if (wc >= 2) return launch_pipe_shape<KIND, 1, 2>(ctx, p, c);
+        return launch_pipe_shape<KIND, 2, 1>(ctx, p, c);
+    }
+    return launch_pipe_shape<KIND, 1, 1>(ctx, p, c);
+}
+
+}  // namespace
+
+// Whether the pipelined kernel takes this product: 16-byte aligned weights, quantised activations and scales, and a
+// whole number of 8-block chunks per row (which also makes every row pitch a multiple of 16 bytes, as a tensor
+// map requires).
+bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n) {
+    if (getenv("TSM_NO_PIPE")) return false;
+    int nb = k / 32;
+    bool aligned = (((uintptr_t)w | (uintptr_t)a.qs | (uintptr_t)a.scales | (uintptr_t)(kind == TSM_Q4_1 ? a.sums : a.scales)) & 15) == 0;
+    return rows >= 1 && nb >= kCB && nb % kCB == 0 && aligned && encode_tiled() != nullptr;
+}
+
+int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                             const float* bias, const float* residual, float* out) {
+    PipeParams p;
+    p.w = w, p.n = n, p.nb = k / 32, p.m = rows, p.groups = (n + 15) / 16, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
+    p.errors = ctx->errors;
+    switch (kind) {
+        case TSM_Q8_0: return launch_pipe_kind<TSM_Q8_0>(ctx, p);
+        case TSM_Q4_0: return launch_pipe_kind<TSM_Q4_0>(ctx, p);
+        case TSM_Q4_1: return launch_pipe_kind<TSM_Q4_1>(ctx, p);
+    }
+    return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
+}
+
+}  // namespace tsm

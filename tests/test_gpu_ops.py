@@ -65,7 +65,8 @@ SHAPES = [(1, 37, 64), (3, 5, 1280), (2, 9, 4096),            # the reference's 
           (1, 1600, 1600), (2, 200, 6400),                    # 50 and 200 blocks (GPT-2 XL's)
           (1, 2048, 2048), (3, 1024, 4096), (1, 256, 14336),  # aligned rows, long rows
           (8, 128, 2048), (16, 64, 576), (1, 7, 4096), (1, 4097, 256),
-          (5, 40, 1536), (33, 48, 4096), (64, 200, 1600), (100, 96, 576), (64, 1024, 2048), (17, 72, 14336)]  # tensor-core kernel
+          (5, 40, 1536), (33, 48, 4096), (64, 200, 1600), (100, 96, 576), (64, 1024, 2048), (17, 72, 14336),  # tensor-core kernels
+          (64, 304, 4096), (70, 100, 1024), (12, 2400, 512), (24, 48, 2048), (64, 5000, 256), (40, 2500, 1024)]  # odd group counts, two slabs of activation rows, several groups per CTA
 
 
 @pytest.mark.parametrize("name", list(KINDS))
@@ -81,6 +82,27 @@ def test_block_product_is_bit_exact(dev, name):
         want = oracle.matmul_reference(kind, x, w, n, bias=bias)
         wb.free()
         assert np.array_equal(bits(got), bits(want)), (name, count, n, k)
+
+
+def test_block_product_with_a_scale_that_is_not_finite(dev):
+    """A Q4_0 block whose scale is infinite: the outputs it reaches are the reference's infinities and NaNs."""
+    rng = np.random.default_rng(12)
+    n, k, count = 64, 1024, 16
+    w = oracle.quantize(oracle.Q4_0, rng.normal(0, 0.02, n * k).astype(np.float32)).copy()
+    blocks = w.reshape(n, k // 32, 18)
+    blocks[3, 5, 0:2] = np.frombuffer(np.float16(np.inf).tobytes(), dtype=np.uint8)
+    blocks[40, 0, 0:2] = np.frombuffer(np.float16(-np.inf).tobytes(), dtype=np.uint8)
+    x = rng.uniform(-3, 3, (count, k)).astype(np.float32)
+    wb = dev.tensor(w)
+    got = dev.block_matmul(x, wb, oracle.Q4_0, n)
+    want = oracle.matmul_reference(oracle.Q4_0, x, w, n)
+    wb.free()
+    assert np.isinf(want[:, 3]).any() or np.isnan(want[:, 3]).any()
+    finite = np.isfinite(want)
+    assert np.array_equal(finite, np.isfinite(got))
+    assert np.array_equal(bits(got[finite]), bits(want[finite]))
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    assert np.array_equal(got[np.isinf(want)], want[np.isinf(want)])
 
 
 def test_a_row_alone_equals_the_row_in_a_batch(dev):
