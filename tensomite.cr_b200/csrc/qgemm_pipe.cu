@@ -24,6 +24,8 @@
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tsm {
@@ -125,7 +127,7 @@ struct PipeLayout {
 struct PipeMaps {
     CUtensorMap weights;  // u16 [n, nb * B / 2], box (kCB * B / 2) x (16 * groups per CTA)
     CUtensorMap acts;     // u8 [m, k], box 128 x COLS, 128-byte swizzle
-    CUtensorMap scales;   // f32 [m, nb], box kCB x COLS
+    CUtensorMap scales;   // f32 [m, nb], box kCB x COLS, 32-byte swizzle (a warp's 16-byte reads then fall in distinct banks)
     CUtensorMap sums;     // the same over the block sums (Q4_1)
 };
 
@@ -263,17 +265,24 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
             // products are exact (dw has 11 significant bits), so the one rounding is that of dot * dw.  With a
             // scale that is not finite the fused form would give NaN where the reference gives an infinity, so
             // such a group of blocks takes the subtract-then-multiply form instead.
-            const bool fused = KIND == TSM_Q4_0 && __all_sync(0xffffffffu, plain);
+            const bool all_plain = KIND == TSM_Q4_0 && __all_sync(0xffffffffu, plain);
+            // the tile loop exists twice, behind a real branch: as one loop with the choice inside, both forms
+            // were issued for every element and one of them predicated off
+            auto tiles = [&](auto fused_tag) {
+            constexpr bool fused = decltype(fused_tag)::value;
 #pragma unroll
             for (int i = 0; i < NT; i++) {
                 if (i < my_tiles) {
                     const int c = lcol0 + 8 * i + 2 * t;
-                    const float4 s0 = *(const float4*)(sc + c * kCB + sub * kSub);
-                    const float4 s1 = *(const float4*)(sc + (c + 1) * kCB + sub * kSub);
+                    // scales are stored with the 32-byte swizzle: the half (blocks 0-3 or 4-7) of column c sits at
+                    // half ^ bit 2 of c, which for columns 8 i + 2 t (+ 1) is bit 1 of t
+                    const int half = (sub ^ (t >> 1)) * kSub;
+                    const float4 s0 = *(const float4*)(sc + c * kCB + half);
+                    const float4 s1 = *(const float4*)(sc + (c + 1) * kCB + half);
                     float4 m0 = make_float4(0.f, 0.f, 0.f, 0.f), m1 = m0;
                     if (KIND == TSM_Q4_1) {
-                        m0 = *(const float4*)(aux + c * kCB + sub * kSub);
-                        m1 = *(const float4*)(aux + (c + 1) * kCB + sub * kSub);
+                        m0 = *(const float4*)(aux + c * kCB + half);
+                        m1 = *(const float4*)(aux + (c + 1) * kCB + half);
                     }
                     const unsigned char* tile = abox + i * 1024;
 #pragma unroll
@@ -310,6 +319,9 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
                     }
                 }
             }
+            };
+            if (all_plain) tiles(std::true_type{});
+            else tiles(std::false_type{});
         }
         __syncwarp();
         if (lane == 0) p_mbar_arrive(&empty[s]);
@@ -404,9 +416,9 @@ int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     TSM_TRY(make_map(ctx, &maps.acts, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.acts.qs, nb * 32, (uint64_t)p.m, nb * 32, 128, COLS,
                      CU_TENSOR_MAP_SWIZZLE_128B));
     TSM_TRY(make_map(ctx, &maps.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.acts.scales, nb, (uint64_t)p.m, nb * 4, kCB, COLS,
-                     CU_TENSOR_MAP_SWIZZLE_NONE));
+                     CU_TENSOR_MAP_SWIZZLE_32B));
     TSM_TRY(make_map(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m, nb * 4,
-                     kCB, COLS, CU_TENSOR_MAP_SWIZZLE_NONE));
+                     kCB, COLS, CU_TENSOR_MAP_SWIZZLE_32B));
     dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
     kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
     count_launch(ctx);
