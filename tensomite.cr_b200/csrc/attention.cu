@@ -533,6 +533,16 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         return launch_fast<128>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
     if (!out) return fail(ctx, TSM_ERR_ARG, "ordered attention needs an F32 output");
     bool launched = false;
+    if (attention_stream_fits(heads, width, kv_heads, q, q_stride, k, v)) {
+        TSM_TRY(ensure_scratch(ctx, ctx->attn, attention_stream_scratch_bytes(tokens, heads, capacity)));
+        TSM_TRY(launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
+                                        (float*)ctx->attn.ptr));
+        if (quantized) {
+            TSM_TRY(launch_quantize_rows(ctx, out, tokens, heads * width, (int64_t)heads * width, (float*)quantized->scales,
+                                         (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs));
+        }
+        return TSM_OK;
+    }
     if (aligned && (width == 64 || width == 128)) {
         int per_kv = heads / kv_heads;
         int pitch = width + 4;

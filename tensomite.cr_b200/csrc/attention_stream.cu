@@ -1,0 +1,334 @@
+// Ordered ("exact") ragged attention for head width 128 and 4 query heads per key/value head, built to keep the
+// memory system busy: the same arithmetic, in the same order, as attention_exact_kernel (the host's sequential
+// sums, Tensor attention in the reference's CPU device), but
+//   * keys and values arrive through ONE ring of shared-memory stages filled by a producer thread with tiled
+//     tensor copies (cp.async.bulk.tensor.2d, 128-byte swizzle, four boxes of 32 floats x 32 positions per tile)
+//     that complete on an mbarrier; the producer runs ahead through the whole key pass and straight on into the
+//     value pass, so the softmax phase in between does not drain the ring;
+//   * scores do not live in shared memory: they go to a scratch array in global memory (it stays in L2), are turned
+//     into exp values in place, and come back tile by tile as weights.  A CTA therefore needs 70 KB instead of
+//     100 KB and three CTAs share an SM, each with two or three tiles in flight;
+//   * consumer warps synchronise among themselves with a named barrier only where data is exchanged (maximum,
+//     denominator, a tile's weights), never with the producer.
+// One CTA per (token, key/value head): 128 consumer threads + one producer warp.
+#include "common.cuh"
+
+namespace tsm {
+
+namespace {
+
+constexpr int kTP = 32;            // positions per tile
+constexpr int kRing = 3;           // stages
+constexpr int kEChunk = 1024;      // positions whose exp values are staged at once for the denominator's chain
+constexpr int kConsumers = 128;
+constexpr unsigned kSpinLimit = 4u << 20;
+
+struct StreamParams {
+    const float* q;
+    int64_t q_stride;
+    int heads, rows, kv_heads, capacity;
+    const int* table;
+    float scale;
+    float* out;
+    ErrorRecord* errors;
+    const int* order;
+    float* scratch;  // [tokens][heads][capacity]: scores, then exp values
+};
+
+struct StreamMaps {
+    CUtensorMap k, v;  // f32 [rows * kv_heads * capacity, width], box 32 x kTP, 128-byte swizzle
+};
+
+__device__ __forceinline__ unsigned s_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void s_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(s_smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void s_mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void s_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s_smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool s_mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(s_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after kSpinLimit polls, or soon after another warp has raised the CTA's abort flag.
+__device__ __forceinline__ bool s_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
+    for (unsigned spin = 0; spin < kSpinLimit; spin++) {
+        if (s_mbar_try_wait(bar, parity)) return true;
+        if (spin > 256) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    return false;
+}
+__device__ __forceinline__ void s_tensor_load(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     s_smem_u32(dst)),
+                 "l"(map), "r"(x), "r"(y), "r"(s_smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+
+template <int WIDTH>
+__global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    constexpr int G = 4;
+    constexpr int BOXES = WIDTH / 32;              // 128-byte wide boxes per row
+    constexpr int BOX_BYTES = kTP * 128;
+    constexpr int STAGE_BYTES = BOXES * BOX_BYTES;
+    constexpr int QP = WIDTH + 4;                  // query row pitch: the four heads' 16-byte reads fall in distinct banks
+    static_assert(WIDTH == kConsumers, "one folding thread per column");
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)smem;              // [kRing]
+    uint64_t* empty = full + kRing;                // [kRing]
+    volatile int* abort_flag = (volatile int*)(smem + 64);   // [1] stays 0
+    float* red = (float*)(smem + 128);             // [4 warps][4 heads]
+    float* maxes = red + 16;                       // [4]
+    float* totals = maxes + 4;                     // [4]
+    unsigned char* stages = smem + 1024;           // [kRing][BOXES][kTP][128 bytes], swizzled
+    float* ebuf = (float*)(stages + kRing * STAGE_BYTES);    // [G][kEChunk]
+    float* wbuf = ebuf + G * kEChunk;              // [2][kTP][G]
+    float* qs = wbuf + 2 * kTP * G;                // [G][QP]
+
+    const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;  // longest tokens first when an order is given
+    const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
+    const int kvh = blockIdx.x / groups_per_kv;
+    const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
+    const int row = p.table[3 * token], limit = p.table[3 * token + 1];
+    if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) {
+        if (threadIdx.x == 0 && blockIdx.x == 0) report_bad_index(p.errors, limit, p.capacity);
+        return;
+    }
+    const int len = limit + 1;
+    const int tiles = (len + kTP - 1) / kTP;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) {
+        for (int s = 0; s < kRing; s++) {
+            s_mbar_init(&full[s], 1);
+            s_mbar_init(&empty[s], kConsumers / 32);
+        }
+        abort_flag[0] = 0, abort_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < G * WIDTH; i += blockDim.x)
+        qs[(i / WIDTH) * QP + i % WIDTH] = p.q[(int64_t)token * p.q_stride + (int64_t)head0 * WIDTH + i];
+    __syncthreads();
+
+    if (warp == kConsumers / 32) {
+        // ------------------------------------------------------------ producer: keys, then values, one ring
+        if (lane != 0) return;
+        const int plane = (row * p.kv_heads + kvh) * p.capacity;   // first row of this (stream, kv head) in the maps
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < 2 * tiles; j++) {
+            int s = j % kRing;
+            if (j >= kRing) ok = s_mbar_wait(&empty[s], (unsigned)((j / kRing - 1) & 1), abort_flag);
+            if (!ok) break;
+            const CUtensorMap* map = j < tiles ? &maps.k : &maps.v;
+            int y = plane + (j < tiles ? j : j - tiles) * kTP;
+            unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
+            s_mbar_expect_tx(&full[s], STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < BOXES; b++) s_tensor_load(dst + b * BOX_BYTES, map, 32 * b, y, &full[s]);
+            issued = j + 1;
+        }
+        if (!ok) {
+            // the consumers stopped arriving: say so, then see the copies already issued land before leaving
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int j = max(0, issued - kRing); j < issued; j++) s_mbar_wait(&full[j % kRing], (unsigned)((j / kRing) & 1), abort_flag + 1);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers
+    // A wait that gives up raises the abort flag and the thread carries on with whatever the stage holds, so that
+    // every named barrier below is still reached by all 128 threads; the results are then dropped.
+    bool ok = true;
+    const int sp = tid >> 2, shd = tid & 3;        // this thread's position within a tile and its head
+    float* srow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;   // + h * capacity + position
+
+    // ---- 1. scores ----
+    float top = -INFINITY;
+    {
+        const int sw = sp & 7;
+        const float4* qr = (const float4*)(qs + shd * QP);
+        for (int tile = 0; tile < tiles; tile++) {
+            int s = tile % kRing;
+            if (!s_mbar_wait(&full[s], (unsigned)((tile / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+            const unsigned char* rowp = stages + (size_t)s * STAGE_BYTES + sp * 128;
+            float dot = 0.0f;
+#pragma unroll
+            for (int c = 0; c < WIDTH / 4; c++) {
+                float4 kv4 = *(const float4*)(rowp + (c >> 3) * BOX_BYTES + (((c & 7) ^ sw) << 4));
+                float4 qv = qr[c];
+                dot = __fadd_rn(dot, __fmul_rn(qv.x, kv4.x));
+                dot = __fadd_rn(dot, __fmul_rn(qv.y, kv4.y));
+                dot = __fadd_rn(dot, __fmul_rn(qv.z, kv4.z));
+                dot = __fadd_rn(dot, __fmul_rn(qv.w, kv4.w));
+            }
+            __syncwarp();
+            if (lane == 0) s_mbar_arrive(&empty[s]);
+            int pos = tile * kTP + sp;
+            if (pos < len) {
+                float sc = __fadd_rn(__fmul_rn(dot, p.scale), 0.0f);
+                srow[(int64_t)shd * p.capacity + pos] = sc;
+                top = fmaxf(top, sc);
+            }
+        }
+    }
+    // ---- 2. softmax: maximum, exp in place, the denominator folded in position order ----
+#pragma unroll
+    for (int off = 16; off >= 4; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    if (lane < 4) red[warp * 4 + lane] = top;
+    consumers_sync();
+    if (tid < 4) maxes[tid] = fmaxf(fmaxf(red[tid], red[4 + tid]), fmaxf(red[8 + tid], red[12 + tid]));
+    consumers_sync();
+    {
+        float total = 0.0f;  // lane 0 of warp h folds head h
+        for (int e0 = 0; e0 < len; e0 += kEChunk) {
+            int count = min(kEChunk, len - e0);
+            // eight loads in flight per thread: the scores come back from L2
+            for (int i0 = 0; i0 < count; i0 += 2 * kConsumers) {
+                float sv[2][G];
+#pragma unroll
+                for (int u = 0; u < 2; u++)
+#pragma unroll
+                    for (int h = 0; h < G; h++) {
+                        int i = i0 + u * kConsumers + tid;
+                        sv[u][h] = i < count ? srow[(int64_t)h * p.capacity + e0 + i] : 0.0f;
+                    }
+#pragma unroll
+                for (int u = 0; u < 2; u++)
+#pragma unroll
+                    for (int h = 0; h < G; h++) {
+                        int i = i0 + u * kConsumers + tid;
+                        if (i < count) {
+                            float e = exact_exp(__fsub_rn(sv[u][h], maxes[h]));
+                            srow[(int64_t)h * p.capacity + e0 + i] = e;
+                            ebuf[h * kEChunk + i] = e;
+                        }
+                    }
+            }
+            consumers_sync();
+            if (lane == 0) {
+                const float* eh = ebuf + warp * kEChunk;
+                int i = 0;
+                for (; i + 8 <= count; i += 8) {
+                    float4 a = *(const float4*)(eh + i), b = *(const float4*)(eh + i + 4);
+                    total = __fadd_rn(total, a.x), total = __fadd_rn(total, a.y), total = __fadd_rn(total, a.z), total = __fadd_rn(total, a.w);
+                    total = __fadd_rn(total, b.x), total = __fadd_rn(total, b.y), total = __fadd_rn(total, b.z), total = __fadd_rn(total, b.w);
+                }
+                for (; i < count; i++) total = __fadd_rn(total, eh[i]);
+            }
+            consumers_sync();
+        }
+        if (lane == 0) totals[warp] = total;
+    }
+    consumers_sync();
+    // ---- 3. outputs: thread `tid` folds column `tid` of all four heads over positions in order ----
+    {
+        const float total = totals[shd];
+        const float* erow = srow + (int64_t)shd * p.capacity + sp;
+        float e_cur = sp < len ? erow[0] : 0.0f;
+        const int col = tid;
+        const unsigned char* colp = stages + (col >> 5) * BOX_BYTES + (col & 3) * 4;
+        const int piece = (col & 31) >> 2;  // a value's 16-byte piece of its 128-byte row sits at piece ^ (position & 7)
+        int voff[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) voff[u] = u * 128 + ((piece ^ u) << 4);
+        float acc[G];
+#pragma unroll
+        for (int i = 0; i < G; i++) acc[i] = 0.0f;
+        for (int tile = 0; tile < tiles; tile++) {
+            float* wt = wbuf + (tile & 1) * kTP * G;
+            wt[sp * G + shd] = __fdiv_rn(e_cur, total);
+            int next = (tile + 1) * kTP + sp;
+            e_cur = next < len ? erow[(tile + 1) * kTP] : 0.0f;
+            consumers_sync();  // this tile's weights are written; the other half of wbuf is no longer read
+            int j = tiles + tile, s = j % kRing;
+            if (!s_mbar_wait(&full[s], (unsigned)((j / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+            const unsigned char* vt = colp + (size_t)s * STAGE_BYTES;
+            int count = min(kTP, len - tile * kTP);
+            int pos = 0;
+            for (; pos + 8 <= count; pos += 8) {
+                float vv[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) vv[u] = *(const float*)(vt + pos * 128 + voff[u]);
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    float4 w4 = *(const float4*)(wt + (pos + u) * G);
+                    acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv[u]));
+                    acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv[u]));
+                    acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv[u]));
+                    acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv[u]));
+                }
+            }
+            for (; pos < count; pos++) {
+                float vv = *(const float*)(vt + pos * 128 + ((piece ^ (pos & 7)) << 4));  // no indexing of voff by a variable: it would move to local memory
+                float4 w4 = *(const float4*)(wt + pos * G);
+                acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv));
+                acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv));
+                acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv));
+                acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv));
+            }
+            __syncwarp();
+            if (lane == 0) s_mbar_arrive(&empty[s]);
+        }
+        if (!ok || *abort_flag) {
+            if (tid == 0) atomicExch(&p.errors->timeout, 1);
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < G; i++) p.out[((int64_t)token * p.heads + head0 + i) * WIDTH + col] = acc[i];
+    }
+}
+
+}  // namespace
+
+int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { return (int64_t)tokens * heads * capacity * 4 + 256; }
+
+// Whether the streaming kernel takes this call.  `scratch` must hold attention_stream_scratch_bytes.
+bool attention_stream_fits(int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k, const float* v) {
+    if (getenv("TSM_NO_ATTN_STREAM")) return false;
+    bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
+    return width == 128 && kv_heads > 0 && heads % kv_heads == 0 && (heads / kv_heads) % 4 == 0 && aligned && tensor_maps_available();
+}
+
+int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
+                            int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
+                            float* scratch) {
+    constexpr int WIDTH = 128;
+    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch};
+    StreamMaps maps;
+    uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
+    size_t smem = 2048 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
+    auto kernel = attention_stream_kernel<WIDTH>;
+    {
+        static std::mutex lock;
+        static std::map<int, bool> done;
+        std::lock_guard<std::mutex> guard(lock);
+        if (!done.count(ctx->ordinal)) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done[ctx->ordinal] = true;
+        }
+    }
+    dim3 grid(kv_heads * (heads / kv_heads / 4), tokens);
+    kernel<<<grid, kConsumers + 32, smem, ctx->stream>>>(p, maps);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+}  // namespace tsm

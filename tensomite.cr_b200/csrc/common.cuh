@@ -1,5 +1,6 @@
 // Shared declarations of the library: the context, status plumbing and small device helpers.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -111,6 +112,15 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out);
 bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+// A rank-2 tensor map over `rows` rows of `width` elements (row pitch in bytes), copied in boxes of box_w x box_h.
+bool tensor_maps_available();
+int make_tensor_map_2d(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows,
+                       uint64_t pitch_bytes, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle swizzle);
+int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity);
+bool attention_stream_fits(int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k, const float* v);
+int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
+                            int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
+                            float* scratch);
 bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                              const float* bias, const float* residual, float* out);

@@ -641,6 +641,8 @@ static int prepare_scratch(tsm_model* m, tsm_cache* cache, int tokens) {
     TSM_TRY(ensure_workspace(m, tokens));
     if (m->ctx->mode == TSM_FAST && (c.head_width == 64 || c.head_width == 128))
         TSM_TRY(ensure_scratch(m->ctx, m->ctx->attn, attention_scratch_bytes(tokens, c.heads, c.head_width, cache->capacity)));
+    if (m->ctx->mode != TSM_FAST && c.head_width == 128 && c.kv_heads > 0 && (c.heads / c.kv_heads) % 4 == 0)
+        TSM_TRY(ensure_scratch(m->ctx, m->ctx->attn, attention_stream_scratch_bytes(tokens, c.heads, cache->capacity)));
     return TSM_OK;
 }
 

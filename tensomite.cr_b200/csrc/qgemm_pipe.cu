@@ -21,7 +21,6 @@
 //
 // Shapes this kernel does not take (blocks per row not a multiple of 8, unaligned operands) stay with
 // matmul_mma_kernel.
-#include <cuda.h>
 #include <stdlib.h>
 
 #include <type_traits>
@@ -346,36 +345,6 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
         }
 }
 
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// cuTensorMapEncodeTiled from the driver that is already loaded (the library links the runtime only).
-EncodeTiled encode_tiled() {
-    static EncodeTiled fn = [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult found;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &found) != cudaSuccess || found != cudaDriverEntryPointSuccess)
-            ptr = nullptr;
-        return (EncodeTiled)ptr;
-    }();
-    return fn;
-}
-
-// A rank-2 map over `rows` rows of `width` elements (pitch `pitch_bytes`), copied in boxes of box_w x box_h elements.
-int make_map(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows, uint64_t pitch_bytes,
-             uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle swizzle) {
-    EncodeTiled encode = encode_tiled();
-    if (!encode) return fail(ctx, TSM_ERR_UNSUPPORTED, "the driver does not export cuTensorMapEncodeTiled");
-    cuuint64_t dims[2] = {width, rows};
-    cuuint64_t strides[1] = {pitch_bytes};
-    cuuint32_t box[2] = {box_w, box_h};
-    cuuint32_t steps[2] = {1, 1};
-    CUresult rc = encode(map, type, 2, const_cast<void*>(base), dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (rc != CUDA_SUCCESS) return fail(ctx, TSM_ERR_ARG, "cuTensorMapEncodeTiled refused a map (code " + std::to_string((int)rc) + ")");
-    return TSM_OK;
-}
-
 template <int KIND, int NT, int WC>
 int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     constexpr int COLS = 8 * NT * WC;
@@ -411,13 +380,13 @@ int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     }
     PipeMaps maps;
     const uint64_t nb = (uint64_t)p.nb;
-    TSM_TRY(make_map(ctx, &maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT16, p.w, nb * B / 2, (uint64_t)p.n, nb * B, kCB * B / 2, 16 * wr_max,
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT16, p.w, nb * B / 2, (uint64_t)p.n, nb * B, kCB * B / 2, 16 * wr_max,
                      CU_TENSOR_MAP_SWIZZLE_NONE));
-    TSM_TRY(make_map(ctx, &maps.acts, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.acts.qs, nb * 32, (uint64_t)p.m, nb * 32, 128, COLS,
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.acts, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.acts.qs, nb * 32, (uint64_t)p.m, nb * 32, 128, COLS,
                      CU_TENSOR_MAP_SWIZZLE_128B));
-    TSM_TRY(make_map(ctx, &maps.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.acts.scales, nb, (uint64_t)p.m, nb * 4, kCB, COLS,
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.acts.scales, nb, (uint64_t)p.m, nb * 4, kCB, COLS,
                      CU_TENSOR_MAP_SWIZZLE_32B));
-    TSM_TRY(make_map(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m, nb * 4,
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m, nb * 4,
                      kCB, COLS, CU_TENSOR_MAP_SWIZZLE_32B));
     dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
     kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
@@ -460,7 +429,7 @@ bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w
     if (getenv("TSM_NO_PIPE")) return false;
     int nb = k / 32;
     bool aligned = (((uintptr_t)w | (uintptr_t)a.qs | (uintptr_t)a.scales | (uintptr_t)(kind == TSM_Q4_1 ? a.sums : a.scales)) & 15) == 0;
-    return rows >= 1 && nb >= kCB && nb % kCB == 0 && aligned && encode_tiled() != nullptr;
+    return rows >= 1 && nb >= kCB && nb % kCB == 0 && aligned && tensor_maps_available();
 }
 
 int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,

@@ -32,15 +32,34 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 // Σ f(row[j]) in index order from 0f, each step rounded (the host's fold, devices/host.cr:391-403,
-// 348-361), by one thread; every thread receives the result.
+// 348-361); every thread receives the result.  All threads first write the terms ((row[j] - shift)² or
+// row[j]) to `terms`, padded to a multiple of 16 with +0 (adding +0 to a sum that started at +0 and only ever
+// had such terms added never changes it: the running sum is never -0); one thread then folds them with
+// 16-byte loads running ahead of the dependent adds, so a step costs the latency of one add.
 template <bool SQUARE>
-__device__ __forceinline__ float ordered_sum(const float* row, int n, float shift, float* scratch) {
+__device__ __forceinline__ float ordered_sum(const float* row, float* terms, int n, float shift, float* scratch) {
+    const int padded = (n + 15) & ~15;
+    for (int j = threadIdx.x; j < padded; j += blockDim.x) {
+        float v = 0.0f;
+        if (j < n) {
+            v = SQUARE ? __fsub_rn(row[j], shift) : row[j];
+            if (SQUARE) v = __fmul_rn(v, v);
+        }
+        terms[j] = v;
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
         float acc = 0.0f;
-        for (int j = 0; j < n; j++) {
-            float v = SQUARE ? __fsub_rn(row[j], shift) : row[j];
-            acc = SQUARE ? __fadd_rn(acc, __fmul_rn(v, v)) : __fadd_rn(acc, v);
+        const float4* t4 = (const float4*)terms;
+        float4 a = t4[0], b = t4[1], c = t4[2], d = t4[3];
+        for (int j = 0; j < padded; j += 16) {
+            float4 na = a, nb = b, nc = c, nd = d;
+            if (j + 16 < padded) na = t4[(j >> 2) + 4], nb = t4[(j >> 2) + 5], nc = t4[(j >> 2) + 6], nd = t4[(j >> 2) + 7];
+            acc = __fadd_rn(acc, a.x), acc = __fadd_rn(acc, a.y), acc = __fadd_rn(acc, a.z), acc = __fadd_rn(acc, a.w);
+            acc = __fadd_rn(acc, b.x), acc = __fadd_rn(acc, b.y), acc = __fadd_rn(acc, b.z), acc = __fadd_rn(acc, b.w);
+            acc = __fadd_rn(acc, c.x), acc = __fadd_rn(acc, c.y), acc = __fadd_rn(acc, c.z), acc = __fadd_rn(acc, c.w);
+            acc = __fadd_rn(acc, d.x), acc = __fadd_rn(acc, d.y), acc = __fadd_rn(acc, d.z), acc = __fadd_rn(acc, d.w);
+            a = na, b = nb, c = nc, d = nd;
         }
         scratch[0] = acc;
     }
@@ -53,8 +72,9 @@ __device__ __forceinline__ float ordered_sum(const float* row, int n, float shif
 template <bool LAYER>
 __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int n,
                             float eps, float* out, QuantOut q, int exact) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];  // [n], then the terms of the ordered sums, 16-byte aligned
     __shared__ float scratch[32];
+    float* terms = row + ((n + 3) & ~3);
     int r = blockIdx.x;
     const float* xr = x + (int64_t)r * n;
     for (int j = threadIdx.x; j < n; j += blockDim.x) row[j] = xr[j];
@@ -64,7 +84,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     if (LAYER) {
         float total;
         if (exact) {
-            total = ordered_sum<false>(row, n, 0.0f, scratch);
+            total = ordered_sum<false>(row, terms, n, 0.0f, scratch);
         } else {
             float part = 0.0f;
             for (int j = threadIdx.x; j < n; j += blockDim.x) part += row[j];
@@ -74,7 +94,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     }
     float squares;
     if (exact) {
-        squares = ordered_sum<true>(row, n, mean, scratch);
+        squares = ordered_sum<true>(row, terms, n, mean, scratch);
     } else {
         float part = 0.0f;
         for (int j = threadIdx.x; j < n; j += blockDim.x) {
@@ -107,16 +127,16 @@ static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w,
                        float* out, const QuantizedActs* quantized) {
     if (rows == 0 || n == 0) return TSM_OK;
     if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
-    if ((size_t)n * 4 > 160 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "norm rows over 40960 values");
+    if ((size_t)n * 4 > 100 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "norm rows over 25600 values");
     int threads = n >= 2048 ? 512 : n >= 512 ? 256 : 128;
-    size_t smem = (size_t)n * 4;
+    size_t smem = (size_t)(((n + 3) & ~3) + ((n + 15) & ~15)) * 4;  // the row and the terms of its ordered sums
     QuantOut q = quant_out(quantized);
     int exact = ctx->mode == TSM_EXACT;
     if (layer) {
-        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         norm_kernel<true><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
     } else {
-        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
         norm_kernel<false><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
     }
     count_launch(ctx);
