@@ -533,7 +533,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         return launch_fast<128>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
     if (!out) return fail(ctx, TSM_ERR_ARG, "ordered attention needs an F32 output");
     bool launched = false;
-    if (attention_stream_fits(heads, width, kv_heads, q, q_stride, k, v)) {
+    if (attention_stream_fits(ctx, tokens, heads, width, kv_heads, q, q_stride, k, v)) {
         TSM_TRY(ensure_scratch(ctx, ctx->attn, attention_stream_scratch_bytes(tokens, heads, capacity)));
         TSM_TRY(launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
                                         (float*)ctx->attn.ptr));

@@ -298,8 +298,15 @@ __global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(Strea
 int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { return (int64_t)tokens * heads * capacity * 4 + 256; }
 
 // Whether the streaming kernel takes this call.  `scratch` must hold attention_stream_scratch_bytes.
-bool attention_stream_fits(int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k, const float* v) {
-    if (getenv("TSM_NO_ATTN_STREAM")) return false;
+bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k,
+                           const float* v) {
+    // Measured on B200: with at most two CTAs per SM this kernel is the faster one (241 against 258 us for 16 streams
+    // of up to 4096 positions); with more, the shared-memory data path saturates (every 16-byte load of a query or a
+    // weight that all lanes share still costs four wavefronts) and attention_exact_kernel, whose CTAs hold eight
+    // warps, finishes sooner (360 against 408 us for 64 streams).  TSM_ATTN_STREAM=0 / 1 forces the choice.
+    static const char* forced = getenv("TSM_ATTN_STREAM");
+    if (forced && forced[0] == '0') return false;
+    if (!(forced && forced[0] == '1') && kv_heads > 0 && (int64_t)tokens * (heads / 4) > 2 * (int64_t)ctx->sm_count) return false;
     bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
     return width == 128 && kv_heads > 0 && heads % kv_heads == 0 && (heads / kv_heads) % 4 == 0 && aligned && tensor_maps_available();
 }

@@ -117,7 +117,8 @@ bool tensor_maps_available();
 int make_tensor_map_2d(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows,
                        uint64_t pitch_bytes, uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle swizzle);
 int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity);
-bool attention_stream_fits(int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k, const float* v);
+bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k,
+                           const float* v);
 int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
                             float* scratch);
