@@ -308,6 +308,9 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 model and the matvec sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="with --gpus N > 1: dp = every rank decodes its own streams on a whole replica (no collective); "
+                         "tp = the ranks share one model split by tensor parallelism (NCCL all-gathers) and decode the same streams")
     ap.add_argument("--case", default=None, help="time one kernel on a small case instead (see kernel_case), e.g. matvec,q4_0,128256,4096")
     ap.add_argument("--repeats", type=int, default=3, help="timed launches of --case")
     args = ap.parse_args()
@@ -334,13 +337,19 @@ def main():
         print(json.dumps(kernel_case(pkg, dev, torch, stream, args.case, args.repeats, peak["hbm_gbs"])))
         dev.close()
         return
-    lengths = draw_lengths(w, rank)
+    tp = world if (args.parallelism == "tp" and args.impl == "ours") else 1
+    if tp > 1:
+        pkg.groups.join_tensor_parallel(dev, dist)
+    data_rank = 0 if tp > 1 else rank          # tensor-parallel ranks decode the same streams
+    jobs = 1 if tp > 1 else world              # independent sets of streams in the job
+    lengths = draw_lengths(w, data_rank)
     model = pkg.Model.random(dev, model_config(w), KIND[w["kind"]], seed=20260101)
     dev.sync()
     rows = w["rows"]
     config = dict(workload=w["name"], streams_per_gpu=rows, kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
                   kv_dtype="f32", weights=w["kind"], l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
-                  parallelism=f"dp{world}" if world > 1 else "single gpu")
+                  parallelism=(f"tp{world}: projections split by output rows, 4 NCCL all-gathers per layer" if tp > 1 else
+                               f"dp{world}: a replica and {rows} streams per GPU, no collective") if world > 1 else "single gpu")
 
     if args.impl == "reference":
         sample_rows, sample_steps = min(rows, 2), 1
@@ -370,7 +379,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    cache, ids = make_streams(pkg, dev, model, w, lengths, W + K + 2, rank)
+    cache, ids = make_streams(pkg, dev, model, w, lengths, W + K + 2, data_rank)
     dev.sync()
     # ---- value: the step loop resident on the device ----------------------------------------------
     if W:
@@ -386,13 +395,13 @@ def main():
         barrier()
     seconds = max_over_ranks(start.elapsed_time(stop) / 1e3)
     counters = dev.counters()
-    value = rows * K * world / seconds
+    value = rows * K * jobs / seconds
     clock_summary = clocks.summary()
     mid_lengths = lengths + W + K // 2
     total_bytes, weight_bytes, kv_bytes = step_bytes(w, mid_lengths)
 
     # ---- e2e: one C-ABI call per step with host buffers ---------------------------------------------
-    refill(cache, lengths, rank)
+    refill(cache, lengths, data_rank)
     dev.sync()
     step_ids = ids.copy()
     for _ in range(W):
@@ -404,22 +413,22 @@ def main():
     torch.cuda.synchronize()
     e2e_seconds = max_over_ranks(time.perf_counter() - t0)
     barrier()
-    e2e = dict(value=rows * K * world / e2e_seconds, unit="tokens/s", h2d_bytes_per_step=rows * 16, d2h_bytes_per_step=rows * 4 + 16,
+    e2e = dict(value=rows * K * jobs / e2e_seconds, unit="tokens/s", h2d_bytes_per_step=rows * 16, d2h_bytes_per_step=rows * 4 + 16,
                ms_per_step=e2e_seconds / K * 1e3)
 
     line = dict(metric="decode_tokens_per_second", value=value, unit="tokens/s", n_gpus=world, steps=K, warmup=W,
-                ms_per_step=seconds / K * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None,
+                ms_per_step=seconds / K * 1e3, higher_is_better=True, scaling="strong" if tp > 1 else "weak", vs_baseline=None,
                 dtype="int8 x int8 -> int32 blocks, f32 accumulate", data="synthetic", config=config, e2e=e2e,
                 gpu_launches=int(counters["launches"]), clocks=clock_summary,
                 step_roofline=dict(bytes_per_step=total_bytes, weight_bytes=weight_bytes, kv_bytes=kv_bytes,
-                                   achieved_gbs=total_bytes / (seconds / K) / 1e9, peak_gbs=peak["hbm_gbs"], peak_kind=peak_kind,
-                                   frac=total_bytes / (seconds / K) / 1e9 / peak["hbm_gbs"]))
+                                   achieved_gbs=total_bytes / (seconds / K) / 1e9, peak_gbs=peak["hbm_gbs"] * tp, peak_kind=peak_kind,
+                                   frac=total_bytes / (seconds / K) / 1e9 / (peak["hbm_gbs"] * tp)))
 
     if rank == 0:
         # ---- roofline of the dominant kernels, timed alone on the same buffers -------------------------
         import ctypes as C
         c = model.config
-        hw, H, KV = c["head_width"], c["heads"], c["kv_heads"]
+        hw, H, KV = c["head_width"], c["heads"] // tp, c["kv_heads"] // tp   # a tensor-parallel rank attends over its own heads
         table = np.stack([np.arange(rows), lengths, lengths + 1], axis=1).astype(np.int32)
         tb = dev.tensor(table)
         q = dev.tensor(np.random.default_rng(3).normal(0, 1, (rows, H * hw)).astype(np.float32))

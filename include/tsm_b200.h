@@ -209,6 +209,20 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
  * feeds its next step on the device (the loop of Generative#generate, generative.cr:181-188, for all rows
  * at once).  ids[row] is each row's first token; tokens receives [steps, rows] on the host. */
 int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int steps, int32_t* tokens);
+/* ---- several GPUs -----------------------------------------------------------------------------------------
+ * The reference runs a model on one device (src/tensomite/device.cr); these entry points have no counterpart there.
+ * One process per GPU.  Independent streams need nothing here: every process loads the whole model and decodes its own
+ * rows.  A model too large or too slow for one GPU is split by tensor parallelism: tsm_tp_init joins the context to a
+ * group of `world` ranks (NCCL over NVLink; the 128-byte id comes from tsm_tp_unique_id on one rank and is carried
+ * to the others by the host), and a model then loaded or drawn on that context holds only its rank's rows of every
+ * projection (its heads of q, k and v, its slice of gate/up, o, down and the vocabulary head) and its own kv heads of
+ * the cache.  Every rank calls tsm_forward / tsm_decode / tsm_decode_run / tsm_generate with the same arguments and
+ * receives the same tokens and logits, bit for bit those of one GPU: projections are split by output rows only, so
+ * no sum is reordered.  Heads, kv heads, width, hidden width and vocabulary must divide by `world`. */
+int tsm_tp_unique_id(uint8_t* out /* [128] */);
+int tsm_tp_init(tsm_ctx* ctx, int rank, int world, const uint8_t* id /* [128] */);
+int tsm_tp_info(tsm_ctx* ctx, int* rank, int* world);
+
 /* Generative#generate with Sampler.greedy (generative.cr:177-190): `count` tokens after `prompt`. */
 int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens);
 

@@ -6,5 +6,5 @@ through ctypes and mirrors the reference's host-side names on top of it; there i
 Python or CPU implementation of any operator here, and every call fails loudly when the
 library or a CUDA device is missing.
 """
-from . import build, gguf  # noqa: F401
+from . import build, gguf, groups  # noqa: F401
 from .binding import *  # noqa: F401,F403

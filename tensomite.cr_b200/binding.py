@@ -82,6 +82,15 @@ def library():
     return lib
 
 
+def tp_unique_id():
+    """128 bytes that name a new tensor-parallel group; made on one rank, carried to the others by the host."""
+    raw = (C.c_uint8 * 128)()
+    rc = library().tsm_tp_unique_id(raw)
+    if rc != 0:
+        raise DeviceError("tsm_tp_unique_id: " + library().tsm_status_name(rc).decode() + " (is NCCL loadable?)")
+    return bytes(raw)
+
+
 def check_exports():
     lib = library()
     missing = [name for name in declared_symbols() if not hasattr(lib, name)]
@@ -142,6 +151,19 @@ class B200:
 
     def set_mode(self, mode):
         self.check(self.lib.tsm_set_mode(self.ctx, C.c_int(mode)), "tsm_set_mode")
+
+    def tp_init(self, rank, world, group_id):
+        """Joins this device to a tensor-parallel group of `world` ranks; `group_id` is tp_unique_id() of one rank.
+        Models loaded or drawn afterwards hold this rank's rows only."""
+        if world > 1 and len(group_id) != 128:
+            raise ShapeError("a group id is 128 bytes")
+        raw = (C.c_uint8 * 128).from_buffer_copy(bytes(group_id)) if world > 1 else None
+        self.check(self.lib.tsm_tp_init(self.ctx, C.c_int(rank), C.c_int(world), raw), "tsm_tp_init")
+
+    def tp_info(self):
+        rank, world = C.c_int(), C.c_int()
+        self.check(self.lib.tsm_tp_info(self.ctx, C.byref(rank), C.byref(world)), "tsm_tp_info")
+        return rank.value, world.value
 
     def alloc(self, nbytes):
         ptr = C.c_uint64()

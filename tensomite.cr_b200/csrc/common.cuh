@@ -52,6 +52,8 @@ struct tsm_ctx {
     tsm::Scratch attn;                        // split-K partials
     tsm::Scratch order;                       // attention's longest-first token order (operator-level calls)
     uint64_t scratch_generation = 1;          // bumped whenever a scratch buffer moves
+    int tp_rank = 0, tp_world = 1;            // this context's place in a tensor-parallel group
+    void* comm = nullptr;                     // its NCCL communicator
     std::mutex message_lock;
     std::string message;
     tsm_counters counters{};
@@ -112,6 +114,10 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out);
 bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+// Tensor-parallel exchanges (collective.cu).
+int tp_all_gather(tsm_ctx* ctx, void* buffer, int64_t bytes);
+int launch_interleave(tsm_ctx* ctx, const float* gathered, float* dst, int rows, int width, int parts, bool add);
+void tp_release(tsm_ctx* ctx);
 // A rank-2 tensor map over `rows` rows of `width` elements (row pitch in bytes), copied in boxes of box_w x box_h.
 bool tensor_maps_available();
 int make_tensor_map_2d(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows,

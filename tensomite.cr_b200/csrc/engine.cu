@@ -8,6 +8,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <memory>
 
 #include "common.cuh"
@@ -45,6 +46,9 @@ struct Workspace {
     float* up = nullptr;     // [T, 2*hidden | hidden]
     float* logits = nullptr; // [T, vocab]
     int* picks = nullptr;    // [T]
+    float* tp_parts = nullptr;   // tensor-parallel: [ranks][T, widest / ranks], the ranks' column slices as gathered
+    float* tp_rows = nullptr;    //                  [T, widest], the same back in row order
+    float* tp_best = nullptr;    //                  [ranks][T] best logit of each rank's vocabulary slice, then [ranks][T] its index
     void* qa = nullptr;      // quantised activations, K = width
     void* qb = nullptr;      // K = heads * hw
     void* qc = nullptr;      // K = hidden
@@ -66,6 +70,13 @@ struct tsm_model {
     std::map<std::string, Named> named;
     Workspace ws;
     uint64_t ws_generation = 1;
+    int tp = 1, tp_rank = 0;     // tensor-parallel group of the context the model was built on
+    Linear head_local;           // this rank's rows of the vocabulary head (a view when the head is the embedding table)
+};
+
+// Rows [start, start + count) of a matrix.
+struct RowRange {
+    int64_t start, count;
 };
 
 struct tsm_cache {
@@ -83,6 +94,40 @@ struct tsm_cache {
 };
 
 namespace tsm {
+
+// Which rows of a projection a rank of a tensor-parallel group holds.  Every projection is split by OUTPUT rows, so
+// each output's sum over blocks stays on one GPU, whole and in block order: the sharded model's bits are the single
+// GPU's.  Joined projections keep their parts: a rank takes its heads' rows of q, of k and of v (its slice of gate
+// and of up).  An empty list means all rows.
+enum { SHARD_QKV, SHARD_WIDTH, SHARD_UP, SHARD_VOCAB };
+static std::vector<RowRange> shard_ranges(const tsm_model* m, int what) {
+    std::vector<RowRange> ranges;
+    if (m->tp <= 1) return ranges;
+    const tsm_model_config& c = m->cfg;
+    int64_t G = m->tp, r = m->tp_rank;
+    int64_t qn = (int64_t)c.heads * c.head_width, kvn = (int64_t)c.kv_heads * c.head_width;
+    switch (what) {
+        case SHARD_QKV:
+            ranges = {{r * qn / G, qn / G}, {qn + r * kvn / G, kvn / G}, {qn + kvn + r * kvn / G, kvn / G}};
+            break;
+        case SHARD_WIDTH: ranges = {{r * c.width / G, c.width / G}}; break;
+        case SHARD_UP:
+            ranges = {{r * c.hidden / G, c.hidden / G}};
+            if (c.arch == 0) ranges.push_back({c.hidden + r * c.hidden / G, c.hidden / G});
+            break;
+        case SHARD_VOCAB: ranges = {{r * c.vocab / G, c.vocab / G}}; break;
+    }
+    return ranges;
+}
+
+static int check_sharding(tsm_model* m) {
+    if (m->tp <= 1) return TSM_OK;
+    const tsm_model_config& c = m->cfg;
+    int G = m->tp;
+    if (c.heads % G || c.kv_heads % G || c.width % G || c.hidden % G || c.vocab % G)
+        return fail(m->ctx, TSM_ERR_ARG, "heads, key/value heads, width, hidden width and vocabulary must all divide by the " + std::to_string(G) + " ranks");
+    return TSM_OK;
+}
 
 static int dev_alloc(tsm_model* m, int64_t bytes, void** out) {
     TSM_TRY(pool_alloc(m->ctx, bytes, out));
@@ -326,7 +371,8 @@ struct RowSource {
 };
 
 // Uploads one or several [n_i, k] block tensors as one row-joined weight (Linear.merge, modules.cr:36-54).
-static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& parts, int k, int expect_n, Linear* out) {
+static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& parts, int k, int expect_n, Linear* out,
+                       const std::vector<RowRange>& ranges = {}) {
     int kind = -2;
     int64_t total_rows = 0;
     for (auto& part : parts) {
@@ -361,9 +407,35 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
         }
         at += rows;
     }
+    if (!ranges.empty()) {  // a tensor-parallel rank keeps its rows only
+        std::vector<uint8_t> kept;
+        int64_t rows = 0;
+        for (auto& range : ranges) {
+            kept.insert(kept.end(), staging.begin() + (size_t)(range.start * row_bytes), staging.begin() + (size_t)((range.start + range.count) * row_bytes));
+            rows += range.count;
+        }
+        staging.swap(kept);
+        expect_n = (int)rows;
+    }
     out->kind = kind, out->n = expect_n, out->k = k;
     TSM_TRY(dev_alloc(m, (int64_t)staging.size(), (void**)&out->w));
     return tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)out->w, staging.data(), (int64_t)staging.size());
+}
+
+// Replaces a full bias vector by the entries of a rank's rows.
+static int shard_bias(tsm_model* m, float** bias, const std::vector<RowRange>& ranges) {
+    if (!*bias || ranges.empty()) return TSM_OK;
+    int64_t rows = 0;
+    for (auto& range : ranges) rows += range.count;
+    float* local = nullptr;
+    TSM_TRY(dev_alloc(m, rows * 4, (void**)&local));
+    int64_t at = 0;
+    for (auto& range : ranges) {
+        TSM_CUDA(m->ctx, cudaMemcpyAsync(local + at, *bias + range.start, (size_t)range.count * 4, cudaMemcpyDeviceToDevice, m->ctx->stream));
+        at += range.count;
+    }
+    *bias = local;  // the full vector stays owned by the model and is freed with it
+    return TSM_OK;
 }
 
 static int load_llama(tsm_model* m, GgufFile& f) {
@@ -395,7 +467,8 @@ static int load_llama(tsm_model* m, GgufFile& f) {
     std::vector<std::string> used;
     auto use = [&](const std::string& name) { used.push_back(name); return name; };
     TSM_TRY(upload_rows(m, f, {{use("token_embd.weight"), 0}}, c.width, c.vocab, &m->embed));
-    if (!c.tied) TSM_TRY(upload_rows(m, f, {{use("output.weight"), 0}}, c.width, c.vocab, &m->head));
+    TSM_TRY(check_sharding(m));
+    if (!c.tied) TSM_TRY(upload_rows(m, f, {{use("output.weight"), 0}}, c.width, c.vocab, &m->head, shard_ranges(m, SHARD_VOCAB)));
     else m->head = m->embed;
     TSM_TRY(upload_f32(m, f, use("output_norm.weight"), c.width, &m->final_w));
     int qn = c.heads * c.head_width, kvn = c.kv_heads * c.head_width;
@@ -406,10 +479,11 @@ static int load_llama(tsm_model* m, GgufFile& f) {
         TSM_TRY(upload_f32(m, f, use(p + "attn_norm.weight"), c.width, &l.norm1_w));
         TSM_TRY(upload_f32(m, f, use(p + "ffn_norm.weight"), c.width, &l.norm2_w));
         TSM_TRY(upload_rows(m, f, {{use(p + "attn_q.weight"), c.heads}, {use(p + "attn_k.weight"), c.kv_heads}, {use(p + "attn_v.weight"), 0}},
-                            c.width, qn + 2 * kvn, &l.qkv));
-        TSM_TRY(upload_rows(m, f, {{use(p + "attn_output.weight"), 0}}, qn, c.width, &l.o));
-        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_gate.weight"), 0}, {use(p + "ffn_up.weight"), 0}}, c.width, 2 * c.hidden, &l.up));
-        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_down.weight"), 0}}, c.hidden, c.width, &l.down));
+                            c.width, qn + 2 * kvn, &l.qkv, shard_ranges(m, SHARD_QKV)));
+        TSM_TRY(upload_rows(m, f, {{use(p + "attn_output.weight"), 0}}, qn, c.width, &l.o, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_gate.weight"), 0}, {use(p + "ffn_up.weight"), 0}}, c.width, 2 * c.hidden, &l.up,
+                            shard_ranges(m, SHARD_UP)));
+        TSM_TRY(upload_rows(m, f, {{use(p + "ffn_down.weight"), 0}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
     }
     // any tensor left over is an error, as the reference's loader raises (llama.cr:202-203)
     for (auto& name : f.order) {
@@ -447,6 +521,7 @@ static int load_gpt2(tsm_model* m, GgufFile& f) {
     c.rope_theta = 0;
     c.tied = 1;
     TSM_TRY(check_config(m->ctx, c));
+    TSM_TRY(check_sharding(m));
     TSM_TRY(upload_rows(m, f, {{"wte.weight", 0}}, c.width, c.vocab, &m->embed));
     TSM_TRY(upload_rows(m, f, {{"wpe.weight", 0}}, c.width, c.context, &m->wpe));
     m->head = m->embed;
@@ -460,31 +535,61 @@ static int load_gpt2(tsm_model* m, GgufFile& f) {
         TSM_TRY(upload_f32(m, f, p + "ln_1.bias", c.width, &l.norm1_b));
         TSM_TRY(upload_f32(m, f, p + "ln_2.weight", c.width, &l.norm2_w));
         TSM_TRY(upload_f32(m, f, p + "ln_2.bias", c.width, &l.norm2_b));
-        TSM_TRY(upload_rows(m, f, {{p + "attn.c_attn.weight", 0}}, c.width, 3 * c.width, &l.qkv));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_attn.weight", 0}}, c.width, 3 * c.width, &l.qkv, shard_ranges(m, SHARD_QKV)));
         TSM_TRY(upload_bias(m, f, p + "attn.c_attn.bias", 3 * c.width, &l.qkv.bias));
-        TSM_TRY(upload_rows(m, f, {{p + "attn.c_proj.weight", 0}}, c.width, c.width, &l.o));
+        TSM_TRY(shard_bias(m, &l.qkv.bias, shard_ranges(m, SHARD_QKV)));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_proj.weight", 0}}, c.width, c.width, &l.o, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(upload_bias(m, f, p + "attn.c_proj.bias", c.width, &l.o.bias));
-        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_fc.weight", 0}}, c.width, c.hidden, &l.up));
+        TSM_TRY(shard_bias(m, &l.o.bias, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_fc.weight", 0}}, c.width, c.hidden, &l.up, shard_ranges(m, SHARD_UP)));
         TSM_TRY(upload_bias(m, f, p + "mlp.c_fc.bias", c.hidden, &l.up.bias));
-        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0}}, c.hidden, c.width, &l.down));
+        TSM_TRY(shard_bias(m, &l.up.bias, shard_ranges(m, SHARD_UP)));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(upload_bias(m, f, p + "mlp.c_proj.bias", c.width, &l.down.bias));
+        TSM_TRY(shard_bias(m, &l.down.bias, shard_ranges(m, SHARD_WIDTH)));
     }
     return TSM_OK;
 }
 
 // ---- random models (Llama.new / GPT2.new with Init.normal(0.02), then Module#quantize) ---------------
 
-static int random_linear(tsm_model* m, int kind, int n, int k, uint64_t seed, bool with_bias, float* scratch, Linear* out) {
-    out->kind = kind, out->n = n, out->k = k;
+// The whole matrix is drawn (so that a rank's rows are the rows of the one-GPU model), the rank's rows are kept.
+static int random_linear(tsm_model* m, int kind, int n, int k, uint64_t seed, bool with_bias, float* scratch, Linear* out,
+                         const std::vector<RowRange>& ranges = {}) {
     int64_t count = (int64_t)n * k;
     TSM_TRY(launch_normal_fill(m->ctx, scratch, count, 0.0f, 0.02f, seed));
-    TSM_TRY(dev_alloc(m, weight_bytes(kind, n, k), (void**)&out->w));
-    TSM_TRY(launch_quantize_blocks(m->ctx, scratch, count, kind, out->w));
+    int64_t local = n;
+    if (!ranges.empty()) {
+        local = 0;
+        for (auto& range : ranges) local += range.count;
+    }
+    out->kind = kind, out->n = (int)local, out->k = k;
+    TSM_TRY(dev_alloc(m, weight_bytes(kind, local, k), (void**)&out->w));
+    if (ranges.empty()) {
+        TSM_TRY(launch_quantize_blocks(m->ctx, scratch, count, kind, out->w));
+    } else {
+        int64_t at = 0;
+        for (auto& range : ranges) {
+            TSM_TRY(launch_quantize_blocks(m->ctx, scratch + range.start * k, range.count * k, kind, out->w + weight_bytes(kind, at, k)));
+            at += range.count;
+        }
+    }
     if (with_bias) {
-        TSM_TRY(dev_alloc(m, (int64_t)n * 4, (void**)&out->bias));
-        TSM_TRY(launch_fill(m->ctx, out->bias, n, 0.0f));
+        TSM_TRY(dev_alloc(m, local * 4, (void**)&out->bias));
+        TSM_TRY(launch_fill(m->ctx, out->bias, local, 0.0f));
     }
     return TSM_OK;
+}
+
+// This rank's rows of the vocabulary head: the head itself on one GPU or when it was built sharded, else a view of the
+// (replicated) embedding table it is tied to.
+static void set_head_local(tsm_model* m) {
+    m->head_local = m->head;
+    if (m->tp > 1 && m->head.n == m->cfg.vocab) {
+        int64_t rows = m->cfg.vocab / m->tp;
+        m->head_local.n = (int)rows;
+        m->head_local.w = m->head.w + weight_bytes(m->head.kind, rows * m->tp_rank, m->head.k);
+    }
 }
 
 static int constant_vector(tsm_model* m, int n, float value, float** out) {
@@ -494,6 +599,7 @@ static int constant_vector(tsm_model* m, int n, float value, float** out) {
 
 static int build_random(tsm_model* m, int kind, uint64_t seed) {
     const tsm_model_config& c = m->cfg;
+    TSM_TRY(check_sharding(m));
     int qn = c.heads * c.head_width, kvn = c.kv_heads * c.head_width;
     int upn = c.arch == 0 ? 2 * c.hidden : c.hidden;
     int64_t biggest = (int64_t)c.vocab * c.width;
@@ -508,10 +614,11 @@ static int build_random(tsm_model* m, int kind, uint64_t seed) {
         if ((rc = random_linear(m, kind, c.vocab, c.width, t++, false, scratch, &m->embed))) break;
         if (gpt && (rc = random_linear(m, kind, c.context, c.width, t++, false, scratch, &m->wpe))) break;
         if (!c.tied) {
-            if ((rc = random_linear(m, kind, c.vocab, c.width, t++, false, scratch, &m->head))) break;
+            if ((rc = random_linear(m, kind, c.vocab, c.width, t++, false, scratch, &m->head, shard_ranges(m, SHARD_VOCAB)))) break;
         } else {
             m->head = m->embed;
         }
+        set_head_local(m);
         if ((rc = constant_vector(m, c.width, 1.0f, &m->final_w))) break;
         if (gpt && (rc = constant_vector(m, c.width, 0.0f, &m->final_b))) break;
         m->layers.resize(c.layers);
@@ -520,10 +627,10 @@ static int build_random(tsm_model* m, int kind, uint64_t seed) {
             if ((rc = constant_vector(m, c.width, 1.0f, &l.norm1_w))) break;
             if ((rc = constant_vector(m, c.width, 1.0f, &l.norm2_w))) break;
             if (gpt && ((rc = constant_vector(m, c.width, 0.0f, &l.norm1_b)) || (rc = constant_vector(m, c.width, 0.0f, &l.norm2_b)))) break;
-            if ((rc = random_linear(m, kind, qn + 2 * kvn, c.width, t++, gpt, scratch, &l.qkv))) break;
-            if ((rc = random_linear(m, kind, c.width, qn, t++, gpt, scratch, &l.o))) break;
-            if ((rc = random_linear(m, kind, upn, c.width, t++, gpt, scratch, &l.up))) break;
-            if ((rc = random_linear(m, kind, c.width, c.hidden, t++, gpt, scratch, &l.down))) break;
+            if ((rc = random_linear(m, kind, qn + 2 * kvn, c.width, t++, gpt, scratch, &l.qkv, shard_ranges(m, SHARD_QKV)))) break;
+            if ((rc = random_linear(m, kind, c.width, qn, t++, gpt, scratch, &l.o, shard_ranges(m, SHARD_WIDTH)))) break;
+            if ((rc = random_linear(m, kind, upn, c.width, t++, gpt, scratch, &l.up, shard_ranges(m, SHARD_UP)))) break;
+            if ((rc = random_linear(m, kind, c.width, c.hidden, t++, gpt, scratch, &l.down, shard_ranges(m, SHARD_WIDTH)))) break;
         }
     } while (0);
     cudaStreamSynchronize(m->ctx->stream);
@@ -537,7 +644,7 @@ static int build_random(tsm_model* m, int kind, uint64_t seed) {
 
 static void free_workspace(tsm_model* m) {
     Workspace& w = m->ws;
-    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc};
+    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc, w.tp_parts, w.tp_rows, w.tp_best};
     for (void* b : bufs) pool_release(m->ctx, b);
     if (w.host) cudaFreeHost(w.host);
     w = Workspace{};
@@ -564,6 +671,12 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     TSM_TRY(pool_alloc(ctx, T * upn * 4, (void**)&w.up));
     TSM_TRY(pool_alloc(ctx, T * c.vocab * 4, (void**)&w.logits));
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.picks));
+    if (m->tp > 1) {
+        int64_t widest = std::max<int64_t>(std::max<int64_t>(qn, c.width), std::max<int64_t>(c.hidden, c.vocab));
+        TSM_TRY(pool_alloc(ctx, T * widest * 4, (void**)&w.tp_parts));
+        TSM_TRY(pool_alloc(ctx, T * std::max<int64_t>(std::max<int64_t>(qn, c.width), c.hidden) * 4, (void**)&w.tp_rows));
+        TSM_TRY(pool_alloc(ctx, (int64_t)m->tp * 2 * T * 4, (void**)&w.tp_best));
+    }
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.width), &w.qa));
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, qn), &w.qb));
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.hidden), &w.qc));
@@ -576,6 +689,98 @@ static int ensure_workspace(tsm_model* m, int tokens) {
 static int product(tsm_model* m, const QuantizedActs& a, int rows, const Linear& l, const float* residual, float* out) {
     if (l.kind == TSM_F32) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "F32 matrices are not supported by this engine; quantise the model");
     return launch_block_matmul(m->ctx, a, rows, l.k, l.w, l.kind, l.n, l.bias, residual, out);
+}
+
+// Tensor-parallel greedy pick: every rank holds, for each row, the best logit of its vocabulary slice and that logit's
+// index within the slice ([ranks][2][rows] as gathered).  The highest wins; equal values go to the lower rank, whose
+// slice holds the lower indices (Sampler.greedy keeps the first maximum).
+__global__ void combine_picks_kernel(const float* __restrict__ best, int rows, int ranks, int slice, int* picks) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= rows) return;
+    float top = best[t];
+    int who = 0;
+    for (int r = 1; r < ranks; r++) {
+        float v = best[(int64_t)r * 2 * rows + t];
+        if (v > top) top = v, who = r;
+    }
+    int index = ((const int*)best)[(int64_t)who * 2 * rows + rows + t];
+    picks[t] = who * slice + index;
+}
+
+// One layer and the head of a tensor-parallel step.  Projections are split by output rows (shard_ranges), so a rank
+// computes whole outputs in block order; what the next projection needs from the other ranks arrives by an in-place
+// all-gather of column slices ([ranks][tokens, slice]) and is put back in row order by launch_interleave, which also
+// performs the residual add where one follows.  Norms and quantisers run on full rows on every rank.  The bits are
+// those of the one-GPU step.
+static int launch_layer_sharded(tsm_model* m, tsm_cache* cache, int i, int total, const int* order, const QuantizedActs& qa,
+                                const QuantizedActs& qb, const QuantizedActs& qc, bool ordered, float scale) {
+    const tsm_model_config& c = m->cfg;
+    tsm_ctx* ctx = m->ctx;
+    Workspace& w = m->ws;
+    Layer& l = m->layers[i];
+    const int G = m->tp, r = m->tp_rank, hw = c.head_width;
+    const int heads_l = c.heads / G, kv_l = c.kv_heads / G, qn = c.heads * hw, qn_l = heads_l * hw, qkvn_l = qn_l + 2 * kv_l * hw;
+    const int hid_l = c.hidden / G, w_l = c.width / G;
+    (void)ordered;
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
+    else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
+    TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+    TSM_TRY(launch_rope_append(ctx, w.qkv, total, heads_l, kv_l, hw, c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr,
+                               c.context, w.table, cache->keys[i], cache->values[i], cache->rows, cache->capacity));
+    TSM_TRY(launch_attention(ctx, w.qkv, qkvn_l, total, heads_l, hw, cache->keys[i], cache->values[i], cache->rows, kv_l, cache->capacity,
+                             w.table, scale, w.tp_parts + (int64_t)r * total * qn_l, nullptr, order));
+    TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * qn_l * 4));
+    TSM_TRY(launch_interleave(ctx, w.tp_parts, w.tp_rows, total, qn_l, G, false));
+    TSM_TRY(launch_quantize_rows(ctx, w.tp_rows, total, qn, qn, (float*)qb.scales, (float*)qb.sums, (int*)qb.totals, (int8_t*)qb.qs));
+    TSM_TRY(product(m, qb, total, l.o, nullptr, w.tp_parts + (int64_t)r * total * w_l));
+    TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * w_l * 4));
+    TSM_TRY(launch_interleave(ctx, w.tp_parts, w.x, total, w_l, G, true));
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
+    else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
+    TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
+    float* hidden_part = w.tp_parts + (int64_t)r * total * hid_l;
+    if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + hid_l, total, hid_l, 2 * (int64_t)hid_l, hidden_part, nullptr));
+    else TSM_TRY(launch_gelu(ctx, w.up, total, hid_l, hidden_part, nullptr));
+    TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * hid_l * 4));
+    TSM_TRY(launch_interleave(ctx, w.tp_parts, w.tp_rows, total, hid_l, G, false));
+    TSM_TRY(launch_quantize_rows(ctx, w.tp_rows, total, c.hidden, c.hidden, (float*)qc.scales, (float*)qc.sums, (int*)qc.totals, (int8_t*)qc.qs));
+    TSM_TRY(product(m, qc, total, l.down, nullptr, w.tp_parts + (int64_t)r * total * w_l));
+    TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * w_l * 4));
+    TSM_TRY(launch_interleave(ctx, w.tp_parts, w.x, total, w_l, G, true));
+    return TSM_OK;
+}
+
+// The head of a tensor-parallel step: this rank's vocabulary slice, the greedy pick across ranks, and (when asked) the
+// full logits in ws.logits.
+static int launch_head_sharded(tsm_model* m, const QuantizedActs& qh, int outputs, bool pick, bool full_logits) {
+    const tsm_model_config& c = m->cfg;
+    tsm_ctx* ctx = m->ctx;
+    Workspace& w = m->ws;
+    const int G = m->tp, r = m->tp_rank, slice = c.vocab / G;
+    Linear head = m->head_local;
+    head.bias = nullptr;
+    float* mine = w.tp_parts + (int64_t)r * outputs * slice;
+    TSM_TRY(launch_block_matmul(ctx, qh, outputs, head.k, head.w, head.kind, head.n, nullptr, nullptr, mine));
+    if (pick) {
+        float* best = w.tp_best + (int64_t)r * 2 * outputs;
+        TSM_TRY(launch_topk(ctx, mine, outputs, slice, 1, (int*)(best + outputs), best));
+        TSM_TRY(tp_all_gather(ctx, w.tp_best, (int64_t)2 * outputs * 4));
+        combine_picks_kernel<<<(outputs + 255) / 256, 256, 0, ctx->stream>>>(w.tp_best, outputs, G, slice, w.picks);
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+    }
+    if (full_logits) {
+        TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)outputs * slice * 4));
+        TSM_TRY(launch_interleave(ctx, w.tp_parts, w.logits, outputs, slice, G, false));
+    }
+    return TSM_OK;
+}
+
+// After a tensor-parallel step that only picked tokens: the ranks' logit slices, still in place, gathered into ws.logits.
+static int gather_full_logits(tsm_model* m, int outputs) {
+    int slice = m->cfg.vocab / m->tp;
+    TSM_TRY(tp_all_gather(m->ctx, m->ws.tp_parts, (int64_t)outputs * slice * 4));
+    return launch_interleave(m->ctx, m->ws.tp_parts, m->ws.logits, outputs, slice, m->tp, false);
 }
 
 // Launches one step over `total` packed tokens whose ids and table are already in the workspace.
@@ -604,6 +809,10 @@ static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, b
         order = w.order;
     }
     for (int i = 0; i < c.layers; i++) {
+        if (m->tp > 1) {
+            TSM_TRY(launch_layer_sharded(m, cache, i, total, order, qa, qb, qc, ordered, scale));
+            continue;
+        }
         Layer& l = m->layers[i];
         if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
         else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
@@ -629,6 +838,7 @@ static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, b
     QuantizedActs qh = quant_scratch_layout(w.qa, outputs, c.width);
     if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, xl, m->final_w, outputs, c.width, c.eps, nullptr, &qh));
     else TSM_TRY(launch_layernorm(ctx, xl, m->final_w, m->final_b, outputs, c.width, c.eps, nullptr, &qh));
+    if (m->tp > 1) return launch_head_sharded(m, qh, outputs, pick, !pick);
     Linear head = m->head;
     head.bias = nullptr;
     TSM_TRY(product(m, qh, outputs, head, nullptr, w.logits));
@@ -714,6 +924,7 @@ int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
     TSM_TRY(gguf_open(ctx, path, f));
     std::unique_ptr<tsm_model> m(new tsm_model());
     m->ctx = ctx;
+    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank;
     std::string arch = f.strings.count("general.architecture") ? f.strings["general.architecture"] : "";
     int rc;
     if (arch == "llama") rc = load_llama(m.get(), f);
@@ -723,6 +934,7 @@ int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
         tsm_model_free(m.release());
         return rc;
     }
+    set_head_local(m.get());
     register_names(m.get());
     *out = m.release();
     return TSM_OK;
@@ -736,6 +948,7 @@ int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uin
     TSM_TRY(check_config(ctx, *config));
     std::unique_ptr<tsm_model> m(new tsm_model());
     m->ctx = ctx;
+    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank;
     m->cfg = *config;
     if (m->cfg.arch == 1) m->cfg.tied = 1;
     int rc = build_random(m.get(), kind, seed);
@@ -774,7 +987,7 @@ int tsm_cache_create(tsm_model* model, int rows, int capacity, tsm_cache** out) 
     std::unique_ptr<tsm_cache> cache(new tsm_cache());
     cache->model = model, cache->rows = rows, cache->capacity = capacity;
     cache->lengths.assign(rows, 0);
-    int64_t bytes = (int64_t)rows * c.kv_heads * capacity * c.head_width * 4;
+    int64_t bytes = (int64_t)rows * (c.kv_heads / model->tp) * capacity * c.head_width * 4;  // a rank holds its own kv heads
     for (int i = 0; i < c.layers; i++) {
         void *kp = nullptr, *vp = nullptr;
         int rc = pool_alloc(model->ctx, bytes, &kp);
@@ -828,9 +1041,11 @@ int tsm_cache_fill(tsm_cache* cache, int row, int length, uint64_t seed) {
     if (row < 0 || row >= cache->rows || length < 0 || length > cache->capacity || length > m->cfg.context)
         return fail(m->ctx, TSM_ERR_ARG, std::to_string(length) + " positions exceed the " + std::to_string(cache->capacity) + " a row holds");
     const tsm_model_config& c = m->cfg;
+    const int kv_local = c.kv_heads / m->tp;
     for (int i = 0; i < c.layers; i++)
-        for (int kh = 0; kh < c.kv_heads; kh++) {
-            int64_t at = ((int64_t)row * c.kv_heads + kh) * cache->capacity * c.head_width;
+        for (int local = 0; local < kv_local; local++) {
+            int kh = m->tp_rank * kv_local + local;  // seeded by the head's place in the whole model: a shard's rows are the whole cache's
+            int64_t at = ((int64_t)row * kv_local + local) * cache->capacity * c.head_width;
             uint64_t s = seed * 7919ull + (uint64_t)((i * c.kv_heads + kh) * 2 + 1) * 1000003ull + (uint64_t)row;
             TSM_TRY(launch_normal_fill(m->ctx, cache->keys[i] + at, (int64_t)length * c.head_width, 0.0f, 1.0f, s));
             TSM_TRY(launch_normal_fill(m->ctx, cache->values[i] + at, (int64_t)length * c.head_width, 0.0f, 1.0f, s + 1));
@@ -876,6 +1091,7 @@ static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* count
     ctx->counters.uploads += 3;
     ctx->counters.upload_bytes += (int64_t)total * 16 + (int64_t)outputs * 4;
     TSM_TRY(launch_step(model, cache, total, outputs, picks != nullptr));
+    if (logits && picks && model->tp > 1) TSM_TRY(gather_full_logits(model, outputs));
     if (logits) {
         TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)outputs * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->counters.downloads++;
@@ -951,6 +1167,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
     ctx->counters.downloads += 1, ctx->counters.download_bytes += (int64_t)rows * 4;
     if (logits) {
+        if (model->tp > 1) TSM_TRY(gather_full_logits(model, rows));
         TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)rows * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->counters.downloads++, ctx->counters.download_bytes += (int64_t)rows * c.vocab * 4;
     }

@@ -169,6 +169,7 @@ int tsm_ctx_create(int ordinal, tsm_ctx** out) {
 int tsm_ctx_destroy(tsm_ctx* ctx) {
     CTX_GUARD(ctx);
     cudaStreamSynchronize(ctx->stream);
+    tsm::tp_release(ctx);
     for (auto& entry : ctx->pool.sizes) cudaFree(entry.first);
     if (ctx->quant.ptr) cudaFree(ctx->quant.ptr);
     if (ctx->attn.ptr) cudaFree(ctx->attn.ptr);

@@ -1,0 +1,83 @@
+"""One rank of the tensor-parallel parity case (run by test_gpu_tp.py under torch.distributed.run, one process per GPU).
+
+Every rank builds its shard of a random model; rank 0 also builds the whole model on a second context of its GPU.
+Prompts, graph-replayed decode steps with logits, a device-resident run and generate must give, on every rank, the
+bits and tokens of the whole model on one GPU."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from tests import helpers  # noqa: E402
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = helpers.load_package()
+    dev = pkg.B200(local)
+    pkg.groups.join_tensor_parallel(dev, dist)
+    assert dev.tp_info() == (rank, world)
+    cases = [("llama", pkg.Q4_0, dict(layers=2, width=256, heads=8, kv_heads=4, head_width=32, hidden=512, vocab=1024, context=256,
+                                      eps=1e-5, rope_theta=10000.0, tied=False)),
+             ("llama", pkg.Q8_0, dict(layers=2, width=512, heads=8, kv_heads=8, head_width=128, hidden=1024, vocab=2048, context=256,
+                                      eps=1e-5, rope_theta=10000.0, tied=True)),
+             ("gpt2", pkg.Q8_0, dict(layers=2, width=256, heads=4, kv_heads=4, head_width=64, hidden=1024, vocab=1024, context=128,
+                                     eps=1e-5, rope_theta=0.0, tied=True))]
+    whole_dev = pkg.B200(local) if rank == 0 else None
+    rng = np.random.default_rng(5)
+    for arch, kind, config in cases:
+        config = dict(config, arch=arch)
+        if config["heads"] % world or config["kv_heads"] % world:
+            continue
+        prompts = [rng.integers(0, config["vocab"], size=n).tolist() for n in (5, 17, 0, 3)]
+        model = pkg.Model.random(dev, config, kind, seed=7)
+        cache = model.new_batch_cache(4, 64)
+        got = [model.forward_last(prompts, cache)]
+        ids = [1, 2, 3, 4]
+        tokens_seen = []
+        for _ in range(4):
+            tokens, logits = model.decode(cache, ids, logits=True)
+            got.append(logits)
+            tokens_seen.append(tokens.tolist())
+            ids = tokens.tolist()
+        run = model.decode_run(cache, ids, 5)
+        text = model.generate(prompts[1], 12)
+        # every rank holds the same results
+        flat = np.concatenate([g.ravel() for g in got]).view(np.uint32).astype(np.int64)
+        mine = torch.tensor([int(flat.sum()), int(np.asarray(tokens_seen).sum()), int(run.sum()), int(np.sum(text))], device=f"cuda:{local}")
+        both = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(b, both[0]) for b in both), (arch, "ranks disagree", both)
+        if rank == 0:
+            whole = pkg.Model.random(whole_dev, config, kind, seed=7)
+            wcache = whole.new_batch_cache(4, 64)
+            want = [whole.forward_last(prompts, wcache)]
+            ids = [1, 2, 3, 4]
+            for step in range(4):
+                tokens, logits = whole.decode(wcache, ids, logits=True)
+                want.append(logits)
+                assert tokens.tolist() == tokens_seen[step], (arch, "decode tokens", step)
+                ids = tokens.tolist()
+            assert np.array_equal(whole.decode_run(wcache, ids, 5), run), (arch, "device-resident run")
+            assert whole.generate(prompts[1], 12) == text, (arch, "generate")
+            for step, (g, w) in enumerate(zip(got, want)):
+                assert np.array_equal(helpers.bits(g), helpers.bits(w)), (arch, "logits differ at", step)
+            wcache.free(), whole.free()
+        cache.free(), model.free()
+        dist.barrier()
+    dev.close()
+    if whole_dev:
+        whole_dev.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("tensor-parallel parity ok")
+
+
+if __name__ == "__main__":
+    main()
