@@ -6,8 +6,11 @@
 //     that complete on an mbarrier; the producer runs ahead through the whole key pass and straight on into the
 //     value pass, so the softmax phase in between does not drain the ring;
 //   * scores do not live in shared memory: they go to a scratch array in global memory (it stays in L2), are turned
-//     into exp values in place, and come back tile by tile as weights.  A CTA therefore needs 70 KB instead of
-//     100 KB and three CTAs share an SM, each with two or three tiles in flight;
+//     into exp values in place, and come back tile by tile as weights;
+//   * the score phase is a pipeline over the four quarters of the width: a warp keeps its quarter of the four heads'
+//     queries in registers and its lanes are the positions of a tile, so keys are read once, with 16-byte loads that
+//     hit 32 distinct rows, and no query is ever re-read from shared memory (a 16-byte shared load costs four
+//     wavefronts even when every lane reads the same address, which is what bounded the earlier kernels);
 //   * consumer warps synchronise among themselves with a named barrier only where data is exchanged (maximum,
 //     denominator, a tile's weights), never with the producer.
 // One CTA per (token, key/value head): 128 consumer threads + one producer warp.
@@ -18,7 +21,7 @@ namespace tsm {
 namespace {
 
 constexpr int kTP = 32;            // positions per tile
-constexpr int kRing = 3;           // stages
+constexpr int kRing = 3;           // stages (5 measured no faster)
 constexpr int kEChunk = 1024;      // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
@@ -78,7 +81,7 @@ __device__ __forceinline__ void s_tensor_load(void* dst, const CUtensorMap* map,
 __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
 
 template <int WIDTH>
-__global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+__global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
     constexpr int G = 4;
     constexpr int BOXES = WIDTH / 32;              // 128-byte wide boxes per row
     constexpr int BOX_BYTES = kTP * 128;
@@ -87,13 +90,15 @@ __global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(Strea
     static_assert(WIDTH == kConsumers, "one folding thread per column");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)smem;              // [kRing]
-    uint64_t* empty = full + kRing;                // [kRing]
-    volatile int* abort_flag = (volatile int*)(smem + 64);   // [1] stays 0
-    float* red = (float*)(smem + 128);             // [4 warps][4 heads]
-    float* maxes = red + 16;                       // [4]
-    float* totals = maxes + 4;                     // [4]
-    unsigned char* stages = smem + 1024;           // [kRing][BOXES][kTP][128 bytes], swizzled
+    static_assert(kRing <= 8 && 512 + 3 * kRing * 512 <= 8192, "the header holds the barriers and the hand-over slots of at most 8 stages");
+    uint64_t* full = (uint64_t*)smem;              // [kRing], bytes 0..63
+    uint64_t* empty = (uint64_t*)(smem + 64);      // [kRing], bytes 64..127
+    uint64_t* ready = (uint64_t*)(smem + 128);     // [3 warps][kRing], bytes 128..319: a tile's running sums are in `hand`
+    volatile int* abort_flag = (volatile int*)(smem + 320);   // [1] stays 0
+    float* maxes = (float*)(smem + 336);           // [4]
+    float* totals = (float*)(smem + 352);          // [4]
+    float* hand = (float*)(smem + 512);            // [3 warps][kRing][32 positions][4 heads]
+    unsigned char* stages = smem + 8192;           // [kRing][BOXES][kTP][128 bytes], swizzled
     float* ebuf = (float*)(stages + kRing * STAGE_BYTES);    // [G][kEChunk]
     float* wbuf = ebuf + G * kEChunk;              // [2][kTP][G]
     float* qs = wbuf + 2 * kTP * G;                // [G][QP]
@@ -115,6 +120,7 @@ __global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(Strea
         for (int s = 0; s < kRing; s++) {
             s_mbar_init(&full[s], 1);
             s_mbar_init(&empty[s], kConsumers / 32);
+            for (int w2 = 0; w2 < 3; w2++) s_mbar_init(&ready[w2 * kRing + s], 1);
         }
         abort_flag[0] = 0, abort_flag[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -154,44 +160,73 @@ __global__ void __launch_bounds__(kConsumers + 32) attention_stream_kernel(Strea
     // A wait that gives up raises the abort flag and the thread carries on with whatever the stage holds, so that
     // every named barrier below is still reached by all 128 threads; the results are then dropped.
     bool ok = true;
-    const int sp = tid >> 2, shd = tid & 3;        // this thread's position within a tile and its head
+    const int sp = tid >> 2, shd = tid & 3;        // in the output phase: the position within a tile and the head whose weight this thread makes
     float* srow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;   // + h * capacity + position
 
-    // ---- 1. scores ----
-    float top = -INFINITY;
+    // ---- 1. scores: a pipeline over the four quarters of the width ----
+    // Warp w owns columns [32 w, 32 w + 32): its lanes are the 32 positions of a tile, and each thread keeps its
+    // quarter of the four heads' queries in registers.  A position's dot products start in warp 0, which folds
+    // columns 0..31 and hands the four running sums to warp 1 through shared memory, and so on: the adds happen in
+    // column order, as one chain, but every warp works on a different tile at any moment.  Keys are read once per
+    // position and quarter with 16-byte loads that hit 32 distinct rows (no broadcast traffic, no query loads).
+    float top[G] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     {
-        const int sw = sp & 7;
-        const float4* qr = (const float4*)(qs + shd * QP);
-        for (int tile = 0; tile < tiles; tile++) {
-            int s = tile % kRing;
-            if (!s_mbar_wait(&full[s], (unsigned)((tile / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
-            const unsigned char* rowp = stages + (size_t)s * STAGE_BYTES + sp * 128;
-            float dot = 0.0f;
+        float qreg[G][32];
 #pragma unroll
-            for (int c = 0; c < WIDTH / 4; c++) {
-                float4 kv4 = *(const float4*)(rowp + (c >> 3) * BOX_BYTES + (((c & 7) ^ sw) << 4));
-                float4 qv = qr[c];
-                dot = __fadd_rn(dot, __fmul_rn(qv.x, kv4.x));
-                dot = __fadd_rn(dot, __fmul_rn(qv.y, kv4.y));
-                dot = __fadd_rn(dot, __fmul_rn(qv.z, kv4.z));
-                dot = __fadd_rn(dot, __fmul_rn(qv.w, kv4.w));
+        for (int h = 0; h < G; h++)
+#pragma unroll
+            for (int j = 0; j < 32; j++) qreg[h][j] = qs[h * QP + 32 * warp + j];
+        const int sw = lane & 7;
+        for (int tile = 0; tile < tiles; tile++) {
+            const int s = tile % kRing;
+            const unsigned parity = (unsigned)((tile / kRing) & 1);
+            if (!s_mbar_wait(&full[s], parity, abort_flag)) ok = false, *abort_flag = 1;
+            float acc[G] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (warp > 0) {
+                if (!s_mbar_wait(&ready[(warp - 1) * kRing + s], parity, abort_flag)) ok = false, *abort_flag = 1;
+                float4 in = *(const float4*)(hand + (((warp - 1) * kRing + s) * 32 + lane) * 4);
+                acc[0] = in.x, acc[1] = in.y, acc[2] = in.z, acc[3] = in.w;
+            }
+            const unsigned char* rowp = stages + (size_t)s * STAGE_BYTES + warp * BOX_BYTES + lane * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {
+                float4 kv4 = *(const float4*)(rowp + ((c ^ sw) << 4));
+#pragma unroll
+                for (int h = 0; h < G; h++) {
+                    acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 0], kv4.x));
+                    acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 1], kv4.y));
+                    acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 2], kv4.z));
+                    acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 3], kv4.w));
+                }
             }
             __syncwarp();
             if (lane == 0) s_mbar_arrive(&empty[s]);
-            int pos = tile * kTP + sp;
-            if (pos < len) {
-                float sc = __fadd_rn(__fmul_rn(dot, p.scale), 0.0f);
-                srow[(int64_t)shd * p.capacity + pos] = sc;
-                top = fmaxf(top, sc);
+            if (warp < 3) {
+                *(float4*)(hand + ((warp * kRing + s) * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                __syncwarp();
+                if (lane == 0) s_mbar_arrive(&ready[warp * kRing + s]);
+            } else {
+                int pos = tile * kTP + lane;
+                if (pos < len) {
+#pragma unroll
+                    for (int h = 0; h < G; h++) {
+                        float sc = __fadd_rn(__fmul_rn(acc[h], p.scale), 0.0f);
+                        srow[(int64_t)h * p.capacity + pos] = sc;
+                        top[h] = fmaxf(top[h], sc);
+                    }
+                }
             }
         }
     }
     // ---- 2. softmax: maximum, exp in place, the denominator folded in position order ----
+    if (warp == 3) {
 #pragma unroll
-    for (int off = 16; off >= 4; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
-    if (lane < 4) red[warp * 4 + lane] = top;
-    consumers_sync();
-    if (tid < 4) maxes[tid] = fmaxf(fmaxf(red[tid], red[4 + tid]), fmaxf(red[8 + tid], red[12 + tid]));
+        for (int h = 0; h < G; h++) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) top[h] = fmaxf(top[h], __shfl_xor_sync(0xffffffffu, top[h], off));
+            if (lane == 0) maxes[h] = top[h];
+        }
+    }
     consumers_sync();
     {
         float total = 0.0f;  // lane 0 of warp h folds head h
@@ -300,13 +335,11 @@ int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { re
 // Whether the streaming kernel takes this call.  `scratch` must hold attention_stream_scratch_bytes.
 bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int kv_heads, const float* q, int64_t q_stride, const float* k,
                            const float* v) {
-    // Measured on B200: with at most two CTAs per SM this kernel is the faster one (241 against 258 us for 16 streams
-    // of up to 4096 positions); with more, the shared-memory data path saturates (every 16-byte load of a query or a
-    // weight that all lanes share still costs four wavefronts) and attention_exact_kernel, whose CTAs hold eight
-    // warps, finishes sooner (360 against 408 us for 64 streams).  TSM_ATTN_STREAM=0 / 1 forces the choice.
+    // Measured on B200 against attention_exact_kernel: 341 against 360 us for 64 ragged streams of up to 4096
+    // positions, 230 against 258 us for 16.  TSM_ATTN_STREAM=0 selects the other kernel, for timing it.
     static const char* forced = getenv("TSM_ATTN_STREAM");
     if (forced && forced[0] == '0') return false;
-    if (!(forced && forced[0] == '1') && kv_heads > 0 && (int64_t)tokens * (heads / 4) > 2 * (int64_t)ctx->sm_count) return false;
+    (void)ctx, (void)tokens;
     bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
     return width == 128 && kv_heads > 0 && heads % kv_heads == 0 && (heads / kv_heads) % 4 == 0 && aligned && tensor_maps_available();
 }
@@ -320,7 +353,7 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
     uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
     TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
-    size_t smem = 2048 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
+    size_t smem = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
     auto kernel = attention_stream_kernel<WIDTH>;
     {
         static std::mutex lock;
