@@ -119,8 +119,9 @@ struct PipeLayout {
     static constexpr int SP = kCB * 4;                       // scales of one activation row
     static constexpr int SCALE_BYTES = COLS * SP * (KIND == TSM_Q4_1 ? 2 : 1);
     __host__ __device__ static constexpr int weights_at() { return 2 * ABOX; }
-    __host__ __device__ static constexpr int scales_at(int row_groups) { return 2 * ABOX + row_groups * 16 * WP; }
-    __host__ __device__ static constexpr int stage_bytes(int row_groups) { return (scales_at(row_groups) + SCALE_BYTES + 1023) / 1024 * 1024; }
+    // `rows` = weight rows a CTA stages; the scale box wants a 256-byte boundary (its swizzle pattern's period)
+    __host__ __device__ static constexpr int scales_at(int rows) { return (2 * ABOX + rows * WP + 255) / 256 * 256; }
+    __host__ __device__ static constexpr int stage_bytes(int rows) { return (scales_at(rows) + SCALE_BYTES + 1023) / 1024 * 1024; }
 };
 
 struct PipeMaps {
@@ -145,8 +146,8 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
     uint64_t* empty = full + kPipeStages;             // [kPipeStages]
     volatile int* abort_flag = (volatile int*)(smem + 96);
     unsigned char* stages = smem + 1024;
-    const int stage_bytes = L::stage_bytes(wr_max);
-    const int scales_at = L::scales_at(wr_max);
+    const int stage_bytes = L::stage_bytes(wr_max * 16);
+    const int scales_at = L::scales_at(wr_max * 16);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int nb = p.nb;
@@ -345,13 +346,211 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
         }
 }
 
+
+// The same pipeline with the operands' roles exchanged, for matrices with few rows: the multiply takes 16 ACTIVATION
+// rows as its A operand and 8 WEIGHT rows as its B operand, so a warp's group is 8 weight rows (twice as many groups
+// to spread over the SMs) and a weight fragment is one word per lane and block, prepared once and used for all the
+// warp's MT tiles of 16 activation rows.  A thread then holds the outputs of activation rows g, g + 8 and weight rows
+// 2t, 2t + 1 of each tile; every output's blocks are still folded in block order.
+template <int KIND, int MT, int WC>
+__global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int wr_max, const __grid_constant__ PipeMaps maps) {
+    constexpr int COLS = 16 * MT * WC;
+    using L = PipeLayout<KIND, COLS>;
+    constexpr int B = L::B, WP = L::WP;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = full + kPipeStages;
+    volatile int* abort_flag = (volatile int*)(smem + 96);
+    unsigned char* stages = smem + 1024;
+    const int stage_bytes = L::stage_bytes(wr_max * 8);
+    const int scales_at = L::scales_at(wr_max * 8);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nb = p.nb;
+    const int groups = (p.n + 7) / 8;
+    const int group0 = (int)((int64_t)blockIdx.x * groups / gridDim.x);
+    const int group_count = (int)((int64_t)(blockIdx.x + 1) * groups / gridDim.x) - group0;
+    const int col0 = blockIdx.y * COLS;
+    const int valid = min(COLS, p.m - col0);
+    const int active_wc = min(WC, (valid + 16 * MT - 1) / (16 * MT));
+    const int chunks = nb / kCB;
+    const int producer_warp = wr_max * WC;
+
+    if (tid == 0) {
+        for (int s = 0; s < kPipeStages; s++) {
+            p_mbar_init(&full[s], 1);
+            p_mbar_init(&empty[s], group_count * active_wc);
+        }
+        abort_flag[0] = 0, abort_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == producer_warp) {
+        if (lane != 0) return;
+        const unsigned tx = (unsigned)(2 * L::ABOX + wr_max * 8 * WP + L::SCALE_BYTES);
+        int issued = 0;
+        bool ok = true;
+        for (int chunk = 0; chunk < chunks; chunk++) {
+            int s = chunk % kPipeStages;
+            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag);
+            if (!ok) break;
+            unsigned char* base = stages + (size_t)s * stage_bytes;
+            p_mbar_expect_tx(&full[s], tx);
+            p_tensor_load(base, &maps.acts, chunk * kCB * 32, col0, &full[s]);
+            p_tensor_load(base + L::ABOX, &maps.acts, chunk * kCB * 32 + 128, col0, &full[s]);
+            p_tensor_load(base + L::weights_at(), &maps.weights, chunk * (kCB * B / 2), group0 * 8, &full[s]);
+            p_tensor_load(base + scales_at, &maps.scales, chunk * kCB, col0, &full[s]);
+            if (KIND == TSM_Q4_1) p_tensor_load(base + scales_at + COLS * L::SP, &maps.sums, chunk * kCB, col0, &full[s]);
+            issued = chunk + 1;
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int chunk = max(0, issued - kPipeStages); chunk < issued; chunk++)
+                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1);
+        }
+        return;
+    }
+
+    const int wr = warp / WC, wc = warp % WC;
+    if (wr >= group_count || wc >= active_wc) return;
+    const int g = lane >> 2, t = lane & 3;
+    const int lcol0 = wc * 16 * MT;
+    const int my_tiles = min(MT, (valid - lcol0 + 15) / 16);
+    const int row0 = (group0 + wr) * 8;
+    // fragment words of activation row 16 i + g (and + 8, 1024 bytes on): 16-byte piece 2u or 2u + 1, stored at piece ^ g
+    int frag_at[kSub];
+#pragma unroll
+    for (int u = 0; u < kSub; u++) frag_at[u] = (lcol0 + g) * 128 + (((2 * u) ^ g) << 4) + 4 * t;
+    const int scale_half = (g >> 2) & 1;  // the 32-byte swizzle of the scale box: bit 2 of the activation row
+
+    int cq[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) asm volatile("mov.b32 %0, 0x4b400000;" : "=r"(cq[e]));
+
+    float acc[MT][4];  // [tile][(act g, weight 2t), (act g, weight 2t+1), (act g+8, weight 2t), (act g+8, weight 2t+1)]
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[i][e] = 0.0f;
+
+    bool ok = true;
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        int s = chunk % kPipeStages;
+        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag);
+        if (!ok) break;
+        const unsigned char* base = stages + (size_t)s * stage_bytes;
+        const unsigned char* wbase = base + L::weights_at() + (size_t)(wr * 8) * WP;
+        const unsigned char* slot_q = wbase + (size_t)g * WP;            // the row whose quantised values this lane feeds
+        const unsigned char* slot_0 = wbase + (size_t)(2 * t) * WP;      // the two rows whose outputs this lane holds
+        const unsigned char* slot_1 = slot_0 + WP;
+        const float* sc = (const float*)(base + scales_at);
+        const float* aux = sc + COLS * kCB;
+#pragma unroll
+        for (int sub = 0; sub < kCB / kSub; sub++) {
+            const unsigned char* abox = base + sub * L::ABOX;
+            unsigned b[kSub][2];
+            float dw0[kSub], dw1[kSub], x0[kSub], x1[kSub];  // x: Q4_0 -kMagic * dw; Q4_1 the block minimum
+            bool plain = true;
+#pragma unroll
+            for (int u = 0; u < kSub; u++) {
+                const int at = (sub * kSub + u) * B;
+                dw0[u] = half_bits_to_float(p_lds_u16(slot_0 + at)), dw1[u] = half_bits_to_float(p_lds_u16(slot_1 + at));
+                if (KIND == TSM_Q8_0) {
+                    b[u][0] = p_lds_u32_at2(slot_q + at + 2 + 4 * t), b[u][1] = p_lds_u32_at2(slot_q + at + 18 + 4 * t);
+                    x0[u] = x1[u] = 0.0f;
+                } else if (KIND == TSM_Q4_0) {
+                    unsigned nq = p_lds_u32_at2(slot_q + at + 2 + 4 * t);
+                    b[u][0] = p_nibbles_minus_8(nq), b[u][1] = p_nibbles_minus_8(nq >> 4);
+                    x0[u] = __fmul_rn(-kMagic, dw0[u]), x1[u] = __fmul_rn(-kMagic, dw1[u]);
+                    plain = plain && fabsf(dw0[u]) <= 65504.0f && fabsf(dw1[u]) <= 65504.0f;
+                } else {
+                    unsigned nq = p_lds_u32_at2(slot_q + at + 4 + 4 * t);
+                    b[u][0] = nq & 0x0f0f0f0fu, b[u][1] = (nq >> 4) & 0x0f0f0f0fu;
+                    x0[u] = half_bits_to_float(p_lds_u16(slot_0 + at + 2)), x1[u] = half_bits_to_float(p_lds_u16(slot_1 + at + 2));
+                }
+            }
+            const bool all_plain = KIND == TSM_Q4_0 && __all_sync(0xffffffffu, plain);
+            auto tiles = [&](auto fused_tag) {
+                constexpr bool fused = decltype(fused_tag)::value;
+#pragma unroll
+                for (int i = 0; i < MT; i++) {
+                    if (i < my_tiles) {
+                        const int r_lo = lcol0 + 16 * i + g;  // activation rows r_lo and r_lo + 8
+                        const int half = (sub ^ scale_half) * kSub;
+                        const float4 s_lo = *(const float4*)(sc + r_lo * kCB + half);
+                        const float4 s_hi = *(const float4*)(sc + (r_lo + 8) * kCB + half);
+                        float4 m_lo = make_float4(0.f, 0.f, 0.f, 0.f), m_hi = m_lo;
+                        if (KIND == TSM_Q4_1) {
+                            m_lo = *(const float4*)(aux + r_lo * kCB + half);
+                            m_hi = *(const float4*)(aux + (r_lo + 8) * kCB + half);
+                        }
+                        const unsigned char* tile = abox + i * 2048;
+#pragma unroll
+                        for (int u = 0; u < kSub; u++) {
+                            unsigned a[4];
+                            a[0] = *(const unsigned*)(tile + frag_at[u]), a[2] = *(const unsigned*)(tile + (frag_at[u] ^ 16));
+                            a[1] = *(const unsigned*)(tile + 1024 + frag_at[u]), a[3] = *(const unsigned*)(tile + 1024 + (frag_at[u] ^ 16));
+                            int d[4];
+                            p_mma_s8(d, a, b[u][0], b[u][1], cq);
+                            const float dx_lo = u == 0 ? s_lo.x : u == 1 ? s_lo.y : u == 2 ? s_lo.z : s_lo.w;
+                            const float dx_hi = u == 0 ? s_hi.x : u == 1 ? s_hi.y : u == 2 ? s_hi.z : s_hi.w;
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float dx = e < 2 ? dx_lo : dx_hi;
+                                const float dw = (e & 1) ? dw1[u] : dw0[u];
+                                const float xw = (e & 1) ? x1[u] : x0[u];
+                                const float bits = __int_as_float(d[e]);
+                                if (KIND == TSM_Q8_0) {
+                                    acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(__fsub_rn(bits, kMagic), __fmul_rn(dw, dx)));
+                                } else if (KIND == TSM_Q4_0) {
+                                    float scaled = fused ? __fmaf_rn(bits, dw, xw) : __fmul_rn(__fsub_rn(bits, kMagic), dw);
+                                    acc[i][e] = __fadd_rn(acc[i][e], __fmul_rn(scaled, dx));
+                                } else {
+                                    const float4& mm = e < 2 ? m_lo : m_hi;
+                                    const float sx = u == 0 ? mm.x : u == 1 ? mm.y : u == 2 ? mm.z : mm.w;
+                                    acc[i][e] = __fadd_rn(acc[i][e], __fadd_rn(__fmul_rn(__fmul_rn(dw, dx), __fsub_rn(bits, kMagic)), __fmul_rn(xw, sx)));
+                                }
+                            }
+                        }
+                    }
+                }
+            };
+            if (all_plain) tiles(std::true_type{});
+            else tiles(std::false_type{});
+        }
+        __syncwarp();
+        if (lane == 0) p_mbar_arrive(&empty[s]);
+    }
+    if (!ok) {
+        *abort_flag = 1;
+        if (lane == 0) atomicExch(&p.errors->timeout, 1);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            int row = row0 + 2 * t + (e & 1);
+            int col = col0 + lcol0 + 16 * i + g + (e < 2 ? 0 : 8);
+            if (row < p.n && col < p.m) {
+                float v = acc[i][e];
+                if (p.bias) v = __fadd_rn(v, p.bias[row]);
+                if (p.residual) v = __fadd_rn(p.residual[(int64_t)col * p.n + row], v);
+                p.out[(int64_t)col * p.n + row] = v;
+            }
+        }
+}
+
 template <int KIND, int NT, int WC>
 int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     constexpr int COLS = 8 * NT * WC;
     using L = PipeLayout<KIND, COLS>;
     constexpr int B = L::B;
     constexpr size_t kSmemBudget = 224 * 1024;
-    auto smem_for = [](int groups) { return (size_t)2048 + (size_t)kPipeStages * L::stage_bytes(groups); };
+    auto smem_for = [](int groups) { return (size_t)2048 + (size_t)kPipeStages * L::stage_bytes(groups * 16); };
     const int wr_cap = 15 / WC;  // 15 consumer warps and the producer: 512 threads
     int wr_max = 0, grid_x = 0;
     // the fewest CTAs per SM whose share of the weight-row groups fits a CTA; every SM then gets the same share
@@ -395,29 +594,101 @@ int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     return TSM_OK;
 }
 
+// The role-swapped kernel's launch: groups of 8 weight rows, tiles of 16 activation rows.
+template <int KIND, int MT, int WC>
+int launch_pipe_t_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
+    constexpr int COLS = 16 * MT * WC;
+    using L = PipeLayout<KIND, COLS>;
+    constexpr int B = L::B;
+    constexpr size_t kSmemBudget = 224 * 1024;
+    auto smem_for = [](int groups) { return (size_t)2048 + (size_t)kPipeStages * L::stage_bytes(groups * 8); };
+    const int groups = (p.n + 7) / 8;
+    const int wr_cap = 15 / WC;
+    int wr_max = 0, grid_x = 0;
+    for (int c = 1; c <= 4 && !wr_max; c++) {
+        if (ctas_per_sm_forced && c != ctas_per_sm_forced) continue;
+        int gx = std::min(groups, ctx->sm_count * c);
+        int need = (groups + gx - 1) / gx;
+        if (need <= wr_cap && smem_for(need) * c <= kSmemBudget && 32 * (need * WC + 1) * c <= 512) wr_max = need, grid_x = gx;
+    }
+    if (!wr_max) {
+        wr_max = wr_cap;
+        while (wr_max > 1 && smem_for(wr_max) > kSmemBudget) wr_max--;
+        grid_x = (groups + wr_max - 1) / wr_max;
+    }
+    size_t smem = smem_for(wr_max);
+    auto kernel = matmul_pipe_t_kernel<KIND, MT, WC>;
+    {
+        static std::mutex lock;
+        static std::map<std::pair<int, const void*>, bool> done;
+        std::lock_guard<std::mutex> guard(lock);
+        auto key = std::make_pair(ctx->ordinal, (const void*)kernel);
+        if (!done.count(key)) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+            done[key] = true;
+        }
+    }
+    PipeMaps maps;
+    const uint64_t nb = (uint64_t)p.nb;
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT16, p.w, nb * B / 2, (uint64_t)p.n, nb * B, kCB * B / 2, 8 * wr_max,
+                               CU_TENSOR_MAP_SWIZZLE_NONE));
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.acts, CU_TENSOR_MAP_DATA_TYPE_UINT8, p.acts.qs, nb * 32, (uint64_t)p.m, nb * 32, 128, COLS,
+                               CU_TENSOR_MAP_SWIZZLE_128B));
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, p.acts.scales, nb, (uint64_t)p.m, nb * 4, kCB, COLS,
+                               CU_TENSOR_MAP_SWIZZLE_32B));
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m,
+                               nb * 4, kCB, COLS, CU_TENSOR_MAP_SWIZZLE_32B));
+    dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
+    kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
 template <int KIND>
 int launch_pipe_kind(tsm_ctx* ctx, const PipeParams& p) {
-    // TSM_PIPE_CONFIG = WC * 10 + CTAs per SM picks a split for timing variants without rebuilding
+    // TSM_PIPE_CONFIG = swapped * 100 + WC * 10 + CTAs per SM picks a shape for timing variants without rebuilding
     static const int forced = getenv("TSM_PIPE_CONFIG") ? atoi(getenv("TSM_PIPE_CONFIG")) : 0;
-    const int tiles = (std::min(p.m, 64) + 7) / 8;
-    // few weight rows: split the activation rows over 2 or 4 warps per group so that every SM still has warps to run
-    int wc = p.groups >= 8 * ctx->sm_count ? 1 : p.groups >= 4 * ctx->sm_count ? 2 : 4;
-    if (forced) wc = forced / 10;
     const int c = forced % 10;
-    if (tiles > 4) {
-        if (wc >= 4) return launch_pipe_shape<KIND, 2, 4>(ctx, p, c);
-        if (wc == 2) return launch_pipe_shape<KIND, 4, 2>(ctx, p, c);
-        return launch_pipe_shape<KIND, 8, 1>(ctx, p, c);
+    const int rows = std::min(p.m, 64);
+    // Many weight rows: 16-row groups, one warp per group over all activation rows (the weight fragments, which cost the
+    // most to prepare, are then used 8 times).  Few: the role-swapped kernel, whose groups are 8 rows and whose weight
+    // fragment is one word, with the activation rows split over 2 or 4 warps when the SMs would otherwise be short of warps.
+    bool swapped = p.groups < 8 * ctx->sm_count;
+    if (forced) swapped = forced / 100 != 0;
+    if (!swapped) {
+        const int tiles = (rows + 7) / 8;
+        int wc = p.groups >= 8 * ctx->sm_count ? 1 : p.groups >= 4 * ctx->sm_count ? 2 : 4;
+        if (forced) wc = forced / 10 % 10;
+        if (tiles > 4) {
+            if (wc >= 4) return launch_pipe_shape<KIND, 2, 4>(ctx, p, c);
+            if (wc == 2) return launch_pipe_shape<KIND, 4, 2>(ctx, p, c);
+            return launch_pipe_shape<KIND, 8, 1>(ctx, p, c);
+        }
+        if (tiles > 2) {
+            if (wc >= 2) return launch_pipe_shape<KIND, 2, 2>(ctx, p, c);
+            return launch_pipe_shape<KIND, 4, 1>(ctx, p, c);
+        }
+        if (tiles > 1) {
+            if (wc >= 2) return launch_pipe_shape<KIND, 1, 2>(ctx, p, c);
+            return launch_pipe_shape<KIND, 2, 1>(ctx, p, c);
+        }
+        return launch_pipe_shape<KIND, 1, 1>(ctx, p, c);
     }
+    const int groups8 = (p.n + 7) / 8;
+    const int tiles = (rows + 15) / 16;
+    int wc = groups8 >= 6 * ctx->sm_count ? 1 : groups8 >= 3 * ctx->sm_count ? 2 : 4;
+    if (forced) wc = forced / 10 % 10;
     if (tiles > 2) {
-        if (wc >= 2) return launch_pipe_shape<KIND, 2, 2>(ctx, p, c);
-        return launch_pipe_shape<KIND, 4, 1>(ctx, p, c);
+        if (wc >= 4) return launch_pipe_t_shape<KIND, 1, 4>(ctx, p, c);
+        if (wc == 2) return launch_pipe_t_shape<KIND, 2, 2>(ctx, p, c);
+        return launch_pipe_t_shape<KIND, 4, 1>(ctx, p, c);
     }
     if (tiles > 1) {
-        if (wc >= 2) return launch_pipe_shape<KIND, 1, 2>(ctx, p, c);
-        return launch_pipe_shape<KIND, 2, 1>(ctx, p, c);
+        if (wc >= 2) return launch_pipe_t_shape<KIND, 1, 2>(ctx, p, c);
+        return launch_pipe_t_shape<KIND, 2, 1>(ctx, p, c);
     }
-    return launch_pipe_shape<KIND, 1, 1>(ctx, p, c);
+    return launch_pipe_t_shape<KIND, 1, 1>(ctx, p, c);
 }
 
 }  // namespace
