@@ -109,6 +109,12 @@ __device__ __forceinline__ void p_mma_s8(int (&d)[4], const unsigned (&a)[4], un
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
+// Four 8-row x 16-byte pieces of shared memory as tensor-core fragments: lane l gives the address of row l % 8 of piece
+// l / 8 and receives, from each piece, the 4 bytes its place in the fragment holds.
+__device__ __forceinline__ void p_ldmatrix4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
 constexpr int kCB = 8;  // blocks of K per stage
 
 template <int KIND, int COLS>
@@ -207,11 +213,13 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
     const int my_tiles = min(NT, (valid - lcol0 + 7) / 8);
     const int row0 = (group0 + wr) * 16;
     const int ra = wr * 16 + g, rbw = ra + 8;         // this thread's two weight rows within the CTA's box
-    // a fragment word of activation row 8 i + g, block u: 16-byte piece 2u (elements 4t..) or 2u + 1 (elements 16 + 4t..)
-    // of the row's 128 bytes, stored at piece ^ (row & 7) = piece ^ g
-    int frag_at[kSub];
+    // The activation fragments of two blocks of a tile are four 8 x 16-byte pieces: (block, low half), (block, high
+    // half), (block + 1, low), (block + 1, high); lane l addresses row l % 8 of piece l / 8, whose 16 bytes (piece
+    // 2 u + half of the row's 128) are stored at piece ^ (row & 7).
+    unsigned frag_at[kSub / 2];
 #pragma unroll
-    for (int u = 0; u < kSub; u++) frag_at[u] = (lcol0 + g) * 128 + (((2 * u) ^ g) << 4) + 4 * t;
+    for (int pair = 0; pair < kSub / 2; pair++)
+        frag_at[pair] = (unsigned)((lcol0 + (lane & 7)) * 128 + (((4 * pair + (lane >> 3)) ^ (lane & 7)) << 4));
 
     int cq[4];  // the accumulator input of every multiply: four registers holding kMagic's bits, set once
 #pragma unroll
@@ -284,11 +292,14 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
                         m0 = *(const float4*)(aux + c * kCB + half);
                         m1 = *(const float4*)(aux + (c + 1) * kCB + half);
                     }
-                    const unsigned char* tile = abox + i * 1024;
+                    const unsigned tile = p_smem_u32(abox) + i * 1024;
+                    unsigned xq[kSub / 2][4];
+#pragma unroll
+                    for (int pair = 0; pair < kSub / 2; pair++) p_ldmatrix4(xq[pair], tile + frag_at[pair]);
 #pragma unroll
                     for (int u = 0; u < kSub; u++) {
                         int d[4];
-                        p_mma_s8(d, a[u], *(const unsigned*)(tile + frag_at[u]), *(const unsigned*)(tile + (frag_at[u] ^ 16)), cq);
+                        p_mma_s8(d, a[u], xq[u >> 1][2 * (u & 1)], xq[u >> 1][2 * (u & 1) + 1], cq);
                         const float dx0 = u == 0 ? s0.x : u == 1 ? s0.y : u == 2 ? s0.z : s0.w;
                         const float dx1 = u == 0 ? s1.x : u == 1 ? s1.y : u == 2 ? s1.z : s1.w;
 #pragma unroll
@@ -420,10 +431,13 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
     const int lcol0 = wc * 16 * MT;
     const int my_tiles = min(MT, (valid - lcol0 + 15) / 16);
     const int row0 = (group0 + wr) * 8;
-    // fragment words of activation row 16 i + g (and + 8, 1024 bytes on): 16-byte piece 2u or 2u + 1, stored at piece ^ g
-    int frag_at[kSub];
+    // A block's activation fragment of a tile is four 8 x 16-byte pieces: (rows 0-7, low half), (rows 8-15, low), (rows
+    // 0-7, high), (rows 8-15, high); lane l addresses row l % 8 of piece l / 8; the 16 bytes (piece 2 u + half of the
+    // row's 128) are stored at piece ^ (row & 7).
+    unsigned frag_at[kSub];
 #pragma unroll
-    for (int u = 0; u < kSub; u++) frag_at[u] = (lcol0 + g) * 128 + (((2 * u) ^ g) << 4) + 4 * t;
+    for (int u = 0; u < kSub; u++)
+        frag_at[u] = (unsigned)((lcol0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * 128 + (((2 * u + (lane >> 4)) ^ (lane & 7)) << 4));
     const int scale_half = (g >> 2) & 1;  // the 32-byte swizzle of the scale box: bit 2 of the activation row
 
     int cq[4];
@@ -487,12 +501,11 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
                             m_lo = *(const float4*)(aux + r_lo * kCB + half);
                             m_hi = *(const float4*)(aux + (r_lo + 8) * kCB + half);
                         }
-                        const unsigned char* tile = abox + i * 2048;
+                        const unsigned tile = p_smem_u32(abox) + i * 2048;
 #pragma unroll
                         for (int u = 0; u < kSub; u++) {
                             unsigned a[4];
-                            a[0] = *(const unsigned*)(tile + frag_at[u]), a[2] = *(const unsigned*)(tile + (frag_at[u] ^ 16));
-                            a[1] = *(const unsigned*)(tile + 1024 + frag_at[u]), a[3] = *(const unsigned*)(tile + 1024 + (frag_at[u] ^ 16));
+                            p_ldmatrix4(a, tile + frag_at[u]);
                             int d[4];
                             p_mma_s8(d, a, b[u][0], b[u][1], cq);
                             const float dx_lo = u == 0 ? s_lo.x : u == 1 ? s_lo.y : u == 2 ? s_lo.z : s_lo.w;

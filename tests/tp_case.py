@@ -71,6 +71,35 @@ def main():
             wcache.free(), whole.free()
         cache.free(), model.free()
         dist.barrier()
+    # models loaded from GGUF files, sharded by the loader, against the CPU oracle (the reference's golden fixtures)
+    import tempfile
+    from oracle import oracle
+    g = np.load(os.path.join(ROOT, "tests", "golden", "reference_fixtures.npz"))
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, f"llama-{rank}.gguf")
+        open(path, "wb").write(g["tiny_llama/q4_0_gguf"].tobytes())
+        ref = helpers.oracle_llama(path)
+        model = pkg.Llama.load(path, dev)
+        prompt = g["tiny_llama/prompt_ids"].tolist()
+        if model.config["kv_heads"] % world == 0 and model.config["vocab"] % world == 0:
+            want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+            got = model.forward([prompt], model.new_batch_cache(1, 64))
+            assert np.array_equal(helpers.bits(got), helpers.bits(want)), "sharded GGUF Llama differs from the oracle"
+            assert model.generate(prompt, 20) == ref.generate(prompt, 20)
+        model.free()
+        st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+        path = os.path.join(tmp, f"gpt2-{rank}.gguf")
+        tensors = helpers.write_gpt2_gguf(path, st, 2, 4, oracle.Q8_0)
+        config = dict(arch="gpt2", layers=2, heads=4, kv_heads=4, width=32, head_width=8, hidden=128, context=64, vocab=400, eps=1e-5)
+        ref = oracle.Model(config, tensors)
+        model = pkg.GPT2.load(path, dev)
+        prompt = g["tiny_gpt2/prompt_ids"].tolist()
+        want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+        got = model.forward([prompt], model.new_batch_cache(1, 64))
+        assert np.array_equal(helpers.bits(got), helpers.bits(want)), "sharded GGUF GPT-2 differs from the oracle"
+        assert model.generate(prompt, 20) == ref.generate(prompt, 20)
+        model.free()
+    dist.barrier()
     dev.close()
     if whole_dev:
         whole_dev.close()
