@@ -295,6 +295,33 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             const unsigned char* vt = colp + (size_t)s * STAGE_BYTES;
             int count = min(kTP, len - tile * kTP);
             int pos = 0;
+            if (count == kTP) {
+                // a whole tile: the loads of the next 8 positions are in flight while the current 8 are folded (a warp
+                // may be alone on its scheduler, so nothing else would hide a shared-memory load's latency)
+                float vv[2][8];
+                float4 ww[2][8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) vv[0][u] = *(const float*)(vt + voff[u]), ww[0][u] = *(const float4*)(wt + u * G);
+#pragma unroll
+                for (int group = 0; group < kTP / 8; group++) {
+                    const int cur = group & 1;
+                    if (group + 1 < kTP / 8) {
+#pragma unroll
+                        for (int u = 0; u < 8; u++) {
+                            vv[cur ^ 1][u] = *(const float*)(vt + (group + 1) * 8 * 128 + voff[u]);
+                            ww[cur ^ 1][u] = *(const float4*)(wt + ((group + 1) * 8 + u) * G);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        acc[0] = __fadd_rn(acc[0], __fmul_rn(ww[cur][u].x, vv[cur][u]));
+                        acc[1] = __fadd_rn(acc[1], __fmul_rn(ww[cur][u].y, vv[cur][u]));
+                        acc[2] = __fadd_rn(acc[2], __fmul_rn(ww[cur][u].z, vv[cur][u]));
+                        acc[3] = __fadd_rn(acc[3], __fmul_rn(ww[cur][u].w, vv[cur][u]));
+                    }
+                }
+                pos = kTP;
+            }
             for (; pos + 8 <= count; pos += 8) {
                 float vv[8];
 #pragma unroll
