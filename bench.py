@@ -205,7 +205,8 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
     """One kernel on a small case, a few launches, for a profiler capture or a timing alone:
          matvec,<kind>,<n>,<k>             batch-1 product over already-quantised activations
          product,<kind>,<n>,<k>,<rows>     quantiser + batched product
-         attention,<tokens>,<heads>,<kv_heads>,<width>,<capacity>   ragged lengths 128..capacity-128 (seed 11)
+         attention,<tokens>,<heads>,<kv_heads>,<width>,<capacity>[,<length>]   ragged lengths 128..capacity-128 (seed 11),
+                                                                          or every stream at <length>
        Returns the JSON record (microseconds per launch, GB/s of algorithmic bytes)."""
     import ctypes as C
     parts = spec.split(",")
@@ -246,6 +247,8 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
             dev.check(dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(b.ptr), C.c_int64(count), C.c_float(0.0), C.c_float(1.0),
                                               C.c_uint64(seed)), "tsm_fill_normal")
         lengths = np.random.default_rng(11).integers(128, cap - 127, size=tokens)
+        if len(parts) > 6:
+            lengths = np.full(tokens, int(parts[6]))
         table = dev.tensor(np.stack([np.arange(tokens), lengths, lengths + 1], 1).astype(np.int32))
         q = dev.tensor(np.random.default_rng(3).normal(0, 1, (tokens, H * W)).astype(np.float32))
         o = dev.alloc(tokens * H * W * 4)
@@ -463,7 +466,7 @@ def main():
         # these shapes and lengths; none for other workloads
         traffic = None
         if args.workload == "c5":
-            traffic = 1252153856 if top is kernels[0] else 68462592
+            traffic = 1310424576 if top is kernels[0] else 67894272
         line["roofline"] = dict(bound="hbm", kernel=top["kernel"], achieved=top["gbs"], peak=peak["hbm_gbs"], unit="GB/s",
                                 frac=top["gbs"] / peak["hbm_gbs"], traffic=traffic, algorithmic_bytes=top["bytes"], peak_kind=peak_kind)
         line["kernels"] = kernels

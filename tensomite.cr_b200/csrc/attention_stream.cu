@@ -22,7 +22,7 @@ namespace {
 
 constexpr int kTP = 32;            // positions per tile
 constexpr int kRing = 3;           // stages (5 measured no faster)
-constexpr int kEChunk = 1024;      // positions whose exp values are staged at once for the denominator's chain
+constexpr int kEChunk = 1024;     // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
 
