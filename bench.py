@@ -76,6 +76,19 @@ class ClockSampler:
             self.proc = None
         return self
 
+    def ready(self, timeout=8.0):
+        """Waits until the sampler has written its first line (nvidia-smi can take a second to start, longer when eight
+        ranks start one each), so that a short timed region still sees samples."""
+        deadline = time.time() + timeout
+        while self.proc and time.time() < deadline and os.path.getsize(self.path) == 0:
+            time.sleep(0.05)
+
+    def begin(self):
+        self.lo = os.path.getsize(self.path) if self.path else 0
+
+    def end(self):
+        self.hi = os.path.getsize(self.path) if self.path else 0
+
     def __exit__(self, *exc):
         if self.proc:
             self.proc.terminate()
@@ -89,7 +102,12 @@ class ClockSampler:
         if not self.path or not os.path.exists(self.path):
             return out
         sm, mx, reasons = [], [], set()
-        for line in open(self.path):
+        text = open(self.path).read()
+        lo, hi = getattr(self, "lo", 0), getattr(self, "hi", len(text))
+        inside = text[lo:hi]
+        if inside.count("\n") < 1:  # a region shorter than the sampling period: the samples on either side of it
+            inside = text[max(0, text.rfind("\n", 0, max(lo - 1, 0)) + 1):text.find("\n", hi) + 1 or len(text)]
+        for line in inside.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -385,16 +403,19 @@ def main():
     cache, ids = make_streams(pkg, dev, model, w, lengths, W + K + 2, data_rank)
     dev.sync()
     # ---- value: the step loop resident on the device ----------------------------------------------
-    if W:
-        model.decode_run(cache, ids, W)
-    dev.reset_counters()
-    barrier()
     with ClockSampler(local) as clocks:
+        clocks.ready()
+        if W:
+            model.decode_run(cache, ids, W)
+        dev.reset_counters()
+        barrier()
+        clocks.begin()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record(stream)
         tokens = model.decode_run(cache, ids, K)
         stop.record(stream)
         stop.synchronize()
+        clocks.end()
         barrier()
     seconds = max_over_ranks(start.elapsed_time(stop) / 1e3)
     counters = dev.counters()

@@ -1192,7 +1192,8 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
         if (cache->lengths[row] + steps > limit)
             return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + steps) + " positions exceed the " + std::to_string(limit) + " a row holds");
     TSM_TRY(prepare_scratch(model, cache, rows));
-    int64_t need = 1 + (int64_t)steps * rows;
+    // room for at least 1024 steps: the captured step holds this buffer's address, so growing it means capturing again
+    int64_t need = 1 + (int64_t)std::max(steps, 1024) * rows;
     if (cache->run_capacity < need) {
         TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         pool_release(ctx, cache->run_state);
@@ -1238,7 +1239,12 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
             return rc;
         }
     }
-    for (int s = 0; s < steps; s++) TSM_CUDA(ctx, cudaGraphLaunch(cache->run_graph, ctx->stream));
+    for (int s = 0; s < steps; s++) {
+        TSM_CUDA(ctx, cudaGraphLaunch(cache->run_graph, ctx->stream));
+        // Measured with 2 to 8 ranks: replays holding NCCL all-gathers queued back to back ran at half the rate of replays
+        // the host waits for one by one, so a tensor-parallel run pays one stream wait per step.
+        if (model->tp > 1 && !getenv("TSM_TP_RUN_QUEUED")) TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
     ctx->counters.graph_replays += steps;
     ctx->counters.launches += (int64_t)steps * cache->run_kernels;
     TSM_CUDA(ctx, cudaMemcpyAsync(tokens, cache->run_state + 1, (size_t)steps * rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
