@@ -223,8 +223,8 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
     """One kernel on a small case, a few launches, for a profiler capture or a timing alone:
          matvec,<kind>,<n>,<k>             batch-1 product over already-quantised activations
          product,<kind>,<n>,<k>,<rows>     quantiser + batched product
-         attention,<tokens>,<heads>,<kv_heads>,<width>,<capacity>[,<length>]   ragged lengths 128..capacity-128 (seed 11),
-                                                                          or every stream at <length>
+         attention,<tokens>,<heads>,<kv_heads>,<width>,<capacity>[,<length>[,shared]]   ragged lengths 128..capacity-128 (seed 11),
+                                                                          or every stream at <length> (0 = ragged); `shared`: all read one cache
        Returns the JSON record (microseconds per launch, GB/s of algorithmic bytes)."""
     import ctypes as C
     parts = spec.split(",")
@@ -265,9 +265,10 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
             dev.check(dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(b.ptr), C.c_int64(count), C.c_float(0.0), C.c_float(1.0),
                                               C.c_uint64(seed)), "tsm_fill_normal")
         lengths = np.random.default_rng(11).integers(128, cap - 127, size=tokens)
-        if len(parts) > 6:
+        if len(parts) > 6 and int(parts[6]) > 0:
             lengths = np.full(tokens, int(parts[6]))
-        table = dev.tensor(np.stack([np.arange(tokens), lengths, lengths + 1], 1).astype(np.int32))
+        shared = len(parts) > 7 and parts[7] == "shared"   # every stream reads stream 0's cache (it stays in L2): the compute-bound time
+        table = dev.tensor(np.stack([np.zeros(tokens, dtype=np.int64) if shared else np.arange(tokens), lengths, lengths + 1], 1).astype(np.int32))
         q = dev.tensor(np.random.default_rng(3).normal(0, 1, (tokens, H * W)).astype(np.float32))
         o = dev.alloc(tokens * H * W * 4)
         algorithmic = int(sum(2 * KV * W * 4 * (int(n) + 1) for n in lengths)) + 2 * tokens * H * W * 4

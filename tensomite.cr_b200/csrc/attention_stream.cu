@@ -100,8 +100,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     float* hand = (float*)(smem + 512);            // [3 warps][kRing][32 positions][4 heads]
     unsigned char* stages = smem + 8192;           // [kRing][BOXES][kTP][128 bytes], swizzled
     float* ebuf = (float*)(stages + kRing * STAGE_BYTES);    // [G][kEChunk]
-    float* wbuf = ebuf + G * kEChunk;              // [2][kTP][G]
-    float* qs = wbuf + 2 * kTP * G;                // [G][QP]
+    float* wbuf = ebuf + G * kEChunk;              // [2][4 tiles][kTP][G]
+    float* qs = wbuf + 2 * 4 * kTP * G;            // [G][QP]
 
     const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;  // longest tokens first when an order is given
     const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
@@ -273,8 +273,11 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     // ---- 3. outputs: thread `tid` folds column `tid` of all four heads over positions in order ----
     {
         const float total = totals[shd];
-        const float* erow = srow + (int64_t)shd * p.capacity + sp;
-        float e_cur = sp < len ? erow[0] : 0.0f;
+        const float* erow = srow + (int64_t)shd * p.capacity + sp;   // this thread makes the weights of positions sp + 32 j, head shd
+        constexpr int kBatch = 4;                  // tiles whose weights are made at once: one barrier per 128 positions
+        float e_next[kBatch];
+#pragma unroll
+        for (int j = 0; j < kBatch; j++) e_next[j] = sp + kTP * j < len ? erow[kTP * j] : 0.0f;
         const int col = tid;
         const unsigned char* colp = stages + (col >> 5) * BOX_BYTES + (col & 3) * 4;
         const int piece = (col & 31) >> 2;  // a value's 16-byte piece of its 128-byte row sits at piece ^ (position & 7)
@@ -284,67 +287,62 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
         float acc[G];
 #pragma unroll
         for (int i = 0; i < G; i++) acc[i] = 0.0f;
-        for (int tile = 0; tile < tiles; tile++) {
-            float* wt = wbuf + (tile & 1) * kTP * G;
-            wt[sp * G + shd] = __fdiv_rn(e_cur, total);
-            int next = (tile + 1) * kTP + sp;
-            e_cur = next < len ? erow[(tile + 1) * kTP] : 0.0f;
-            consumers_sync();  // this tile's weights are written; the other half of wbuf is no longer read
-            int j = tiles + tile, s = j % kRing;
-            if (!s_mbar_wait(&full[s], (unsigned)((j / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
-            const unsigned char* vt = colp + (size_t)s * STAGE_BYTES;
-            int count = min(kTP, len - tile * kTP);
-            int pos = 0;
-            if (count == kTP) {
-                // a whole tile: the loads of the next 8 positions are in flight while the current 8 are folded (a warp
-                // may be alone on its scheduler, so nothing else would hide a shared-memory load's latency)
-                float vv[2][8];
-                float4 ww[2][8];
+        for (int tile0 = 0; tile0 < tiles; tile0 += kBatch) {
+            float* wb = wbuf + ((tile0 / kBatch) & 1) * kBatch * kTP * G;
 #pragma unroll
-                for (int u = 0; u < 8; u++) vv[0][u] = *(const float*)(vt + voff[u]), ww[0][u] = *(const float4*)(wt + u * G);
+            for (int j = 0; j < kBatch; j++) wb[(kTP * j + sp) * G + shd] = __fdiv_rn(e_next[j], total);
 #pragma unroll
-                for (int group = 0; group < kTP / 8; group++) {
-                    const int cur = group & 1;
-                    if (group + 1 < kTP / 8) {
+            for (int j = 0; j < kBatch; j++) {  // the exp values of the next batch travel from L2 while this one is folded
+                int next = (tile0 + kBatch + j) * kTP + sp;
+                e_next[j] = next < len ? erow[(tile0 + kBatch + j) * kTP] : 0.0f;
+            }
+            consumers_sync();  // this batch's weights are written; the other half of wbuf is no longer read
+            const int last = min(tiles, tile0 + kBatch);
+            for (int tile = tile0; tile < last; tile++) {
+                const float* wt = wb + (tile - tile0) * kTP * G;
+                int j = tiles + tile, s = j % kRing;
+                if (!s_mbar_wait(&full[s], (unsigned)((j / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+                const unsigned char* vt = colp + (size_t)s * STAGE_BYTES;
+                int count = min(kTP, len - tile * kTP);
+                int pos = 0;
+                if (count == kTP) {
+                    // a whole tile: the loads of the next 8 positions are in flight while the current 8 are folded (a
+                    // warp may be alone on its scheduler, so nothing else would hide a shared-memory load's latency)
+                    float vv[2][8];
+                    float4 ww[2][8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++) vv[0][u] = *(const float*)(vt + voff[u]), ww[0][u] = *(const float4*)(wt + u * G);
+#pragma unroll
+                    for (int group = 0; group < kTP / 8; group++) {
+                        const int cur = group & 1;
+                        if (group + 1 < kTP / 8) {
+#pragma unroll
+                            for (int u = 0; u < 8; u++) {
+                                vv[cur ^ 1][u] = *(const float*)(vt + (group + 1) * 8 * 128 + voff[u]);
+                                ww[cur ^ 1][u] = *(const float4*)(wt + ((group + 1) * 8 + u) * G);
+                            }
+                        }
 #pragma unroll
                         for (int u = 0; u < 8; u++) {
-                            vv[cur ^ 1][u] = *(const float*)(vt + (group + 1) * 8 * 128 + voff[u]);
-                            ww[cur ^ 1][u] = *(const float4*)(wt + ((group + 1) * 8 + u) * G);
+                            acc[0] = __fadd_rn(acc[0], __fmul_rn(ww[cur][u].x, vv[cur][u]));
+                            acc[1] = __fadd_rn(acc[1], __fmul_rn(ww[cur][u].y, vv[cur][u]));
+                            acc[2] = __fadd_rn(acc[2], __fmul_rn(ww[cur][u].z, vv[cur][u]));
+                            acc[3] = __fadd_rn(acc[3], __fmul_rn(ww[cur][u].w, vv[cur][u]));
                         }
                     }
-#pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        acc[0] = __fadd_rn(acc[0], __fmul_rn(ww[cur][u].x, vv[cur][u]));
-                        acc[1] = __fadd_rn(acc[1], __fmul_rn(ww[cur][u].y, vv[cur][u]));
-                        acc[2] = __fadd_rn(acc[2], __fmul_rn(ww[cur][u].z, vv[cur][u]));
-                        acc[3] = __fadd_rn(acc[3], __fmul_rn(ww[cur][u].w, vv[cur][u]));
-                    }
+                    pos = kTP;
                 }
-                pos = kTP;
-            }
-            for (; pos + 8 <= count; pos += 8) {
-                float vv[8];
-#pragma unroll
-                for (int u = 0; u < 8; u++) vv[u] = *(const float*)(vt + pos * 128 + voff[u]);
-#pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    float4 w4 = *(const float4*)(wt + (pos + u) * G);
-                    acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv[u]));
-                    acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv[u]));
-                    acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv[u]));
-                    acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv[u]));
+                for (; pos < count; pos++) {
+                    float vv = *(const float*)(vt + pos * 128 + ((piece ^ (pos & 7)) << 4));  // no indexing of voff by a variable: it would move to local memory
+                    float4 w4 = *(const float4*)(wt + pos * G);
+                    acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv));
+                    acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv));
+                    acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv));
+                    acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv));
                 }
+                __syncwarp();
+                if (lane == 0) s_mbar_arrive(&empty[s]);
             }
-            for (; pos < count; pos++) {
-                float vv = *(const float*)(vt + pos * 128 + ((piece ^ (pos & 7)) << 4));  // no indexing of voff by a variable: it would move to local memory
-                float4 w4 = *(const float4*)(wt + pos * G);
-                acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv));
-                acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv));
-                acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv));
-                acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv));
-            }
-            __syncwarp();
-            if (lane == 0) s_mbar_arrive(&empty[s]);
         }
         if (!ok || *abort_flag) {
             if (tid == 0) atomicExch(&p.errors->timeout, 1);
@@ -380,7 +378,7 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
     uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
     TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
-    size_t smem = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
+    size_t smem = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * 4 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
     auto kernel = attention_stream_kernel<WIDTH>;
     {
         static std::mutex lock;
