@@ -15,7 +15,8 @@
  *  - Kernels never trap on bad data.  An out-of-range row id is recorded in a 3-int error
  *    record (count, first id, limit) that tsm_sync reads and clears, returning
  *    TSM_ERR_EXECUTION (kernels.cu:178-183, cuda.cr:967-983).
- *  - All work of a context runs on one in-order stream (DESIGN.md:570 of the reference).
+ *  - All work of a context runs on one in-order stream, as the reference's CUDA device does
+ *    (one stream per device, cuda.cr:200-253).
  *  - There is no CPU implementation behind any entry point: without a CUDA device every
  *    compute call fails with TSM_ERR_CUDA.
  */

@@ -1,6 +1,6 @@
 """Builds tests/golden/reference_fixtures.npz from the reference's own test fixtures.
 
-Run once where the reference tree is mounted:  python tests/golden/make_golden.py [/root/reference]
+Run once where the reference tree is mounted:  python tests/golden/make_golden.py <reference tree>
 The arrays are the golden vectors the reference's specs check against
 (spec/quant_spec.cr:15-27,115-134; spec/llama_spec.cr:50-87; spec/gpt2_spec.cr:54-102;
 spec/block_matmul_spec.cr:244-284), repacked as numpy arrays so that the tests can run
