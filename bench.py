@@ -333,6 +333,9 @@ def main():
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="with --gpus N > 1: dp = every rank decodes its own streams on a whole replica (no collective); "
                          "tp = the ranks share one model split by tensor parallelism (NCCL all-gathers) and decode the same streams")
+    ap.add_argument("--mode", default="exact", choices=["exact", "fast"],
+                    help="exact (default): the CPU path's bits; fast: tree sums and split-K attention, held to the reference's GPU budget "
+                         "of 0.001 nats KL per token, not to its bits")
     ap.add_argument("--case", default=None, help="time one kernel on a small case instead (see kernel_case), e.g. matvec,q4_0,128256,4096")
     ap.add_argument("--repeats", type=int, default=3, help="timed launches of --case")
     args = ap.parse_args()
@@ -355,6 +358,8 @@ def main():
     dev = pkg.B200(local)
     stream = torch.cuda.ExternalStream(dev.stream, device=local)
     peak, peak_kind = peaks()
+    if args.mode == "fast":
+        dev.set_mode(pkg.FAST)
     if args.case:
         print(json.dumps(kernel_case(pkg, dev, torch, stream, args.case, args.repeats, peak["hbm_gbs"])))
         dev.close()
@@ -369,7 +374,7 @@ def main():
     dev.sync()
     rows = w["rows"]
     config = dict(workload=w["name"], streams_per_gpu=rows, kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
-                  kv_dtype="f32", weights=w["kind"], l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
+                  kv_dtype="f32", weights=w["kind"], mode=args.mode, l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
                   parallelism=(f"tp{world}: projections split by output rows, 4 NCCL all-gathers per layer" if tp > 1 else
                                f"dp{world}: a replica and {rows} streams per GPU, no collective") if world > 1 else "single gpu")
 
