@@ -35,7 +35,8 @@ struct StreamParams {
     float* out;
     ErrorRecord* errors;
     const int* order;
-    float* scratch;  // [tokens][heads][capacity]: scores, then exp values
+    float* scratch;  // [tokens][heads][capacity]: scores, then exp values (split path: then weights)
+    int splits;      // split path: CTAs that share one (token, kv head)'s key positions
 };
 
 struct StreamMaps {
@@ -353,6 +354,285 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     }
 }
 
+
+// ---- the same attention as three launches, for calls with fewer (token, kv head) pairs than SMs ------------------
+// One CTA per pair walks up to `capacity` positions alone, so a launch that cannot fill the GPU (a tensor-parallel rank
+// with one or two kv heads, a handful of long streams) lasts as long as its longest stream takes on one SM.  Here the
+// score pass is cut by position ranges and the value pass by quarters of the width, with the softmax in between; every
+// sum is made in the same order as in the single launch, so the bits are the same.
+
+// Scores of the positions of tiles [first, last) of one (token, kv head): the quarter pipeline of the kernel above.
+template <int WIDTH>
+__global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    constexpr int G = 4;
+    constexpr int BOXES = WIDTH / 32;
+    constexpr int BOX_BYTES = kTP * 128;
+    constexpr int STAGE_BYTES = BOXES * BOX_BYTES;
+    constexpr int QP = WIDTH + 4;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)smem;
+    uint64_t* empty = (uint64_t*)(smem + 64);
+    uint64_t* ready = (uint64_t*)(smem + 128);
+    volatile int* abort_flag = (volatile int*)(smem + 320);
+    float* hand = (float*)(smem + 512);
+    unsigned char* stages = smem + 8192;
+    float* qs = (float*)(stages + kRing * STAGE_BYTES);    // [G][QP]
+
+    const int token = blockIdx.y;
+    const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
+    const int kvh = blockIdx.x / groups_per_kv;
+    const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
+    const int row = p.table[3 * token], limit = p.table[3 * token + 1];
+    if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0) report_bad_index(p.errors, limit, p.capacity);
+        return;
+    }
+    const int len = limit + 1;
+    const int all_tiles = (len + kTP - 1) / kTP;
+    const int first = (int)((int64_t)blockIdx.z * all_tiles / p.splits), last = (int)((int64_t)(blockIdx.z + 1) * all_tiles / p.splits);
+    const int tiles = last - first;
+    if (tiles <= 0) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    if (tid == 0) {
+        for (int s = 0; s < kRing; s++) {
+            s_mbar_init(&full[s], 1);
+            s_mbar_init(&empty[s], kConsumers / 32);
+            for (int w2 = 0; w2 < 3; w2++) s_mbar_init(&ready[w2 * kRing + s], 1);
+        }
+        abort_flag[0] = 0, abort_flag[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < G * WIDTH; i += blockDim.x)
+        qs[(i / WIDTH) * QP + i % WIDTH] = p.q[(int64_t)token * p.q_stride + (int64_t)head0 * WIDTH + i];
+    __syncthreads();
+
+    if (warp == kConsumers / 32) {
+        if (lane != 0) return;
+        const int plane = (row * p.kv_heads + kvh) * p.capacity;
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < tiles; j++) {
+            int s = j % kRing;
+            if (j >= kRing) ok = s_mbar_wait(&empty[s], (unsigned)((j / kRing - 1) & 1), abort_flag);
+            if (!ok) break;
+            unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
+            s_mbar_expect_tx(&full[s], STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < BOXES; b++) s_tensor_load(dst + b * BOX_BYTES, &maps.k, 32 * b, plane + (first + j) * kTP, &full[s]);
+            issued = j + 1;
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int j = max(0, issued - kRing); j < issued; j++) s_mbar_wait(&full[j % kRing], (unsigned)((j / kRing) & 1), abort_flag + 1);
+        }
+        return;
+    }
+
+    float* srow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;
+    float qreg[G][32];
+#pragma unroll
+    for (int h = 0; h < G; h++)
+#pragma unroll
+        for (int j = 0; j < 32; j++) qreg[h][j] = qs[h * QP + 32 * warp + j];
+    const int sw = lane & 7;
+    bool ok = true;
+    for (int tile = 0; tile < tiles; tile++) {
+        const int s = tile % kRing;
+        const unsigned parity = (unsigned)((tile / kRing) & 1);
+        if (!s_mbar_wait(&full[s], parity, abort_flag)) ok = false, *abort_flag = 1;
+        float acc[G] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (warp > 0) {
+            if (!s_mbar_wait(&ready[(warp - 1) * kRing + s], parity, abort_flag)) ok = false, *abort_flag = 1;
+            float4 in = *(const float4*)(hand + (((warp - 1) * kRing + s) * 32 + lane) * 4);
+            acc[0] = in.x, acc[1] = in.y, acc[2] = in.z, acc[3] = in.w;
+        }
+        const unsigned char* rowp = stages + (size_t)s * STAGE_BYTES + warp * BOX_BYTES + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {
+            float4 kv4 = *(const float4*)(rowp + ((c ^ sw) << 4));
+#pragma unroll
+            for (int h = 0; h < G; h++) {
+                acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 0], kv4.x));
+                acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 1], kv4.y));
+                acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 2], kv4.z));
+                acc[h] = __fadd_rn(acc[h], __fmul_rn(qreg[h][4 * c + 3], kv4.w));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) s_mbar_arrive(&empty[s]);
+        if (warp < 3) {
+            *(float4*)(hand + ((warp * kRing + s) * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            __syncwarp();
+            if (lane == 0) s_mbar_arrive(&ready[warp * kRing + s]);
+        } else {
+            int pos = (first + tile) * kTP + lane;
+            if (pos < len) {
+#pragma unroll
+                for (int h = 0; h < G; h++) srow[(int64_t)h * p.capacity + pos] = __fadd_rn(__fmul_rn(acc[h], p.scale), 0.0f);
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(&p.errors->timeout, 1);
+}
+
+// One (token, head): maximum, exp, the denominator folded in position order, weights = exp / denominator in place.
+__global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p) {
+    __shared__ __align__(16) float ebuf[kEChunk];
+    __shared__ float red[8];
+    __shared__ float shared_total;
+    const int token = blockIdx.y, head = blockIdx.x;
+    const int row = p.table[3 * token], limit = p.table[3 * token + 1];
+    if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) return;  // reported by the score kernel
+    const int len = limit + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* sr = p.scratch + ((int64_t)token * p.heads + head) * p.capacity;
+    float top = -INFINITY;
+    for (int i = tid; i < len; i += 256) top = fmaxf(top, sr[i]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+    if (lane == 0) red[warp] = top;
+    __syncthreads();
+    top = red[0];
+#pragma unroll
+    for (int w2 = 1; w2 < 8; w2++) top = fmaxf(top, red[w2]);
+    float total = 0.0f;
+    for (int e0 = 0; e0 < len; e0 += kEChunk) {
+        int count = min(kEChunk, len - e0);
+        float sv[kEChunk / 256];
+#pragma unroll
+        for (int u = 0; u < kEChunk / 256; u++) sv[u] = u * 256 + tid < count ? sr[e0 + u * 256 + tid] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < kEChunk / 256; u++)
+            if (u * 256 + tid < count) {
+                float e = exact_exp(__fsub_rn(sv[u], top));
+                sr[e0 + u * 256 + tid] = e;
+                ebuf[u * 256 + tid] = e;
+            }
+        __syncthreads();
+        if (tid == 0) {
+            int i = 0;
+            for (; i + 8 <= count; i += 8) {
+                float4 a = *(const float4*)(ebuf + i), b = *(const float4*)(ebuf + i + 4);
+                total = __fadd_rn(total, a.x), total = __fadd_rn(total, a.y), total = __fadd_rn(total, a.z), total = __fadd_rn(total, a.w);
+                total = __fadd_rn(total, b.x), total = __fadd_rn(total, b.y), total = __fadd_rn(total, b.z), total = __fadd_rn(total, b.w);
+            }
+            for (; i < count; i++) total = __fadd_rn(total, ebuf[i]);
+        }
+        __syncthreads();
+    }
+    if (tid == 0) shared_total = total;
+    __syncthreads();
+    total = shared_total;
+    for (int i = tid; i < len; i += 256) sr[i] = __fdiv_rn(sr[i], total);
+}
+
+// Outputs of one quarter of the width (32 columns) of one (token, kv head): one consumer warp folds weight * value over all
+// positions in order, its box of every value tile arriving through a ring; the weights come from the scratch array.
+template <int WIDTH>
+__global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    constexpr int G = 4;
+    constexpr int BOX_BYTES = kTP * 128;
+    constexpr int kDeep = 6;                       // stages of 4 KB
+    __shared__ __align__(1024) unsigned char stages[kDeep * BOX_BYTES];
+    __shared__ __align__(16) float wbuf[2][kTP * G];
+    __shared__ uint64_t full[kDeep], empty[kDeep];
+    __shared__ int abort_words[2];
+    volatile int* abort_flag = abort_words;
+
+    const int token = blockIdx.y;
+    const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
+    const int quarter = blockIdx.x & 3, group = blockIdx.x >> 2;
+    const int kvh = group / groups_per_kv;
+    const int head0 = kvh * per_kv + (group % groups_per_kv) * G;
+    const int row = p.table[3 * token], limit = p.table[3 * token + 1];
+    if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) return;
+    const int len = limit + 1;
+    const int tiles = (len + kTP - 1) / kTP;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < kDeep; s++) s_mbar_init(&full[s], 1), s_mbar_init(&empty[s], 1);
+        abort_words[0] = 0, abort_words[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 1) {
+        if (lane != 0) return;
+        const int plane = (row * p.kv_heads + kvh) * p.capacity;
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < tiles; j++) {
+            int s = j % kDeep;
+            if (j >= kDeep) ok = s_mbar_wait(&empty[s], (unsigned)((j / kDeep - 1) & 1), abort_flag);
+            if (!ok) break;
+            s_mbar_expect_tx(&full[s], BOX_BYTES);
+            s_tensor_load(stages + s * BOX_BYTES, &maps.v, 32 * quarter, plane + j * kTP, &full[s]);
+            issued = j + 1;
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int j = max(0, issued - kDeep); j < issued; j++) s_mbar_wait(&full[j % kDeep], (unsigned)((j / kDeep) & 1), abort_flag + 1);
+        }
+        return;
+    }
+    // consumer warp: lane = column 32 quarter + lane
+    const float* wrow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;   // weights [h][position]
+    const int piece = lane >> 2;
+    int voff[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) voff[u] = u * 128 + ((piece ^ u) << 4) + (lane & 3) * 4;
+    float acc[G] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float w_next[G];   // lane's position of the next tile, four heads
+#pragma unroll
+    for (int h = 0; h < G; h++) w_next[h] = lane < len ? wrow[(int64_t)h * p.capacity + lane] : 0.0f;
+    bool ok = true;
+    for (int tile = 0; tile < tiles; tile++) {
+        float* wt = wbuf[tile & 1];
+        *(float4*)(wt + lane * G) = make_float4(w_next[0], w_next[1], w_next[2], w_next[3]);
+        int next = (tile + 1) * kTP + lane;
+#pragma unroll
+        for (int h = 0; h < G; h++) w_next[h] = next < len ? wrow[(int64_t)h * p.capacity + next] : 0.0f;
+        __syncwarp();
+        int s = tile % kDeep;
+        if (!s_mbar_wait(&full[s], (unsigned)((tile / kDeep) & 1), abort_flag)) ok = false, *abort_flag = 1;
+        const unsigned char* vt = stages + s * BOX_BYTES;
+        int count = min(kTP, len - tile * kTP);
+        int pos = 0;
+        for (; pos + 8 <= count; pos += 8) {
+            float vv[8];
+            float4 ww[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) vv[u] = *(const float*)(vt + pos * 128 + voff[u]), ww[u] = *(const float4*)(wt + (pos + u) * G);
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                acc[0] = __fadd_rn(acc[0], __fmul_rn(ww[u].x, vv[u]));
+                acc[1] = __fadd_rn(acc[1], __fmul_rn(ww[u].y, vv[u]));
+                acc[2] = __fadd_rn(acc[2], __fmul_rn(ww[u].z, vv[u]));
+                acc[3] = __fadd_rn(acc[3], __fmul_rn(ww[u].w, vv[u]));
+            }
+        }
+        for (; pos < count; pos++) {
+            float vv = *(const float*)(vt + pos * 128 + ((piece ^ (pos & 7)) << 4) + (lane & 3) * 4);
+            float4 w4 = *(const float4*)(wt + pos * G);
+            acc[0] = __fadd_rn(acc[0], __fmul_rn(w4.x, vv));
+            acc[1] = __fadd_rn(acc[1], __fmul_rn(w4.y, vv));
+            acc[2] = __fadd_rn(acc[2], __fmul_rn(w4.z, vv));
+            acc[3] = __fadd_rn(acc[3], __fmul_rn(w4.w, vv));
+        }
+        __syncwarp();
+        if (lane == 0) s_mbar_arrive(&empty[s]);
+    }
+    if (!ok) {
+        if (lane == 0) atomicExch(&p.errors->timeout, 1);
+        return;
+    }
+#pragma unroll
+    for (int i = 0; i < G; i++) p.out[((int64_t)token * p.heads + head0 + i) * WIDTH + 32 * quarter + lane] = acc[i];
+}
+
 }  // namespace
 
 int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { return (int64_t)tokens * heads * capacity * 4 + 256; }
@@ -373,11 +653,43 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
                             float* scratch) {
     constexpr int WIDTH = 128;
-    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch};
+    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch, 1};
     StreamMaps maps;
     uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
     TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
+    const int groups = kv_heads * (heads / kv_heads / 4);
+    // At most two (token, kv head) pairs per SM and long caches (measured: 102 against 181 us for 8 streams of up to 4096
+    // positions, 156 against 209 for 16, 236 against 253 for 32; 433 against 307 for 64, where the single launch stays): three launches that cut the score pass by positions and the
+    // value pass by quarters of the width, so that the longest stream does not set the time alone.  TSM_ATTN_SPLIT=0 / 1
+    // forces the choice.
+    static const char* forced = getenv("TSM_ATTN_SPLIT");
+    bool split = (int64_t)tokens * groups <= 2 * (int64_t)ctx->sm_count && capacity >= 1024;
+    if (forced) split = forced[0] == '1';
+    if (split) {
+        size_t smem_scores = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + 4 * (WIDTH + 4) * 4;
+        {
+            static std::mutex lock;
+            static std::map<int, bool> done;
+            std::lock_guard<std::mutex> guard(lock);
+            if (!done.count(ctx->ordinal)) {
+                TSM_CUDA(ctx, cudaFuncSetAttribute(attention_scores_kernel<WIDTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_scores));
+                done[ctx->ordinal] = true;
+            }
+        }
+        int64_t pairs = (int64_t)tokens * groups;
+        p.splits = (int)std::max<int64_t>(1, std::min<int64_t>(8, (2 * (int64_t)ctx->sm_count + pairs - 1) / pairs));
+        attention_scores_kernel<WIDTH><<<dim3(groups, tokens, p.splits), kConsumers + 32, smem_scores, ctx->stream>>>(p, maps);
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        attention_weights_kernel<<<dim3(heads, tokens), 256, 0, ctx->stream>>>(p);
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        attention_values_kernel<WIDTH><<<dim3(groups * 4, tokens), 64, 0, ctx->stream>>>(p, maps);
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        return TSM_OK;
+    }
     size_t smem = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * 4 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
     auto kernel = attention_stream_kernel<WIDTH>;
     {
@@ -389,7 +701,7 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
             done[ctx->ordinal] = true;
         }
     }
-    dim3 grid(kv_heads * (heads / kv_heads / 4), tokens);
+    dim3 grid(groups, tokens);
     kernel<<<grid, kConsumers + 32, smem, ctx->stream>>>(p, maps);
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);

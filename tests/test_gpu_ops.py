@@ -217,6 +217,19 @@ def test_ragged_attention(dev, width, group):
     assert np.array_equal(bits(dev.ragged_attention(q[1:2], k, v, table[1:2], scale)[0]), bits(exact[1]))
 
 
+def test_long_caches_with_few_streams_take_the_three_launch_path(dev):
+    """Few (token, kv head) pairs and a long cache: the score pass is cut by positions and the value pass by quarters of the
+    width; the bits stay those of the oracle (and of the single launch, which the case above exercises)."""
+    rng = np.random.default_rng(12)
+    lengths = [(0, 1500), (1, 33), (2, 1024), (0, 1), (1, 1279)]
+    q, k, v, table, heads = attention_case(rng, 3, 2, 4, 1536, 128, lengths)
+    scale = np.float32(1.0 / np.sqrt(128))
+    want = oracle_attention(q, k, v, table, scale)
+    got = dev.ragged_attention(q, k, v, table, scale)
+    assert np.array_equal(bits(got), bits(want))
+    assert np.array_equal(bits(dev.ragged_attention(q[2:3], k, v, table[2:3], scale)[0]), bits(got[2]))
+
+
 def test_sampler_picks(dev):
     logits = np.array([[0.5, 2.0, 2.0, -1.0, 2.0, 1.5], [3.0, 1.0, 3.0, 0.0, 0.0, 0.0]], dtype=np.float32)
     assert dev.argmax(logits).tolist() == [1, 0]
