@@ -493,7 +493,7 @@ def main():
         # these shapes and lengths; none for other workloads
         traffic = None
         if args.workload == "c5":
-            traffic = 1310424576 if top is kernels[0] else 67894272
+            traffic = 1310231256 if top is kernels[0] else 67894272
         line["roofline"] = dict(bound="hbm", kernel=top["kernel"], achieved=top["gbs"], peak=peak["hbm_gbs"], unit="GB/s",
                                 frac=top["gbs"] / peak["hbm_gbs"], traffic=traffic, algorithmic_bytes=top["bytes"], peak_kind=peak_kind)
         line["kernels"] = kernels
