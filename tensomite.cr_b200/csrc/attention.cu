@@ -37,6 +37,7 @@ __global__ void __launch_bounds__(256) attention_chunk_kernel(const float* __res
                                                               int rows, int kv_heads, int capacity,
                                                               const int* __restrict__ table, float scale, int chunks,
                                                               float* part_o, float* part_ml, ErrorRecord* errors) {
+    chained_kernel_entry();
     constexpr int LPP = WIDTH / 16;  // lanes per position in the score phase (16 values each)
     constexpr int PPW = 32 / LPP;    // positions per warp iteration
     constexpr int TPR = WIDTH / 4;   // threads per value row in the output phase
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(256) attention_chunk_kernel(const float* __res
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int heads,
                                        int width, int chunks, const int* __restrict__ table, int capacity, float* out,
                                        QuantOutA qo) {
+    chained_kernel_entry();
     int token = blockIdx.y;
     int lane = threadIdx.x & 31;
     int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // 32-column block of the token's [heads*width]
@@ -220,6 +222,7 @@ __global__ void attention_ordered_kernel(const float* __restrict__ q, int64_t q_
                                          const float* __restrict__ k, const float* __restrict__ v, int rows, int kv_heads,
                                          int capacity, const int* __restrict__ table, float scale, float* out,
                                          ErrorRecord* errors) {
+    chained_kernel_entry();
     extern __shared__ float sh[];
     float* qs = sh;              // width
     float* scores = sh + width;  // len
@@ -294,6 +297,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
                                                                   int rows, int kv_heads, int capacity,
                                                                   const int* __restrict__ table, float scale, float* out,
                                                                   ErrorRecord* errors, const int* __restrict__ order) {
+    chained_kernel_entry();
     constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
     constexpr int PITCH = WIDTH + 4;            // floats per staged key row
     constexpr int CHUNKS = WIDTH / 4;           // 16-byte pieces per key row
@@ -463,6 +467,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
 // Ranks tokens by visible positions, most first: with one long-running CTA per (token, kv group) and ragged
 // lengths, starting the longest first keeps the last wave short.
 __global__ void length_order_kernel(const int* __restrict__ table, int tokens, int* order) {
+    chained_kernel_entry();
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tokens) return;
     int mine = table[3 * t + 1], rank = 0;
@@ -475,7 +480,7 @@ __global__ void length_order_kernel(const int* __restrict__ table, int tokens, i
 
 int launch_length_order(tsm_ctx* ctx, const int* table, int tokens, int* order) {
     if (tokens == 0) return TSM_OK;
-    length_order_kernel<<<(tokens + 255) / 256, 256, 0, ctx->stream>>>(table, tokens, order);
+    TSM_CUDA(ctx, launch_chained(ctx, length_order_kernel, dim3((tokens + 255) / 256), dim3(256), 0, table, tokens, order));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -500,9 +505,9 @@ static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int token
     int per_kv = heads / kv_heads;
     int group = per_kv <= 4 ? per_kv : (per_kv % 4 == 0 ? 4 : (per_kv % 2 == 0 ? 2 : 1));
     dim3 grid(chunks, kv_heads * (per_kv / group), tokens);
-#define TSM_ATTN(G)                                                                                                     \
-    attention_chunk_kernel<WIDTH, G><<<grid, 256, 0, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, \
-                                                                    table, scale, chunks, part_o, part_ml, ctx->errors)
+#define TSM_ATTN(G)                                                                                                      \
+    TSM_CUDA(ctx, launch_chained(ctx, attention_chunk_kernel<WIDTH, G>, grid, dim3(256), 0, q, q_stride, heads, k, v, rows, kv_heads, \
+                                 capacity, table, scale, chunks, part_o, part_ml, ctx->errors))
     if (group == 1) TSM_ATTN(1);
     else if (group == 2) TSM_ATTN(2);
     else if (group == 3) TSM_ATTN(3);
@@ -514,7 +519,7 @@ static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int token
     if (quantized) qo = QuantOutA{(float*)quantized->scales, (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs};
     int items = (heads * WIDTH + 31) / 32;
     dim3 mgrid((items + 3) / 4, tokens);
-    attention_merge_kernel<<<mgrid, 128, 0, ctx->stream>>>(part_o, part_ml, heads, WIDTH, chunks, table, capacity, out, qo);
+    TSM_CUDA(ctx, launch_chained(ctx, attention_merge_kernel, mgrid, dim3(128), 0, part_o, part_ml, heads, WIDTH, chunks, table, capacity, out, qo));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -559,8 +564,8 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     do {                                                                                                                  \
         auto kernel = attention_exact_kernel<W, G, T, TP, S, U>;                                                          \
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
-        kernel<<<grid, T, smem, ctx->stream>>>(q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, out,      \
-                                               ctx->errors, order);                                                       \
+        TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(T), smem, q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, \
+                                     out, ctx->errors, order));                                                           \
     } while (0)
 #define TSM_EXACT_STAGES(W, G, T, TP, U)          \
     do {                                          \
@@ -597,8 +602,8 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
             TSM_CUDA(ctx, cudaFuncSetAttribute(attention_ordered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         dim3 grid(heads, tokens);
         int threads = capacity >= 1024 ? 256 : 128;
-        attention_ordered_kernel<<<grid, threads, smem, ctx->stream>>>(q, q_stride, heads, width, k, v, rows, kv_heads, capacity,
-                                                                       table, scale, out, ctx->errors);
+        TSM_CUDA(ctx, launch_chained(ctx, attention_ordered_kernel, grid, dim3(threads), smem, q, q_stride, heads, width, k, v, rows, kv_heads,
+                                     capacity, table, scale, out, ctx->errors));
     }
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);

@@ -83,6 +83,7 @@ __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;
 
 template <int WIDTH>
 __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    chained_kernel_entry();
     constexpr int G = 4;
     constexpr int BOXES = WIDTH / 32;              // 128-byte wide boxes per row
     constexpr int BOX_BYTES = kTP * 128;
@@ -364,6 +365,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
 // Scores of the positions of tiles [first, last) of one (token, kv head): the quarter pipeline of the kernel above.
 template <int WIDTH>
 __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    chained_kernel_entry();
     constexpr int G = 4;
     constexpr int BOXES = WIDTH / 32;
     constexpr int BOX_BYTES = kTP * 128;
@@ -480,6 +482,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
 
 // One (token, head): maximum, exp, the denominator folded in position order, weights = exp / denominator in place.
 __global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p) {
+    chained_kernel_entry();
     __shared__ __align__(16) float ebuf[kEChunk];
     __shared__ float red[8];
     __shared__ float shared_total;
@@ -533,6 +536,7 @@ __global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p) 
 // positions in order, its box of every value tile arriving through a ring; the weights come from the scratch array.
 template <int WIDTH>
 __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    chained_kernel_entry();
     constexpr int G = 4;
     constexpr int BOX_BYTES = kTP * 128;
     constexpr int kDeep = 6;                       // stages of 4 KB
@@ -679,13 +683,13 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         }
         int64_t pairs = (int64_t)tokens * groups;
         p.splits = (int)std::max<int64_t>(1, std::min<int64_t>(8, (2 * (int64_t)ctx->sm_count + pairs - 1) / pairs));
-        attention_scores_kernel<WIDTH><<<dim3(groups, tokens, p.splits), kConsumers + 32, smem_scores, ctx->stream>>>(p, maps);
+        TSM_CUDA(ctx, launch_chained(ctx, attention_scores_kernel<WIDTH>, dim3(groups, tokens, p.splits), dim3(kConsumers + 32), smem_scores, p, maps));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
-        attention_weights_kernel<<<dim3(heads, tokens), 256, 0, ctx->stream>>>(p);
+        TSM_CUDA(ctx, launch_chained(ctx, attention_weights_kernel, dim3(heads, tokens), dim3(256), 0, p));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
-        attention_values_kernel<WIDTH><<<dim3(groups * 4, tokens), 64, 0, ctx->stream>>>(p, maps);
+        TSM_CUDA(ctx, launch_chained(ctx, attention_values_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(64), 0, p, maps));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
         return TSM_OK;
@@ -702,7 +706,7 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         }
     }
     dim3 grid(groups, tokens);
-    kernel<<<grid, kConsumers + 32, smem, ctx->stream>>>(p, maps);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(kConsumers + 32), smem, p, maps));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -61,6 +61,7 @@ constexpr int kNcclInt8 = 0;  // ncclDataType_t: bytes are gathered, whatever th
 // dst[t, seg * width + j] (+)= src[seg, t, j]: the ranks' column slices, as an all-gather leaves them, back in row order.
 template <bool ADD>
 __global__ void interleave_kernel(const float* __restrict__ src, float* dst, int rows, int width, int parts) {
+    chained_kernel_entry();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     int64_t total = (int64_t)rows * width * parts;
     if (i >= total) return;
@@ -87,8 +88,8 @@ int launch_interleave(tsm_ctx* ctx, const float* gathered, float* dst, int rows,
     int64_t total = (int64_t)rows * width * parts;
     if (total == 0) return TSM_OK;
     unsigned grid = (unsigned)((total + 255) / 256);
-    if (add) interleave_kernel<true><<<grid, 256, 0, ctx->stream>>>(gathered, dst, rows, width, parts);
-    else interleave_kernel<false><<<grid, 256, 0, ctx->stream>>>(gathered, dst, rows, width, parts);
+    if (add) TSM_CUDA(ctx, launch_chained(ctx, interleave_kernel<true>, dim3(grid), dim3(256), 0, gathered, dst, rows, width, parts));
+    else TSM_CUDA(ctx, launch_chained(ctx, interleave_kernel<false>, dim3(grid), dim3(256), 0, gathered, dst, rows, width, parts));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -695,6 +695,7 @@ static int product(tsm_model* m, const QuantizedActs& a, int rows, const Linear&
 // index within the slice ([ranks][2][rows] as gathered).  The highest wins; equal values go to the lower rank, whose
 // slice holds the lower indices (Sampler.greedy keeps the first maximum).
 __global__ void combine_picks_kernel(const float* __restrict__ best, int rows, int ranks, int slice, int* picks) {
+    chained_kernel_entry();
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= rows) return;
     float top = best[t];
@@ -765,7 +766,7 @@ static int launch_head_sharded(tsm_model* m, const QuantizedActs& qh, int output
         float* best = w.tp_best + (int64_t)r * 2 * outputs;
         TSM_TRY(launch_topk(ctx, mine, outputs, slice, 1, (int*)(best + outputs), best));
         TSM_TRY(tp_all_gather(ctx, w.tp_best, (int64_t)2 * outputs * 4));
-        combine_picks_kernel<<<(outputs + 255) / 256, 256, 0, ctx->stream>>>(w.tp_best, outputs, G, slice, w.picks);
+        TSM_CUDA(ctx, launch_chained(ctx, combine_picks_kernel, dim3((outputs + 255) / 256), dim3(256), 0, w.tp_best, outputs, G, slice, w.picks));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
     }
@@ -785,7 +786,16 @@ static int gather_full_logits(tsm_model* m, int outputs) {
 
 // Launches one step over `total` packed tokens whose ids and table are already in the workspace.
 // `outputs` rows (indices in ws.last when fewer than total) go through the final norm and the head.
+static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int outputs, bool pick);
+
 static int launch_step(tsm_model* m, tsm_cache* cache, int total, int outputs, bool pick) {
+    m->ctx->chain_launches = total <= 4;  // a few rows: a chain of very short kernels, worth overlapping their launches
+    int rc = launch_step_kernels(m, cache, total, outputs, pick);
+    m->ctx->chain_launches = false;
+    return rc;
+}
+
+static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int outputs, bool pick) {
     const tsm_model_config& c = m->cfg;
     tsm_ctx* ctx = m->ctx;
     Workspace& w = m->ws;
@@ -883,6 +893,7 @@ static void drop_run_graph(tsm_cache* cache) {
 // Between the steps of a device-resident run: each row's pick becomes its next token and its
 // position moves on, so that no step waits for the host.
 __global__ void run_advance_kernel(int* ids, int* table, const int* picks, int rows, const int* state) {
+    chained_kernel_entry();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= rows || state[0] == 0) return;
     ids[r] = picks[r];
@@ -891,6 +902,7 @@ __global__ void run_advance_kernel(int* ids, int* table, const int* picks, int r
 }
 
 __global__ void run_record_kernel(const int* picks, int rows, int* state) {
+    chained_kernel_entry();
     int r = blockIdx.x * blockDim.x + threadIdx.x;
     int step = state[0];
     if (r < rows) state[1 + (int64_t)step * rows + r] = picks[r];
@@ -1219,12 +1231,12 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
     if (!cache->run_graph) {
         cudaGraph_t graph = nullptr;
         TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        run_advance_kernel<<<(rows + 255) / 256, 256, 0, ctx->stream>>>(w.ids, w.table, w.picks, rows, cache->run_state);
+        cudaError_t e0 = launch_chained(ctx, run_advance_kernel, dim3((rows + 255) / 256), dim3(256), 0, w.ids, w.table, w.picks, rows, cache->run_state);
         count_launch(ctx);
         int rc = launch_step(model, cache, rows, rows, true);
-        run_record_kernel<<<1, 1024, 0, ctx->stream>>>(w.picks, rows, cache->run_state);
+        if (e0 == cudaSuccess) e0 = launch_chained(ctx, run_record_kernel, dim3(1), dim3(1024), 0, w.picks, rows, cache->run_state);
         count_launch(ctx);
-        cudaError_t e1 = cudaGetLastError();
+        cudaError_t e1 = e0 != cudaSuccess ? e0 : cudaGetLastError();
         cudaError_t e2 = cudaStreamEndCapture(ctx->stream, &graph);
         if (rc == TSM_OK && (e1 != cudaSuccess || e2 != cudaSuccess)) rc = cuda_fail(ctx, e1 != cudaSuccess ? e1 : e2, "capture of a decode step");
         if (rc == TSM_OK) {

@@ -112,6 +112,7 @@ __host__ __device__ constexpr int chunk_blocks(int cols) { return cols >= 64 ? 4
 // cp.async; scales are staged [block][activation row], so that a thread's two activation rows are one 8-byte load.
 template <int KIND, int NT, int WR, int WC>
 __global__ void __launch_bounds__(32 * WR * WC) matmul_mma_kernel(GemmParams p) {
+    chained_kernel_entry();
     constexpr int B = GFmt<KIND>::B;
     constexpr int ROWS = 16 * WR, COLS = 8 * NT * WC, THREADS = 32 * WR * WC;
     constexpr int kChunkBlocks = chunk_blocks(COLS);
@@ -304,7 +305,7 @@ int launch_shape(tsm_ctx* ctx, const GemmParams& p) {
         }
     }
     dim3 grid((p.n + ROWS - 1) / ROWS, (p.m + COLS - 1) / COLS);
-    kernel<<<grid, THREADS, smem, ctx->stream>>>(p);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(THREADS), smem, p));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -142,6 +142,7 @@ struct PipeMaps {
 // [b * groups / gridDim.x, (b + 1) * groups / gridDim.x): at most wr_max of them by the host's choice of grid.
 template <int KIND, int NT, int WC>
 __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int wr_max, const __grid_constant__ PipeMaps maps) {
+    chained_kernel_entry();
     constexpr int COLS = 8 * NT * WC;
     using L = PipeLayout<KIND, COLS>;
     constexpr int B = L::B, WP = L::WP;
@@ -365,6 +366,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
 // 2t, 2t + 1 of each tile; every output's blocks are still folded in block order.
 template <int KIND, int MT, int WC>
 __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int wr_max, const __grid_constant__ PipeMaps maps) {
+    chained_kernel_entry();
     constexpr int COLS = 16 * MT * WC;
     using L = PipeLayout<KIND, COLS>;
     constexpr int B = L::B, WP = L::WP;
@@ -601,7 +603,7 @@ int launch_pipe_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     TSM_TRY(make_tensor_map_2d(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m, nb * 4,
                      kCB, COLS, CU_TENSOR_MAP_SWIZZLE_32B));
     dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
-    kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(32 * (wr_max * WC + 1)), smem, p, wr_max, maps));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -652,7 +654,7 @@ int launch_pipe_t_shape(tsm_ctx* ctx, PipeParams p, int ctas_per_sm_forced) {
     TSM_TRY(make_tensor_map_2d(ctx, &maps.sums, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, KIND == TSM_Q4_1 ? p.acts.sums : p.acts.scales, nb, (uint64_t)p.m,
                                nb * 4, kCB, COLS, CU_TENSOR_MAP_SWIZZLE_32B));
     dim3 grid(grid_x, (p.m + COLS - 1) / COLS);
-    kernel<<<grid, 32 * (wr_max * WC + 1), smem, ctx->stream>>>(p, wr_max, maps);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(32 * (wr_max * WC + 1)), smem, p, wr_max, maps));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -93,6 +93,7 @@ __host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (k
 
 template <int KIND, int C, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
+    chained_kernel_entry();
     using F = Fmt<KIND>;
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = p.nb;
@@ -355,6 +356,7 @@ __device__ __forceinline__ unsigned load_u32_2(const uint8_t* p) {  // p is 2-by
 template <int KIND>
 __global__ void matvec_generic_kernel(const uint8_t* __restrict__ w, int n, int nb, QuantizedActs acts, int rows,
                                       const float* __restrict__ bias, const float* __restrict__ residual, float* out) {
+    chained_kernel_entry();
     constexpr int B = Fmt<KIND>::B;
     int lane = threadIdx.x & 31;
     int64_t col = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -473,7 +475,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
     p.cap = cap, p.stages = stages;
     p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
-    kernel<<<grid, kThreads, smem, ctx->stream>>>(p);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, dim3(grid), dim3(kThreads), smem, p));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     *taken = true;
@@ -493,7 +495,7 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
     if (rows > 4 && mma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_mma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     int nb = k / 32;
     int64_t grid = ((int64_t)n + 3) / 4;
-    matvec_generic_kernel<KIND><<<(unsigned)grid, 128, 0, ctx->stream>>>(w, n, nb, a, rows, bias, residual, out);
+    TSM_CUDA(ctx, launch_chained(ctx, matvec_generic_kernel<KIND>, dim3((unsigned)grid), dim3(128), 0, w, n, nb, a, rows, bias, residual, out));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -7,6 +7,7 @@ namespace tsm {
 // ---- activation quantiser (quantize_block_q8 in common.cuh): one warp per block of 32 -------------
 __global__ void quantize_rows_kernel(const float* __restrict__ x, int rows, int k, int64_t x_stride, float* scales,
                                      float* sums, int* totals, int8_t* qs) {
+    chained_kernel_entry();
     int lane = threadIdx.x & 31;
     int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int nb = k >> 5;
@@ -40,7 +41,7 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
     int64_t blocks = (int64_t)rows * (k / 32);
     if (blocks == 0) return TSM_OK;
     int64_t grid = (blocks + 7) / 8;
-    quantize_rows_kernel<<<(unsigned)grid, 256, 0, ctx->stream>>>(x, rows, k, x_stride, scales, sums, totals, qs);
+    TSM_CUDA(ctx, launch_chained(ctx, quantize_rows_kernel, dim3((unsigned)grid), dim3(256), 0, x, rows, k, x_stride, scales, sums, totals, qs));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -162,6 +163,7 @@ int launch_dequantize_blocks(tsm_ctx* ctx, const uint8_t* blocks, int64_t count,
 __global__ void gather_blocks_kernel(const uint8_t* __restrict__ table, int kind, int table_rows, int width,
                                      const int* __restrict__ ids, int64_t total, float* out, ErrorRecord* errors,
                                      const uint8_t* __restrict__ table2, const int* __restrict__ ids2, int ids2_stride) {
+    chained_kernel_entry();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     int token = (int)(i / width), col = (int)(i % width);
@@ -184,8 +186,8 @@ int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table
     if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
     int64_t total = (int64_t)count * width;
     if (total == 0) return TSM_OK;
-    gather_blocks_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(table, kind, table_rows, width, ids, total,
-                                                                                  out, ctx->errors, table2, ids2, ids2_stride);
+    TSM_CUDA(ctx, launch_chained(ctx, gather_blocks_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, table, kind, table_rows, width, ids,
+                                 total, out, ctx->errors, table2, ids2, ids2_stride));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -193,6 +195,7 @@ int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table
 
 __global__ void gather_f32_kernel(const float* __restrict__ table, int table_rows, int width, const int* __restrict__ ids,
                                   int64_t total, float* out, ErrorRecord* errors) {
+    chained_kernel_entry();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     int token = (int)(i / width), col = (int)(i % width);
@@ -208,8 +211,7 @@ __global__ void gather_f32_kernel(const float* __restrict__ table, int table_row
 int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out) {
     int64_t total = (int64_t)count * width;
     if (total == 0) return TSM_OK;
-    gather_f32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(table, table_rows, width, ids, total, out,
-                                                                               ctx->errors);
+    TSM_CUDA(ctx, launch_chained(ctx, gather_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, table, table_rows, width, ids, total, out, ctx->errors));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

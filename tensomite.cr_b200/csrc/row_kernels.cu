@@ -72,6 +72,7 @@ __device__ __forceinline__ float ordered_sum(const float* row, float* terms, int
 template <bool LAYER>
 __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int n,
                             float eps, float* out, QuantOut q, int exact) {
+    chained_kernel_entry();
     extern __shared__ __align__(16) float row[];  // [n], then the terms of the ordered sums, 16-byte aligned
     __shared__ float scratch[32];
     float* terms = row + ((n + 3) & ~3);
@@ -134,10 +135,10 @@ static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w,
     int exact = ctx->mode == TSM_EXACT;
     if (layer) {
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
-        norm_kernel<true><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
+        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<true>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact));
     } else {
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
-        norm_kernel<false><<<rows, threads, smem, ctx->stream>>>(x, w, b, n, eps, out, q, exact);
+        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<false>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact));
     }
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
@@ -233,6 +234,7 @@ int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capac
 __global__ void rope_append_kernel(float* qkv, int tokens, int heads, int kv_heads, int width, const float* __restrict__ cos_table,
                                    const float* __restrict__ sin_table, int context, const int* __restrict__ table,
                                    float* keys, float* values, int rows, int capacity, ErrorRecord* errors) {
+    chained_kernel_entry();
     int half = width >> 1;
     int all = heads + 2 * kv_heads;
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -268,8 +270,8 @@ int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_h
     if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "head width must be even, not " + std::to_string(width));
     int64_t total = (int64_t)tokens * (heads + 2 * kv_heads) * (width / 2);
     if (total == 0) return TSM_OK;
-    rope_append_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(
-        qkv, tokens, heads, kv_heads, width, cos_table, sin_table, context, table, keys, values, rows, capacity, ctx->errors);
+    TSM_CUDA(ctx, launch_chained(ctx, rope_append_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, qkv, tokens, heads, kv_heads, width,
+                                 cos_table, sin_table, context, table, keys, values, rows, capacity, ctx->errors));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -301,6 +303,7 @@ __device__ __forceinline__ float gelu_value(float x) {
 template <bool GELU>
 __global__ void activation_kernel(const float* __restrict__ a, const float* __restrict__ b, int rows, int n, int64_t in_stride,
                                   float* out, QuantOut q) {
+    chained_kernel_entry();
     int lane = threadIdx.x & 31;
     int blocks = (n + 31) >> 5;
     int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -325,8 +328,8 @@ static int launch_activation(tsm_ctx* ctx, bool gelu, const float* a, const floa
     int64_t items = (int64_t)rows * ((n + 31) / 32);
     unsigned grid = (unsigned)((items + 7) / 8);
     QuantOut q = quant_out(quantized);
-    if (gelu) activation_kernel<true><<<grid, 256, 0, ctx->stream>>>(a, b, rows, n, in_stride, out, q);
-    else activation_kernel<false><<<grid, 256, 0, ctx->stream>>>(a, b, rows, n, in_stride, out, q);
+    if (gelu) TSM_CUDA(ctx, launch_chained(ctx, activation_kernel<true>, dim3(grid), dim3(256), 0, a, b, rows, n, in_stride, out, q));
+    else TSM_CUDA(ctx, launch_chained(ctx, activation_kernel<false>, dim3(grid), dim3(256), 0, a, b, rows, n, in_stride, out, q));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -362,6 +365,7 @@ __device__ __forceinline__ bool ahead(float va, int ia, float vb, int ib) { retu
 // One CTA per row.  Round r picks the best candidate that comes after round r-1's pick, so no row
 // is modified and ties keep index order.  count = 1 is the greedy pick.
 __global__ void topk_kernel(const float* __restrict__ logits, int n, int count, int* out_ids, float* out_values) {
+    chained_kernel_entry();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     __shared__ float last_v;
@@ -400,7 +404,7 @@ __global__ void topk_kernel(const float* __restrict__ logits, int n, int count, 
 int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, int* out_ids, float* out_values) {
     if (count < 1 || count > n) return fail(ctx, TSM_ERR_ARG, "top " + std::to_string(count) + " of " + std::to_string(n));
     if (rows == 0) return TSM_OK;
-    topk_kernel<<<rows, 1024, 0, ctx->stream>>>(logits, n, count, out_ids, out_values);
+    TSM_CUDA(ctx, launch_chained(ctx, topk_kernel, dim3(rows), dim3(1024), 0, logits, n, count, out_ids, out_values));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -23,6 +23,11 @@ int cuda_fail(tsm_ctx* ctx, cudaError_t err, const char* what) {
     return err == cudaErrorMemoryAllocation ? TSM_ERR_MEMORY : TSM_ERR_CUDA;
 }
 
+bool chained_launch_enabled() {
+    static const bool on = !(getenv("TSM_CHAINED_LAUNCH") && getenv("TSM_CHAINED_LAUNCH")[0] == '0');
+    return on;
+}
+
 int ensure_scratch(tsm_ctx* ctx, Scratch& s, int64_t bytes) {
     if (s.bytes >= bytes) return TSM_OK;
     cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
