@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
                                                                   const float* __restrict__ k, const float* __restrict__ v,
                                                                   int rows, int kv_heads, int capacity,
                                                                   const int* __restrict__ table, float scale, float* out,
-                                                                  ErrorRecord* errors, const int* __restrict__ order) {
+                                                                  ErrorRecord* errors, const int* __restrict__ order, QuantSink sink) {
     chained_kernel_entry();
     constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
     constexpr int PITCH = WIDTH + 4;            // floats per staged key row
@@ -458,9 +458,13 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
         }
         __syncthreads();
     }
-    if (folds) {
+    if (folds) {  // warps 0 .. WIDTH / 32 - 1, all lanes: a warp holds one 32-column block of each of its heads
 #pragma unroll
-        for (int i = 0; i < G; i++) out[((int64_t)token * heads + head0 + i) * WIDTH + col] = acc[i];
+        for (int i = 0; i < G; i++) {
+            int64_t at = ((int64_t)token * heads + head0 + i) * WIDTH + col;
+            if (out) out[at] = acc[i];
+            if (sink.qs) quantize_block_q8(acc[i], lane, sink.scales + (at >> 5), sink.sums + (at >> 5), sink.totals + (at >> 5), sink.qs + at);
+        }
     }
 }
 
@@ -538,15 +542,11 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         return launch_fast<128>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
     if (!out) return fail(ctx, TSM_ERR_ARG, "ordered attention needs an F32 output");
     bool launched = false;
+    const QuantSink sink = quant_sink(quantized);  // the kernels for widths 64 and 128 quantise their rows themselves
     if (attention_stream_fits(ctx, tokens, heads, width, kv_heads, q, q_stride, k, v)) {
         TSM_TRY(ensure_scratch(ctx, ctx->attn, attention_stream_scratch_bytes(tokens, heads, capacity)));
-        TSM_TRY(launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
-                                        (float*)ctx->attn.ptr));
-        if (quantized) {
-            TSM_TRY(launch_quantize_rows(ctx, out, tokens, heads * width, (int64_t)heads * width, (float*)quantized->scales,
-                                         (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs));
-        }
-        return TSM_OK;
+        return launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
+                                       (float*)ctx->attn.ptr, sink);
     }
     if (aligned && (width == 64 || width == 128)) {
         int per_kv = heads / kv_heads;
@@ -565,7 +565,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         auto kernel = attention_exact_kernel<W, G, T, TP, S, U>;                                                          \
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
         TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(T), smem, q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, \
-                                     out, ctx->errors, order));                                                           \
+                                     out, ctx->errors, order, sink));                                                     \
     } while (0)
 #define TSM_EXACT_STAGES(W, G, T, TP, U)          \
     do {                                          \
@@ -595,6 +595,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
             }
         }
     }
+    const bool fused_quantiser = launched;
     if (!launched) {
         size_t smem = (size_t)(width + capacity) * 4;
         if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "ordered attention over more than 51000 positions");
@@ -607,7 +608,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     }
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
-    if (quantized) {
+    if (quantized && !fused_quantiser) {
         TSM_TRY(launch_quantize_rows(ctx, out, tokens, heads * width, (int64_t)heads * width, (float*)quantized->scales,
                                      (float*)quantized->sums, (int*)quantized->totals, (int8_t*)quantized->qs));
     }

@@ -37,6 +37,7 @@ struct StreamParams {
     const int* order;
     float* scratch;  // [tokens][heads][capacity]: scores, then exp values (split path: then weights)
     int splits;      // split path: CTAs that share one (token, kv head)'s key positions
+    QuantSink sink;  // where the output rows also go quantised (or nulls)
 };
 
 struct StreamMaps {
@@ -351,7 +352,11 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             return;
         }
 #pragma unroll
-        for (int i = 0; i < G; i++) p.out[((int64_t)token * p.heads + head0 + i) * WIDTH + col] = acc[i];
+        for (int i = 0; i < G; i++) {  // a warp holds one 32-column block of each head
+            int64_t at = ((int64_t)token * p.heads + head0 + i) * WIDTH + col;
+            if (p.out) p.out[at] = acc[i];
+            if (p.sink.qs) quantize_block_q8(acc[i], lane, p.sink.scales + (at >> 5), p.sink.sums + (at >> 5), p.sink.totals + (at >> 5), p.sink.qs + at);
+        }
     }
 }
 
@@ -634,7 +639,11 @@ __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, co
         return;
     }
 #pragma unroll
-    for (int i = 0; i < G; i++) p.out[((int64_t)token * p.heads + head0 + i) * WIDTH + 32 * quarter + lane] = acc[i];
+    for (int i = 0; i < G; i++) {
+        int64_t at = ((int64_t)token * p.heads + head0 + i) * WIDTH + 32 * quarter + lane;
+        if (p.out) p.out[at] = acc[i];
+        if (p.sink.qs) quantize_block_q8(acc[i], lane, p.sink.scales + (at >> 5), p.sink.sums + (at >> 5), p.sink.totals + (at >> 5), p.sink.qs + at);
+    }
 }
 
 }  // namespace
@@ -655,9 +664,9 @@ bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int k
 
 int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
-                            float* scratch) {
+                            float* scratch, QuantSink sink) {
     constexpr int WIDTH = 128;
-    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch, 1};
+    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch, 1, sink};
     StreamMaps maps;
     uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));

@@ -128,6 +128,19 @@ struct QuantizedActs {
     const int8_t* qs;     // [rows, k]
 };
 
+// Where a kernel that also quantises its output rows writes them (all null: it does not).
+struct QuantSink {
+    float* scales;
+    float* sums;
+    int* totals;
+    int8_t* qs;
+};
+inline QuantSink quant_sink(const QuantizedActs* q) {
+    QuantSink o{nullptr, nullptr, nullptr, nullptr};
+    if (q) o = QuantSink{(float*)q->scales, (float*)q->sums, (int*)q->totals, (int8_t*)q->qs};
+    return o;
+}
+
 int64_t quant_scratch_bytes(int rows, int k);
 QuantizedActs quant_scratch_layout(void* base, int rows, int k);
 
@@ -149,7 +162,7 @@ bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int k
                            const float* v);
 int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
-                            float* scratch);
+                            float* scratch, QuantSink sink);
 bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                              const float* bias, const float* residual, float* out);

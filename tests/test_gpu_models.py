@@ -143,6 +143,29 @@ def test_random_model_batched_decode(dev, arch, kind):
     model.free()
 
 
+@pytest.mark.parametrize("capacity", [64, 1100])
+def test_heads_of_width_128_in_groups_of_four(dev, capacity):
+    """The streaming attention kernels (one launch for short caches, three for a long cache with few streams), which also
+    write the quantised rows the next product reads: whole-model logits against the oracle, bit for bit."""
+    config = dict(arch="llama", layers=2, width=512, heads=8, kv_heads=2, head_width=128, hidden=512, vocab=1024, context=2048,
+                  eps=1e-5, rope_theta=10000.0, tied=True)
+    model = pkg.Model.random(dev, config, pkg.Q4_0, seed=11)
+    ref = helpers.oracle_from_device_model(model)
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(0, 1024, size=n).tolist() for n in (9, 40, 3)]
+    cache, rcache = model.new_batch_cache(3, capacity), ref.new_cache(3, capacity)
+    check(pkg.EXACT, model.forward_last(prompts, cache), ref.forward(rcache, prompts), "prompts")
+    ids = [5, 6, 7]
+    for step in range(4):
+        tokens, logits = model.decode(cache, ids, logits=True)
+        want = ref.forward(rcache, [[t] for t in ids])
+        check(pkg.EXACT, logits, want, ("decode", step))
+        ids = [oracle.argmax_first(r) for r in want]
+        assert tokens.tolist() == ids
+    cache.free()
+    model.free()
+
+
 def test_generate_matches_the_oracle_token_for_token(dev):
     config = dict(SMALL, arch="llama", layers=3, vocab=2048)
     model = pkg.Model.random(dev, config, pkg.Q8_0, seed=3)
