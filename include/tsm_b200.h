@@ -180,6 +180,12 @@ typedef struct {
 int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out);
 /* Llama.new(config) / GPT2.new(config) with Init.normal(0.02) then Module#quantize(kind, embeddings: true)
  * (module.cr, builder.cr): weights drawn on the device from `seed`, quantised on the device. */
+/* GPT2.load / Llama.load of Hugging Face safetensors weights (gpt2.cr:69-101, llama.cr:163-175, safetensors.cr), followed by
+ * Module#quantize(kind, embeddings: true) (module.cr:262-274) on the device: F32 / F16 / BF16 matrices, GPT-2's Conv1D
+ * weights transposed, every Linear and both embedding tables quantised to `kind`.  config->arch picks the family.  GPT-2
+ * takes config->heads only; Llama takes heads, kv_heads, head_width (0: width / heads), eps, rope_theta and context
+ * (what the model directory's config.json holds); all other sizes come from the tensor shapes. */
+int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_config* config, int kind, tsm_model** out);
 int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uint64_t seed, tsm_model** out);
 int tsm_model_config_get(tsm_model* model, tsm_model_config* out);
 int tsm_model_free(tsm_model* model);

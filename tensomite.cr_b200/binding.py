@@ -477,6 +477,18 @@ class Model:
         return cls(device, handle)
 
     @classmethod
+    def load_safetensors(cls, path, device, config, kind):
+        """GPT2.load / Llama.load of a Hugging Face safetensors file, then .quantize(kind, embeddings: true) on the device.
+        `config` needs arch and heads (GPT-2), or arch, heads, kv_heads, eps, rope_theta, context (Llama)."""
+        cfg = ModelConfig(0 if config["arch"] == "llama" else 1, 0, 0, config["heads"], config.get("kv_heads", config["heads"]),
+                          config.get("head_width", 0), 0, 0, config.get("context", 0), config.get("eps", 1e-5),
+                          config.get("rope_theta", 10000.0), 0)
+        handle = C.c_void_p()
+        device.check(device.lib.tsm_model_load_safetensors(device.ctx, str(path).encode(), C.byref(cfg), C.c_int(kind), C.byref(handle)),
+                     "tsm_model_load_safetensors")
+        return cls(device, handle)
+
+    @classmethod
     def random(cls, device, config, kind, seed):
         """Llama.new(config) / GPT2.new(config) with normal(0.02) weights from `seed`, quantised to `kind`."""
         cfg = ModelConfig(0 if config["arch"] == "llama" else 1, config["layers"], config["width"], config["heads"],

@@ -113,6 +113,40 @@ def read_safetensors(raw):
     return out
 
 
+def write_safetensors(path, tensors):
+    """A safetensors file of F32 tensors (name -> array), as safetensors.cr reads them."""
+    header, payload, at = {}, [], 0
+    for name, array in tensors.items():
+        array = np.ascontiguousarray(array, dtype=np.float32)
+        header[name] = {"dtype": "F32", "shape": list(array.shape), "data_offsets": [at, at + array.nbytes]}
+        payload.append(array.tobytes())
+        at += array.nbytes
+    text = json.dumps(header).encode()
+    text += b" " * (-len(text) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(text)) + text + b"".join(payload))
+
+
+def llama_tensors_from_hf(st, layers, kind):
+    """Hugging Face Llama names -> oracle tensors, every Linear and the embedding table quantised to `kind`."""
+    def q(w):
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        return (kind, oracle.quantize(kind, w).reshape(w.shape[0], -1))
+
+    t = {"embed": q(st["model.embed_tokens.weight"]), "final_w": (-1, st["model.norm.weight"])}
+    if "lm_head.weight" in st:
+        t["head"] = q(st["lm_head.weight"])
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        t[f"{i}.norm1_w"] = (-1, st[p + "input_layernorm.weight"])
+        t[f"{i}.norm2_w"] = (-1, st[p + "post_attention_layernorm.weight"])
+        t[f"{i}.qkv"] = q(np.concatenate([st[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]))
+        t[f"{i}.o"] = q(st[p + "self_attn.o_proj.weight"])
+        t[f"{i}.up"] = q(np.concatenate([st[p + "mlp.gate_proj.weight"], st[p + "mlp.up_proj.weight"]]))
+        t[f"{i}.down"] = q(st[p + "mlp.down_proj.weight"])
+    return t
+
+
 def gpt2_tensors_from_hf(st, layers, quantize_kind=None, embeddings=False):
     """Hugging Face GPT-2 names ([in,out] Conv1D weights) -> oracle tensors ([out,in] rows).
 

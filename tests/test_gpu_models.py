@@ -97,6 +97,59 @@ def test_tiny_gpt2_q8_0_with_quantised_embeddings(dev, tmp_path):
     model.free()
 
 
+def test_gpt2_from_safetensors_quantised_on_the_device(dev, tmp_path):
+    """GPT2.load("model.safetensors").quantize(Q8_0, embeddings: true): Hugging Face names, Conv1D weights transposed, the
+    device's quantiser; logits against the oracle over the oracle-quantised tensors, bit for bit."""
+    g = golden()
+    path = tmp_path / "model.safetensors"
+    path.write_bytes(g["tiny_gpt2/safetensors"].tobytes())
+    st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+    config = dict(arch="gpt2", layers=2, heads=4, kv_heads=4, width=32, head_width=8, hidden=128, context=64, vocab=400, eps=1e-5)
+    ref = oracle.Model(config, helpers.gpt2_tensors_from_hf(st, 2, quantize_kind=oracle.Q8_0, embeddings=True))
+    model = pkg.GPT2.load_safetensors(path, dev, dict(arch="gpt2", heads=4), pkg.Q8_0)
+    assert {k: model.config[k] for k in ("layers", "width", "hidden", "context", "vocab")} == dict(layers=2, width=32, hidden=128, context=64, vocab=400)
+    prompt = g["tiny_gpt2/prompt_ids"].tolist()
+    want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+    check(pkg.EXACT, model.forward([prompt], model.new_batch_cache(1, 64)), want)
+    assert model.generate(prompt, 20) == ref.generate(prompt, 20)
+    model.free()
+    with pytest.raises(pkg.Error):
+        pkg.GPT2.load_safetensors(tmp_path / "absent.safetensors", dev, dict(arch="gpt2", heads=4), pkg.Q8_0)
+
+
+@pytest.mark.parametrize("kind,tied", [(pkg.Q4_0, True), (pkg.Q4_1, False)])
+def test_llama_from_safetensors_quantised_on_the_device(dev, tmp_path, kind, tied):
+    rng = np.random.default_rng(21)
+    layers, width, heads, kv_heads, hw, hidden, vocab = 2, 128, 4, 2, 32, 256, 512
+    st = {"model.embed_tokens.weight": rng.normal(0, 0.02, (vocab, width)), "model.norm.weight": rng.normal(1, 0.1, width)}
+    if not tied:
+        st["lm_head.weight"] = rng.normal(0, 0.02, (vocab, width))
+    for i in range(layers):
+        p = f"model.layers.{i}."
+        st[p + "input_layernorm.weight"] = rng.normal(1, 0.1, width)
+        st[p + "post_attention_layernorm.weight"] = rng.normal(1, 0.1, width)
+        st[p + "self_attn.q_proj.weight"] = rng.normal(0, 0.02, (heads * hw, width))
+        st[p + "self_attn.k_proj.weight"] = rng.normal(0, 0.02, (kv_heads * hw, width))
+        st[p + "self_attn.v_proj.weight"] = rng.normal(0, 0.02, (kv_heads * hw, width))
+        st[p + "self_attn.o_proj.weight"] = rng.normal(0, 0.02, (width, heads * hw))
+        st[p + "mlp.gate_proj.weight"] = rng.normal(0, 0.02, (hidden, width))
+        st[p + "mlp.up_proj.weight"] = rng.normal(0, 0.02, (hidden, width))
+        st[p + "mlp.down_proj.weight"] = rng.normal(0, 0.02, (width, hidden))
+    st = {k: np.asarray(v, dtype=np.float32) for k, v in st.items()}
+    path = tmp_path / "model.safetensors"
+    helpers.write_safetensors(path, st)
+    config = dict(arch="llama", layers=layers, width=width, heads=heads, kv_heads=kv_heads, head_width=hw, hidden=hidden, vocab=vocab,
+                  context=128, eps=1e-5, rope_theta=10000.0, tied=tied)
+    ref = oracle.Model(config, helpers.llama_tensors_from_hf(st, layers, kind))
+    model = pkg.Llama.load_safetensors(path, dev, dict(arch="llama", heads=heads, kv_heads=kv_heads, context=128, eps=1e-5, rope_theta=10000.0), kind)
+    assert model.config["hidden"] == hidden and model.config["tied"] == (1 if tied else 0)
+    prompt = rng.integers(0, vocab, size=24).tolist()
+    want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+    check(pkg.EXACT, model.forward([prompt], model.new_batch_cache(1, 64)), want)
+    assert model.generate(prompt, 16) == ref.generate(prompt, 16)
+    model.free()
+
+
 SMALL = dict(layers=2, width=256, heads=4, kv_heads=2, head_width=64, hidden=512, vocab=1024, context=256,
              eps=1e-5, rope_theta=10000.0, tied=True)
 
