@@ -67,7 +67,8 @@ SHAPES = [(1, 37, 64), (3, 5, 1280), (2, 9, 4096),            # the reference's 
           (8, 128, 2048), (16, 64, 576), (1, 7, 4096), (1, 4097, 256),
           (5, 40, 1536), (33, 48, 4096), (64, 200, 1600), (100, 96, 576), (64, 1024, 2048), (17, 72, 14336),  # tensor-core kernels
           (64, 304, 4096), (70, 100, 1024), (12, 2400, 512), (24, 48, 2048), (64, 5000, 256), (40, 2500, 1024),  # odd group counts, two slabs of activation rows, several groups per CTA
-          (64, 19008, 256), (9, 20000, 512), (70, 19200, 256)]  # many rows: 16-row groups, one warp per group
+          (64, 19008, 256), (9, 20000, 512), (70, 19200, 256),  # many rows: 16-row groups, one warp per group
+          (9, 40000, 256), (33, 44, 2048), (64, 1000, 512)]  # more groups than one wave of CTAs holds; a last group of 4 rows
 
 
 @pytest.mark.parametrize("name", list(KINDS))
