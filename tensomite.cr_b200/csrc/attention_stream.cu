@@ -13,7 +13,9 @@
 //     wavefronts even when every lane reads the same address, which is what bounded the earlier kernels);
 //   * consumer warps synchronise among themselves with a named barrier only where data is exchanged (maximum,
 //     denominator, a tile's weights), never with the producer.
-// One CTA per (token, key/value head): 128 consumer threads + one producer warp.
+// One CTA per (token, key/value head): 128 consumer threads + one producer warp.  The output rows can be written
+// quantised for the product that follows (QuantSink).  Further down: the same arithmetic as three launches
+// (attention_scores_kernel, attention_weights_kernel, attention_values_kernel) for calls that cannot fill the GPU.
 #include "common.cuh"
 
 namespace tsm {

@@ -17,7 +17,10 @@
 //     loaded, so a stage of activations is staged once per SM and used by every consumer warp;
 //   * a consumer warp prepares the weight fragments of 4 blocks, then walks its tiles of 8 activation rows with
 //     the 4 blocks innermost: the activation scales of a tile arrive as one 16-byte load per column, and the
-//     int -> float conversion of the dot product is folded into the first multiply (Q4_0).
+//     int -> float conversion of the dot product is folded into the first multiply (Q4_0); activation fragments come
+//     by ldmatrix, four 8 x 16-byte pieces per instruction.
+// matmul_pipe_t_kernel is the same pipeline with the operands' roles exchanged (8 weight rows as the multiply's B
+// operand, 16 activation rows as A), for matrices with too few rows to give every SM enough 16-row groups.
 //
 // Shapes this kernel does not take (blocks per row not a multiple of 8, unaligned operands) stay with
 // matmul_mma_kernel.
