@@ -330,9 +330,10 @@ def main():
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 model and the matvec sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp", "tp_reduce"],
                     help="with --gpus N > 1: dp = every rank decodes its own streams on a whole replica (no collective); "
-                         "tp = the ranks share one model split by tensor parallelism (NCCL all-gathers) and decode the same streams")
+                         "tp = the ranks share one model split by tensor parallelism (NCCL all-gathers, the bits of one GPU) and decode "
+                         "the same streams; tp_reduce = the same with o and down split by input columns and all-reduced (not bit-exact)")
     ap.add_argument("--mode", default="exact", choices=["exact", "fast"],
                     help="exact (default): the CPU path's bits; fast: tree sums and split-K attention, held to the reference's GPU budget "
                          "of 0.001 nats KL per token, not to its bits")
@@ -364,9 +365,11 @@ def main():
         print(json.dumps(kernel_case(pkg, dev, torch, stream, args.case, args.repeats, peak["hbm_gbs"])))
         dev.close()
         return
-    tp = world if (args.parallelism == "tp" and args.impl == "ours") else 1
+    tp = world if (args.parallelism != "dp" and args.impl == "ours") else 1
     if tp > 1:
         pkg.groups.join_tensor_parallel(dev, dist)
+        if args.parallelism == "tp_reduce":
+            dev.tp_variant(pkg.TP_REDUCE)
     data_rank = 0 if tp > 1 else rank          # tensor-parallel ranks decode the same streams
     jobs = 1 if tp > 1 else world              # independent sets of streams in the job
     lengths = draw_lengths(w, data_rank)
@@ -375,7 +378,8 @@ def main():
     rows = w["rows"]
     config = dict(workload=w["name"], streams_per_gpu=rows, kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
                   kv_dtype="f32", weights=w["kind"], mode=args.mode, l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
-                  parallelism=(f"tp{world}: projections split by output rows, 4 NCCL all-gathers per layer" if tp > 1 else
+                  parallelism=((f"tp{world}: projections split by output rows, 4 NCCL all-gathers per layer" if args.parallelism == "tp" else
+                                f"tp{world}: o and down split by input columns, 2 NCCL all-reduces per layer (not bit-exact)") if tp > 1 else
                                f"dp{world}: a replica and {rows} streams per GPU, no collective") if world > 1 else "single gpu")
 
     if args.impl == "reference":

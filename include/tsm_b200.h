@@ -229,6 +229,15 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
 int tsm_tp_unique_id(uint8_t* out /* [128] */);
 int tsm_tp_init(tsm_ctx* ctx, int rank, int world, const uint8_t* id /* [128] */);
 int tsm_tp_info(tsm_ctx* ctx, int* rank, int* world);
+/* How models built on this context AFTER the call are split (set it between tsm_tp_init and the load):
+ *   TSM_TP_GATHER (default) every projection by output rows, all-gathers between them: the bits of one GPU;
+ *   TSM_TP_REDUCE           q/k/v, gate/up and the head by output rows, o and down by INPUT columns (each rank multiplies its
+ *                           own heads' / hidden slice's columns) with an NCCL all-reduce of the partial sums after each: two
+ *                           exchanges per layer instead of four and a shorter K loop per rank, but an output's blocks are then
+ *                           summed in another order, so results agree with one GPU within the fast mode's budget (0.001 nats
+ *                           KL per token), not bit for bit. */
+typedef enum { TSM_TP_GATHER = 0, TSM_TP_REDUCE = 1 } tsm_tp_split;
+int tsm_tp_variant(tsm_ctx* ctx, int variant);
 
 /* Generative#generate with Sampler.greedy (generative.cr:177-190): `count` tokens after `prompt`. */
 int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens);

@@ -19,6 +19,7 @@ HEADER = os.path.join(HERE, "..", "include", "tsm_b200.h")
 Q8_0, Q4_0, Q4_1, F32 = 0, 1, 2, -1
 BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q4_1: 20}
 FAST, EXACT = 0, 1
+TP_GATHER, TP_REDUCE = 0, 1
 
 
 class Error(Exception):
@@ -159,6 +160,11 @@ class B200:
             raise ShapeError("a group id is 128 bytes")
         raw = (C.c_uint8 * 128).from_buffer_copy(bytes(group_id)) if world > 1 else None
         self.check(self.lib.tsm_tp_init(self.ctx, C.c_int(rank), C.c_int(world), raw), "tsm_tp_init")
+
+    def tp_variant(self, variant):
+        """TP_GATHER (default: the bits of one GPU) or TP_REDUCE (o and down over input columns, all-reduced); set before
+        the model is loaded."""
+        self.check(self.lib.tsm_tp_variant(self.ctx, C.c_int(variant)), "tsm_tp_variant")
 
     def tp_info(self):
         rank, world = C.c_int(), C.c_int()
@@ -575,6 +581,6 @@ class GPT2(Model):
     pass
 
 
-__all__ = ["Q8_0", "Q4_0", "Q4_1", "F32", "BLOCK_BYTES", "FAST", "EXACT", "Error", "DeviceError", "ShapeError", "ExecutionError",
+__all__ = ["Q8_0", "Q4_0", "Q4_1", "F32", "BLOCK_BYTES", "FAST", "EXACT", "TP_GATHER", "TP_REDUCE", "Error", "DeviceError", "ShapeError", "ExecutionError",
            "DTypeError", "ModelConfig", "Counters", "declared_symbols", "library", "check_exports", "Buffer", "B200", "BatchCache",
            "Model", "Llama", "GPT2"]

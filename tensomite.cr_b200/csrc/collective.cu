@@ -18,6 +18,7 @@ struct NcclId {
 typedef int (*GetUniqueId)(NcclId*);
 typedef int (*CommInitRank)(void**, int, NcclId, int);
 typedef int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t);
 typedef int (*CommDestroy)(void*);
 typedef const char* (*GetErrorString)(int);
 
@@ -26,6 +27,7 @@ struct Nccl {
     GetUniqueId get_unique_id = nullptr;
     CommInitRank comm_init_rank = nullptr;
     AllGather all_gather = nullptr;
+    AllReduce all_reduce = nullptr;
     CommDestroy comm_destroy = nullptr;
     GetErrorString error_string = nullptr;
     std::string problem;
@@ -43,9 +45,10 @@ Nccl& nccl() {
         n.get_unique_id = (GetUniqueId)dlsym(n.handle, "ncclGetUniqueId");
         n.comm_init_rank = (CommInitRank)dlsym(n.handle, "ncclCommInitRank");
         n.all_gather = (AllGather)dlsym(n.handle, "ncclAllGather");
+        n.all_reduce = (AllReduce)dlsym(n.handle, "ncclAllReduce");
         n.comm_destroy = (CommDestroy)dlsym(n.handle, "ncclCommDestroy");
         n.error_string = (GetErrorString)dlsym(n.handle, "ncclGetErrorString");
-        if (!n.get_unique_id || !n.comm_init_rank || !n.all_gather || !n.comm_destroy) n.problem = "the NCCL library lacks an entry point";
+        if (!n.get_unique_id || !n.comm_init_rank || !n.all_gather || !n.all_reduce || !n.comm_destroy) n.problem = "the NCCL library lacks an entry point";
         return n;
     }();
     return lib;
@@ -57,6 +60,7 @@ int nccl_fail(tsm_ctx* ctx, int rc, const char* call) {
 }
 
 constexpr int kNcclInt8 = 0;  // ncclDataType_t: bytes are gathered, whatever they hold
+constexpr int kNcclFloat32 = 7, kNcclSum = 0;
 
 // dst[t, seg * width + j] (+)= src[seg, t, j]: the ranks' column slices, as an all-gather leaves them, back in row order.
 template <bool ADD>
@@ -80,6 +84,15 @@ int tp_all_gather(tsm_ctx* ctx, void* buffer, int64_t bytes) {
     Nccl& n = nccl();
     int rc = n.all_gather((const char*)buffer + (int64_t)ctx->tp_rank * bytes, buffer, (size_t)bytes, kNcclInt8, ctx->comm, ctx->stream);
     if (rc != 0) return nccl_fail(ctx, rc, "ncclAllGather");
+    ctx->counters.host_ops++;
+    return TSM_OK;
+}
+
+// Every rank's `count` floats are replaced by their sum over the ranks, in NCCL's order of addition.
+int tp_all_reduce_sum(tsm_ctx* ctx, float* buffer, int64_t count) {
+    if (ctx->tp_world <= 1) return TSM_OK;
+    int rc = nccl().all_reduce(buffer, buffer, (size_t)count, kNcclFloat32, kNcclSum, ctx->comm, ctx->stream);
+    if (rc != 0) return nccl_fail(ctx, rc, "ncclAllReduce");
     ctx->counters.host_ops++;
     return TSM_OK;
 }
@@ -128,6 +141,13 @@ int tsm_tp_init(tsm_ctx* ctx, int rank, int world, const uint8_t* id) {
     int rc = n.comm_init_rank(&comm, world, uid, rank);
     if (rc != 0) return tsm::nccl_fail(ctx, rc, "ncclCommInitRank");
     ctx->comm = comm, ctx->tp_rank = rank, ctx->tp_world = world;
+    return TSM_OK;
+}
+
+int tsm_tp_variant(tsm_ctx* ctx, int variant) {
+    if (!ctx) return TSM_ERR_ARG;
+    if (variant != TSM_TP_GATHER && variant != TSM_TP_REDUCE) return tsm::fail(ctx, TSM_ERR_ARG, "unknown tensor-parallel variant");
+    ctx->tp_variant = variant;
     return TSM_OK;
 }
 

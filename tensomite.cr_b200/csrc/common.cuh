@@ -56,6 +56,7 @@ struct tsm_ctx {
     int tp_rank = 0, tp_world = 1;            // this context's place in a tensor-parallel group
     bool chain_launches = false;              // the engine sets it around steps of a few rows (see launch_chained)
     void* comm = nullptr;                     // its NCCL communicator
+    int tp_variant = 0;                       // TSM_TP_GATHER or TSM_TP_REDUCE: how models built on this context are split
     std::mutex message_lock;
     std::string message;
     tsm_counters counters{};
@@ -151,6 +152,7 @@ int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, c
 bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 // Tensor-parallel exchanges (collective.cu).
 int tp_all_gather(tsm_ctx* ctx, void* buffer, int64_t bytes);
+int tp_all_reduce_sum(tsm_ctx* ctx, float* buffer, int64_t count);
 int launch_interleave(tsm_ctx* ctx, const float* gathered, float* dst, int rows, int width, int parts, bool add);
 void tp_release(tsm_ctx* ctx);
 // A rank-2 tensor map over `rows` rows of `width` elements (row pitch in bytes), copied in boxes of box_w x box_h.

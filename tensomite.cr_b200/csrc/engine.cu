@@ -71,6 +71,7 @@ struct tsm_model {
     Workspace ws;
     uint64_t ws_generation = 1;
     int tp = 1, tp_rank = 0;     // tensor-parallel group of the context the model was built on
+    bool tp_reduce = false;      // o and down split by input columns and all-reduced (TSM_TP_REDUCE), not by output rows
     Linear head_local;           // this rank's rows of the vocabulary head (a view when the head is the embedding table)
 };
 
@@ -95,6 +96,8 @@ struct tsm_cache {
 
 namespace tsm {
 
+static int dev_alloc(tsm_model* m, int64_t bytes, void** out);
+
 // Which rows of a projection a rank of a tensor-parallel group holds.  Every projection is split by OUTPUT rows, so
 // each output's sum over blocks stays on one GPU, whole and in block order: the sharded model's bits are the single
 // GPU's.  Joined projections keep their parts: a rank takes its heads' rows of q, of k and of v (its slice of gate
@@ -110,7 +113,9 @@ static std::vector<RowRange> shard_ranges(const tsm_model* m, int what) {
         case SHARD_QKV:
             ranges = {{r * qn / G, qn / G}, {qn + r * kvn / G, kvn / G}, {qn + kvn + r * kvn / G, kvn / G}};
             break;
-        case SHARD_WIDTH: ranges = {{r * c.width / G, c.width / G}}; break;
+        case SHARD_WIDTH:  // o and down: by output rows, unless they are split by input columns (shard_inputs)
+            if (!m->tp_reduce) ranges = {{r * c.width / G, c.width / G}};
+            break;
         case SHARD_UP:
             ranges = {{r * c.hidden / G, c.hidden / G}};
             if (c.arch == 0) ranges.push_back({c.hidden + r * c.hidden / G, c.hidden / G});
@@ -126,6 +131,39 @@ static int check_sharding(tsm_model* m) {
     int G = m->tp;
     if (c.heads % G || c.kv_heads % G || c.width % G || c.hidden % G || c.vocab % G)
         return fail(m->ctx, TSM_ERR_ARG, "heads, key/value heads, width, hidden width and vocabulary must all divide by the " + std::to_string(G) + " ranks");
+    if (m->tp_reduce && ((c.heads / G * c.head_width) % 32 || (c.hidden / G) % 32))
+        return fail(m->ctx, TSM_ERR_ARG, "a rank's share of the attention output and of the hidden width must be whole blocks of 32");
+    return TSM_OK;
+}
+
+// Keeps block columns [first, first + blocks) of every row of a quantised matrix: a rank's share of the INPUT columns.
+static int keep_block_columns(tsm_model* m, Linear* l, int64_t first, int64_t blocks) {
+    int64_t B = block_bytes(l->kind), nb = l->k / 32;
+    uint8_t* narrow = nullptr;
+    TSM_TRY(dev_alloc(m, (int64_t)l->n * blocks * B, (void**)&narrow));
+    TSM_CUDA(m->ctx, cudaMemcpy2DAsync(narrow, (size_t)(blocks * B), l->w + first * B, (size_t)(nb * B), (size_t)(blocks * B), (size_t)l->n,
+                                       cudaMemcpyDeviceToDevice, m->ctx->stream));
+    TSM_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+    for (size_t i = 0; i < m->owned.size(); i++)
+        if (m->owned[i] == (void*)l->w) {
+            m->owned.erase(m->owned.begin() + (long)i);
+            pool_release(m->ctx, l->w);
+            break;
+        }
+    l->w = narrow, l->k = (int)(blocks * 32);
+    return TSM_OK;
+}
+
+// TSM_TP_REDUCE: a layer's o and down keep all their rows but only this rank's input columns (its heads' attention
+// outputs, its slice of the hidden width); their biases are added once, by rank 0.
+static int shard_inputs(tsm_model* m, Layer& l) {
+    if (!m->tp_reduce) return TSM_OK;
+    const tsm_model_config& c = m->cfg;
+    int64_t G = m->tp, r = m->tp_rank;
+    int64_t o_blocks = (int64_t)c.heads * c.head_width / G / 32, down_blocks = (int64_t)c.hidden / G / 32;
+    TSM_TRY(keep_block_columns(m, &l.o, r * o_blocks, o_blocks));
+    TSM_TRY(keep_block_columns(m, &l.down, r * down_blocks, down_blocks));
+    if (r != 0) l.o.bias = nullptr, l.down.bias = nullptr;
     return TSM_OK;
 }
 
@@ -484,6 +522,7 @@ static int load_llama(tsm_model* m, GgufFile& f) {
         TSM_TRY(upload_rows(m, f, {{use(p + "ffn_gate.weight"), 0}, {use(p + "ffn_up.weight"), 0}}, c.width, 2 * c.hidden, &l.up,
                             shard_ranges(m, SHARD_UP)));
         TSM_TRY(upload_rows(m, f, {{use(p + "ffn_down.weight"), 0}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(shard_inputs(m, l));
     }
     // any tensor left over is an error, as the reference's loader raises (llama.cr:202-203)
     for (auto& name : f.order) {
@@ -547,6 +586,7 @@ static int load_gpt2(tsm_model* m, GgufFile& f) {
         TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(upload_bias(m, f, p + "mlp.c_proj.bias", c.width, &l.down.bias));
         TSM_TRY(shard_bias(m, &l.down.bias, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(shard_inputs(m, l));
     }
     return TSM_OK;
 }
@@ -631,6 +671,7 @@ static int build_random(tsm_model* m, int kind, uint64_t seed) {
             if ((rc = random_linear(m, kind, c.width, qn, t++, gpt, scratch, &l.o, shard_ranges(m, SHARD_WIDTH)))) break;
             if ((rc = random_linear(m, kind, upn, c.width, t++, gpt, scratch, &l.up, shard_ranges(m, SHARD_UP)))) break;
             if ((rc = random_linear(m, kind, c.width, c.hidden, t++, gpt, scratch, &l.down, shard_ranges(m, SHARD_WIDTH)))) break;
+            if ((rc = shard_inputs(m, l))) break;
         }
     } while (0);
     cudaStreamSynchronize(m->ctx->stream);
@@ -908,6 +949,7 @@ static int load_gpt2_safetensors(tsm_model* m, StFile& f, int heads, int kind) {
         TSM_TRY(st_linear(m, f, {h + "mlp.c_proj.weight"}, c.hidden, true, kind, &l.down, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(st_vector(m, f, h + "mlp.c_proj.bias", c.width, &l.down.bias));
         TSM_TRY(shard_bias(m, &l.down.bias, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(shard_inputs(m, l));
     }
     return TSM_OK;
 }
@@ -947,6 +989,7 @@ static int load_llama_safetensors(tsm_model* m, StFile& f, const tsm_model_confi
         TSM_TRY(st_linear(m, f, {p + "self_attn.o_proj.weight"}, qn, false, kind, &l.o, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(st_linear(m, f, {p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight"}, c.width, false, kind, &l.up, shard_ranges(m, SHARD_UP)));
         TSM_TRY(st_linear(m, f, {p + "mlp.down_proj.weight"}, c.hidden, false, kind, &l.down, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(shard_inputs(m, l));
     }
     return make_rope_tables(m);
 }
@@ -1062,6 +1105,40 @@ static int launch_layer_sharded(tsm_model* m, tsm_cache* cache, int i, int total
     return TSM_OK;
 }
 
+// One layer of a TSM_TP_REDUCE step: q/k/v and gate/up by output rows as above, then o and down over this rank's own input
+// columns (its heads' attention output, its slice of the hidden width, quantised where they are made) with an all-reduce of
+// the partial sums; two exchanges per layer.  The partial sums are added in NCCL's order, not in block order.
+static int launch_layer_reduced(tsm_model* m, tsm_cache* cache, int i, int total, const int* order, const QuantizedActs& qa, float scale) {
+    const tsm_model_config& c = m->cfg;
+    tsm_ctx* ctx = m->ctx;
+    Workspace& w = m->ws;
+    Layer& l = m->layers[i];
+    const int G = m->tp, hw = c.head_width;
+    const int heads_l = c.heads / G, kv_l = c.kv_heads / G, qn_l = heads_l * hw, qkvn_l = qn_l + 2 * kv_l * hw, hid_l = c.hidden / G;
+    QuantizedActs qb = quant_scratch_layout(w.qb, total, qn_l);
+    QuantizedActs qc = quant_scratch_layout(w.qc, total, hid_l);
+    const int64_t count = (int64_t)total * c.width;
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
+    else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
+    TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+    TSM_TRY(launch_rope_append(ctx, w.qkv, total, heads_l, kv_l, hw, c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr,
+                               c.context, w.table, cache->keys[i], cache->values[i], cache->rows, cache->capacity));
+    TSM_TRY(launch_attention(ctx, w.qkv, qkvn_l, total, heads_l, hw, cache->keys[i], cache->values[i], cache->rows, kv_l, cache->capacity,
+                             w.table, scale, w.att, &qb, order));
+    TSM_TRY(product(m, qb, total, l.o, nullptr, w.tp_rows));
+    TSM_TRY(tp_all_reduce_sum(ctx, w.tp_rows, count));
+    TSM_TRY(launch_add(ctx, w.x, w.tp_rows, count, w.x));
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
+    else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
+    TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
+    if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + hid_l, total, hid_l, 2 * (int64_t)hid_l, nullptr, &qc));
+    else TSM_TRY(launch_gelu(ctx, w.up, total, hid_l, nullptr, &qc));
+    TSM_TRY(product(m, qc, total, l.down, nullptr, w.tp_rows));
+    TSM_TRY(tp_all_reduce_sum(ctx, w.tp_rows, count));
+    TSM_TRY(launch_add(ctx, w.x, w.tp_rows, count, w.x));
+    return TSM_OK;
+}
+
 // The head of a tensor-parallel step: this rank's vocabulary slice, the greedy pick across ranks, and (when asked) the
 // full logits in ws.logits.
 static int launch_head_sharded(tsm_model* m, const QuantizedActs& qh, int outputs, bool pick, bool full_logits) {
@@ -1131,7 +1208,8 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
     }
     for (int i = 0; i < c.layers; i++) {
         if (m->tp > 1) {
-            TSM_TRY(launch_layer_sharded(m, cache, i, total, order, qa, qb, qc, ordered, scale));
+            if (m->tp_reduce) TSM_TRY(launch_layer_reduced(m, cache, i, total, order, qa, scale));
+            else TSM_TRY(launch_layer_sharded(m, cache, i, total, order, qa, qb, qc, ordered, scale));
             continue;
         }
         Layer& l = m->layers[i];
@@ -1247,7 +1325,7 @@ int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
     TSM_TRY(gguf_open(ctx, path, f));
     std::unique_ptr<tsm_model> m(new tsm_model());
     m->ctx = ctx;
-    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank;
+    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank, m->tp_reduce = ctx->tp_world > 1 && ctx->tp_variant == TSM_TP_REDUCE;
     std::string arch = f.strings.count("general.architecture") ? f.strings["general.architecture"] : "";
     int rc;
     if (arch == "llama") rc = load_llama(m.get(), f);
@@ -1272,7 +1350,7 @@ int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_c
     TSM_TRY(st_open(ctx, path, f));
     std::unique_ptr<tsm_model> m(new tsm_model());
     m->ctx = ctx;
-    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank;
+    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank, m->tp_reduce = ctx->tp_world > 1 && ctx->tp_variant == TSM_TP_REDUCE;
     int rc;
     if (config->arch == 1) rc = load_gpt2_safetensors(m.get(), f, config->heads, kind);
     else if (config->arch == 0) rc = load_llama_safetensors(m.get(), f, *config, kind);
@@ -1295,7 +1373,7 @@ int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uin
     TSM_TRY(check_config(ctx, *config));
     std::unique_ptr<tsm_model> m(new tsm_model());
     m->ctx = ctx;
-    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank;
+    m->tp = ctx->tp_world, m->tp_rank = ctx->tp_rank, m->tp_reduce = ctx->tp_world > 1 && ctx->tp_variant == TSM_TP_REDUCE;
     m->cfg = *config;
     if (m->cfg.arch == 1) m->cfg.tied = 1;
     int rc = build_random(m.get(), kind, seed);

@@ -71,6 +71,49 @@ def main():
             wcache.free(), whole.free()
         cache.free(), model.free()
         dist.barrier()
+    # ---- the all-reduce variant: o and down over each rank's own input columns.  Not the bits of one GPU: the reference's
+    #      budget for a GPU path, 0.001 nats KL per token and a few percent of the largest logit; every rank the same bits.
+    def kl_per_token(want, got):
+        def log_softmax(x):
+            x = x.astype(np.float64)
+            x = x - x.max(axis=-1, keepdims=True)
+            return x - np.log(np.exp(x).sum(axis=-1, keepdims=True))
+        lw, lg = log_softmax(want), log_softmax(got)
+        return float((np.exp(lw) * (lw - lg)).sum(axis=-1).max())
+
+    rdev = pkg.B200(local)
+    pkg.groups.join_tensor_parallel(rdev, dist)
+    rdev.tp_variant(pkg.TP_REDUCE)
+    for arch, kind, config in cases:
+        config = dict(config, arch=arch)
+        if config["heads"] % world or config["kv_heads"] % world:
+            continue
+        prompts = [rng.integers(0, config["vocab"], size=n).tolist() for n in (5, 17, 0, 3)]
+        model = pkg.Model.random(rdev, config, kind, seed=7)
+        cache = model.new_batch_cache(4, 64)
+        got = [model.forward_last(prompts, cache)]
+        ids = [1, 2, 3, 4]
+        for _ in range(3):
+            tokens, logits = model.decode(cache, ids, logits=True)
+            got.append(logits)
+            ids = tokens.tolist()
+        run = model.decode_run(cache, ids, 4)
+        flat = np.concatenate([g.ravel() for g in got]).view(np.uint32).astype(np.int64)
+        mine = torch.tensor([int(flat.sum()), int(run.sum())], device=f"cuda:{local}")
+        both = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(both, mine)
+        assert all(torch.equal(b, both[0]) for b in both), (arch, "ranks disagree under all-reduce", both)
+        if rank == 0:
+            whole = pkg.Model.random(whole_dev, config, kind, seed=7)
+            wcache = whole.new_batch_cache(4, 64)
+            want = whole.forward_last(prompts, wcache)
+            rel = float(np.abs(got[0] - want).max() / np.abs(want).max())
+            assert rel <= 5e-2 and kl_per_token(want, got[0]) <= 1e-3, (arch, "all-reduce variant too far from one GPU", rel)
+            wcache.free(), whole.free()
+        cache.free(), model.free()
+        dist.barrier()
+    rdev.close()
+
     # models loaded from GGUF files, sharded by the loader, against the CPU oracle (the reference's golden fixtures)
     import tempfile
     from oracle import oracle
