@@ -78,7 +78,24 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     float* terms = row + ((n + 3) & ~3);
     int r = blockIdx.x;
     const float* xr = x + (int64_t)r * n;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) row[j] = xr[j];
+    // Rows of up to 8 values per thread: a thread keeps its values, and fetches their weights now, so that those loads are
+    // in flight while one thread folds the ordered sums and nothing but arithmetic is left for afterwards.
+    constexpr int kKeep = 8;
+    const bool kept = n <= kKeep * (int)blockDim.x;
+    float xv[kKeep], wv[kKeep], bv[kKeep];
+    if (kept) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            int j = threadIdx.x + i * blockDim.x;
+            bool in = j < n;
+            xv[i] = in ? xr[j] : 0.0f;
+            wv[i] = in && w ? w[j] : 1.0f;
+            bv[i] = LAYER && in ? b[j] : 0.0f;
+            if (in) row[j] = xv[i];
+        }
+    } else {
+        for (int j = threadIdx.x; j < n; j += blockDim.x) row[j] = xr[j];
+    }
     __syncthreads();
     float count = (float)n;
     float mean = 0.0f, denom;
@@ -107,6 +124,28 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, count), eps));
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     int blocks = (n + 31) >> 5;
+    if (kept) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            int blk = warp + i * warps;  // block blk's element `lane` is this thread's value i
+            if (blk < blocks) {
+                int j = blk * 32 + lane;
+                float y = 0.0f;
+                if (j < n) {
+                    float c = LAYER ? __fsub_rn(xv[i], mean) : xv[i];
+                    y = __fdiv_rn(c, denom);
+                    if (w) y = __fmul_rn(y, wv[i]);
+                    if (LAYER) y = __fadd_rn(y, bv[i]);
+                    if (out) out[(int64_t)r * n + j] = y;
+                }
+                if (q.qs) {
+                    int64_t at = (int64_t)r * (n >> 5) + blk;
+                    quantize_block_q8(y, lane, q.scales + at, q.sums + at, q.totals + at, q.qs + (int64_t)r * n + j);
+                }
+            }
+        }
+        return;
+    }
     for (int blk = warp; blk < blocks; blk += warps) {
         int j = blk * 32 + lane;
         float y = 0.0f;
