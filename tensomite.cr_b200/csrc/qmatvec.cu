@@ -463,6 +463,12 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     if (per_sm < 1) return TSM_OK;
     int slots = per_sm * ctx->sm_count;
     int tiles = (n + max_rows - 1) / max_rows;
+    if (tiles < ctx->sm_count) {
+        // a small matrix: full tiles would leave most SMs without work, and the kernel's time is then one CTA's latency
+        // chain over many rows; tiles of a few rows (at least 4) give every SM one
+        int few = std::max(4, (n + ctx->sm_count - 1) / ctx->sm_count);
+        if (few < max_rows) max_rows = few, tiles = (n + max_rows - 1) / max_rows;
+    }
     int grid = tiles < slots ? tiles : slots;
     int per_cta = (tiles + grid - 1) / grid;
     int rows_per_tile = (n + grid * per_cta - 1) / (grid * per_cta);
