@@ -416,10 +416,22 @@ __global__ void topk_kernel(const float* __restrict__ logits, int n, int count, 
         int li = last_i;
         float v = 0.0f;
         int at = -1;
-        for (int j = threadIdx.x; j < n; j += blockDim.x) {
-            float x = row[j];
-            if (round > 0 && !ahead(lv, li, x, j)) continue;  // not after the last pick
-            if (at < 0 || ahead(x, j, v, at)) v = x, at = j;
+        // eight loads in flight per thread: one at a time, each would wait out a trip to L2
+        for (int j0 = threadIdx.x; j0 < n; j0 += 8 * blockDim.x) {
+            float xs[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                int j = j0 + u * blockDim.x;
+                xs[u] = j < n ? row[j] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                int j = j0 + u * blockDim.x;
+                if (j >= n) break;
+                float x = xs[u];
+                if (round > 0 && !ahead(lv, li, x, j)) continue;  // not after the last pick
+                if (at < 0 || ahead(x, j, v, at)) v = x, at = j;
+            }
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
