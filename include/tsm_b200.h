@@ -106,6 +106,10 @@ int tsm_block_matmul(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride
  * block_matmul_lanes_f32, kernels.cu:1233-1328). */
 int tsm_block_matmul_quantized(tsm_ctx* ctx, tsm_dptr scales, tsm_dptr sums, tsm_dptr qs, int rows, int k, tsm_dptr w,
                                int kind, int n, tsm_dptr bias, tsm_dptr out);
+/* Op::MatMul of a Linear whose weight stayed F32 (Tensor#linear on an F32 leaf; host matmul, devices/host.cr:700-721;
+ * matmul_f32, kernels.cu:357-375): out[rows,n] = x[rows,k] . w[n,k]^T (+ bias[n]); every output adds its k products in
+ * index order, product and sum rounded separately, so the bits are the host's.  bias may be 0. */
+int tsm_matmul_f32(tsm_ctx* ctx, tsm_dptr x, int rows, int k, tsm_dptr w, int n, tsm_dptr bias, tsm_dptr out);
 
 /* tsm_block_matmul without any allocation (no counterpart in the reference, whose CUDA device allocates its
  * scratch from a pool on demand, cuda.cr:791-798).  For callers that cannot allocate device memory while they
@@ -176,16 +180,19 @@ typedef struct {
 } tsm_model_config;
 
 /* Llama.load / GPT2.load of a .gguf file (llama.cr:165-206, gpt2.cr:75-89): reads the configuration
- * from the metadata, uploads every tensor, un-permutes q/k rows, joins [q;k;v] and [gate;up]. */
+ * from the metadata, uploads every tensor, un-permutes q/k rows, joins [q;k;v] and [gate;up].  Matrices may be
+ * Q8_0, Q4_0, Q4_1 or F32 (F16 / BF16 are widened to F32, gguf.cr:112-136); a Linear over an F32 matrix runs as
+ * tsm_matmul_f32, and token tables may stay F32 beside quantised layers (Module#quantize without embeddings). */
 int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out);
-/* Llama.new(config) / GPT2.new(config) with Init.normal(0.02) then Module#quantize(kind, embeddings: true)
- * (module.cr, builder.cr): weights drawn on the device from `seed`, quantised on the device. */
 /* GPT2.load / Llama.load of Hugging Face safetensors weights (gpt2.cr:69-101, llama.cr:163-175, safetensors.cr), followed by
  * Module#quantize(kind, embeddings: true) (module.cr:262-274) on the device: F32 / F16 / BF16 matrices, GPT-2's Conv1D
- * weights transposed, every Linear and both embedding tables quantised to `kind`.  config->arch picks the family.  GPT-2
+ * weights transposed, every Linear and both embedding tables quantised to `kind`; with kind TSM_F32 nothing is quantised
+ * and the model runs in F32 as loaded.  config->arch picks the family.  GPT-2
  * takes config->heads only; Llama takes heads, kv_heads, head_width (0: width / heads), eps, rope_theta and context
  * (what the model directory's config.json holds); all other sizes come from the tensor shapes. */
 int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_config* config, int kind, tsm_model** out);
+/* Llama.new(config) / GPT2.new(config) with Init.normal(0.02) then Module#quantize(kind, embeddings: true)
+ * (module.cr, builder.cr): weights drawn on the device from `seed`, quantised on the device. */
 int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uint64_t seed, tsm_model** out);
 int tsm_model_config_get(tsm_model* model, tsm_model_config* out);
 int tsm_model_free(tsm_model* model);

@@ -261,6 +261,25 @@ class B200:
                 b.free()
         return result
 
+    def matmul_f32(self, x, w, bias=None):
+        """Tensor#linear on an F32 weight: x float32 [rows,k], w float32 [n,k] -> numpy [rows,n], sums in index order."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        rows, k = x.shape
+        n = w.shape[0]
+        xb, wb = self.tensor(x), self.tensor(w)
+        bb = self.tensor(np.ascontiguousarray(bias, dtype=np.float32)) if bias is not None else None
+        out = self.alloc(max(rows * n * 4, 1))
+        try:
+            self.check(self.lib.tsm_matmul_f32(self.ctx, C.c_uint64(xb.ptr), C.c_int(rows), C.c_int(k), C.c_uint64(wb.ptr), C.c_int(n),
+                                               C.c_uint64(bb.ptr if bb else 0), C.c_uint64(out.ptr)), "tsm_matmul_f32")
+            self.sync()
+            return out.numpy(np.float32)[:rows * n].reshape(rows, n)
+        finally:
+            for b in (xb, wb, bb, out):
+                if b:
+                    b.free()
+
     def block_matmul_static(self, x, w, kind, n, bias=None):
         """As block_matmul, through tsm_block_matmul_static: the product's scratch is a fixed array in the library."""
         x = np.ascontiguousarray(x, dtype=np.float32)

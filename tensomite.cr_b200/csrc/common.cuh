@@ -174,7 +174,12 @@ int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind
 int launch_dequantize_blocks(tsm_ctx* ctx, const uint8_t* blocks, int64_t count, int kind, float* out);
 int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table_rows, int width, const int* ids,
                          int count, float* out, const uint8_t* table2, const int* ids2, int ids2_stride);
-int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out);
+// With a second table (GPT-2's positions) the two rows are added: table[ids[t]] + table2[ids2[t * ids2_stride]].
+int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out,
+                      const float* table2 = nullptr, const int* ids2 = nullptr, int ids2_stride = 0);
+// The unquantised product x [rows, k] by w [n, k] -> out [rows, n], sums over k in index order; bias, residual may be null.
+int launch_matmul_f32(tsm_ctx* ctx, const float* x, int rows, int k, const float* w, int n, const float* bias, const float* residual,
+                      float* out);
 int launch_rmsnorm(tsm_ctx* ctx, const float* x, const float* w, int rows, int n, float eps, float* out,
                    const QuantizedActs* quantized);
 int launch_layernorm(tsm_ctx* ctx, const float* x, const float* w, const float* b, int rows, int n, float eps, float* out,

@@ -44,6 +44,7 @@ struct Workspace {
     float* qkv = nullptr;    // [T, (heads + 2 kv) * hw]
     float* att = nullptr;    // [T, heads * hw] (ordered attention writes F32 first)
     float* up = nullptr;     // [T, 2*hidden | hidden]
+    float* h = nullptr;      // [T, max(width, hidden)] normed rows / activation output, when the next weight is F32
     float* logits = nullptr; // [T, vocab]
     int* picks = nullptr;    // [T]
     float* tp_parts = nullptr;   // tensor-parallel: [ranks][T, widest / ranks], the ranks' column slices as gathered
@@ -374,6 +375,18 @@ static int gguf_open(tsm_ctx* ctx, const char* path, GgufFile& f) {
     return TSM_OK;
 }
 
+// F16 (GGUF type 1) or BF16 (type 30) values widened to F32, exactly (gguf.cr:112-136 widens them the same way).
+static void widen_halves(const uint16_t* h, int64_t count, bool bf16, float* out) {
+    for (int64_t i = 0; i < count; i++) {
+        if (bf16) {
+            uint32_t u = (uint32_t)h[i] << 16;
+            memcpy(&out[i], &u, 4);
+        } else {
+            out[i] = __half2float(__ushort_as_half(h[i]));
+        }
+    }
+}
+
 // Uploads an F32 / F16 / BF16 vector or matrix as F32.
 static int upload_f32(tsm_model* m, GgufFile& f, const std::string& name, int64_t expect, float** out) {
     auto found = f.entries.find(name);
@@ -386,15 +399,7 @@ static int upload_f32(tsm_model* m, GgufFile& f, const std::string& name, int64_
     const void* src = f.data + e.offset;
     if (e.kind == 1 || e.kind == 30) {
         wide.resize((size_t)count);
-        const uint16_t* h = (const uint16_t*)src;
-        for (int64_t i = 0; i < count; i++) {
-            if (e.kind == 30) {
-                uint32_t u = (uint32_t)h[i] << 16;
-                memcpy(&wide[i], &u, 4);
-            } else {
-                wide[i] = __half2float(__ushort_as_half(h[i]));
-            }
-        }
+        widen_halves((const uint16_t*)src, count, e.kind == 30, wide.data());
         src = wide.data();
     } else if (e.kind != 0) {
         return fail(m->ctx, TSM_ERR_UNSUPPORTED, name + " is a block format where F32 is expected");
@@ -420,7 +425,6 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
         if (e.shape.size() != 2 || e.shape[1] != k)
             return fail(m->ctx, TSM_ERR_ARG, part.name + ": the file's shape does not match the model's [" + std::to_string(expect_n) + ", " + std::to_string(k) + "]");
         int this_kind = gguf_kind_to_tsm(e.kind);
-        if (e.kind == 1 || e.kind == 30) return fail(m->ctx, TSM_ERR_UNSUPPORTED, part.name + ": F16 matrices are not supported; quantise or store F32");
         if (kind != -2 && kind != this_kind) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "joined projections must share a format");
         kind = this_kind;
         total_rows += e.shape[0];
@@ -433,6 +437,12 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
         const GgufEntry& e = f.entries[part.name];
         const uint8_t* src = f.data + e.offset;
         int64_t rows = e.shape[0];
+        std::vector<float> wide;
+        if (e.kind == 1 || e.kind == 30) {  // F16 / BF16 matrices become F32 weights
+            wide.resize((size_t)(rows * k));
+            widen_halves((const uint16_t*)src, rows * k, e.kind == 30, wide.data());
+            src = (const uint8_t*)wide.data();
+        }
         if (part.heads > 0) {
             int64_t half = rows / part.heads / 2;
             int64_t dst_row = 0;
@@ -862,6 +872,20 @@ static int st_vector(tsm_model* m, StFile& f, const std::string& name, int64_t n
 // Row-major [n, k] F32 values -> a quantised Linear holding the rows of `ranges` (all when empty).
 static int linear_from_values(tsm_model* m, const std::vector<float>& values, int64_t n, int64_t k, int kind, Linear* out,
                               const std::vector<RowRange>& ranges = {}) {
+    if (kind == TSM_F32) {  // kept as it is: Module#load without Module#quantize
+        std::vector<RowRange> keep = ranges;
+        if (keep.empty()) keep.push_back({0, n});
+        int64_t local = 0;
+        for (auto& range : keep) local += range.count;
+        out->kind = kind, out->n = (int)local, out->k = (int)k;
+        TSM_TRY(dev_alloc(m, weight_bytes(kind, local, k), (void**)&out->w));
+        int64_t at = 0;
+        for (auto& range : keep) {
+            TSM_TRY(tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)(out->w + weight_bytes(kind, at, k)), values.data() + range.start * k, range.count * k * 4));
+            at += range.count;
+        }
+        return TSM_OK;
+    }
     if (k % 32 != 0) return fail(m->ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
     float* staged = nullptr;
     TSM_TRY(pool_alloc(m->ctx, n * k * 4, (void**)&staged));
@@ -996,9 +1020,17 @@ static int load_llama_safetensors(tsm_model* m, StFile& f, const tsm_model_confi
 
 // ---- one packed step -----------------------------------------------------------------------------
 
+// Whether any Linear of the model (the head included) kept an F32 weight.
+static bool has_f32_matrix(const tsm_model* m) {
+    if (m->head.kind == TSM_F32) return true;
+    for (const Layer& l : m->layers)
+        if (l.qkv.kind == TSM_F32 || l.o.kind == TSM_F32 || l.up.kind == TSM_F32 || l.down.kind == TSM_F32) return true;
+    return false;
+}
+
 static void free_workspace(tsm_model* m) {
     Workspace& w = m->ws;
-    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.logits, w.picks, w.qa, w.qb, w.qc, w.tp_parts, w.tp_rows, w.tp_best};
+    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.h, w.logits, w.picks, w.qa, w.qb, w.qc, w.tp_parts, w.tp_rows, w.tp_best};
     for (void* b : bufs) pool_release(m->ctx, b);
     if (w.host) cudaFreeHost(w.host);
     w = Workspace{};
@@ -1023,6 +1055,7 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     TSM_TRY(pool_alloc(ctx, T * (qn + 2 * kvn) * 4, (void**)&w.qkv));
     TSM_TRY(pool_alloc(ctx, T * qn * 4, (void**)&w.att));
     TSM_TRY(pool_alloc(ctx, T * upn * 4, (void**)&w.up));
+    if (has_f32_matrix(m)) TSM_TRY(pool_alloc(ctx, T * std::max(c.width, c.hidden) * 4, (void**)&w.h));
     TSM_TRY(pool_alloc(ctx, T * c.vocab * 4, (void**)&w.logits));
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.picks));
     if (m->tp > 1) {
@@ -1040,9 +1073,20 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     return TSM_OK;
 }
 
-static int product(tsm_model* m, const QuantizedActs& a, int rows, const Linear& l, const float* residual, float* out) {
-    if (l.kind == TSM_F32) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "F32 matrices are not supported by this engine; quantise the model");
+// A Linear over `rows` rows.  A block weight reads the quantised rows `a`; a weight that stayed F32 reads the rows
+// themselves, `plain`.  Whoever produces the rows asks feeds() which of the two this Linear wants.
+static int product(tsm_model* m, const QuantizedActs& a, const float* plain, int rows, const Linear& l, const float* residual, float* out) {
+    if (l.kind == TSM_F32) return launch_matmul_f32(m->ctx, plain, rows, l.k, (const float*)l.w, l.n, l.bias, residual, out);
     return launch_block_matmul(m->ctx, a, rows, l.k, l.w, l.kind, l.n, l.bias, residual, out);
+}
+
+// Where the producer of a Linear's input writes: F32 rows for an F32 weight, quantised blocks otherwise.
+struct Feed {
+    float* plain;
+    const QuantizedActs* quantized;
+};
+static Feed feeds(const Linear& l, float* plain, const QuantizedActs* quantized) {
+    return l.kind == TSM_F32 ? Feed{plain, nullptr} : Feed{nullptr, quantized};
 }
 
 // Tensor-parallel greedy pick: every rank holds, for each row, the best logit of its vocabulary slice and that logit's
@@ -1079,7 +1123,7 @@ static int launch_layer_sharded(tsm_model* m, tsm_cache* cache, int i, int total
     (void)ordered;
     if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
     else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
-    TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+    TSM_TRY(product(m, qa, nullptr, total, l.qkv, nullptr, w.qkv));
     TSM_TRY(launch_rope_append(ctx, w.qkv, total, heads_l, kv_l, hw, c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr,
                                c.context, w.table, cache->keys[i], cache->values[i], cache->rows, cache->capacity));
     TSM_TRY(launch_attention(ctx, w.qkv, qkvn_l, total, heads_l, hw, cache->keys[i], cache->values[i], cache->rows, kv_l, cache->capacity,
@@ -1087,19 +1131,19 @@ static int launch_layer_sharded(tsm_model* m, tsm_cache* cache, int i, int total
     TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * qn_l * 4));
     TSM_TRY(launch_interleave(ctx, w.tp_parts, w.tp_rows, total, qn_l, G, false));
     TSM_TRY(launch_quantize_rows(ctx, w.tp_rows, total, qn, qn, (float*)qb.scales, (float*)qb.sums, (int*)qb.totals, (int8_t*)qb.qs));
-    TSM_TRY(product(m, qb, total, l.o, nullptr, w.tp_parts + (int64_t)r * total * w_l));
+    TSM_TRY(product(m, qb, nullptr, total, l.o, nullptr, w.tp_parts + (int64_t)r * total * w_l));
     TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * w_l * 4));
     TSM_TRY(launch_interleave(ctx, w.tp_parts, w.x, total, w_l, G, true));
     if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
     else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
-    TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
+    TSM_TRY(product(m, qa, nullptr, total, l.up, nullptr, w.up));
     float* hidden_part = w.tp_parts + (int64_t)r * total * hid_l;
     if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + hid_l, total, hid_l, 2 * (int64_t)hid_l, hidden_part, nullptr));
     else TSM_TRY(launch_gelu(ctx, w.up, total, hid_l, hidden_part, nullptr));
     TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * hid_l * 4));
     TSM_TRY(launch_interleave(ctx, w.tp_parts, w.tp_rows, total, hid_l, G, false));
     TSM_TRY(launch_quantize_rows(ctx, w.tp_rows, total, c.hidden, c.hidden, (float*)qc.scales, (float*)qc.sums, (int*)qc.totals, (int8_t*)qc.qs));
-    TSM_TRY(product(m, qc, total, l.down, nullptr, w.tp_parts + (int64_t)r * total * w_l));
+    TSM_TRY(product(m, qc, nullptr, total, l.down, nullptr, w.tp_parts + (int64_t)r * total * w_l));
     TSM_TRY(tp_all_gather(ctx, w.tp_parts, (int64_t)total * w_l * 4));
     TSM_TRY(launch_interleave(ctx, w.tp_parts, w.x, total, w_l, G, true));
     return TSM_OK;
@@ -1120,20 +1164,20 @@ static int launch_layer_reduced(tsm_model* m, tsm_cache* cache, int i, int total
     const int64_t count = (int64_t)total * c.width;
     if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
     else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
-    TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+    TSM_TRY(product(m, qa, nullptr, total, l.qkv, nullptr, w.qkv));
     TSM_TRY(launch_rope_append(ctx, w.qkv, total, heads_l, kv_l, hw, c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr,
                                c.context, w.table, cache->keys[i], cache->values[i], cache->rows, cache->capacity));
     TSM_TRY(launch_attention(ctx, w.qkv, qkvn_l, total, heads_l, hw, cache->keys[i], cache->values[i], cache->rows, kv_l, cache->capacity,
                              w.table, scale, w.att, &qb, order));
-    TSM_TRY(product(m, qb, total, l.o, nullptr, w.tp_rows));
+    TSM_TRY(product(m, qb, nullptr, total, l.o, nullptr, w.tp_rows));
     TSM_TRY(tp_all_reduce_sum(ctx, w.tp_rows, count));
     TSM_TRY(launch_add(ctx, w.x, w.tp_rows, count, w.x));
     if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
     else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
-    TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
+    TSM_TRY(product(m, qa, nullptr, total, l.up, nullptr, w.up));
     if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + hid_l, total, hid_l, 2 * (int64_t)hid_l, nullptr, &qc));
     else TSM_TRY(launch_gelu(ctx, w.up, total, hid_l, nullptr, &qc));
-    TSM_TRY(product(m, qc, total, l.down, nullptr, w.tp_rows));
+    TSM_TRY(product(m, qc, nullptr, total, l.down, nullptr, w.tp_rows));
     TSM_TRY(tp_all_reduce_sum(ctx, w.tp_rows, count));
     TSM_TRY(launch_add(ctx, w.x, w.tp_rows, count, w.x));
     return TSM_OK;
@@ -1194,12 +1238,16 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
     float scale = (float)(1.0 / sqrt((double)hw));
     bool ordered = ctx->mode == TSM_EXACT || !(hw == 64 || hw == 128);
 
-    if (m->embed.kind == TSM_F32) return fail(ctx, TSM_ERR_UNSUPPORTED, "F32 embedding tables are not supported by this engine; quantise the model with its embeddings");
-    if (c.arch == 0) {
-        TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, nullptr, nullptr, 0));
+    if (m->tp > 1 && (has_f32_matrix(m) || m->embed.kind == TSM_F32))
+        return fail(ctx, TSM_ERR_UNSUPPORTED, "tensor parallelism takes block-quantised weights only");
+    if (c.arch == 1 && m->wpe.kind != m->embed.kind) return fail(ctx, TSM_ERR_UNSUPPORTED, "token and position tables must share a format");
+    const int* positions = c.arch == 1 ? w.table + 1 : nullptr;  // gpt2.cr:189-191: wte(ids) + wpe(positions)
+    if (m->embed.kind == TSM_F32) {
+        TSM_TRY(launch_gather_f32(ctx, (const float*)m->embed.w, c.vocab, c.width, w.ids, total, w.x, c.arch == 1 ? (const float*)m->wpe.w : nullptr,
+                                  positions, 3));
     } else {
-        if (m->wpe.kind != m->embed.kind) return fail(ctx, TSM_ERR_UNSUPPORTED, "token and position tables must share a format");
-        TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, m->wpe.w, w.table + 1, 3));
+        TSM_TRY(launch_gather_blocks(ctx, m->embed.w, m->embed.kind, c.vocab, c.width, w.ids, total, w.x, c.arch == 1 ? m->wpe.w : nullptr,
+                                     positions, 3));
     }
     const int* order = nullptr;
     if (total > 1 && total <= 4096) {  // the same order serves every layer of the step
@@ -1213,21 +1261,25 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
             continue;
         }
         Layer& l = m->layers[i];
-        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, nullptr, &qa));
-        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, nullptr, &qa));
-        TSM_TRY(product(m, qa, total, l.qkv, nullptr, w.qkv));
+        Feed f = feeds(l.qkv, w.h, &qa);
+        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, f.plain, f.quantized));
+        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, f.plain, f.quantized));
+        TSM_TRY(product(m, qa, w.h, total, l.qkv, nullptr, w.qkv));
         TSM_TRY(launch_rope_append(ctx, w.qkv, total, c.heads, c.kv_heads, hw, c.arch == 0 ? m->rope_cos : nullptr,
                                    c.arch == 0 ? m->rope_sin : nullptr, c.context, w.table, cache->keys[i], cache->values[i],
                                    cache->rows, cache->capacity));
+        f = feeds(l.o, w.att, &qb);
         TSM_TRY(launch_attention(ctx, w.qkv, qkvn, total, c.heads, hw, cache->keys[i], cache->values[i], cache->rows, c.kv_heads,
-                                 cache->capacity, w.table, scale, ordered ? w.att : nullptr, &qb, order));
-        TSM_TRY(product(m, qb, total, l.o, w.x, w.x));
-        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, nullptr, &qa));
-        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, nullptr, &qa));
-        TSM_TRY(product(m, qa, total, l.up, nullptr, w.up));
-        if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + c.hidden, total, c.hidden, 2 * (int64_t)c.hidden, nullptr, &qc));
-        else TSM_TRY(launch_gelu(ctx, w.up, total, c.hidden, nullptr, &qc));
-        TSM_TRY(product(m, qc, total, l.down, w.x, w.x));
+                                 cache->capacity, w.table, scale, ordered || f.plain ? w.att : nullptr, f.quantized, order));
+        TSM_TRY(product(m, qb, w.att, total, l.o, w.x, w.x));
+        f = feeds(l.up, w.h, &qa);
+        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, f.plain, f.quantized));
+        else TSM_TRY(launch_layernorm(ctx, w.x, l.norm2_w, l.norm2_b, total, c.width, c.eps, f.plain, f.quantized));
+        TSM_TRY(product(m, qa, w.h, total, l.up, nullptr, w.up));
+        f = feeds(l.down, w.h, &qc);
+        if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + c.hidden, total, c.hidden, 2 * (int64_t)c.hidden, f.plain, f.quantized));
+        else TSM_TRY(launch_gelu(ctx, w.up, total, c.hidden, f.plain, f.quantized));
+        TSM_TRY(product(m, qc, w.h, total, l.down, w.x, w.x));
     }
     const float* xl = w.x;
     if (outputs < total) {
@@ -1235,12 +1287,13 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
         xl = w.xl;
     }
     QuantizedActs qh = quant_scratch_layout(w.qa, outputs, c.width);
-    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, xl, m->final_w, outputs, c.width, c.eps, nullptr, &qh));
-    else TSM_TRY(launch_layernorm(ctx, xl, m->final_w, m->final_b, outputs, c.width, c.eps, nullptr, &qh));
+    Feed f = feeds(m->head, w.h, &qh);
+    if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, xl, m->final_w, outputs, c.width, c.eps, f.plain, f.quantized));
+    else TSM_TRY(launch_layernorm(ctx, xl, m->final_w, m->final_b, outputs, c.width, c.eps, f.plain, f.quantized));
     if (m->tp > 1) return launch_head_sharded(m, qh, outputs, pick, !pick);
     Linear head = m->head;
     head.bias = nullptr;
-    TSM_TRY(product(m, qh, outputs, head, nullptr, w.logits));
+    TSM_TRY(product(m, qh, w.h, outputs, head, nullptr, w.logits));
     if (pick) TSM_TRY(launch_argmax(ctx, w.logits, outputs, c.vocab, w.picks));
     return TSM_OK;
 }
@@ -1345,7 +1398,7 @@ int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_c
     if (!ctx || !path || !config || !out) return TSM_ERR_ARG;
     tsm::DeviceGuard guard(ctx->ordinal);
     *out = nullptr;
-    if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
+    if (kind < TSM_F32 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a weight format");
     StFile f;
     TSM_TRY(st_open(ctx, path, f));
     std::unique_ptr<tsm_model> m(new tsm_model());

@@ -194,7 +194,8 @@ int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table
 }
 
 __global__ void gather_f32_kernel(const float* __restrict__ table, int table_rows, int width, const int* __restrict__ ids,
-                                  int64_t total, float* out, ErrorRecord* errors) {
+                                  int64_t total, float* out, ErrorRecord* errors, const float* __restrict__ table2,
+                                  const int* __restrict__ ids2, int ids2_stride) {
     chained_kernel_entry();
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
@@ -205,13 +206,17 @@ __global__ void gather_f32_kernel(const float* __restrict__ table, int table_row
         out[i] = 0.0f;
         return;
     }
-    out[i] = table[(int64_t)id * width + col];
+    float v = table[(int64_t)id * width + col];
+    if (table2) v = __fadd_rn(v, table2[(int64_t)ids2[(int64_t)token * ids2_stride] * width + col]);
+    out[i] = v;
 }
 
-int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out) {
+int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out,
+                      const float* table2, const int* ids2, int ids2_stride) {
     int64_t total = (int64_t)count * width;
     if (total == 0) return TSM_OK;
-    TSM_CUDA(ctx, launch_chained(ctx, gather_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, table, table_rows, width, ids, total, out, ctx->errors));
+    TSM_CUDA(ctx, launch_chained(ctx, gather_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, table, table_rows, width, ids, total, out,
+                                 ctx->errors, table2, ids2, ids2_stride));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;

@@ -329,6 +329,11 @@ int tsm_gather_f32(tsm_ctx* ctx, tsm_dptr table, int table_rows, int width, tsm_
     return launch_gather_f32(ctx, PCF(table), table_rows, width, PCI(ids), count, PF(out));
 }
 
+int tsm_matmul_f32(tsm_ctx* ctx, tsm_dptr x, int rows, int k, tsm_dptr w, int n, tsm_dptr bias, tsm_dptr out) {
+    CTX_GUARD(ctx);
+    return launch_matmul_f32(ctx, PCF(x), rows, k, PCF(w), n, PCF(bias), nullptr, PF(out));
+}
+
 int tsm_rmsnorm(tsm_ctx* ctx, tsm_dptr x, tsm_dptr w, int rows, int n, float eps, tsm_dptr out) {
     CTX_GUARD(ctx);
     return launch_rmsnorm(ctx, PCF(x), PCF(w), rows, n, eps, PF(out), nullptr);

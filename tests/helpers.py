@@ -198,13 +198,15 @@ def oracle_from_device_model(model, threads=1):
     return oracle.Model(c, t, threads=threads)
 
 
-def write_gpt2_gguf(path, st, layers, heads, kind):
-    """A GPT-2 in tensomite's own GGUF names (gpt2.cr:75-89), Linear weights and both tables quantised."""
-    t = gpt2_tensors_from_hf(st, layers, quantize_kind=kind, embeddings=True)
+def write_gpt2_gguf(path, st, layers, heads, kind, embeddings=True):
+    """A GPT-2 in tensomite's own GGUF names (gpt2.cr:75-89), Linear weights quantised and, with `embeddings`, both
+    tables too (Module#quantize(kind, embeddings: true)); without, the tables stay F32 and so does the tied head."""
+    t = gpt2_tensors_from_hf(st, layers, quantize_kind=kind, embeddings=embeddings)
     gk = GGUF_OF_KIND[kind]
+    tk = gk if embeddings else gguf.F32
     d = st["transformer.wte.weight"].shape[1]
-    tensors = [("wte.weight", gk, list(st["transformer.wte.weight"].shape), t["embed"][1]),
-               ("wpe.weight", gk, list(st["transformer.wpe.weight"].shape), t["wpe"][1]),
+    tensors = [("wte.weight", tk, list(st["transformer.wte.weight"].shape), t["embed"][1]),
+               ("wpe.weight", tk, list(st["transformer.wpe.weight"].shape), t["wpe"][1]),
                ("ln_f.weight", gguf.F32, [d], t["final_w"][1]), ("ln_f.bias", gguf.F32, [d], t["final_b"][1])]
     for i in range(layers):
         for ours, theirs in (("norm1", "ln_1"), ("norm2", "ln_2")):

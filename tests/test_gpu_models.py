@@ -75,6 +75,63 @@ def test_tiny_llama_gguf(dev, tmp_path, name):
     model.free()
 
 
+def test_tiny_llama_f32_gguf_matches_pytorch_logits(dev, tmp_path):
+    """spec/llama_spec.cr:50-87 on the device: the reference's F32 fixture through the unquantised product.  Logits within
+    1e-4 of PyTorch's and greedy tokens equal (the fixture), the oracle's bits, prefill == decode."""
+    g = golden()
+    path = write_golden(tmp_path, "tiny_llama/f32_gguf", "model.gguf")
+    ref = helpers.oracle_llama(path)
+    model = pkg.Llama.load(path, dev)
+    assert model.tensor("0.qkv")[1] == pkg.F32 and model.tensor("embed")[1] == pkg.F32
+    prompt = g["tiny_llama/prompt_ids"].tolist()
+    cache = model.new_batch_cache(1, 64)
+    got = model.forward([prompt], cache)
+    assert np.max(np.abs(got - g["tiny_llama/logits"])) < 1e-4
+    check(pkg.EXACT, got, ref.forward(ref.new_cache(1, 64), [prompt], last=False), "prefill")
+    cache2 = model.new_batch_cache(1, 64)
+    rows = np.stack([model.forward_last([[t]], cache2)[0] for t in prompt])
+    assert np.array_equal(bits(rows), bits(got))
+    assert model.generate(prompt, 20) == g["tiny_llama/greedy"].tolist()
+    assert dev.counters()["host_ops"] == 0
+    cache.free(), cache2.free()
+    model.free()
+
+
+def test_tiny_gpt2_f32_safetensors_matches_pytorch_logits(dev, tmp_path):
+    """spec/gpt2_spec.cr:54-102 on the device: GPT2.load("model.safetensors") kept in F32."""
+    g = golden()
+    path = tmp_path / "model.safetensors"
+    path.write_bytes(g["tiny_gpt2/safetensors"].tobytes())
+    st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+    config = dict(arch="gpt2", layers=2, heads=4, kv_heads=4, width=32, head_width=8, hidden=128, context=64, vocab=400, eps=1e-5)
+    ref = oracle.Model(config, helpers.gpt2_tensors_from_hf(st, 2))
+    model = pkg.GPT2.load_safetensors(path, dev, dict(arch="gpt2", heads=4), pkg.F32)
+    prompt = g["tiny_gpt2/prompt_ids"].tolist()
+    got = model.forward([prompt], model.new_batch_cache(1, 64))
+    assert np.max(np.abs(got - g["tiny_gpt2/logits"])) < 1e-4
+    check(pkg.EXACT, got, ref.forward(ref.new_cache(1, 64), [prompt], last=False))
+    assert model.generate(prompt, 20) == g["tiny_gpt2/greedy"].tolist()
+    model.free()
+
+
+def test_tiny_gpt2_q8_0_with_f32_embeddings(dev, tmp_path):
+    """Module#quantize(Q8_0) without embeddings: the tables stay F32, so the tied head is an F32 product fed by F32 rows
+    while every layer reads quantised ones."""
+    g = golden()
+    st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+    path = str(tmp_path / "gpt2-q8_0-f32-tables.gguf")
+    tensors = helpers.write_gpt2_gguf(path, st, 2, 4, oracle.Q8_0, embeddings=False)
+    config = dict(arch="gpt2", layers=2, heads=4, kv_heads=4, width=32, head_width=8, hidden=128, context=64, vocab=400, eps=1e-5)
+    ref = oracle.Model(config, tensors)
+    model = pkg.GPT2.load(path, dev)
+    assert model.tensor("embed")[1] == pkg.F32 and model.tensor("0.qkv")[1] == pkg.Q8_0
+    prompt = g["tiny_gpt2/prompt_ids"].tolist()
+    want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+    check(pkg.EXACT, model.forward([prompt], model.new_batch_cache(1, 64)), want)
+    assert model.generate(prompt, 20) == ref.generate(prompt, 20)
+    model.free()
+
+
 def test_tiny_gpt2_q8_0_with_quantised_embeddings(dev, tmp_path):
     g = golden()
     st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])

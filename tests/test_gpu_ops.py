@@ -107,6 +107,25 @@ def test_block_product_with_a_scale_that_is_not_finite(dev):
     assert np.array_equal(got[np.isinf(want)], want[np.isinf(want)])
 
 
+def host_matmul_f32(x, w, bias=None):
+    """devices/host.cr:700-734: every output adds its k products in index order, product and sum rounded separately."""
+    acc = np.zeros((x.shape[0], w.shape[0]), dtype=np.float32)
+    for s in range(x.shape[1]):
+        acc = acc + x[:, s, None] * w[None, :, s]
+    return acc + bias[None, :] if bias is not None else acc
+
+
+@pytest.mark.parametrize("rows,k,n", [(1, 576, 300), (5, 100, 129), (9, 33, 64), (8, 32, 128), (64, 256, 1000), (3, 1, 7)])
+def test_f32_product_has_the_hosts_bits(dev, rows, k, n):
+    """A Linear whose weight stayed F32 (spec/llama_spec.cr and spec/gpt2_spec.cr run whole F32 models through it)."""
+    rng = np.random.default_rng(rows * 1000 + k)
+    x = rng.normal(0, 1, (rows, k)).astype(np.float32)
+    w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
+    bias = rng.normal(0, 1, n).astype(np.float32)
+    assert np.array_equal(bits(dev.matmul_f32(x, w)), bits(host_matmul_f32(x, w)))
+    assert np.array_equal(bits(dev.matmul_f32(x, w, bias)), bits(host_matmul_f32(x, w, bias)))
+
+
 def test_a_row_alone_equals_the_row_in_a_batch(dev):
     rng = np.random.default_rng(4)
     n, k = 512, 2048
