@@ -157,6 +157,8 @@ int tsm_ragged_attention(tsm_ctx* ctx, tsm_dptr q, int64_t q_stride, int tokens,
 /* Tensor#swiglu / #gelu (kernels.cr:4,18): elementwise over [rows,n]; strides in floats. */
 int tsm_swiglu(tsm_ctx* ctx, tsm_dptr gate, tsm_dptr up, int rows, int n, int64_t in_stride, tsm_dptr out);
 int tsm_gelu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out);
+/* Tensor#silu (kernels.cr:15): x / (exp(-x) + 1) with the reference's own exp. */
+int tsm_silu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out);
 /* Op::Add (tensor/elementwise.cr:4-6). */
 int tsm_add(tsm_ctx* ctx, tsm_dptr a, tsm_dptr b, int64_t count, tsm_dptr out);
 
@@ -194,6 +196,11 @@ int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_c
 /* Llama.new(config) / GPT2.new(config) with Init.normal(0.02) then Module#quantize(kind, embeddings: true)
  * (module.cr, builder.cr): weights drawn on the device from `seed`, quantised on the device. */
 int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uint64_t seed, tsm_model** out);
+/* Module#save("model.gguf") (module.cr:148-164; GGUF.write, gguf.cr:156-191): the model as the device holds it, block
+ * formats byte for byte, written to a temporary beside `path` and renamed.  A Llama is written under llama.cpp's names with
+ * llama.* metadata and q/k rows in llama.cpp's rotary order, a GPT-2 under tensomite's names with gpt2.heads, so the file
+ * loads again through tsm_model_load_gguf and through the reference's Llama.load / GPT2.load.  One GPU only. */
+int tsm_model_save_gguf(tsm_model* model, const char* path);
 int tsm_model_config_get(tsm_model* model, tsm_model_config* out);
 int tsm_model_free(tsm_model* model);
 /* The weight behind a parameter ("embed", "head", "final_w", "final_b", "wpe", "<layer>.qkv", ".o", ".up",

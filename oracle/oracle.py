@@ -184,6 +184,13 @@ def swiglu(gate, up):
     return out
 
 
+def silu(x):
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib.orc_silu(_p(x, _f32p), C.c_int64(x.size), _p(out, _f32p))
+    return out
+
+
 def gelu(x):
     x = _f32(x)
     out = np.empty_like(x)

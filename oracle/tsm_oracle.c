@@ -550,6 +550,15 @@ void orc_rope_row(const float* x, const float* c, const float* s, int n, float* 
     }
 }
 
+/* kernels.cr:15 through kernel.cr:259-300: x / (exp(-x) + 1). */
+void orc_silu(const float* x, int64_t count, float* dst) {
+    for (int64_t i = 0; i < count; i++) {
+        float t1 = orc_exp(-x[i]);
+        float t2 = t1 + 1.0f;
+        dst[i] = x[i] / t2;
+    }
+}
+
 /* kernels.cr:18 through kernel.cr:259-300: gate / (exp(-gate) + 1) * up. */
 void orc_swiglu(const float* gate, const float* up, int64_t count, float* dst) {
     for (int64_t i = 0; i < count; i++) {

@@ -378,6 +378,10 @@ class B200:
         return self._unary_rows(lambda xb, out: self.lib.tsm_gelu(self.ctx, C.c_uint64(xb.ptr), C.c_int64(x.size), C.c_uint64(out.ptr)),
                                 "tsm_gelu", x)
 
+    def silu(self, x):
+        return self._unary_rows(lambda xb, out: self.lib.tsm_silu(self.ctx, C.c_uint64(xb.ptr), C.c_int64(x.size), C.c_uint64(out.ptr)),
+                                "tsm_silu", x)
+
     def add(self, a, b):
         bb = self.tensor(np.ascontiguousarray(b, dtype=np.float32))
         try:
@@ -524,6 +528,10 @@ class Model:
         device.check(device.lib.tsm_model_random(device.ctx, C.byref(cfg), C.c_int(kind), C.c_uint64(seed), C.byref(handle)),
                      "tsm_model_random")
         return cls(device, handle)
+
+    def save(self, path):
+        """Module#save to a .gguf file: quantised weights as they are."""
+        self.device.check(self.device.lib.tsm_model_save_gguf(self.handle, str(path).encode()), "tsm_model_save_gguf")
 
     def tensor(self, name):
         """(Buffer, kind, n, k) of a parameter."""

@@ -203,6 +203,7 @@ int64_t attention_scratch_bytes(int tokens, int heads, int width, int capacity);
 int launch_swiglu(tsm_ctx* ctx, const float* gate, const float* up, int rows, int n, int64_t in_stride, float* out,
                   const QuantizedActs* quantized);
 int launch_gelu(tsm_ctx* ctx, const float* x, int rows, int n, float* out, const QuantizedActs* quantized);
+int launch_silu(tsm_ctx* ctx, const float* x, int64_t count, float* out);
 int launch_add(tsm_ctx* ctx, const float* a, const float* b, int64_t count, float* out);
 int launch_argmax(tsm_ctx* ctx, const float* logits, int rows, int n, int* out);
 int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, int* out_ids, float* out_values);

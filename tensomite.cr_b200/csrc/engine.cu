@@ -3,6 +3,7 @@
 // models/{generative,llama,gpt2}.cr and modules.cr; the op order of one step is theirs.
 #include <fcntl.h>
 #include <math.h>
+#include <stdio.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
@@ -1358,6 +1359,68 @@ __global__ void run_record_kernel(const int* picks, int rows, int* state) {
     if (!(m) || !(m)->ctx) return TSM_ERR_ARG;        \
     tsm::DeviceGuard device_guard__((m)->ctx->ordinal)
 
+// ---- Module#save to a .gguf file (module.cr:148-164; GGUF.write, gguf.cr:156-191) ---------------------------------
+//
+// Writes the model as it is held on the device: block formats keep their bytes, F32 stays F32.  A Llama goes out under
+// llama.cpp's names with its llama.* metadata and with q and k rows back in llama.cpp's rotary order (the inverse of what
+// the loader undoes, llama.cr:226-235), the joined projections cut back into their parts; a GPT-2 under tensomite's own
+// names with gpt2.heads.  Either file loads again here and in the reference.
+
+struct SavedTensor {
+    std::string name;
+    uint32_t kind;               // GGUF's type number
+    std::vector<int64_t> shape;  // outermost first
+    std::vector<uint8_t> bytes;
+};
+
+static uint32_t gguf_kind_of(int kind) { return kind == TSM_Q8_0 ? 8 : kind == TSM_Q4_0 ? 2 : kind == TSM_Q4_1 ? 3 : 0; }
+
+// Rows [first, first + rows) of a weight, downloaded; heads > 0 puts them back into llama.cpp's rotary order.
+static int saved_rows(tsm_model* m, const Linear& l, const std::string& name, int64_t first, int64_t rows, int heads, std::vector<SavedTensor>& out) {
+    SavedTensor t;
+    t.name = name, t.kind = gguf_kind_of(l.kind), t.shape = {rows, (int64_t)l.k};
+    int64_t row_bytes = weight_bytes(l.kind, 1, l.k);
+    t.bytes.resize((size_t)(rows * row_bytes));
+    TSM_TRY(tsm_download(m->ctx, t.bytes.data(), (tsm_dptr)(uintptr_t)(l.w + first * row_bytes), rows * row_bytes));
+    if (heads > 0) {
+        std::vector<uint8_t> file((size_t)(rows * row_bytes));
+        int64_t half = rows / heads / 2, held = 0;
+        for (int head = 0; head < heads; head++)
+            for (int pair = 0; pair < 2; pair++)
+                for (int64_t i = 0; i < half; i++, held++)
+                    memcpy(&file[(size_t)((head * 2 * half + 2 * i + pair) * row_bytes)], &t.bytes[(size_t)(held * row_bytes)], (size_t)row_bytes);
+        t.bytes.swap(file);
+    }
+    out.push_back(std::move(t));
+    return TSM_OK;
+}
+
+static int saved_vector(tsm_model* m, const float* values, const std::string& name, int64_t count, std::vector<SavedTensor>& out) {
+    if (!values) return TSM_OK;
+    SavedTensor t;
+    t.name = name, t.kind = 0, t.shape = {count};
+    t.bytes.resize((size_t)count * 4);
+    TSM_TRY(tsm_download(m->ctx, t.bytes.data(), (tsm_dptr)(uintptr_t)values, count * 4));
+    out.push_back(std::move(t));
+    return TSM_OK;
+}
+
+struct GgufWriter {
+    std::vector<uint8_t> bytes;
+    template <typename T>
+    void put(T v) {
+        const uint8_t* p = (const uint8_t*)&v;
+        bytes.insert(bytes.end(), p, p + sizeof(T));
+    }
+    void str(const std::string& s) {
+        put<uint64_t>(s.size());
+        bytes.insert(bytes.end(), s.begin(), s.end());
+    }
+    void u32(const std::string& key, uint32_t v) { str(key), put<uint32_t>(4), put<uint32_t>(v); }
+    void f32(const std::string& key, float v) { str(key), put<uint32_t>(6), put<float>(v); }
+    void text(const std::string& key, const std::string& v) { str(key), put<uint32_t>(8), str(v); }
+};
+
 extern "C" {
 
 int tsm_model_free(tsm_model* model) {
@@ -1436,6 +1499,105 @@ int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uin
     }
     register_names(m.get());
     *out = m.release();
+    return TSM_OK;
+}
+
+int tsm_model_save_gguf(tsm_model* m, const char* path) {
+    if (!m || !path) return TSM_ERR_ARG;
+    tsm_ctx* ctx = m->ctx;
+    tsm::DeviceGuard guard(ctx->ordinal);
+    if (m->tp > 1) return fail(ctx, TSM_ERR_UNSUPPORTED, "a tensor-parallel rank holds a part of the model; save from one GPU");
+    const tsm_model_config& c = m->cfg;
+    TSM_TRY(tsm_sync(ctx));
+    std::vector<SavedTensor> tensors;
+    GgufWriter head;
+    uint64_t keys = 0;
+    const int64_t qn = (int64_t)c.heads * c.head_width, kvn = (int64_t)c.kv_heads * c.head_width;
+    if (c.arch == 0) {
+        head.text("general.architecture", "llama"), keys++;
+        head.u32("llama.block_count", (uint32_t)c.layers), keys++;
+        head.u32("llama.context_length", (uint32_t)c.context), keys++;
+        head.u32("llama.embedding_length", (uint32_t)c.width), keys++;
+        head.u32("llama.feed_forward_length", (uint32_t)c.hidden), keys++;
+        head.u32("llama.attention.head_count", (uint32_t)c.heads), keys++;
+        head.u32("llama.attention.head_count_kv", (uint32_t)c.kv_heads), keys++;
+        head.u32("llama.rope.dimension_count", (uint32_t)c.head_width), keys++;
+        head.u32("llama.vocab_size", (uint32_t)c.vocab), keys++;
+        head.f32("llama.rope.freq_base", (float)c.rope_theta), keys++;
+        head.f32("llama.attention.layer_norm_rms_epsilon", c.eps), keys++;
+        TSM_TRY(saved_rows(m, m->embed, "token_embd.weight", 0, c.vocab, 0, tensors));
+        if (!c.tied) TSM_TRY(saved_rows(m, m->head, "output.weight", 0, c.vocab, 0, tensors));
+        TSM_TRY(saved_vector(m, m->final_w, "output_norm.weight", c.width, tensors));
+        for (int i = 0; i < c.layers; i++) {
+            std::string p = "blk." + std::to_string(i) + ".";
+            Layer& l = m->layers[i];
+            TSM_TRY(saved_vector(m, l.norm1_w, p + "attn_norm.weight", c.width, tensors));
+            TSM_TRY(saved_vector(m, l.norm2_w, p + "ffn_norm.weight", c.width, tensors));
+            TSM_TRY(saved_rows(m, l.qkv, p + "attn_q.weight", 0, qn, c.heads, tensors));
+            TSM_TRY(saved_rows(m, l.qkv, p + "attn_k.weight", qn, kvn, c.kv_heads, tensors));
+            TSM_TRY(saved_rows(m, l.qkv, p + "attn_v.weight", qn + kvn, kvn, 0, tensors));
+            TSM_TRY(saved_rows(m, l.o, p + "attn_output.weight", 0, c.width, 0, tensors));
+            TSM_TRY(saved_rows(m, l.up, p + "ffn_gate.weight", 0, c.hidden, 0, tensors));
+            TSM_TRY(saved_rows(m, l.up, p + "ffn_up.weight", c.hidden, c.hidden, 0, tensors));
+            TSM_TRY(saved_rows(m, l.down, p + "ffn_down.weight", 0, c.width, 0, tensors));
+        }
+    } else {
+        head.text("general.architecture", "gpt2"), keys++;
+        head.text("gpt2.heads", std::to_string(c.heads)), keys++;
+        TSM_TRY(saved_rows(m, m->embed, "wte.weight", 0, c.vocab, 0, tensors));
+        TSM_TRY(saved_rows(m, m->wpe, "wpe.weight", 0, c.context, 0, tensors));
+        TSM_TRY(saved_vector(m, m->final_w, "ln_f.weight", c.width, tensors));
+        TSM_TRY(saved_vector(m, m->final_b, "ln_f.bias", c.width, tensors));
+        for (int i = 0; i < c.layers; i++) {
+            std::string p = "h." + std::to_string(i) + ".";
+            Layer& l = m->layers[i];
+            TSM_TRY(saved_vector(m, l.norm1_w, p + "ln_1.weight", c.width, tensors));
+            TSM_TRY(saved_vector(m, l.norm1_b, p + "ln_1.bias", c.width, tensors));
+            TSM_TRY(saved_vector(m, l.norm2_w, p + "ln_2.weight", c.width, tensors));
+            TSM_TRY(saved_vector(m, l.norm2_b, p + "ln_2.bias", c.width, tensors));
+            const std::pair<const Linear*, const char*> parts[] = {{&l.qkv, "attn.c_attn"}, {&l.o, "attn.c_proj"}, {&l.up, "mlp.c_fc"}, {&l.down, "mlp.c_proj"}};
+            for (auto& part : parts) {
+                TSM_TRY(saved_rows(m, *part.first, p + part.second + ".weight", 0, part.first->n, 0, tensors));
+                TSM_TRY(saved_vector(m, part.first->bias, p + part.second + ".bias", part.first->n, tensors));
+            }
+        }
+    }
+    const int64_t alignment = 32;
+    GgufWriter file;
+    file.put<uint32_t>(0x46554747u);  // "GGUF"
+    file.put<uint32_t>(3);
+    file.put<uint64_t>(tensors.size());
+    file.put<uint64_t>(keys);
+    file.bytes.insert(file.bytes.end(), head.bytes.begin(), head.bytes.end());
+    int64_t offset = 0;
+    std::vector<int64_t> offsets;
+    for (auto& t : tensors) {
+        file.str(t.name);
+        file.put<uint32_t>((uint32_t)t.shape.size());
+        for (auto d = t.shape.rbegin(); d != t.shape.rend(); ++d) file.put<uint64_t>((uint64_t)*d);  // innermost first
+        file.put<uint32_t>(t.kind);
+        file.put<uint64_t>((uint64_t)offset);
+        offsets.push_back(offset);
+        offset = (offset + (int64_t)t.bytes.size() + alignment - 1) / alignment * alignment;
+    }
+    file.bytes.resize((file.bytes.size() + alignment - 1) / alignment * alignment, 0);
+    // a temporary beside the target, renamed when whole, as GGUF.write does (gguf.cr:165-190)
+    std::string temp = std::string(path) + "." + std::to_string((long)getpid()) + ".tmp";
+    FILE* fp = fopen(temp.c_str(), "wb");
+    if (!fp) return fail(ctx, TSM_ERR_IO, "cannot write " + temp);
+    bool ok = fwrite(file.bytes.data(), 1, file.bytes.size(), fp) == file.bytes.size();
+    static const uint8_t zeros[32] = {0};
+    for (size_t i = 0; ok && i < tensors.size(); i++) {
+        const SavedTensor& t = tensors[i];
+        ok = fwrite(t.bytes.data(), 1, t.bytes.size(), fp) == t.bytes.size();
+        size_t pad = (size_t)((alignment - (int64_t)t.bytes.size() % alignment) % alignment);
+        if (ok && pad) ok = fwrite(zeros, 1, pad, fp) == pad;
+    }
+    ok = (fclose(fp) == 0) && ok;
+    if (!ok || rename(temp.c_str(), path) != 0) {
+        remove(temp.c_str());
+        return fail(ctx, TSM_ERR_IO, std::string("cannot write ") + path);
+    }
     return TSM_OK;
 }
 

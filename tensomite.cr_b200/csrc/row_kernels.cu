@@ -383,6 +383,22 @@ int launch_gelu(tsm_ctx* ctx, const float* x, int rows, int n, float* out, const
     return launch_activation(ctx, true, x, nullptr, rows, n, n, out, quantized);
 }
 
+// kernels.cr:15: x / (exp(-x) + 1), the tape's four steps each rounded on its own.
+__global__ void silu_kernel(const float* __restrict__ x, int64_t count, float* out) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float v = x[i];
+    out[i] = __fdiv_rn(v, __fadd_rn(exact_exp(-v), 1.0f));
+}
+
+int launch_silu(tsm_ctx* ctx, const float* x, int64_t count, float* out) {
+    if (count == 0) return TSM_OK;
+    silu_kernel<<<(unsigned)((count + 255) / 256), 256, 0, ctx->stream>>>(x, count, out);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t count, float* out) {
     int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count) out[i] = __fadd_rn(a[i], b[i]);

@@ -374,6 +374,12 @@ int tsm_swiglu(tsm_ctx* ctx, tsm_dptr gate, tsm_dptr up, int rows, int n, int64_
     return launch_swiglu(ctx, PCF(gate), PCF(up), rows, n, in_stride, PF(out), nullptr);
 }
 
+int tsm_silu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out) {
+    CTX_GUARD(ctx);
+    if (count < 0 || count > 0x7fffffff) return fail(ctx, TSM_ERR_ARG, "silu of more than 2^31 values");
+    return launch_silu(ctx, PCF(x), count, PF(out));
+}
+
 int tsm_gelu(tsm_ctx* ctx, tsm_dptr x, int64_t count, tsm_dptr out) {
     CTX_GUARD(ctx);
     if (count > 0x7fffffff) return fail(ctx, TSM_ERR_ARG, "gelu of more than 2^31 values");

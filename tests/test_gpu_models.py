@@ -97,6 +97,86 @@ def test_tiny_llama_f32_gguf_matches_pytorch_logits(dev, tmp_path):
     model.free()
 
 
+@pytest.mark.parametrize("name", ["q4_0", "f32"])
+def test_a_saved_llama_is_the_file_it_was_loaded_from(dev, tmp_path, name):
+    """Module#save("model.gguf"): the tensors go out under llama.cpp's names with q and k rows back in llama.cpp's order, so
+    every tensor of the reference's fixture comes back byte for byte, the metadata the loader reads is kept, and the saved
+    file loads to the same logits."""
+    g = golden()
+    path = write_golden(tmp_path, f"tiny_llama/{name}_gguf", f"model-{name}.gguf")
+    model = pkg.Llama.load(path, dev)
+    saved = str(tmp_path / "saved.gguf")
+    model.save(saved)
+    a, b = helpers.gguf.File(path), helpers.gguf.File(saved)
+    assert sorted(a.entries) == sorted(b.entries)
+    for tensor in a.entries:
+        ka, sa, ra = a.raw(tensor)
+        kb, sb, rb = b.raw(tensor)
+        assert ka == kb and list(sa) == list(sb) and ra.tobytes() == rb.tobytes(), tensor
+    for key, value in b.metadata.items():
+        assert a.metadata[key] == pytest.approx(value), key
+    again = pkg.Llama.load(saved, dev)
+    assert again.config == model.config
+    prompt = g["tiny_llama/prompt_ids"].tolist()
+    want = model.forward([prompt], model.new_batch_cache(1, 64))
+    assert np.array_equal(bits(again.forward([prompt], again.new_batch_cache(1, 64))), bits(want))
+    model.free(), again.free()
+
+
+def test_a_gpt2_quantised_on_the_device_saves_ggmls_bytes(dev, tmp_path):
+    """model.quantize(Q8_0, embeddings: true).save("model.gguf") (module.cr:154-156): the file holds the bytes of the
+    oracle's quantiser under tensomite's names and loads to the same logits."""
+    g = golden()
+    path = tmp_path / "model.safetensors"
+    path.write_bytes(g["tiny_gpt2/safetensors"].tobytes())
+    st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+    model = pkg.GPT2.load_safetensors(path, dev, dict(arch="gpt2", heads=4), pkg.Q8_0)
+    saved = str(tmp_path / "saved.gguf")
+    model.save(saved)
+    want_path = str(tmp_path / "want.gguf")
+    helpers.write_gpt2_gguf(want_path, st, 2, 4, oracle.Q8_0)
+    a, b = helpers.gguf.File(want_path), helpers.gguf.File(saved)
+    assert sorted(a.entries) == sorted(b.entries)
+    for tensor in a.entries:
+        ka, sa, ra = a.raw(tensor)
+        kb, sb, rb = b.raw(tensor)
+        assert ka == kb and list(sa) == list(sb) and ra.tobytes() == rb.tobytes(), tensor
+    assert b.metadata["gpt2.heads"] == "4"
+    again = pkg.GPT2.load(saved, dev)
+    prompt = g["tiny_gpt2/prompt_ids"].tolist()
+    want = model.forward([prompt], model.new_batch_cache(1, 64))
+    assert np.array_equal(bits(again.forward([prompt], again.new_batch_cache(1, 64))), bits(want))
+    model.free(), again.free()
+
+
+@pytest.mark.parametrize("half", ["F16", "BF16"])
+def test_tiny_llama_gguf_with_half_matrices_is_widened(dev, tmp_path, half):
+    """gguf.cr:112-136: F16 / BF16 tensors widen to F32 at load; the model then runs as the F32 one over the widened values."""
+    g = golden()
+    gg = helpers.gguf
+    src = gg.File(write_golden(tmp_path, "tiny_llama/f32_gguf", "model.gguf"))
+    tensors = []
+    for name, (kind, shape, _) in src.entries.items():
+        values = src.f32(name)
+        if len(shape) == 2:
+            if half == "F16":
+                tensors.append((name, gg.F16, list(shape), values.astype(np.float16)))
+            else:
+                tensors.append((name, gg.BF16, list(shape), (values.view(np.uint32) >> 16).astype(np.uint16)))
+        else:
+            tensors.append((name, gg.F32, list(shape), values))
+    path = str(tmp_path / f"model-{half}.gguf")
+    gg.write(path, {k: v for k, v in src.metadata.items() if not isinstance(v, list)}, tensors)  # the tokeniser's lists are not needed
+    ref = helpers.oracle_llama(path)
+    model = pkg.Llama.load(path, dev)
+    assert model.tensor("0.down")[1] == pkg.F32
+    prompt = g["tiny_llama/prompt_ids"].tolist()
+    want = ref.forward(ref.new_cache(1, 64), [prompt], last=False)
+    check(pkg.EXACT, model.forward([prompt], model.new_batch_cache(1, 64)), want)
+    assert model.generate(prompt, 12) == ref.generate(prompt, 12)
+    model.free()
+
+
 def test_tiny_gpt2_f32_safetensors_matches_pytorch_logits(dev, tmp_path):
     """spec/gpt2_spec.cr:54-102 on the device: GPT2.load("model.safetensors") kept in F32."""
     g = golden()

@@ -195,6 +195,7 @@ def test_activations_are_bit_exact(dev):
     up = rng.normal(0, 1, gate.shape).astype(np.float32)
     assert np.array_equal(bits(dev.swiglu(gate, up)), bits(oracle.swiglu(gate, up)))
     assert np.array_equal(bits(dev.gelu(gate)), bits(oracle.gelu(gate)))
+    assert np.array_equal(bits(dev.silu(gate)), bits(oracle.silu(gate)))
     assert np.array_equal(bits(dev.add(gate, up)), bits(gate + up))
 
 
