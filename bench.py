@@ -520,7 +520,7 @@ def main():
         if world == 1 and not args.no_cpu:
             refill(cache, lengths, rank)
             dev.sync()
-            sample_rows, sample_steps = min(rows, 4), 2
+            sample_rows, sample_steps = min(rows, 4), 5   # about 10 s of host work at the headline shape
             arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, sample_steps + 1)
             arm.step()  # warm-up: threads start, pages are touched
             cpu_seconds = sum(arm.step() for _ in range(sample_steps))
