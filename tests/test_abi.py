@@ -54,3 +54,22 @@ def test_unpermute_order_inverts_llama_cpps_rotary_layout():
     # models/llama.cr:226-235: loaded row head*hw + pair*(hw/2) + i = stored row head*hw + 2i + pair
     order = helpers.unpermute_order(16, 2)
     assert order[:8] == [0, 2, 4, 6, 1, 3, 5, 7] and order[8:] == [8, 10, 12, 14, 9, 11, 13, 15]
+
+
+def test_the_crystal_stub_binds_every_entry_point():
+    """INTEGRATION.md's `lib LibTSM` is what a maintainer copies: every function the header declares has its `fun` line,
+    with as many arguments as the C declaration."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "tsm_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    stub = open(os.path.join(root, "INTEGRATION.md")).read()
+    declared = {name: args for name, args in re.findall(r"\b(tsm_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header)}
+    assert set(declared) == set(pkg.declared_symbols())
+    for name, args in declared.items():
+        found = re.search(r"fun \w+ = " + name + r"\(([^)]*)\)", stub)
+        assert found, f"{name} has no fun line in INTEGRATION.md"
+        want = 0 if args.strip() in ("", "void") else args.count(",") + 1
+        got = 0 if not found.group(1).strip() else found.group(1).count(",") + 1
+        assert want == got, (name, want, got)
