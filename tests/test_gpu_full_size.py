@@ -47,6 +47,48 @@ def test_products_of_the_headline_model(dev, n, k):
     wb.free()
 
 
+def random_blocks(rng, kind, n, k):
+    """n rows of k/32 ggml blocks of `kind` with random payload bytes (every int8 and nibble value occurs) under F16 scales
+    (and, for Q4_1, minima) of the size N(0, 0.02) weights give."""
+    count = n * (k // 32)
+    size = oracle.BLOCK_BYTES[kind]
+    blocks = rng.integers(0, 256, size=(count, size), dtype=np.uint8)
+    scales = rng.uniform(0.0002 if kind == oracle.Q8_0 else 0.004, 0.0006 if kind == oracle.Q8_0 else 0.012, count).astype(np.float16)
+    blocks[:, 0:2] = scales.view(np.uint8).reshape(-1, 2)
+    if kind == oracle.Q4_1:
+        minima = rng.uniform(-0.08, -0.02, count).astype(np.float16)
+        blocks[:, 2:4] = minima.view(np.uint8).reshape(-1, 2)
+    return blocks.reshape(n, (k // 32) * size)
+
+
+# The products of the baseline's other configurations, with the rows they run at: 135M-shaped Q8_0 and GPT-2-XL-shaped Q8_0
+# (with biases) at one row, 1.7B-shaped Q4_1 at sixteen.
+OTHER_PRODUCTS = [("Q8_0", 1, 960, 576, False), ("Q8_0", 1, 576, 576, False), ("Q8_0", 1, 3072, 576, False), ("Q8_0", 1, 576, 1536, False),
+                  ("Q8_0", 1, 49152, 576, False),
+                  ("Q4_1", 16, 6144, 2048, False), ("Q4_1", 16, 2048, 2048, False), ("Q4_1", 16, 16384, 2048, False),
+                  ("Q4_1", 16, 2048, 8192, False), ("Q4_1", 16, 49152, 2048, False),
+                  ("Q8_0", 1, 4800, 1600, True), ("Q8_0", 1, 1600, 1600, True), ("Q8_0", 1, 6400, 1600, True), ("Q8_0", 1, 1600, 6400, True),
+                  ("Q8_0", 1, 50257, 1600, False)]
+
+
+@pytest.mark.parametrize("name,rows,n,k,with_bias", OTHER_PRODUCTS)
+def test_products_of_the_other_configurations(dev, name, rows, n, k, with_bias):
+    kind = oracle.KIND_NAMES[name]
+    rng = np.random.default_rng(n * 7 + k)
+    w = random_blocks(rng, kind, n, k)
+    x = rng.normal(0, 1, (rows, k)).astype(np.float32)
+    bias = rng.normal(0, 0.1, n).astype(np.float32) if with_bias else None
+    wb = dev.tensor(w)
+    got = dev.block_matmul(x, wb, kind, n, bias)
+    sample = np.unique(np.concatenate([[0, 1, n - 2, n - 1], rng.integers(0, n, 124)]))
+    want = oracle.matmul_reference(kind, x, np.ascontiguousarray(w[sample]), len(sample), bias=bias[sample] if with_bias else None)
+    assert np.array_equal(bits(got[:, sample]), bits(want))
+    if rows > 1:
+        alone = dev.block_matmul(x[rows - 1:rows], wb, kind, n, bias)
+        assert np.array_equal(bits(alone[0]), bits(got[rows - 1]))
+    wb.free()
+
+
 def uniform_fill(rng, shape):
     values = rng.random(shape, dtype=np.float32)
     values *= 2.0
@@ -75,3 +117,24 @@ def test_attention_of_the_headline_step(dev):
     for t in (3, 40):  # one token alone is cut into position ranges and quarters of the width: the same bits
         alone = dev.ragged_attention(q[t:t + 1], k, v, table[t:t + 1], scale)
         assert np.array_equal(bits(alone[0]), bits(got[t])), t
+
+
+@pytest.mark.parametrize("streams,heads,kv_heads,capacity,low,high", [(1, 25, 25, 1024, 576, 576),    # GPT-2-XL-shaped, one stream
+                                                                      (16, 32, 32, 512, 128, 384),   # 1.7B-shaped, sixteen streams
+                                                                      (1, 9, 3, 256, 160, 160)])     # 135M-shaped, one stream
+def test_attention_of_the_other_configurations(dev, streams, heads, kv_heads, capacity, low, high):
+    """Heads of width 64 at the baseline's other shapes: every output against the oracle."""
+    rng = np.random.default_rng(streams * 100 + heads)
+    width, group = 64, heads // kv_heads
+    lengths = rng.integers(low, high + 1, streams)
+    k = uniform_fill(rng, (streams, kv_heads, capacity, width))
+    v = uniform_fill(rng, (streams, kv_heads, capacity, width))
+    q = rng.normal(0, 1, (streams, heads, width)).astype(np.float32)
+    table = np.array([[row, length - 1, length] for row, length in enumerate(lengths)], dtype=np.int32)
+    scale = np.float32(1.0 / np.sqrt(width))
+    got = dev.ragged_attention(q, k, v, table, scale)
+    for t in range(streams):
+        held = int(lengths[t])
+        for h in range(heads):
+            want = oracle.attend(q[t, h], k[t, h // group, :held], v[t, h // group, :held], scale)
+            assert np.array_equal(bits(got[t, h]), bits(want)), (t, h, held)
