@@ -522,9 +522,27 @@ def main():
             dev.sync()
             sample_rows, sample_steps = min(rows, 4), 5   # about 10 s of host work at the headline shape
             arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, sample_steps + 1)
+            cpu_tokens = []
             arm.step()  # warm-up: threads start, pages are touched
-            cpu_seconds = sum(arm.step() for _ in range(sample_steps))
+            cpu_tokens.append(list(arm.tokens))
+            cpu_seconds = 0.0
+            for _ in range(sample_steps):
+                cpu_seconds += arm.step()
+                cpu_tokens.append(list(arm.tokens))
             rate = sample_rows * sample_steps / cpu_seconds
+            # The same steps on the device from the same caches and first tokens: the sampled streams' greedy tokens must be the
+            # CPU path's, step for step (rows are independent, so the other 60 streams do not matter).
+            try:
+                refill(cache, lengths, rank)
+                dev.sync()
+                step_ids, gpu_tokens = ids.copy(), []
+                for _ in range(sample_steps + 1):
+                    step_ids = model.decode(cache, step_ids)
+                    gpu_tokens.append([int(t) for t in step_ids[:sample_rows]])
+                line["parity"] = dict(streams=sample_rows, steps=sample_steps + 1, identical_tokens=gpu_tokens == cpu_tokens,
+                                      against="the CPU oracle's greedy tokens for the sampled streams at this workload's full size")
+            except Exception as problem:  # the check must never cost the bench its line
+                line["parity"] = dict(error=str(problem))
             line["cpu_baseline"] = dict(value=rate, unit="tokens/s", cores=threads, kind="port",
                                         sample=f"{sample_rows} of {rows} streams x {sample_steps} decode steps, {cpu_seconds:.1f} s, "
                                                f"oracle's threaded product on {threads} threads, other host ops on one thread")
