@@ -11,7 +11,8 @@ positions and the device->host copy of the picked tokens inside every step.  Wit
 its own 64 streams on a full replica (no collective), so the job is 64*N streams ("weak").
 
 Also on the line: `roofline` of the dominant kernel timed alone with CUDA events on the same buffers,
-`cpu_baseline` (rank 0, N = 1: the CPU oracle's threaded decode on a bounded sample), `extra` with the
+`cpu_baseline` (rank 0, N = 1: the CPU oracle's threaded decode on a bounded sample), `parity` (the same sampled streams
+decoded on the device from the same caches and first tokens: are their greedy tokens the CPU's), `extra` with the
 batch-1 numbers (135M-shaped Q8_0 model; matvec GB/s per shape and format), clocks, launch counts.
 
 `--impl reference` times the CPU restatement of the reference's threaded decode (oracle/) on the host
