@@ -374,42 +374,47 @@ int load_gguf_model(tsm_model* m, const char* path) {
 // the loader undoes, llama.cr:226-235), the joined projections cut back into their parts; a GPT-2 under tensomite's own
 // names with gpt2.heads.  Either file loads again here and in the reference.
 
+// One tensor of the file to be written: where its bytes are on the device.  The bytes are fetched when the tensor's turn
+// to be written comes, so the host never holds more than the largest tensor.
 struct SavedTensor {
     std::string name;
     uint32_t kind;               // GGUF's type number
     std::vector<int64_t> shape;  // outermost first
-    std::vector<uint8_t> bytes;
+    const uint8_t* source;       // device address
+    int64_t size;                // bytes
+    int64_t row_bytes;
+    int heads;                   // > 0: rows go back into llama.cpp's rotary order for this many heads
 };
 
 static uint32_t gguf_kind_of(int kind) { return kind == TSM_Q8_0 ? 8 : kind == TSM_Q4_0 ? 2 : kind == TSM_Q4_1 ? 3 : 0; }
 
-// Rows [first, first + rows) of a weight, downloaded; heads > 0 puts them back into llama.cpp's rotary order.
+// Rows [first, first + rows) of a weight; heads > 0 puts them back into llama.cpp's rotary order.
 static int saved_rows(tsm_model* m, const Linear& l, const std::string& name, int64_t first, int64_t rows, int heads, std::vector<SavedTensor>& out) {
-    SavedTensor t;
-    t.name = name, t.kind = gguf_kind_of(l.kind), t.shape = {rows, (int64_t)l.k};
+    (void)m;
     int64_t row_bytes = weight_bytes(l.kind, 1, l.k);
-    t.bytes.resize((size_t)(rows * row_bytes));
-    TSM_TRY(tsm_download(m->ctx, t.bytes.data(), (tsm_dptr)(uintptr_t)(l.w + first * row_bytes), rows * row_bytes));
-    if (heads > 0) {
-        std::vector<uint8_t> file((size_t)(rows * row_bytes));
-        int64_t half = rows / heads / 2, held = 0;
-        for (int head = 0; head < heads; head++)
-            for (int pair = 0; pair < 2; pair++)
-                for (int64_t i = 0; i < half; i++, held++)
-                    memcpy(&file[(size_t)((head * 2 * half + 2 * i + pair) * row_bytes)], &t.bytes[(size_t)(held * row_bytes)], (size_t)row_bytes);
-        t.bytes.swap(file);
-    }
-    out.push_back(std::move(t));
+    out.push_back(SavedTensor{name, gguf_kind_of(l.kind), {rows, (int64_t)l.k}, l.w + first * row_bytes, rows * row_bytes, row_bytes, heads});
     return TSM_OK;
 }
 
 static int saved_vector(tsm_model* m, const float* values, const std::string& name, int64_t count, std::vector<SavedTensor>& out) {
-    if (!values) return TSM_OK;
-    SavedTensor t;
-    t.name = name, t.kind = 0, t.shape = {count};
-    t.bytes.resize((size_t)count * 4);
-    TSM_TRY(tsm_download(m->ctx, t.bytes.data(), (tsm_dptr)(uintptr_t)values, count * 4));
-    out.push_back(std::move(t));
+    (void)m;
+    if (values) out.push_back(SavedTensor{name, 0, {count}, (const uint8_t*)values, count * 4, count * 4, 0});
+    return TSM_OK;
+}
+
+// Downloads a tensor's bytes in the order the file holds them.
+static int fetch_saved(tsm_model* m, const SavedTensor& t, std::vector<uint8_t>& bytes) {
+    bytes.resize((size_t)t.size);
+    TSM_TRY(tsm_download(m->ctx, bytes.data(), (tsm_dptr)(uintptr_t)t.source, t.size));
+    if (t.heads > 0) {
+        std::vector<uint8_t> file((size_t)t.size);
+        int64_t rows = t.size / t.row_bytes, half = rows / t.heads / 2, held = 0;
+        for (int head = 0; head < t.heads; head++)
+            for (int pair = 0; pair < 2; pair++)
+                for (int64_t i = 0; i < half; i++, held++)
+                    memcpy(&file[(size_t)((head * 2 * half + 2 * i + pair) * t.row_bytes)], &bytes[(size_t)(held * t.row_bytes)], (size_t)t.row_bytes);
+        bytes.swap(file);
+    }
     return TSM_OK;
 }
 
@@ -495,15 +500,13 @@ int save_gguf_model(tsm_model* m, const char* path) {
     file.put<uint64_t>(keys);
     file.bytes.insert(file.bytes.end(), head.bytes.begin(), head.bytes.end());
     int64_t offset = 0;
-    std::vector<int64_t> offsets;
     for (auto& t : tensors) {
         file.str(t.name);
         file.put<uint32_t>((uint32_t)t.shape.size());
         for (auto d = t.shape.rbegin(); d != t.shape.rend(); ++d) file.put<uint64_t>((uint64_t)*d);  // innermost first
         file.put<uint32_t>(t.kind);
         file.put<uint64_t>((uint64_t)offset);
-        offsets.push_back(offset);
-        offset = (offset + (int64_t)t.bytes.size() + alignment - 1) / alignment * alignment;
+        offset = (offset + t.size + alignment - 1) / alignment * alignment;
     }
     file.bytes.resize((file.bytes.size() + alignment - 1) / alignment * alignment, 0);
     // a temporary beside the target, renamed when whole, as GGUF.write does (gguf.cr:165-190)
@@ -512,13 +515,20 @@ int save_gguf_model(tsm_model* m, const char* path) {
     if (!fp) return fail(ctx, TSM_ERR_IO, "cannot write " + temp);
     bool ok = fwrite(file.bytes.data(), 1, file.bytes.size(), fp) == file.bytes.size();
     static const uint8_t zeros[32] = {0};
+    std::vector<uint8_t> bytes;
+    int fetched = TSM_OK;
     for (size_t i = 0; ok && i < tensors.size(); i++) {
         const SavedTensor& t = tensors[i];
-        ok = fwrite(t.bytes.data(), 1, t.bytes.size(), fp) == t.bytes.size();
-        size_t pad = (size_t)((alignment - (int64_t)t.bytes.size() % alignment) % alignment);
+        if ((fetched = fetch_saved(m, t, bytes)) != TSM_OK) break;
+        ok = fwrite(bytes.data(), 1, bytes.size(), fp) == bytes.size();
+        size_t pad = (size_t)((alignment - t.size % alignment) % alignment);
         if (ok && pad) ok = fwrite(zeros, 1, pad, fp) == pad;
     }
     ok = (fclose(fp) == 0) && ok;
+    if (fetched != TSM_OK) {
+        remove(temp.c_str());
+        return fetched;
+    }
     if (!ok || rename(temp.c_str(), path) != 0) {
         remove(temp.c_str());
         return fail(ctx, TSM_ERR_IO, std::string("cannot write ") + path);
