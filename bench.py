@@ -7,13 +7,19 @@ streams whose F32 KV caches hold ragged lengths drawn uniformly from 128..4096 (
 seeded N(0,1) values.  A step is one greedy decode step of all 64 streams.  `value` is tokens/s with the
 step loop resident on the device (`tsm_decode_run`: each step's picks feed the next on the device);
 `e2e` is tokens/s through `tsm_decode` with host token buffers, the host->device copy of ids and
-positions and the device->host copy of the picked tokens inside every step.  With N > 1 every rank runs
-its own 64 streams on a full replica (no collective), so the job is 64*N streams ("weak").
+positions and the device->host copy of the picked tokens inside every step.
+
+With N > 1 the N ranks share ONE model, split by tensor parallelism, and decode the same 64 streams: the job's work is
+fixed ("strong"), which is the scaling the baseline asks of this configuration.  `--parallelism dp` runs a replica and its
+own 64 streams per rank instead (no collective, "weak").  At N > 1 `extra.c3_dp` also times the baseline's data-parallel
+configuration (the 1.7B-shaped Q4_1 model, its 16 streams split over the ranks) and `parity.tp_tokens_identical` compares
+the group's greedy tokens with those of the whole model on one GPU.
 
 Also on the line: `roofline` of the dominant kernel timed alone with CUDA events on the same buffers,
 `cpu_baseline` (rank 0, N = 1: the CPU oracle's threaded decode on a bounded sample), `parity` (the same sampled streams
 decoded on the device from the same caches and first tokens: are their greedy tokens the CPU's), `extra` with the
-batch-1 numbers (135M-shaped Q8_0 model; matvec GB/s per shape and format), clocks, launch counts.
+batch-1 models, the format x shape x columns sweep of the products (GB/s per kernel), prefill and load figures, the fast
+mode's cost and error, clocks, launch counts.
 
 `--impl reference` times the CPU restatement of the reference's threaded decode (oracle/) on the host
 cores for the same workload; Crystal is not installed, so the reference's own binary cannot be built.
@@ -174,12 +180,18 @@ def time_kernel(torch, stream, fn, repeats):
     return start.elapsed_time(stop) / repeats / 1e3
 
 
-def matvec_sweep(pkg, dev, torch, stream, peak):
-    """Batch-1 quantised products of the baseline's shapes: GB/s of algorithmic bytes, timed alone.
-    Between launches a 512 MB buffer is rewritten so that no weight is served from L2."""
+def product_sweep(pkg, dev, torch, stream, peak):
+    """The baseline's standalone sweep: Q4_0 / Q4_1 / Q8_0 x five shapes x 1, 8, 64 and 256 activation columns (rows of x),
+    each product timed alone on already-quantised activations: GB/s of algorithmic bytes per kernel.  Between launches a
+    512 MB buffer is rewritten so that no weight is served from L2 (its time is measured alone and taken out)."""
     import ctypes as C
     shapes = [(576, 1536), (2048, 8192), (4096, 14336), (14336, 4096), (128256, 4096)]
     flush = dev.alloc(512 << 20)
+
+    def flush_l2():
+        dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(flush.ptr), C.c_int64((512 << 20) // 4), C.c_float(0.0), C.c_float(1.0), C.c_uint64(1))
+
+    only = time_kernel(torch, stream, flush_l2, 5)
     out = []
     for name, kind in KIND.items():
         for n, k in shapes:
@@ -193,28 +205,26 @@ def matvec_sweep(pkg, dev, torch, stream, peak):
                                                   C.c_uint64(n * 31 + r0)), "tsm_fill_normal")
                 dev.check(dev.lib.tsm_quantize_blocks(dev.ctx, C.c_uint64(src.ptr), C.c_int64(rows * k), C.c_int(kind),
                                                       C.c_uint64(wbuf.ptr + r0 * (k // 32) * BLOCK[kind])), "tsm_quantize_blocks")
-            x = dev.tensor(np.random.default_rng(5).normal(0, 1, (1, k)).astype(np.float32))
-            scales, sums, qs, y = dev.alloc(k // 32 * 4), dev.alloc(k // 32 * 4), dev.alloc(k), dev.alloc(n * 4)
-            dev.check(dev.lib.tsm_quantize_rows_q8(dev.ctx, C.c_uint64(x.ptr), 1, k, C.c_int64(k), C.c_uint64(scales.ptr),
-                                                   C.c_uint64(sums.ptr), C.c_uint64(qs.ptr)), "tsm_quantize_rows_q8")
+            src.free()
+            for columns in (1, 8, 64, 256):
+                x = dev.tensor(np.random.default_rng(5).normal(0, 1, (columns, k)).astype(np.float32))
+                scales, sums, qs, y = (dev.alloc(columns * (k // 32) * 4), dev.alloc(columns * (k // 32) * 4), dev.alloc(columns * k),
+                                       dev.alloc(columns * n * 4))
+                dev.check(dev.lib.tsm_quantize_rows_q8(dev.ctx, C.c_uint64(x.ptr), columns, k, C.c_int64(k), C.c_uint64(scales.ptr),
+                                                       C.c_uint64(sums.ptr), C.c_uint64(qs.ptr)), "tsm_quantize_rows_q8")
 
-            def run():
-                dev.lib.tsm_block_matmul_quantized(dev.ctx, C.c_uint64(scales.ptr), C.c_uint64(sums.ptr), C.c_uint64(qs.ptr), 1, k,
-                                                   C.c_uint64(wbuf.ptr), kind, n, C.c_uint64(0), C.c_uint64(y.ptr))
+                def run():
+                    dev.lib.tsm_block_matmul_quantized(dev.ctx, C.c_uint64(scales.ptr), C.c_uint64(sums.ptr), C.c_uint64(qs.ptr), columns, k,
+                                                       C.c_uint64(wbuf.ptr), kind, n, C.c_uint64(0), C.c_uint64(y.ptr))
 
-            def flush_l2():
-                dev.lib.tsm_fill_normal(dev.ctx, C.c_uint64(flush.ptr), C.c_int64((512 << 20) // 4), C.c_float(0.0), C.c_float(1.0),
-                                        C.c_uint64(1))
-
-            # time (flush + product) and (flush) alone, so the flush is taken out of the figure
-            both = time_kernel(torch, stream, lambda: (flush_l2(), run()), 5)
-            only = time_kernel(torch, stream, flush_l2, 5)
-            seconds = max(both - only, 1e-9)
-            algorithmic = blocks * BLOCK[kind] + k * 4 + n * 4
-            out.append(dict(kind=name, n=n, k=k, us=round(seconds * 1e6, 2), gbs=round(algorithmic / seconds / 1e9, 1),
-                            frac=round(algorithmic / seconds / 1e9 / peak, 3)))
-            for b in (wbuf, src, x, scales, sums, qs, y):
-                b.free()
+                both = time_kernel(torch, stream, lambda: (flush_l2(), run()), 5)
+                seconds = max(both - only, 1e-9)
+                algorithmic = blocks * BLOCK[kind] + columns * k * 4 + columns * n * 4
+                out.append(dict(kind=name, n=n, k=k, columns=columns, us=round(seconds * 1e6, 2), gbs=round(algorithmic / seconds / 1e9, 1),
+                                frac=round(algorithmic / seconds / 1e9 / peak, 3)))
+                for b in (x, scales, sums, qs, y):
+                    b.free()
+            wbuf.free()
     flush.free()
     dev.sync()
     return out
@@ -299,66 +309,129 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
                 frac=algorithmic / seconds / 1e9 / peak)
 
 
-def oracle_model_from_device(model, threads):
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    from tests import helpers
-    return helpers.oracle_from_device_model(model, threads=threads)
+def pick_sample(lengths, count=2):
+    """The streams whose cached lengths bracket the workload's mean: the nearest below it and the nearest above (then the
+    next nearest, alternately).  The CPU legs decode these, so that their tokens/s is that of a stream of average length."""
+    lengths = np.asarray(lengths)
+    mean = float(lengths.mean())
+    below = sorted((i for i in range(len(lengths)) if lengths[i] <= mean), key=lambda i: mean - lengths[i])
+    above = sorted((i for i in range(len(lengths)) if lengths[i] > mean), key=lambda i: lengths[i] - mean)
+    order = [i for pair in zip(below, above) for i in pair] + below[len(above):] + above[len(below):]
+    return sorted(order[:min(count, len(order))])
 
 
 class CpuArm:
-    """The CPU oracle's threaded decode over the first `sample_rows` streams of the device workload: same
-    weights (downloaded once through the C ABI), same KV contents, same first tokens."""
+    """The CPU oracle's threaded decode over the streams `rows` of the device workload: same weights (downloaded once
+    through the C ABI), same KV contents, same first tokens."""
 
-    def __init__(self, pkg, model, cache, lengths, ids, threads, sample_rows, budget_steps):
-        self.ref = oracle_model_from_device(model, threads)
-        self.rows = sample_rows
-        self.rcache = self.ref.new_cache(sample_rows, int(max(lengths[:sample_rows])) + budget_steps + 2)
-        c = model.config
-        row_floats = c["kv_heads"] * cache.capacity * c["head_width"]
-        for layer in range(c["layers"]):
-            kb, vb = cache.layer(layer)
-            for row in range(sample_rows):
-                n = int(lengths[row])
-                for src, dst in ((kb, self.rcache.keys[layer]), (vb, self.rcache.values[layer])):
-                    part = pkg.Buffer(model.device, src.ptr + row * row_floats * 4, row_floats * 4).numpy(np.float32)
-                    dst[row, :, :n, :] = part.reshape(c["kv_heads"], cache.capacity, c["head_width"])[:, :n, :]
-        for row in range(sample_rows):
-            self.rcache.lengths[row] = int(lengths[row])
-        self.tokens = [int(t) for t in ids[:sample_rows]]
+    def __init__(self, pkg, model, cache, lengths, ids, threads, rows, budget_steps):
+        from oracle import oracle   # the checker and the CPU baseline: the only use of oracle/ in this file
+        self.oracle = oracle
+        self.ref = oracle.model_from_device(model, threads=threads)
+        self.rows = list(rows)
+        held = [int(lengths[r]) for r in self.rows]
+        self.rcache = oracle.cache_from_device(self.ref, model, cache, self.rows, held, max(held) + budget_steps + 2)
+        self.tokens = [int(ids[r]) for r in self.rows]
+        self.logits = None
 
     def step(self):
         """One greedy decode step of the sample's streams; returns seconds."""
         start = time.perf_counter()
-        logits = self.ref.forward(self.rcache, [[t] for t in self.tokens])
-        self.tokens = [int(np.argmax(r)) for r in logits]
+        self.logits = self.ref.forward(self.rcache, [[t] for t in self.tokens])
+        self.tokens = [self.oracle.argmax_first(r) for r in self.logits]
         return time.perf_counter() - start
+
+
+def kl_per_token(want, got):
+    """Mean KL(softmax(want) || softmax(got)) in nats per row."""
+    def log_softmax(x):
+        x = x.astype(np.float64)
+        x = x - x.max(axis=-1, keepdims=True)
+        return x - np.log(np.exp(x).sum(axis=-1, keepdims=True))
+    lw, lg = log_softmax(want), log_softmax(got)
+    return float((np.exp(lw) * (lw - lg)).sum(axis=-1).mean())
+
+
+def load_traffic():
+    """DRAM bytes (read + written) of one launch of the dominant kernels, from the profiler captures summarised under
+    profiles/ (profiles/traffic.json names the commit, the case and the command of each)."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        return json.load(open(path))
+    except Exception:
+        return {}
+
+
+def batch1_model(pkg, dev, torch, stream, w, seed, tokens, peak):
+    """A batch-1 configuration: prompt through the packed step, then `tokens` greedy steps resident on the device."""
+    m = pkg.Model.random(dev, model_config(w), KIND[w["kind"]], seed=seed)
+    prompt = np.random.default_rng(7).integers(0, w["vocab"], size=w["len_lo"]).astype(np.int32)
+    cache = m.new_batch_cache(1, w["len_lo"] + tokens + 16)
+    first = np.argmax(m.forward_last([prompt.tolist()], cache), axis=1).astype(np.int32)
+    first = m.decode_run(cache, first, 4)[-1]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(stream)
+    m.decode_run(cache, first, tokens)
+    stop.record(stream)
+    stop.synchronize()
+    seconds = start.elapsed_time(stop) / 1e3 / tokens
+    nbytes, _, _ = step_bytes(w, np.array([w["len_lo"] + 4 + tokens // 2]))
+    cache.free(), m.free()
+    return dict(workload=w["name"], tokens_per_second=1 / seconds, us_per_token=seconds * 1e6, bytes_per_token=nbytes,
+                frac_of_hbm=nbytes / seconds / 1e9 / peak)
+
+
+def prefill_rate(pkg, dev, torch, stream, model, rows, prompt_tokens, vocab):
+    """Tokens/s of a packed prefill: `rows` streams of `prompt_tokens` seeded tokens each through one tsm_forward."""
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, vocab, size=prompt_tokens).tolist() for _ in range(rows)]
+    cache = model.new_batch_cache(rows, prompt_tokens + 8)
+    model.forward_last(prompts, cache)   # warm-up: sizes the workspace
+    best = None
+    for _ in range(2):
+        for row in range(rows):
+            cache.reset(row)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        model.forward_last(prompts, cache)
+        stop.record(stream)
+        stop.synchronize()
+        seconds = start.elapsed_time(stop) / 1e3
+        best = seconds if best is None else min(best, seconds)
+    cache.free()
+    return dict(streams=rows, prompt_tokens=prompt_tokens, ms=best * 1e3, tokens_per_second=rows * prompt_tokens / best)
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 model and the matvec sweep")
+    ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 models, the product sweep, prefill, load and fast-mode figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp", "tp_reduce"],
-                    help="with --gpus N > 1: dp = every rank decodes its own streams on a whole replica (no collective); "
-                         "tp = the ranks share one model split by tensor parallelism (NCCL all-gathers, the bits of one GPU) and decode "
-                         "the same streams; tp_reduce = the same with o and down split by input columns and all-reduced (not bit-exact)")
+    ap.add_argument("--parallelism", default="auto", choices=["auto", "dp", "tp", "tp_reduce"],
+                    help="with --gpus N > 1: tp_reduce (auto) = the ranks share one model split by tensor parallelism with o and down over "
+                         "input columns and their partial sums exchanged (the split the baseline names; not bit-exact) and decode the "
+                         "same streams; tp = every projection split by output rows with all-gathers (the bits of one GPU); "
+                         "dp = every rank decodes its own streams on a whole replica (no collective)")
     ap.add_argument("--mode", default="exact", choices=["exact", "fast"],
                     help="exact (default): the CPU path's bits; fast: tree sums and split-K attention, held to the reference's GPU budget "
                          "of 0.001 nats KL per token, not to its bits")
     ap.add_argument("--case", default=None, help="time one kernel on a small case instead (see kernel_case), e.g. matvec,q4_0,128256,4096")
     ap.add_argument("--repeats", type=int, default=3, help="timed launches of --case")
+    ap.add_argument("--parity-steps", type=int, default=6,
+                    help="greedy steps over which the sampled streams are compared with the CPU oracle (N = 1); 128 is the whole generation")
+    ap.add_argument("--profile", action="store_true", help="also print (to stderr) the per-operator GPU time of one decode step")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     w = dict(WORKLOADS[args.workload])
-    K, W = args.steps, max(args.warmup, 0)
+    K, W = max(args.steps, 1), max(args.warmup, 0)
     threads = os.cpu_count() or 1
+    parallelism = args.parallelism if args.parallelism != "auto" else "tp_reduce"
 
     if args.impl == "reference" and rank != 0:
         return
@@ -378,36 +451,43 @@ def main():
         print(json.dumps(kernel_case(pkg, dev, torch, stream, args.case, args.repeats, peak["hbm_gbs"])))
         dev.close()
         return
-    tp = world if (args.parallelism != "dp" and args.impl == "ours") else 1
+    tp = world if (parallelism != "dp" and args.impl == "ours") else 1
     if tp > 1:
         pkg.groups.join_tensor_parallel(dev, dist)
-        if args.parallelism == "tp_reduce":
+        if parallelism == "tp_reduce":
             dev.tp_variant(pkg.TP_REDUCE)
     data_rank = 0 if tp > 1 else rank          # tensor-parallel ranks decode the same streams
     jobs = 1 if tp > 1 else world              # independent sets of streams in the job
     lengths = draw_lengths(w, data_rank)
+    load_start = time.perf_counter()
     model = pkg.Model.random(dev, model_config(w), KIND[w["kind"]], seed=20260101)
     dev.sync()
+    draw_seconds = time.perf_counter() - load_start
     rows = w["rows"]
-    config = dict(workload=w["name"], streams_per_gpu=rows, kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
+    config = dict(workload=w["name"], streams_per_gpu=rows if tp == 1 else f"{rows} shared by the {world} ranks",
+                  kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
                   kv_dtype="f32", weights=w["kind"], mode=args.mode, l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
-                  parallelism=((f"tp{world}: projections split by output rows, 4 NCCL all-gathers per layer" if args.parallelism == "tp" else
-                                f"tp{world}: o and down split by input columns, 2 NCCL all-reduces per layer (not bit-exact)") if tp > 1 else
+                  parallelism=((f"tp{world}: projections split by output rows, NCCL all-gathers between them (the bits of one GPU)" if parallelism == "tp" else
+                                f"tp{world}: q/k/v, gate/up and the head split by output rows, o and down by input columns with their partial "
+                                f"sums exchanged over NVLink (not bit-exact)") if tp > 1 else
                                f"dp{world}: a replica and {rows} streams per GPU, no collective") if world > 1 else "single gpu")
+    sample = pick_sample(lengths, 2)
+    sample_note = f"streams {sample} of {rows} (cached lengths {[int(lengths[r]) for r in sample]}, workload mean {float(np.mean(lengths)):.0f})"
 
     if args.impl == "reference":
-        sample_rows, sample_steps = min(rows, 2), 1
         cache, ids = make_streams(pkg, dev, model, w, lengths, 8 + K + W, rank)
         dev.sync()
-        arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, W + K)
+        arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample, W + K)
         times = [arm.step() for _ in range(W + K)][W:]
-        value = sample_rows * len(times) / float(np.sum(times))
+        value = len(sample) * len(times) / float(np.sum(times))
         ms = float(np.mean(times)) * 1e3
-        sample = f"{sample_rows} of {rows} streams x {sample_steps} decode step per bench step, all {threads} host threads"
+        note = (f"{sample_note} x 1 decode step per bench step, all {threads} host threads; weights and cache contents are drawn on the "
+                f"device (set-up only) and copied to the host before the timed region")
         print(json.dumps(dict(metric="decode_tokens_per_second", value=value, unit="tokens/s", n_gpus=args.gpus, steps=K, warmup=W,
-                              ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8 x int8 -> int32 blocks, f32 accumulate",
+                              ms_per_step=ms, higher_is_better=True, scaling="strong" if (world > 1 and parallelism != "dp") else "weak",
+                              vs_baseline=None, dtype="int8 x int8 -> int32 blocks, f32 accumulate",
                               data="synthetic", config=config, impl="reference",
-                              cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=sample),
+                              cpu_baseline=dict(value=value, unit="tokens/s", cores=threads, kind="port", sample=note),
                               e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))))
         return
 
@@ -423,7 +503,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    cache, ids = make_streams(pkg, dev, model, w, lengths, W + K + 2, data_rank)
+    cache, ids = make_streams(pkg, dev, model, w, lengths, max(W + K, args.parity_steps + 1, 24) + 2, data_rank)
     dev.sync()
     # ---- value: the step loop resident on the device ----------------------------------------------
     with ClockSampler(local) as clocks:
@@ -466,10 +546,47 @@ def main():
     line = dict(metric="decode_tokens_per_second", value=value, unit="tokens/s", n_gpus=world, steps=K, warmup=W,
                 ms_per_step=seconds / K * 1e3, higher_is_better=True, scaling="strong" if tp > 1 else "weak", vs_baseline=None,
                 dtype="int8 x int8 -> int32 blocks, f32 accumulate", data="synthetic", config=config, e2e=e2e,
-                gpu_launches=int(counters["launches"]), clocks=clock_summary,
+                gpu_launches=int(counters["launches"]), collectives=int(counters["collectives"]), clocks=clock_summary,
                 step_roofline=dict(bytes_per_step=total_bytes, weight_bytes=weight_bytes, kv_bytes=kv_bytes,
                                    achieved_gbs=total_bytes / (seconds / K) / 1e9, peak_gbs=peak["hbm_gbs"] * tp, peak_kind=peak_kind,
                                    frac=total_bytes / (seconds / K) / 1e9 / (peak["hbm_gbs"] * tp)))
+
+    # ---- per-operator GPU time of one step (the library's profile mode) ------------------------------
+    if args.profile:
+        refill(cache, lengths, data_rank)
+        dev.sync()
+        model.decode(cache, ids)
+        dev.profile(shapes=True)
+        model.decode(cache, ids)
+        table = dev.profile_read(end=True)
+        if rank == 0:
+            print(f"per-operator GPU time of one decode step ({config['parallelism']}):", file=sys.stderr)
+            for label, count, secs in table:
+                print(f"  {count:5d}  {secs * 1e3:9.3f} ms  {secs / max(count, 1) * 1e6:9.1f} us/launch  {label}", file=sys.stderr)
+        barrier()
+
+    # ---- tensor parallel: the group's tokens against the whole model on one GPU -----------------------
+    if tp > 1:
+        check_steps = min(K, 32)
+        refill(cache, lengths, data_rank)
+        dev.sync()
+        tp_tokens = model.decode_run(cache, ids, check_steps)
+        barrier()
+        if rank == 0:
+            try:
+                whole_dev = pkg.B200(local)
+                whole = pkg.Model.random(whole_dev, model_config(w), KIND[w["kind"]], seed=20260101)
+                wcache, _ = make_streams(pkg, whole_dev, whole, w, lengths, check_steps + 2, data_rank)
+                want = whole.decode_run(wcache, ids, check_steps)
+                same = tp_tokens == want
+                first_off = int(np.argmax(~same.all(axis=1))) if not same.all() else None
+                line["parity"] = dict(tp_tokens_identical=bool(same.all()), steps=check_steps, streams=rows,
+                                      agreeing_tokens=float(same.mean()), first_step_that_differs=first_off,
+                                      against="the whole model's greedy tokens on one GPU, same weights, caches and first tokens")
+                wcache.free(), whole.free(), whole_dev.close()
+            except Exception as problem:  # the check must never cost the bench its line
+                line["parity"] = dict(error=str(problem))
+        barrier()
 
     if rank == 0:
         # ---- roofline of the dominant kernels, timed alone on the same buffers -------------------------
@@ -501,79 +618,153 @@ def main():
         up_bytes = n * (k // 32) * BLOCK[kind] + rows * k * 4 + rows * n * 4
         L = c["layers"]
         attn_share, up_share = attn_s * L, up_s * L
-        kernels = [dict(kernel=f"ordered ragged attention (one layer, {rows} streams)", bytes=attn_bytes, us=attn_s * 1e6, gbs=attn_bytes / attn_s / 1e9,
-                        share_of_step=attn_share / (seconds / K)),
-                   dict(kernel=f"block product {n}x{k} {w['kind']} rows={rows} (+quantiser)", bytes=up_bytes, us=up_s * 1e6,
+        kernels = [dict(kernel=f"ordered ragged attention (one layer, {rows} streams)", key="attention", bytes=attn_bytes, us=attn_s * 1e6,
+                        gbs=attn_bytes / attn_s / 1e9, share_of_step=attn_share / (seconds / K)),
+                   dict(kernel=f"block product {n}x{k} {w['kind']} rows={rows} (+quantiser)", key="up_product", bytes=up_bytes, us=up_s * 1e6,
                         gbs=up_bytes / up_s / 1e9, share_of_step=up_share / (seconds / K))]
         top = max(kernels, key=lambda e: e["share_of_step"])
-        # DRAM bytes (read + written) of one launch from the profiler captures summarised under profiles/, taken on exactly
-        # these shapes and lengths; none for other workloads
-        traffic = None
-        if args.workload == "c5":
-            traffic = 1310231256 if top is kernels[0] else 67894272
+        # DRAM bytes (read + written) of one launch from the profiler captures summarised under profiles/: taken on exactly
+        # this workload's shapes and lengths at one GPU; none for other workloads or shards
+        traffic = load_traffic().get(args.workload, {}).get(top["key"], {}).get("dram_bytes") if tp == 1 else None
         line["roofline"] = dict(bound="hbm", kernel=top["kernel"], achieved=top["gbs"], peak=peak["hbm_gbs"], unit="GB/s",
                                 frac=top["gbs"] / peak["hbm_gbs"], traffic=traffic, algorithmic_bytes=top["bytes"], peak_kind=peak_kind)
         line["kernels"] = kernels
         for b in (tb, q, o, x, y):
             b.free()
 
-        # ---- CPU baseline on a bounded sample (N = 1 only) -----------------------------------------------
+        # ---- CPU baseline on a bounded sample, and the same streams on the device (N = 1 only) ------------
         if world == 1 and not args.no_cpu:
+            parity_steps = max(args.parity_steps, 2)
+            timed_steps = 5                       # about 10 s of host work at the headline shape
             refill(cache, lengths, rank)
             dev.sync()
-            sample_rows, sample_steps = min(rows, 4), 5   # about 10 s of host work at the headline shape
-            arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample_rows, sample_steps + 1)
-            cpu_tokens = []
-            arm.step()  # warm-up: threads start, pages are touched
-            cpu_tokens.append(list(arm.tokens))
-            cpu_seconds = 0.0
-            for _ in range(sample_steps):
-                cpu_seconds += arm.step()
+            arm = CpuArm(pkg, model, cache, lengths, ids, threads, sample, parity_steps + 1)
+            cpu_tokens, cpu_seconds, first_logits = [], 0.0, None
+            for step in range(parity_steps):
+                took = arm.step()
+                if step == 0:
+                    first_logits = arm.logits.copy()   # warm-up step: threads start, pages are touched; its logits serve the fast mode's check
+                elif step <= timed_steps:
+                    cpu_seconds += took
                 cpu_tokens.append(list(arm.tokens))
-            rate = sample_rows * sample_steps / cpu_seconds
+            timed = min(timed_steps, parity_steps - 1)
+            rate = len(sample) * timed / cpu_seconds
             # The same steps on the device from the same caches and first tokens: the sampled streams' greedy tokens must be the
-            # CPU path's, step for step (rows are independent, so the other 60 streams do not matter).
+            # CPU path's, step for step (rows are independent, so the other streams do not matter).
             try:
                 refill(cache, lengths, rank)
                 dev.sync()
-                step_ids, gpu_tokens = ids.copy(), []
-                for _ in range(sample_steps + 1):
-                    step_ids = model.decode(cache, step_ids)
-                    gpu_tokens.append([int(t) for t in step_ids[:sample_rows]])
-                line["parity"] = dict(streams=sample_rows, steps=sample_steps + 1, identical_tokens=gpu_tokens == cpu_tokens,
+                run = model.decode_run(cache, ids, parity_steps)
+                gpu_tokens = [[int(t) for t in run[step, sample]] for step in range(parity_steps)]
+                line["parity"] = dict(streams=len(sample), sample=sample_note, steps=parity_steps, identical_tokens=gpu_tokens == cpu_tokens,
                                       against="the CPU oracle's greedy tokens for the sampled streams at this workload's full size")
             except Exception as problem:  # the check must never cost the bench its line
                 line["parity"] = dict(error=str(problem))
             line["cpu_baseline"] = dict(value=rate, unit="tokens/s", cores=threads, kind="port",
-                                        sample=f"{sample_rows} of {rows} streams x {sample_steps} decode steps, {cpu_seconds:.1f} s, "
+                                        sample=f"{sample_note} x {timed} decode steps, {cpu_seconds:.1f} s, "
                                                f"oracle's threaded product on {threads} threads, other host ops on one thread")
+            # ---- the fast mode (tree sums, split-K online softmax) on the same workload: its speed and its distance from the CPU ----
+            if not args.no_extra and args.mode == "exact":
+                try:
+                    dev.set_mode(pkg.FAST)
+                    refill(cache, lengths, rank)
+                    dev.sync()
+                    fast_tokens, fast_logits = model.decode(cache, ids, logits=True)
+                    model.decode_run(cache, fast_tokens, 3)
+                    refill(cache, lengths, rank)
+                    dev.sync()
+                    fs, fe = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    fs.record(stream)
+                    fast_run = model.decode_run(cache, ids, min(K, 20))
+                    fe.record(stream)
+                    fe.synchronize()
+                    fast_seconds = fs.elapsed_time(fe) / 1e3 / min(K, 20)
+                    got = fast_logits[sample]
+                    rel = float(np.max(np.abs(got - first_logits)) / np.max(np.abs(first_logits)))
+                    steps_same = 0
+                    for step in range(min(parity_steps, fast_run.shape[0])):
+                        if [int(t) for t in fast_run[step, sample]] != cpu_tokens[step]:
+                            break
+                        steps_same += 1
+                    line.setdefault("extra", {})["c5_fast"] = dict(
+                        tokens_per_second=rows / fast_seconds, ms_per_step=fast_seconds * 1e3, speedup_over_exact=(seconds / K) / fast_seconds,
+                        max_relative_logit_error=rel, kl_nats_per_token=kl_per_token(first_logits, got),
+                        greedy_steps_identical_to_cpu=steps_same, of_steps=min(parity_steps, fast_run.shape[0]), sample=sample_note)
+                except Exception as problem:
+                    line.setdefault("extra", {})["c5_fast"] = dict(error=str(problem))
+                finally:
+                    dev.set_mode(pkg.EXACT)
         else:
             line["cpu_baseline"] = None
+    # ---- prefill of one long stream of this model (rank 0, N = 1) -------------------------------------
+    if rank == 0 and world == 1 and not args.no_extra:
+        try:
+            line.setdefault("extra", {})["prefill_c5_one_stream"] = prefill_rate(pkg, dev, torch, stream, model, 1, 2048, w["vocab"])
+        except Exception as problem:
+            line.setdefault("extra", {})["prefill_c5_one_stream"] = dict(error=str(problem))
     cache.free()
+    # ---- load time: the model written to a GGUF file and read back (rank 0, N = 1) -------------------
+    if rank == 0 and world == 1 and not args.no_extra:
+        try:
+            path = os.path.join(tempfile.gettempdir(), f"tsm_bench_{os.getpid()}.gguf")
+            t0 = time.perf_counter()
+            model.save(path)
+            save_seconds = time.perf_counter() - t0
+            size = os.path.getsize(path)
+            t0 = time.perf_counter()
+            again = pkg.Model.load(path, dev)
+            dev.sync()
+            load_seconds = time.perf_counter() - t0
+            again.free()
+            os.unlink(path)
+            line.setdefault("extra", {})["load"] = dict(file_bytes=size, load_seconds=load_seconds, load_gbs=size / load_seconds / 1e9,
+                                                        save_seconds=save_seconds, draw_and_quantise_on_device_seconds=draw_seconds,
+                                                        note="page cache warm: the file was just written")
+        except Exception as problem:
+            line.setdefault("extra", {})["load"] = dict(error=str(problem))
     model.free()
 
-    # ---- batch 1: the 135M-shaped model and the matvec sweep (rank 0, N = 1) ----------------------------
+    # ---- batch 1 (135M- and GPT-2-XL-shaped), the 1.7B-shaped batch, the product sweep (rank 0, N = 1) ----
     if rank == 0 and world == 1 and not args.no_extra:
-        extra = {}
-        w1 = WORKLOADS["c1"]
-        m1 = pkg.Model.random(dev, model_config(w1), KIND[w1["kind"]], seed=20260102)
-        prompt = np.random.default_rng(7).integers(0, w1["vocab"], size=32).astype(np.int32)
-        c1 = m1.new_batch_cache(1, 32 + 128 + 8)
-        m1.forward_last([prompt.tolist()], c1)
-        first = np.array([1], dtype=np.int32)
-        m1.decode_run(c1, first, 4)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record(stream)
-        m1.decode_run(c1, first, 120)
-        stop.record(stream)
-        stop.synchronize()
-        s1 = start.elapsed_time(stop) / 1e3 / 120
-        b1, _, _ = step_bytes(w1, np.array([32 + 64]))
-        extra["c1_batch1"] = dict(workload=w1["name"], tokens_per_second=1 / s1, us_per_token=s1 * 1e6,
-                                  bytes_per_token=b1, frac_of_hbm=b1 / s1 / 1e9 / peak["hbm_gbs"])
-        c1.free(), m1.free()
-        extra["matvec_batch1"] = matvec_sweep(pkg, dev, torch, stream, peak["hbm_gbs"])
-        line["extra"] = extra
+        extra = line.setdefault("extra", {})
+        extra["c1_batch1"] = batch1_model(pkg, dev, torch, stream, WORKLOADS["c1"], 20260102, 120, peak["hbm_gbs"])
+        extra["c4_batch1"] = batch1_model(pkg, dev, torch, stream, WORKLOADS["c4"], 20260104, 120, peak["hbm_gbs"])
+        w3 = WORKLOADS["c3"]
+        m3 = pkg.Model.random(dev, model_config(w3), KIND[w3["kind"]], seed=20260103)
+        extra["prefill_c3"] = prefill_rate(pkg, dev, torch, stream, m3, 16, 128, w3["vocab"])
+        m3.free()
+        extra["product_sweep"] = product_sweep(pkg, dev, torch, stream, peak["hbm_gbs"])
+        extra["matvec_batch1"] = [e for e in extra["product_sweep"] if e["columns"] == 1]
+
+    # ---- N > 1: the baseline's data-parallel configuration, its 16 streams split over the ranks --------
+    if world > 1 and not args.no_extra:
+        w3 = WORKLOADS["c3"]
+        first, count = pkg.groups.stream_share(w3["rows"], world, rank)
+        solo = pkg.B200(local)   # a context of its own, outside the tensor-parallel group: a whole replica
+        m3 = pkg.Model.random(solo, model_config(w3), KIND[w3["kind"]], seed=20260103)
+        dp_steps = min(K, 50)
+        seconds3 = 0.0
+        if count > 0:
+            c3 = m3.new_batch_cache(count, w3["len_lo"] + dp_steps + 8)
+            for row in range(count):
+                c3.fill(row, w3["len_lo"], seed=3000 + first + row)
+            ids3 = np.random.default_rng(7).integers(0, w3["vocab"], size=w3["rows"]).astype(np.int32)[first:first + count]
+            m3.decode_run(c3, ids3, 3)
+        barrier()
+        if count > 0:
+            solo_stream = torch.cuda.ExternalStream(solo.stream, device=local)
+            s3, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s3.record(solo_stream)
+            m3.decode_run(c3, ids3, dp_steps)
+            e3.record(solo_stream)
+            e3.synchronize()
+            seconds3 = s3.elapsed_time(e3) / 1e3
+            c3.free()
+        seconds3 = max_over_ranks(seconds3)
+        m3.free(), solo.close()
+        if rank == 0:
+            line.setdefault("extra", {})["c3_dp"] = dict(workload=w3["name"], parallelism=f"dp{world}: {w3['rows']} streams split over the ranks, a replica each, no collective",
+                                                          tokens_per_second=w3["rows"] * dp_steps / seconds3, ms_per_step=seconds3 / dp_steps * 1e3, scaling="strong")
     if rank == 0:
         print(json.dumps(line))
     dev.close()

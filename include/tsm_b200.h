@@ -72,9 +72,32 @@ typedef struct {
     int64_t allocs, pool_hits, pool_misses, pool_held_bytes, frees;
     int64_t host_ops;     /* always 0: no operator has a host fallback (fused_llama_spec.cr:82-90) */
     int64_t graph_replays;
+    int64_t collectives;  /* exchanges queued between the GPUs of a tensor-parallel group (no counterpart in the reference) */
 } tsm_counters;
 int tsm_counters_read(tsm_ctx* ctx, tsm_counters* out);
 int tsm_counters_reset(tsm_ctx* ctx);
+
+/* CUDA::Profile with per_kernel (and shapes) set (cuda.cr:256-303, 463-477; cuda/report.cr): between tsm_profile_begin and
+ * tsm_profile_end every operator's kernels are bracketed by two events on the context's stream; tsm_profile_read waits for
+ * the stream and returns, longest total first, each operator's launches and GPU seconds, keyed by its name ("BlockMatMul
+ * q4_0", "RaggedAttention", ...) and, with `shapes`, its sizes too ("BlockMatMul q4_0 [64,4096,28672]").  *count receives
+ * how many labels there are; at most `capacity` are written.  While a profile is on, tsm_decode and tsm_decode_run launch
+ * their steps kernel by kernel instead of replaying the captured graph, whose nodes cannot be timed one by one. */
+typedef struct {
+    char label[80];
+    int64_t count;
+    double seconds;
+} tsm_profile_entry;
+int tsm_profile_begin(tsm_ctx* ctx, int shapes);
+int tsm_profile_read(tsm_ctx* ctx, tsm_profile_entry* entries, int capacity, int* count);
+int tsm_profile_end(tsm_ctx* ctx);
+
+/* For tests of the bounded device-side waits (no counterpart in the reference, whose kernels do not wait): `spins` replaces
+ * the number of polls after which a kernel's wait for an asynchronous copy gives up (0: the built-in limit), and with
+ * `starve_copies` = 1 the next batched products' copy threads leave out the last stage of their operands, so the warps
+ * waiting for it run into that limit, set the record's timeout word, and return; tsm_sync then gives TSM_ERR_TIMEOUT.
+ * Nothing traps and the context stays usable.  Call again with (0, 0) to restore. */
+int tsm_debug_wait_limit(tsm_ctx* ctx, unsigned spins, int starve_copies);
 
 /* How norms and attention add (both modes keep the block products bit-exact):
  *   TSM_EXACT  (default) the host's index-order sums and its own exp polynomial: the host's bits, so
@@ -146,6 +169,11 @@ int tsm_rope(tsm_ctx* ctx, tsm_dptr x, int tokens, int heads, int width, int64_t
 int tsm_write_rows(tsm_ctx* ctx, tsm_dptr cache, int rows, int heads, int capacity, int width, tsm_dptr values,
                    int64_t v_stride, int tokens, tsm_dptr slots);
 
+/* Op::Write (Tensor#write, tensor/structural.cr:64-74; copy_into_f32, kernels.cu:59-63): `value`, dense, with dst's shape
+ * except `extent` along `axis`, is written into dst (dense, `ndim` <= 8 axes of `shape`) at `start` along `axis`, in place:
+ * what the single-stream CausalSelfAttention::Cache does for each step's keys and values (modules.cr:137-188). */
+int tsm_write(tsm_ctx* ctx, tsm_dptr dst, const int32_t* shape, int ndim, tsm_dptr value, int extent, int axis, int start);
+
 /* Op::RaggedAttention (Tensor.ragged_attention, tensor/composite.cr:210-227; attention_ragged_f32,
  * kernels.cu:1081-1097) and, with one row, Op::Attention (attention_f32, kernels.cu:1058-1073):
  * q [tokens,heads,width] (token stride q_stride); k, v [rows,kv_heads,capacity,width];
@@ -186,6 +214,10 @@ typedef struct {
  * Q8_0, Q4_0, Q4_1 or F32 (F16 / BF16 are widened to F32, gguf.cr:112-136); a Linear over an F32 matrix runs as
  * tsm_matmul_f32, and token tables may stay F32 beside quantised layers (Module#quantize without embeddings). */
 int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out);
+/* GGUF.open (gguf.cr:90-99, 297-325) alone: parses the header, the metadata and the tensor table and checks that every tensor
+ * lies inside the file, without a device.  TSM_OK, or TSM_ERR_IO / TSM_ERR_UNSUPPORTED with the reason in `reason`
+ * (a truncated file, an offset outside it, an empty axis, a token table that is not a matrix ...). */
+int tsm_gguf_check(const char* path, char* reason, int capacity);
 /* GPT2.load / Llama.load of Hugging Face safetensors weights (gpt2.cr:69-101, llama.cr:163-175, safetensors.cr), followed by
  * Module#quantize(kind, embeddings: true) (module.cr:262-274) on the device: F32 / F16 / BF16 matrices, GPT-2's Conv1D
  * weights transposed, every Linear and both embedding tables quantised to `kind`; with kind TSM_F32 nothing is quantised
@@ -253,8 +285,25 @@ int tsm_tp_info(tsm_ctx* ctx, int* rank, int* world);
 typedef enum { TSM_TP_GATHER = 0, TSM_TP_REDUCE = 1 } tsm_tp_split;
 int tsm_tp_variant(tsm_ctx* ctx, int variant);
 
+/* Leaves the group without waiting for the other ranks (ncclCommAbort): what a rank does once the host has learnt that a
+ * peer is gone.  Every later exchange on this context returns TSM_ERR_COMM.  An exchange that fails, and a wait during which
+ * the communicator reports a failure of its own (ncclCommGetAsyncError is polled while the host waits for a step), return
+ * TSM_ERR_COMM too; a step that makes no progress for TSM_TP_TIMEOUT_MS (default 60000) returns TSM_ERR_TIMEOUT. */
+int tsm_tp_abort(tsm_ctx* ctx);
+
 /* Generative#generate with Sampler.greedy (generative.cr:177-190): `count` tokens after `prompt`. */
 int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int count, int32_t* tokens);
+
+/* Generative#generate(prompt, count, sampler, stop) (generative.cr:177-190) with the sampler's draw left to the host:
+ * after each step the device keeps the `top_k` highest logits of the last position, highest first and equal logits by lower
+ * index, as Sampler#top orders its candidates (sampler.cr:77-96), and hands their ids and values to `pick`, which returns the
+ * chosen token (Sampler#pick_among, sampler.cr:57-72: the caller applies its temperature and makes its seeded draw).
+ * top_k = 0 hands over the whole row of logits in index order (ids is then NULL and count the vocabulary).  pick = NULL is
+ * Sampler.greedy on the device.  Generation ends after `count` tokens or after a token found in `stop` (which is the last
+ * one returned); *produced receives how many tokens were written. */
+typedef int32_t (*tsm_pick_fn)(void* user, int step, const int32_t* ids, const float* logits, int count);
+int tsm_generate_sampled(tsm_model* model, const int32_t* prompt, int prompt_size, int count, const int32_t* stop, int stop_size,
+                         int top_k, tsm_pick_fn pick, void* user, int32_t* tokens, int* produced);
 
 #ifdef __cplusplus
 }

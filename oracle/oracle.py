@@ -24,11 +24,19 @@ _i8p = C.POINTER(C.c_int8)
 _i32p = C.POINTER(C.c_int32)
 
 
-def build(ref=True):
-    """Compiles liboracle.so and, when the reference tree is present, _ref/libkernels.so."""
+def build(ref=True, reference=None):
+    """Compiles liboracle.so and, when a checkout of the reference is at hand, _ref/libkernels.so from its sources.
+
+    The checkout is `reference`, else $TENSOMITE_REFERENCE, else the Makefile's own default (`make ref REFERENCE=...`)."""
     subprocess.run(["make", "-s", "-C", HERE], check=True)
-    if ref and os.path.isdir("/root/reference/src/tensomite/cuda"):
-        subprocess.run(["make", "-s", "-C", HERE, "ref"], check=True)
+    if not ref:
+        return
+    where = reference or os.environ.get("TENSOMITE_REFERENCE")
+    if where is None:
+        shown = subprocess.run(["make", "-s", "-C", HERE, "print-reference"], capture_output=True, text=True)
+        where = shown.stdout.strip() if shown.returncode == 0 else ""
+    if where and os.path.isdir(os.path.join(where, "src", "tensomite", "cuda")):
+        subprocess.run(["make", "-s", "-C", HERE, "ref", "REFERENCE=" + where], check=True)
 
 
 def _load():
@@ -338,6 +346,46 @@ class Model:
             if i < count - 1:
                 logits = self.forward(cache, [[token]])
         return tokens
+
+
+def model_from_device(model, threads=1):
+    """An oracle Model over the very weights a device model holds, downloaded through the C ABI (`model` is the
+    binding's Model: only its `config` and `tensor(name)` are used)."""
+    c = dict(model.config)
+    names = ["embed", "final_w"] + (["wpe", "final_b"] if c["arch"] == "gpt2" else [])
+    if not c["tied"]:
+        names.append("head")
+    for i in range(c["layers"]):
+        names += [f"{i}.{p}" for p in ("norm1_w", "norm2_w", "qkv", "o", "up", "down")]
+        if c["arch"] == "gpt2":
+            names += [f"{i}.{p}" for p in ("norm1_b", "norm2_b", "qkv_b", "o_b", "up_b", "down_b")]
+    t = {}
+    for name in names:
+        buf, kind, n, k = model.tensor(name)
+        if kind < 0:
+            t[name] = (-1, buf.numpy(np.float32).reshape(-1) if n == 1 else buf.numpy(np.float32).reshape(n, k))
+        else:
+            t[name] = (kind, buf.numpy(np.uint8).reshape(n, -1))
+    return Model(c, t, threads=threads)
+
+
+def cache_from_device(ref, device_model, device_cache, rows, lengths, capacity):
+    """An oracle Cache of `capacity` positions holding what rows `rows` of a device batch cache hold: lengths[i] positions
+    of row rows[i], keys and values of every layer, read back through the C ABI."""
+    c = device_model.config
+    out = ref.new_cache(len(rows), capacity)
+    row_floats = c["kv_heads"] * device_cache.capacity * c["head_width"]
+    piece = type(device_cache.layer(0)[0])
+    for layer in range(c["layers"]):
+        kb, vb = device_cache.layer(layer)
+        for i, (row, n) in enumerate(zip(rows, lengths)):
+            n = int(n)
+            for src, dst in ((kb, out.keys[layer]), (vb, out.values[layer])):
+                part = piece(device_model.device, src.ptr + int(row) * row_floats * 4, row_floats * 4).numpy(np.float32)
+                dst[i, :, :n, :] = part.reshape(c["kv_heads"], device_cache.capacity, c["head_width"])[:, :n, :]
+    for i, n in enumerate(lengths):
+        out.lengths[i] = int(n)
+    return out
 
 
 class Cache:

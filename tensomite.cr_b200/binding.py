@@ -42,8 +42,16 @@ class DTypeError(Error):
     pass
 
 
-_STATUS = {1: DeviceError, 2: ShapeError, 3: ExecutionError, 4: DeviceError, 5: Error, 6: DTypeError, 7: DeviceError,
-           8: DeviceError}
+class CommError(DeviceError):
+    """The tensor-parallel group failed (TSM_ERR_COMM)."""
+
+
+class TimeoutError_(DeviceError):
+    """A bounded wait ran out (TSM_ERR_TIMEOUT)."""
+
+
+_STATUS = {1: DeviceError, 2: ShapeError, 3: ExecutionError, 4: DeviceError, 5: Error, 6: DTypeError, 7: TimeoutError_,
+           8: CommError}
 
 _lib = None
 
@@ -57,7 +65,14 @@ class ModelConfig(C.Structure):
 class Counters(C.Structure):
     _fields_ = [(name, C.c_int64) for name in
                 ("launches", "uploads", "downloads", "upload_bytes", "download_bytes", "allocs", "pool_hits",
-                 "pool_misses", "pool_held_bytes", "frees", "host_ops", "graph_replays")]
+                 "pool_misses", "pool_held_bytes", "frees", "host_ops", "graph_replays", "collectives")]
+
+
+class ProfileEntry(C.Structure):
+    _fields_ = [("label", C.c_char * 80), ("count", C.c_int64), ("seconds", C.c_double)]
+
+
+PICK_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float), C.c_int)
 
 
 def declared_symbols():
@@ -165,6 +180,27 @@ class B200:
         """TP_GATHER (default: the bits of one GPU) or TP_REDUCE (o and down over input columns, all-reduced); set before
         the model is loaded."""
         self.check(self.lib.tsm_tp_variant(self.ctx, C.c_int(variant)), "tsm_tp_variant")
+
+    def tp_abort(self):
+        """Leaves the group without waiting for the other ranks; later exchanges raise CommError."""
+        self.check(self.lib.tsm_tp_abort(self.ctx), "tsm_tp_abort")
+
+    def profile(self, shapes=False):
+        """cuda.profile = CUDA::Profile.new(per_kernel: true, shapes: shapes): starts timing every operator on the GPU."""
+        self.check(self.lib.tsm_profile_begin(self.ctx, C.c_int(1 if shapes else 0)), "tsm_profile_begin")
+
+    def profile_read(self, end=False):
+        """[(label, launches, GPU seconds)], longest first; with `end` the profile stops."""
+        count = C.c_int()
+        self.check(self.lib.tsm_profile_read(self.ctx, None, C.c_int(0), C.byref(count)), "tsm_profile_read")
+        entries = (ProfileEntry * max(count.value, 1))()
+        self.check(self.lib.tsm_profile_read(self.ctx, entries, C.c_int(count.value), C.byref(count)), "tsm_profile_read")
+        if end:
+            self.check(self.lib.tsm_profile_end(self.ctx), "tsm_profile_end")
+        return [(entries[i].label.decode(), int(entries[i].count), float(entries[i].seconds)) for i in range(count.value)]
+
+    def debug_wait_limit(self, spins, starve_copies):
+        self.check(self.lib.tsm_debug_wait_limit(self.ctx, C.c_uint(spins), C.c_int(starve_copies)), "tsm_debug_wait_limit")
 
     def tp_info(self):
         rank, world = C.c_int(), C.c_int()
@@ -407,6 +443,21 @@ class B200:
             for b in (cb, vb, sb):
                 b.free()
 
+    def write(self, dst, value, axis, start):
+        """Tensor#write: dst (numpy, returned updated) with `value` written at `start` along `axis`, in place on the device."""
+        dst = np.ascontiguousarray(dst, dtype=np.float32)
+        value = np.ascontiguousarray(value, dtype=np.float32)
+        db, vb = self.tensor(dst), self.tensor(value)
+        shape = (C.c_int32 * dst.ndim)(*dst.shape)
+        try:
+            self.check(self.lib.tsm_write(self.ctx, C.c_uint64(db.ptr), shape, C.c_int(dst.ndim), C.c_uint64(vb.ptr),
+                                          C.c_int(value.shape[axis]), C.c_int(axis), C.c_int(start)), "tsm_write")
+            self.sync()
+            return db.numpy(np.float32, dst.shape)
+        finally:
+            db.free()
+            vb.free()
+
     def ragged_attention(self, q, k, v, table, scale):
         """q [tokens, heads, width]; k, v [rows, kv_heads, capacity, width]; table int32 [tokens, 3]."""
         q = np.ascontiguousarray(q, dtype=np.float32)
@@ -594,6 +645,25 @@ class Model:
                           "tsm_generate")
         return tokens[:count].tolist()
 
+    def generate_sampled(self, prompt, count, pick=None, top_k=0, stop=()):
+        """Generative#generate(prompt, count, sampler, stop): `pick(step, ids, logits)` chooses among the `top_k` candidates the
+        device kept (ids None and every logit in index order when top_k is 0); None is the greedy sampler on the device."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        stop = np.ascontiguousarray(list(stop), dtype=np.int32)
+        tokens = np.empty(max(count, 1), dtype=np.int32)
+        produced = C.c_int()
+
+        def trampoline(user, step, ids, logits, n):
+            values = np.ctypeslib.as_array(logits, shape=(n,)).copy()
+            which = np.ctypeslib.as_array(ids, shape=(n,)).copy() if ids else None
+            return int(pick(step, which, values))
+
+        callback = PICK_FN(trampoline) if pick is not None else C.cast(None, PICK_FN)
+        self.device.check(self.device.lib.tsm_generate_sampled(self.handle, _ptr(prompt), C.c_int(prompt.size), C.c_int(count),
+                                                               _ptr(stop) if stop.size else None, C.c_int(stop.size), C.c_int(top_k),
+                                                               callback, None, _ptr(tokens), C.byref(produced)), "tsm_generate_sampled")
+        return tokens[:produced.value].tolist()
+
     def free(self):
         if self.handle:
             self.device.lib.tsm_model_free(self.handle)
@@ -609,5 +679,5 @@ class GPT2(Model):
 
 
 __all__ = ["Q8_0", "Q4_0", "Q4_1", "F32", "BLOCK_BYTES", "FAST", "EXACT", "TP_GATHER", "TP_REDUCE", "Error", "DeviceError", "ShapeError", "ExecutionError",
-           "DTypeError", "ModelConfig", "Counters", "declared_symbols", "library", "check_exports", "Buffer", "B200", "BatchCache",
+           "DTypeError", "CommError", "TimeoutError_", "ModelConfig", "Counters", "declared_symbols", "library", "check_exports", "Buffer", "B200", "BatchCache",
            "Model", "Llama", "GPT2"]

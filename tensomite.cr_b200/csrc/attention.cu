@@ -483,6 +483,7 @@ __global__ void length_order_kernel(const int* __restrict__ table, int tokens, i
 }
 
 int launch_length_order(tsm_ctx* ctx, const int* table, int tokens, int* order) {
+    OpTimer timer(ctx, "Attention order", tokens);
     if (tokens == 0) return TSM_OK;
     TSM_CUDA(ctx, launch_chained(ctx, length_order_kernel, dim3((tokens + 255) / 256), dim3(256), 0, table, tokens, order));
     count_launch(ctx);
@@ -532,6 +533,7 @@ static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int token
 int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
                      const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
                      const QuantizedActs* quantized, const int* order) {
+    OpTimer timer(ctx, "RaggedAttention", tokens, heads, width);
     if (kv_heads <= 0 || heads % kv_heads != 0)
         return fail(ctx, TSM_ERR_ARG, std::to_string(heads) + " query heads do not group into " + std::to_string(kv_heads) + " key and value heads");
     if (tokens == 0) return TSM_OK;

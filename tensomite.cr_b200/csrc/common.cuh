@@ -39,6 +39,20 @@ struct Scratch {
     int64_t bytes = 0;
 };
 
+// Per-operator GPU time, collected while tsm_profile_begin is in force: every launcher brackets its kernels with two
+// events (OpTimer below); tsm_profile_read waits for the stream and adds the elapsed times up by label.
+struct ProfileSpan {
+    std::string label;
+    cudaEvent_t start, stop;
+};
+struct Profile {
+    bool on = false, shapes = false;
+    std::vector<ProfileSpan> spans;          // recorded, not yet read
+    std::vector<cudaEvent_t> spare;          // events ready for reuse
+    std::map<std::string, std::pair<int64_t, double>> totals;  // label -> (count, seconds), from spans already read
+    int depth = 0;                           // launchers nest (a product calls its quantiser): only the outermost is timed
+};
+
 }  // namespace tsm
 
 struct tsm_ctx {
@@ -56,11 +70,15 @@ struct tsm_ctx {
     int tp_rank = 0, tp_world = 1;            // this context's place in a tensor-parallel group
     bool chain_launches = false;              // the engine sets it around steps of a few rows (see launch_chained)
     void* comm = nullptr;                     // its NCCL communicator
+    bool comm_failed = false;                 // an exchange failed or the group was aborted: every later one is refused
     int tp_variant = 0;                       // TSM_TP_GATHER or TSM_TP_REDUCE: how models built on this context are split
     std::mutex message_lock;
     std::string message;
     tsm_counters counters{};
     std::mutex counter_lock;
+    tsm::Profile profile;
+    unsigned wait_spins = 0;                  // tsm_debug_wait_limit: a shorter limit for the kernels' bounded waits (0: theirs)
+    int starve_copies = 0;                    //                       and a stage the next product's producer leaves out
 };
 
 namespace tsm {
@@ -73,6 +91,19 @@ int check_error_record(tsm_ctx* ctx);  // inspects the host copy of the record; 
 int pool_alloc(tsm_ctx* ctx, int64_t bytes, void** out);
 void pool_release(tsm_ctx* ctx, void* p);
 inline void count_launch(tsm_ctx* ctx, int n = 1) { ctx->counters.launches += n; }
+
+// Brackets the kernels a launcher queues with two events while the context's profile is on (and the stream is not being
+// captured: a captured step cannot be timed node by node, so tsm_decode runs its step uncaptured under a profile).
+// `label` is the operator's name; with shapes on, the sizes follow it, as the reference's per-kernel profile keys
+// "MatMul [64,768]x[768,2304]" (cuda.cr:256-303, 463-477).
+struct OpTimer {
+    tsm_ctx* ctx;
+    bool active = false;
+    cudaEvent_t start = nullptr;
+    std::string label;
+    OpTimer(tsm_ctx* c, const char* name, int64_t a = -1, int64_t b = -1, int64_t d = -1);
+    ~OpTimer();
+};
 
 // A launch that may begin while the kernel before it on the stream is still draining (programmatic dependent launch): the
 // kernel's blocks are scheduled as soon as every block of its predecessor has started, run nothing but
@@ -155,6 +186,8 @@ int tp_all_gather(tsm_ctx* ctx, void* buffer, int64_t bytes);
 int tp_all_reduce_sum(tsm_ctx* ctx, float* buffer, int64_t count);
 int launch_interleave(tsm_ctx* ctx, const float* gathered, float* dst, int rows, int width, int parts, bool add);
 void tp_release(tsm_ctx* ctx);
+void tp_abort(tsm_ctx* ctx);
+int tp_stream_wait(tsm_ctx* ctx);  // the stream wait of a group member: bounded, polls the communicator for failures
 // A rank-2 tensor map over `rows` rows of `width` elements (row pitch in bytes), copied in boxes of box_w x box_h.
 bool tensor_maps_available();
 int make_tensor_map_2d(tsm_ctx* ctx, CUtensorMap* map, CUtensorMapDataType type, const void* base, uint64_t width, uint64_t rows,
@@ -184,6 +217,8 @@ int launch_rmsnorm(tsm_ctx* ctx, const float* x, const float* w, int rows, int n
                    const QuantizedActs* quantized);
 int launch_layernorm(tsm_ctx* ctx, const float* x, const float* w, const float* b, int rows, int n, float eps, float* out,
                      const QuantizedActs* quantized);
+// Op::Write: `outer` runs of `chunk` floats of src, run o landing at dst[o * pitch + offset ...].
+int launch_write_region(tsm_ctx* ctx, float* dst, const float* src, int64_t outer, int64_t pitch, int64_t chunk, int64_t offset);
 int launch_rope(tsm_ctx* ctx, const float* x, int tokens, int heads, int width, int64_t x_stride, const float* cos_table,
                 const float* sin_table, int context, const int* positions, float* out);
 int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capacity, int width, const float* values,

@@ -383,6 +383,16 @@ int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
     return TSM_OK;
 }
 
+int tsm_gguf_check(const char* path, char* reason, int capacity) {
+    std::string why;
+    int rc = check_gguf_file(path, &why);
+    if (reason && capacity > 0) {
+        strncpy(reason, why.c_str(), (size_t)capacity - 1);
+        reason[capacity - 1] = 0;
+    }
+    return rc;
+}
+
 int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_config* config, int kind, tsm_model** out) {
     if (!ctx || !path || !config || !out) return TSM_ERR_ARG;
     tsm::DeviceGuard guard(ctx->ordinal);
@@ -524,8 +534,8 @@ int tsm_cache_fill(tsm_cache* cache, int row, int length, uint64_t seed) {
 
 // Generative#packed (generative.cr:112-125) with optional greedy picks of each output row.
 static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* counts, const int32_t* ids, int last, float* logits,
-                        int32_t* picks) {
-    if (!cache || cache->model != model || !counts || !ids || (!logits && !picks)) return fail(model->ctx, TSM_ERR_ARG, "forward needs a cache of this model, counts, ids and a place for logits");
+                        int32_t* picks, bool keep_on_device = false) {
+    if (!cache || cache->model != model || !counts || !ids || (!logits && !picks && !keep_on_device)) return fail(model->ctx, TSM_ERR_ARG, "forward needs a cache of this model, counts, ids and a place for logits");
     tsm_ctx* ctx = model->ctx;
     const tsm_model_config& c = model->cfg;
     int total = 0, active = 0;
@@ -560,6 +570,10 @@ static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* count
     ctx->counters.upload_bytes += (int64_t)total * 16 + (int64_t)outputs * 4;
     TSM_TRY(launch_step(model, cache, total, outputs, picks != nullptr));
     if (logits && picks && model->tp > 1) TSM_TRY(gather_full_logits(model, outputs));
+    if (keep_on_device) {  // the caller reads ws.logits itself, after its own kernels
+        for (int row = 0; row < cache->rows; row++) cache->lengths[row] += counts[row];
+        return TSM_OK;
+    }
     if (logits) {
         TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)outputs * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->counters.downloads++;
@@ -591,6 +605,11 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     for (int row = 0; row < rows; row++)
         if (cache->lengths[row] + 1 > limit)
             return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + 1) + " positions exceed the " + std::to_string(limit) + " a row holds");
+    if (ctx->profile.on) {
+        // a profile times operators one by one, which a replayed graph does not allow: the same step, launched directly
+        std::vector<int32_t> ones(rows, 1);
+        return forward_impl(model, cache, ones.data(), ids, 1, logits, tokens);
+    }
     TSM_TRY(prepare_scratch(model, cache, rows));
     // a captured step holds the addresses of the workspace and of the scratch memory, and the mode's kernels
     uint64_t stamp = model->ws_generation * 1000003ull + ctx->scratch_generation * 10ull + (uint64_t)ctx->mode;
@@ -639,7 +658,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
         TSM_CUDA(ctx, cudaMemcpyAsync(logits, w.logits, (size_t)rows * c.vocab * 4, cudaMemcpyDeviceToHost, ctx->stream));
         ctx->counters.downloads++, ctx->counters.download_bytes += (int64_t)rows * c.vocab * 4;
     }
-    TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TSM_TRY(tp_stream_wait(ctx));
     TSM_TRY(check_error_record(ctx));  // the replayed step copied the record to the host
     for (int row = 0; row < rows; row++) {
         tokens[row] = h_picks[row];
@@ -659,6 +678,14 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
     for (int row = 0; row < rows; row++)
         if (cache->lengths[row] + steps > limit)
             return fail(ctx, TSM_ERR_ARG, std::to_string(cache->lengths[row] + steps) + " positions exceed the " + std::to_string(limit) + " a row holds");
+    if (ctx->profile.on) {
+        std::vector<int32_t> feed(ids, ids + rows);
+        for (int s = 0; s < steps; s++) {
+            TSM_TRY(tsm_decode(model, cache, feed.data(), tokens + (int64_t)s * rows, nullptr));
+            feed.assign(tokens + (int64_t)s * rows, tokens + (int64_t)(s + 1) * rows);
+        }
+        return TSM_OK;
+    }
     TSM_TRY(prepare_scratch(model, cache, rows));
     // room for at least 1024 steps: the captured step holds this buffer's address, so growing it means capturing again
     int64_t need = 1 + (int64_t)std::max(steps, 1024) * rows;
@@ -711,7 +738,7 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
         TSM_CUDA(ctx, cudaGraphLaunch(cache->run_graph, ctx->stream));
         // Measured with 2 to 8 ranks: replays holding NCCL all-gathers queued back to back ran at half the rate of replays
         // the host waits for one by one, so a tensor-parallel run pays one stream wait per step.
-        if (model->tp > 1 && !getenv("TSM_TP_RUN_QUEUED")) TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (model->tp > 1 && !getenv("TSM_TP_RUN_QUEUED")) TSM_TRY(tp_stream_wait(ctx));
     }
     ctx->counters.graph_replays += steps;
     ctx->counters.launches += (int64_t)steps * cache->run_kernels;
@@ -735,6 +762,70 @@ int tsm_generate(tsm_model* model, const int32_t* prompt, int prompt_size, int c
     int rc = forward_impl(model, cache, counts, prompt, 1, nullptr, &tokens[0]);
     if (rc == TSM_OK && count > 1) rc = tsm_decode_run(model, cache, &tokens[0], count - 1, &tokens[1]);
     tsm_cache_free(cache);
+    return rc;
+}
+
+int tsm_generate_sampled(tsm_model* model, const int32_t* prompt, int prompt_size, int count, const int32_t* stop, int stop_size,
+                         int top_k, tsm_pick_fn pick, void* user, int32_t* tokens, int* produced) {
+    MODEL_GUARD(model);
+    tsm_ctx* ctx = model->ctx;
+    if (produced) *produced = 0;
+    if (!prompt || prompt_size < 1 || count < 0 || (count > 0 && !tokens) || stop_size < 0 || (stop_size > 0 && !stop) || top_k < 0)
+        return fail(ctx, TSM_ERR_ARG, "generate needs a prompt, a place for tokens and a stop list that matches its size");
+    const tsm_model_config& c = model->cfg;
+    if (top_k >= c.vocab) top_k = 0;  // Sampler#pick: every token, in index order (sampler.cr:38)
+    if (pick && top_k > 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "at most 1024 candidates are kept on the device");
+    if (count == 0) return TSM_OK;
+    int capacity = prompt_size + count < c.context ? prompt_size + count : c.context;
+    tsm_cache* cache = nullptr;
+    TSM_TRY(tsm_cache_create(model, 1, capacity, &cache));
+    const int kept = pick ? (top_k > 0 ? top_k : c.vocab) : 0;
+    std::vector<int32_t> cand_ids(top_k > 0 ? top_k : 0);
+    std::vector<float> cand_values(kept);
+    int* d_ids = nullptr;
+    float* d_values = nullptr;
+    int rc = TSM_OK;
+    if (pick && top_k > 0) {
+        rc = pool_alloc(ctx, (int64_t)top_k * 4, (void**)&d_ids);
+        if (rc == TSM_OK) rc = pool_alloc(ctx, (int64_t)top_k * 4, (void**)&d_values);
+    }
+    int made = 0;
+    int32_t counts[1] = {prompt_size};
+    const int32_t* feed = prompt;
+    int32_t last_token = 0;
+    while (rc == TSM_OK && made < count) {
+        int32_t token = 0;
+        if (!pick) {
+            rc = forward_impl(model, cache, counts, feed, 1, nullptr, &token);   // Sampler.greedy on the device (sampler.cr:36)
+        } else if (top_k > 0) {
+            rc = forward_impl(model, cache, counts, feed, 1, nullptr, nullptr, true);
+            if (rc == TSM_OK) rc = launch_topk(ctx, model->ws.logits, 1, c.vocab, top_k, d_ids, d_values);
+            if (rc == TSM_OK) {
+                cudaError_t e = cudaMemcpyAsync(cand_ids.data(), d_ids, (size_t)top_k * 4, cudaMemcpyDeviceToHost, ctx->stream);
+                if (e == cudaSuccess) e = cudaMemcpyAsync(cand_values.data(), d_values, (size_t)top_k * 4, cudaMemcpyDeviceToHost, ctx->stream);
+                if (e != cudaSuccess) rc = cuda_fail(ctx, e, "cudaMemcpyAsync");
+                ctx->counters.downloads += 2, ctx->counters.download_bytes += (int64_t)top_k * 8;
+            }
+            if (rc == TSM_OK) rc = tsm_sync(ctx);
+            if (rc == TSM_OK) token = pick(user, made, cand_ids.data(), cand_values.data(), top_k);
+        } else {
+            rc = forward_impl(model, cache, counts, feed, 1, cand_values.data(), nullptr);
+            if (rc == TSM_OK) token = pick(user, made, nullptr, cand_values.data(), c.vocab);
+        }
+        if (rc != TSM_OK) break;
+        if (token < 0 || token >= c.vocab) {
+            rc = fail(ctx, TSM_ERR_ARG, "the sampler returned token " + std::to_string(token) + " of a vocabulary of " + std::to_string(c.vocab));
+            break;
+        }
+        tokens[made++] = token;
+        bool stopped = false;
+        for (int i = 0; i < stop_size; i++) stopped = stopped || stop[i] == token;
+        if (stopped) break;
+        last_token = token, feed = &last_token, counts[0] = 1;
+    }
+    pool_release(ctx, d_ids), pool_release(ctx, d_values);
+    tsm_cache_free(cache);
+    if (produced) *produced = made;
     return rc;
 }
 

@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(kF32Cols) matmul_f32_kernel(const float* __res
 
 int launch_matmul_f32(tsm_ctx* ctx, const float* x, int rows, int k, const float* w, int n, const float* bias, const float* residual,
                       float* out) {
+    OpTimer timer(ctx, "MatMul", rows, k, n);
     if (rows < 0 || n < 0 || k < 0) return fail(ctx, TSM_ERR_ARG, "negative product shape");
     if (rows == 0 || n == 0) return TSM_OK;
     dim3 grid((unsigned)((n + kF32Cols - 1) / kF32Cols), (unsigned)((rows + kF32Rows - 1) / kF32Rows));

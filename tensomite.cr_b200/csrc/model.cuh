@@ -100,6 +100,7 @@ void register_names(tsm_model* m);
 void set_head_local(tsm_model* m);
 // The three ways a model is filled (model_gguf.cu, model_safetensors.cu, model.cu) and the way it is written out.
 int load_gguf_model(tsm_model* m, const char* path);
+int check_gguf_file(const char* path, std::string* why);
 int save_gguf_model(tsm_model* m, const char* path);
 int load_safetensors_model(tsm_model* m, const char* path, const tsm_model_config& config, int kind);
 int build_random(tsm_model* m, int kind, uint64_t seed);

@@ -94,6 +94,7 @@ static int64_t gguf_bytes(uint32_t kind, int64_t count) {
 static int gguf_kind_to_tsm(uint32_t kind) { return kind == 8 ? TSM_Q8_0 : kind == 2 ? TSM_Q4_0 : kind == 3 ? TSM_Q4_1 : TSM_F32; }
 
 static int gguf_open(tsm_ctx* ctx, const char* path, GgufFile& f) {
+    if (!path) return fail(ctx, TSM_ERR_ARG, "no path");
     int fd = open(path, O_RDONLY);
     if (fd < 0) return fail(ctx, TSM_ERR_IO, std::string(path) + " cannot be opened");
     struct stat st;
@@ -122,10 +123,16 @@ static int gguf_open(tsm_ctx* ctx, const char* path, GgufFile& f) {
         uint32_t nd = f.read<uint32_t>();
         if (nd > 8) { f.bad = true; break; }
         std::vector<int64_t> dims(nd);
-        for (uint32_t d = 0; d < nd; d++) dims[d] = (int64_t)f.read<uint64_t>();
+        for (uint32_t d = 0; d < nd; d++) {
+            uint64_t extent = f.read<uint64_t>();
+            if (extent == 0 || extent > (uint64_t)1 << 40) f.bad = true;  // no axis of a weight is empty or anywhere near 2^40 long
+            dims[d] = (int64_t)extent;
+        }
         info.shape.assign(dims.rbegin(), dims.rend());
         info.kind = f.read<uint32_t>();
-        info.offset = (int64_t)f.read<uint64_t>();
+        uint64_t offset = f.read<uint64_t>();
+        if (offset > (uint64_t)f.size) f.bad = true;  // also what a negative offset looks like once it is unsigned
+        info.offset = (int64_t)offset;
         infos.push_back(info);
     }
     if (f.bad) return fail(ctx, TSM_ERR_IO, std::string(path) + " is malformed");
@@ -134,12 +141,15 @@ static int gguf_open(tsm_ctx* ctx, const char* path, GgufFile& f) {
     int64_t start = (f.pos + alignment - 1) / alignment * alignment;
     for (auto& info : infos) {
         int64_t count = 1;
-        for (int64_t d : info.shape) count *= d;
+        for (int64_t d : info.shape) {
+            if (count > ((int64_t)1 << 46) / d) return fail(ctx, TSM_ERR_IO, info.name + ": more values than any file holds");
+            count *= d;
+        }
         int64_t bytes = gguf_bytes(info.kind, count);
         if (bytes < 0) return fail(ctx, TSM_ERR_UNSUPPORTED, info.name + ": GGUF tensor type " + std::to_string(info.kind) + " is not supported yet");
         if ((info.kind == 2 || info.kind == 3 || info.kind == 8) && (info.shape.empty() || info.shape.back() % 32 != 0))
             return fail(ctx, TSM_ERR_IO, info.name + ": rows of " + std::to_string(info.shape.empty() ? 0 : info.shape.back()) + " do not split into blocks of 32");
-        if (info.offset % alignment != 0 || start + info.offset + bytes > f.size)
+        if (info.offset < 0 || info.offset % alignment != 0 || bytes > f.size || start + info.offset > f.size - bytes)
             return fail(ctx, TSM_ERR_IO, info.name + ": " + std::to_string(bytes) + " bytes at " + std::to_string(info.offset) + " do not fit " + path);
         f.entries[info.name] = GgufEntry{info.kind, info.shape, start + info.offset, bytes};
         f.order.push_back(info.name);
@@ -183,6 +193,10 @@ static int upload_f32(tsm_model* m, GgufFile& f, const std::string& name, int64_
 struct RowSource {
     std::string name;
     int heads;  // > 0: undo llama.cpp's rotary row order for this many heads (llama.cr:226-235)
+    // A Linear under tensomite's own names: while it is unquantised the file holds it as the module does, [inputs, outputs]
+    // (modules.cr:1-20; Module#load reverses the shape for block formats only, module.cr:217-228), so it is transposed on
+    // the way in; a block format is [outputs, inputs] already.
+    bool linear_of_module = false;
 };
 
 // Uploads one or several [n_i, k] block tensors as one row-joined weight (Linear.merge, modules.cr:36-54).
@@ -194,12 +208,14 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
         auto found = f.entries.find(part.name);
         if (found == f.entries.end()) return fail(m->ctx, TSM_ERR_IO, "the file lacks " + part.name);
         const GgufEntry& e = found->second;
-        if (e.shape.size() != 2 || e.shape[1] != k)
-            return fail(m->ctx, TSM_ERR_ARG, part.name + ": the file's shape does not match the model's [" + std::to_string(expect_n) + ", " + std::to_string(k) + "]");
+        const bool flip = part.linear_of_module && (e.kind == 0 || e.kind == 1 || e.kind == 30);
+        if (e.shape.size() != 2 || e.shape[flip ? 0 : 1] != k)
+            return fail(m->ctx, TSM_ERR_ARG, part.name + ": the file's shape does not match the model's " +
+                                                 (flip ? "[" + std::to_string(k) + ", " + std::to_string(expect_n) + "]" : "[" + std::to_string(expect_n) + ", " + std::to_string(k) + "]"));
         int this_kind = gguf_kind_to_tsm(e.kind);
         if (kind != -2 && kind != this_kind) return fail(m->ctx, TSM_ERR_UNSUPPORTED, "joined projections must share a format");
         kind = this_kind;
-        total_rows += e.shape[0];
+        total_rows += e.shape[flip ? 1 : 0];
     }
     if (total_rows != expect_n) return fail(m->ctx, TSM_ERR_ARG, parts[0].name + ": the file holds " + std::to_string(total_rows) + " rows, the model " + std::to_string(expect_n));
     int64_t row_bytes = weight_bytes(kind, 1, k);
@@ -208,12 +224,20 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
     for (auto& part : parts) {
         const GgufEntry& e = f.entries[part.name];
         const uint8_t* src = f.data + e.offset;
-        int64_t rows = e.shape[0];
-        std::vector<float> wide;
+        const bool flip = part.linear_of_module && (e.kind == 0 || e.kind == 1 || e.kind == 30);
+        int64_t rows = e.shape[flip ? 1 : 0];
+        std::vector<float> wide, turned;
         if (e.kind == 1 || e.kind == 30) {  // F16 / BF16 matrices become F32 weights
             wide.resize((size_t)(rows * k));
             widen_halves((const uint16_t*)src, rows * k, e.kind == 30, wide.data());
             src = (const uint8_t*)wide.data();
+        }
+        if (flip) {  // [k, rows] in the file -> the rows the products read
+            const float* from = (const float*)src;
+            turned.resize((size_t)(rows * k));
+            for (int64_t i = 0; i < (int64_t)k; i++)
+                for (int64_t r = 0; r < rows; r++) turned[(size_t)(r * k + i)] = from[i * rows + r];
+            src = (const uint8_t*)turned.data();
         }
         if (part.heads > 0) {
             int64_t half = rows / part.heads / 2;
@@ -265,6 +289,7 @@ static int load_llama(tsm_model* m, GgufFile& f) {
     if (f.strings.count("llama.rope.scaling.type") && f.strings["llama.rope.scaling.type"] != "none")
         return fail(m->ctx, TSM_ERR_UNSUPPORTED, "rope scaling " + f.strings["llama.rope.scaling.type"] + " is not supported");
     if (!f.entries.count("token_embd.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks token_embd.weight");
+    if (f.entries["token_embd.weight"].shape.size() != 2) return fail(m->ctx, TSM_ERR_IO, "token_embd.weight is not a matrix");
     c.vocab = (int)num("vocab_size", (double)f.entries["token_embd.weight"].shape[0], false, &missing);
     c.tied = f.entries.count("output.weight") ? 0 : 1;
     TSM_TRY(check_config(m->ctx, c));
@@ -314,6 +339,8 @@ static int load_gpt2(tsm_model* m, GgufFile& f) {
     if (!f.strings.count("gpt2.heads")) return fail(m->ctx, TSM_ERR_IO, "the file lacks gpt2.heads");
     c.heads = atoi(f.strings["gpt2.heads"].c_str());
     if (!f.entries.count("wte.weight") || !f.entries.count("wpe.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks wte.weight or wpe.weight");
+    if (f.entries["wte.weight"].shape.size() != 2 || f.entries["wpe.weight"].shape.size() != 2)
+        return fail(m->ctx, TSM_ERR_IO, "wte.weight and wpe.weight must be matrices");
     c.vocab = (int)f.entries["wte.weight"].shape[0];
     c.width = (int)f.entries["wte.weight"].shape[1];
     c.context = (int)f.entries["wpe.weight"].shape[0];
@@ -340,21 +367,41 @@ static int load_gpt2(tsm_model* m, GgufFile& f) {
         TSM_TRY(upload_f32(m, f, p + "ln_1.bias", c.width, &l.norm1_b));
         TSM_TRY(upload_f32(m, f, p + "ln_2.weight", c.width, &l.norm2_w));
         TSM_TRY(upload_f32(m, f, p + "ln_2.bias", c.width, &l.norm2_b));
-        TSM_TRY(upload_rows(m, f, {{p + "attn.c_attn.weight", 0}}, c.width, 3 * c.width, &l.qkv, shard_ranges(m, SHARD_QKV)));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_attn.weight", 0, true}}, c.width, 3 * c.width, &l.qkv, shard_ranges(m, SHARD_QKV)));
         TSM_TRY(upload_bias(m, f, p + "attn.c_attn.bias", 3 * c.width, &l.qkv.bias));
         TSM_TRY(shard_bias(m, &l.qkv.bias, shard_ranges(m, SHARD_QKV)));
-        TSM_TRY(upload_rows(m, f, {{p + "attn.c_proj.weight", 0}}, c.width, c.width, &l.o, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(upload_rows(m, f, {{p + "attn.c_proj.weight", 0, true}}, c.width, c.width, &l.o, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(upload_bias(m, f, p + "attn.c_proj.bias", c.width, &l.o.bias));
         TSM_TRY(shard_bias(m, &l.o.bias, shard_ranges(m, SHARD_WIDTH)));
-        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_fc.weight", 0}}, c.width, c.hidden, &l.up, shard_ranges(m, SHARD_UP)));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_fc.weight", 0, true}}, c.width, c.hidden, &l.up, shard_ranges(m, SHARD_UP)));
         TSM_TRY(upload_bias(m, f, p + "mlp.c_fc.bias", c.hidden, &l.up.bias));
         TSM_TRY(shard_bias(m, &l.up.bias, shard_ranges(m, SHARD_UP)));
-        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
+        TSM_TRY(upload_rows(m, f, {{p + "mlp.c_proj.weight", 0, true}}, c.hidden, c.width, &l.down, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(upload_bias(m, f, p + "mlp.c_proj.bias", c.width, &l.down.bias));
         TSM_TRY(shard_bias(m, &l.down.bias, shard_ranges(m, SHARD_WIDTH)));
         TSM_TRY(shard_inputs(m, l));
     }
     return TSM_OK;
+}
+
+// Reads a file's header and tensor table the way the loaders do, without a device: TSM_OK, or TSM_ERR_IO / _UNSUPPORTED with
+// the reason in `why`.
+int check_gguf_file(const char* path, std::string* why) {
+    tsm_ctx scratch;  // only its message slot is used
+    GgufFile f;
+    int rc = gguf_open(&scratch, path, f);
+    if (rc == TSM_OK) {
+        std::string arch = f.strings.count("general.architecture") ? f.strings["general.architecture"] : "";
+        if (arch == "llama") {
+            if (!f.entries.count("token_embd.weight") || f.entries["token_embd.weight"].shape.size() != 2)
+                rc = fail(&scratch, TSM_ERR_IO, "token_embd.weight is missing or not a matrix");
+        } else if (f.strings.count("gpt2.heads")) {
+            for (const char* name : {"wte.weight", "wpe.weight"})
+                if (!f.entries.count(name) || f.entries[name].shape.size() != 2) rc = fail(&scratch, TSM_ERR_IO, std::string(name) + " is missing or not a matrix");
+        }
+    }
+    if (why) *why = scratch.message;
+    return rc;
 }
 
 // Llama.load / GPT2.load of a .gguf file: the family is read from the metadata.
@@ -384,6 +431,7 @@ struct SavedTensor {
     int64_t size;                // bytes
     int64_t row_bytes;
     int heads;                   // > 0: rows go back into llama.cpp's rotary order for this many heads
+    bool turned = false;         // an unquantised Linear under tensomite's names goes out [inputs, outputs]
 };
 
 static uint32_t gguf_kind_of(int kind) { return kind == TSM_Q8_0 ? 8 : kind == TSM_Q4_0 ? 2 : kind == TSM_Q4_1 ? 3 : 0; }
@@ -406,6 +454,15 @@ static int saved_vector(tsm_model* m, const float* values, const std::string& na
 static int fetch_saved(tsm_model* m, const SavedTensor& t, std::vector<uint8_t>& bytes) {
     bytes.resize((size_t)t.size);
     TSM_TRY(tsm_download(m->ctx, bytes.data(), (tsm_dptr)(uintptr_t)t.source, t.size));
+    if (t.turned) {  // held [n, k], written [k, n]
+        const int64_t k = t.shape[0], n = t.shape[1];
+        std::vector<uint8_t> file((size_t)t.size);
+        const float* held = (const float*)bytes.data();
+        float* out = (float*)file.data();
+        for (int64_t r = 0; r < n; r++)
+            for (int64_t i = 0; i < k; i++) out[i * n + r] = held[r * k + i];
+        bytes.swap(file);
+    }
     if (t.heads > 0) {
         std::vector<uint8_t> file((size_t)t.size);
         int64_t rows = t.size / t.row_bytes, half = rows / t.heads / 2, held = 0;
@@ -488,6 +545,10 @@ int save_gguf_model(tsm_model* m, const char* path) {
             const std::pair<const Linear*, const char*> parts[] = {{&l.qkv, "attn.c_attn"}, {&l.o, "attn.c_proj"}, {&l.up, "mlp.c_fc"}, {&l.down, "mlp.c_proj"}};
             for (auto& part : parts) {
                 TSM_TRY(saved_rows(m, *part.first, p + part.second + ".weight", 0, part.first->n, 0, tensors));
+                if (part.first->kind == TSM_F32) {  // as Module#save writes an unquantised Linear: [inputs, outputs]
+                    tensors.back().turned = true;
+                    tensors.back().shape = {(int64_t)part.first->k, (int64_t)part.first->n};
+                }
                 TSM_TRY(saved_vector(m, part.first->bias, p + part.second + ".bias", part.first->n, tensors));
             }
         }

@@ -254,6 +254,8 @@ static int st_linear(tsm_model* m, StFile& f, const std::vector<std::string>& na
 static int load_gpt2_safetensors(tsm_model* m, StFile& f, int heads, int kind) {
     std::string p = f.entries.count("transformer.wte.weight") ? "transformer." : "";
     if (!f.entries.count(p + "wte.weight") || !f.entries.count(p + "wpe.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks wte.weight or wpe.weight");
+    if (f.entries[p + "wte.weight"].shape.size() != 2 || f.entries[p + "wpe.weight"].shape.size() != 2)
+        return fail(m->ctx, TSM_ERR_IO, "wte.weight and wpe.weight must be matrices");
     tsm_model_config& c = m->cfg;
     c.arch = 1;
     c.vocab = (int)f.entries[p + "wte.weight"].shape[0];
@@ -301,6 +303,7 @@ static int load_gpt2_safetensors(tsm_model* m, StFile& f, int heads, int kind) {
 // directory's config.json, which the host reads: llama.cr:165-175); the other sizes from the shapes.
 static int load_llama_safetensors(tsm_model* m, StFile& f, const tsm_model_config& given, int kind) {
     if (!f.entries.count("model.embed_tokens.weight")) return fail(m->ctx, TSM_ERR_IO, "the file lacks model.embed_tokens.weight");
+    if (f.entries["model.embed_tokens.weight"].shape.size() != 2) return fail(m->ctx, TSM_ERR_IO, "model.embed_tokens.weight must be a matrix");
     tsm_model_config& c = m->cfg;
     c = given;
     c.arch = 0;
@@ -311,6 +314,8 @@ static int load_llama_safetensors(tsm_model* m, StFile& f, const tsm_model_confi
     if (c.layers < 1) return fail(m->ctx, TSM_ERR_IO, "the file has no model.layers.0");
     if (c.head_width <= 0 && c.heads > 0) c.head_width = c.width / c.heads;
     if (c.kv_heads <= 0) c.kv_heads = c.heads;
+    if (!f.entries.count("model.layers.0.mlp.gate_proj.weight") || f.entries["model.layers.0.mlp.gate_proj.weight"].shape.size() != 2)
+        return fail(m->ctx, TSM_ERR_IO, "model.layers.0.mlp.gate_proj.weight is missing or not a matrix");
     c.hidden = (int)f.entries["model.layers.0.mlp.gate_proj.weight"].shape[0];
     c.tied = f.entries.count("lm_head.weight") ? 0 : 1;
     TSM_TRY(check_config(m->ctx, c));

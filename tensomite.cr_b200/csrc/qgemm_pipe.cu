@@ -52,6 +52,8 @@ struct PipeParams {
     const float* residual;
     float* out;            // [m, n]
     ErrorRecord* errors;
+    unsigned spins;        // polls after which a wait gives up
+    int skip_chunks;       // stages the producer leaves out at the end (0 but for tsm_debug_wait_limit's test of the waits)
 };
 
 __device__ __forceinline__ unsigned p_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -73,9 +75,10 @@ __device__ __forceinline__ bool p_mbar_try_wait(uint64_t* bar, unsigned parity) 
         : "memory");
     return ok != 0;
 }
-// Bounded: gives up after kPipeSpins polls, or as soon as another warp has raised the CTA's abort flag.
-__device__ __forceinline__ bool p_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
-    for (unsigned spin = 0; spin < kPipeSpins; spin++) {
+// Bounded: gives up after `limit` polls (kPipeSpins unless a test lowered it), or as soon as another warp has raised the
+// CTA's abort flag.
+__device__ __forceinline__ bool p_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned limit) {
+    for (unsigned spin = 0; spin < limit; spin++) {
         if (p_mbar_try_wait(bar, parity)) return true;
         if (spin > 1024) {
             if (*abort_flag) return false;
@@ -186,9 +189,9 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
         const unsigned tx = (unsigned)(2 * L::ABOX + wr_max * 16 * WP + L::SCALE_BYTES);
         int issued = 0;
         bool ok = true;
-        for (int chunk = 0; chunk < chunks; chunk++) {
+        for (int chunk = 0; chunk < chunks - p.skip_chunks; chunk++) {
             int s = chunk % kPipeStages;
-            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag);
+            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag, p.spins);
             if (!ok) break;
             unsigned char* base = stages + (size_t)s * stage_bytes;
             p_mbar_expect_tx(&full[s], tx);
@@ -204,7 +207,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
             *abort_flag = 1;
             atomicExch(&p.errors->timeout, 1);
             for (int chunk = max(0, issued - kPipeStages); chunk < issued; chunk++)
-                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1);
+                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1, p.spins);
         }
         return;
     }
@@ -238,7 +241,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
     bool ok = true;
     for (int chunk = 0; chunk < chunks; chunk++) {
         int s = chunk % kPipeStages;
-        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag);
+        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag, p.spins);
         if (!ok) break;
         const unsigned char* base = stages + (size_t)s * stage_bytes;
         const unsigned char* slot_a = base + L::weights_at() + (size_t)ra * WP;
@@ -408,9 +411,9 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
         const unsigned tx = (unsigned)(2 * L::ABOX + wr_max * 8 * WP + L::SCALE_BYTES);
         int issued = 0;
         bool ok = true;
-        for (int chunk = 0; chunk < chunks; chunk++) {
+        for (int chunk = 0; chunk < chunks - p.skip_chunks; chunk++) {
             int s = chunk % kPipeStages;
-            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag);
+            if (chunk >= kPipeStages) ok = p_mbar_wait(&empty[s], (unsigned)((chunk / kPipeStages - 1) & 1), abort_flag, p.spins);
             if (!ok) break;
             unsigned char* base = stages + (size_t)s * stage_bytes;
             p_mbar_expect_tx(&full[s], tx);
@@ -425,7 +428,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
             *abort_flag = 1;
             atomicExch(&p.errors->timeout, 1);
             for (int chunk = max(0, issued - kPipeStages); chunk < issued; chunk++)
-                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1);
+                p_mbar_wait(&full[chunk % kPipeStages], (unsigned)((chunk / kPipeStages) & 1), abort_flag + 1, p.spins);
         }
         return;
     }
@@ -458,7 +461,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
     bool ok = true;
     for (int chunk = 0; chunk < chunks; chunk++) {
         int s = chunk % kPipeStages;
-        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag);
+        ok = p_mbar_wait(&full[s], (unsigned)((chunk / kPipeStages) & 1), abort_flag, p.spins);
         if (!ok) break;
         const unsigned char* base = stages + (size_t)s * stage_bytes;
         const unsigned char* wbase = base + L::weights_at() + (size_t)(wr * 8) * WP;
@@ -726,6 +729,8 @@ int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int
     PipeParams p;
     p.w = w, p.n = n, p.nb = k / 32, p.m = rows, p.groups = (n + 15) / 16, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
     p.errors = ctx->errors;
+    p.spins = ctx->wait_spins ? ctx->wait_spins : kPipeSpins;
+    p.skip_chunks = ctx->starve_copies ? 1 : 0;
     switch (kind) {
         case TSM_Q8_0: return launch_pipe_kind<TSM_Q8_0>(ctx, p);
         case TSM_Q4_0: return launch_pipe_kind<TSM_Q4_0>(ctx, p);

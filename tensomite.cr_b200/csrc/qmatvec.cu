@@ -509,6 +509,7 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
 
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out) {
+    OpTimer timer(ctx, kind == TSM_Q8_0 ? "BlockMatMul q8_0" : kind == TSM_Q4_0 ? "BlockMatMul q4_0" : "BlockMatMul q4_1", rows, k, n);
     if (k <= 0 || k % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
     if (((uintptr_t)w & 1) != 0) return fail(ctx, TSM_ERR_ARG, "block weights must start at an even address");
     if (rows == 0 || n == 0) return TSM_OK;

@@ -37,6 +37,7 @@ QuantizedActs quant_scratch_layout(void* base, int rows, int k) {
 
 int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t x_stride, float* scales, float* sums,
                          int* totals, int8_t* qs) {
+    OpTimer timer(ctx, "QuantizeRows", rows, k);
     if (k % 32 != 0 || rows < 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
     int64_t blocks = (int64_t)rows * (k / 32);
     if (blocks == 0) return TSM_OK;
@@ -108,6 +109,7 @@ __global__ void quantize_blocks_kernel(const float* __restrict__ x, int64_t bloc
 }
 
 int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind, uint8_t* out) {
+    OpTimer timer(ctx, "Quantize", count);
     if (count % 32 != 0) return fail(ctx, TSM_ERR_ARG, std::to_string(count) + " values do not split into blocks of 32");
     if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
     int64_t blocks = count / 32;
@@ -149,6 +151,7 @@ __global__ void dequantize_blocks_kernel(const uint8_t* __restrict__ blocks, int
 }
 
 int launch_dequantize_blocks(tsm_ctx* ctx, const uint8_t* blocks, int64_t count, int kind, float* out) {
+    OpTimer timer(ctx, "Dequantize", count);
     if (count % 32 != 0) return fail(ctx, TSM_ERR_ARG, std::to_string(count) + " values do not split into blocks of 32");
     if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
     if (count == 0) return TSM_OK;
@@ -182,6 +185,7 @@ __global__ void gather_blocks_kernel(const uint8_t* __restrict__ table, int kind
 
 int launch_gather_blocks(tsm_ctx* ctx, const uint8_t* table, int kind, int table_rows, int width, const int* ids,
                          int count, float* out, const uint8_t* table2, const int* ids2, int ids2_stride) {
+    OpTimer timer(ctx, "Gather blocks", count, width);
     if (width % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(width) + " do not split into blocks of 32");
     if (kind < 0 || kind > 2) return fail(ctx, TSM_ERR_UNSUPPORTED, "not a block format");
     int64_t total = (int64_t)count * width;
@@ -213,6 +217,7 @@ __global__ void gather_f32_kernel(const float* __restrict__ table, int table_row
 
 int launch_gather_f32(tsm_ctx* ctx, const float* table, int table_rows, int width, const int* ids, int count, float* out,
                       const float* table2, const int* ids2, int ids2_stride) {
+    OpTimer timer(ctx, "Gather", count, width);
     int64_t total = (int64_t)count * width;
     if (total == 0) return TSM_OK;
     TSM_CUDA(ctx, launch_chained(ctx, gather_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, table, table_rows, width, ids, total, out,
@@ -246,6 +251,7 @@ __global__ void normal_fill_kernel(float* out, int64_t count, float mean, float 
 }
 
 int launch_normal_fill(tsm_ctx* ctx, float* out, int64_t count, float mean, float stddev, uint64_t seed) {
+    OpTimer timer(ctx, "Fill normal", count);
     if (count == 0) return TSM_OK;
     int64_t pairs = (count + 1) / 2;
     normal_fill_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, ctx->stream>>>(out, count, mean, stddev, seed);

@@ -165,6 +165,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
 
 static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w, const float* b, int rows, int n, float eps,
                        float* out, const QuantizedActs* quantized) {
+    OpTimer timer(ctx, layer ? "LayerNorm" : "RMSNorm", rows, n);
     if (rows == 0 || n == 0) return TSM_OK;
     if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
     if ((size_t)n * 4 > 100 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "norm rows over 25600 values");
@@ -228,6 +229,7 @@ __global__ void rope_kernel(const float* __restrict__ x, int tokens, int heads, 
 
 int launch_rope(tsm_ctx* ctx, const float* x, int tokens, int heads, int width, int64_t x_stride, const float* cos_table,
                 const float* sin_table, int context, const int* positions, float* out) {
+    OpTimer timer(ctx, "Rope", tokens, heads, width);
     if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "rotary embeddings need an even width, not " + std::to_string(width));
     int64_t total = (int64_t)tokens * heads * (width / 2);
     if (total == 0) return TSM_OK;
@@ -259,10 +261,31 @@ __global__ void write_rows_kernel(float* cache, int rows, int heads, int capacit
 
 int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capacity, int width, const float* values,
                       int64_t v_stride, int tokens, const int* slots) {
+    OpTimer timer(ctx, "WriteRows", tokens, heads, width);
     int64_t total = (int64_t)tokens * heads * width;
     if (total == 0) return TSM_OK;
     write_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(cache, rows, heads, capacity, width, values,
                                                                                v_stride, total, slots, ctx->errors);
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
+}
+
+// Op::Write (Tensor#write, tensor/structural.cr:64-74; copy_into_f32, kernels.cu:59-63) for a dense value written into a
+// slice of a dense tensor along one axis: the region is `outer` runs of `chunk` consecutive floats, run o starting at
+// dst[o * pitch + offset].
+__global__ void write_region_kernel(float* dst, const float* __restrict__ src, int64_t total, int64_t pitch, int64_t chunk, int64_t offset) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    int64_t o = i / chunk, j = i % chunk;
+    dst[o * pitch + offset + j] = src[i];
+}
+
+int launch_write_region(tsm_ctx* ctx, float* dst, const float* src, int64_t outer, int64_t pitch, int64_t chunk, int64_t offset) {
+    OpTimer timer(ctx, "Write", outer, chunk);
+    int64_t total = outer * chunk;
+    if (total == 0) return TSM_OK;
+    write_region_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(dst, src, total, pitch, chunk, offset);
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
@@ -306,6 +329,7 @@ __global__ void rope_append_kernel(float* qkv, int tokens, int heads, int kv_hea
 int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_heads, int width, const float* cos_table,
                        const float* sin_table, int context, const int* table, float* keys, float* values, int rows,
                        int capacity) {
+    OpTimer timer(ctx, "Rope+WriteRows", tokens, heads + 2 * kv_heads, width);
     if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "head width must be even, not " + std::to_string(width));
     int64_t total = (int64_t)tokens * (heads + 2 * kv_heads) * (width / 2);
     if (total == 0) return TSM_OK;
@@ -362,6 +386,7 @@ __global__ void activation_kernel(const float* __restrict__ a, const float* __re
 
 static int launch_activation(tsm_ctx* ctx, bool gelu, const float* a, const float* b, int rows, int n, int64_t in_stride,
                              float* out, const QuantizedActs* quantized) {
+    OpTimer timer(ctx, gelu ? "Kernel gelu" : "Kernel swiglu", rows, n);
     if (rows == 0 || n == 0) return TSM_OK;
     if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
     int64_t items = (int64_t)rows * ((n + 31) / 32);
@@ -392,6 +417,7 @@ __global__ void silu_kernel(const float* __restrict__ x, int64_t count, float* o
 }
 
 int launch_silu(tsm_ctx* ctx, const float* x, int64_t count, float* out) {
+    OpTimer timer(ctx, "Kernel silu", count);
     if (count == 0) return TSM_OK;
     silu_kernel<<<(unsigned)((count + 255) / 256), 256, 0, ctx->stream>>>(x, count, out);
     count_launch(ctx);
@@ -405,6 +431,7 @@ __global__ void add_kernel(const float* __restrict__ a, const float* __restrict_
 }
 
 int launch_add(tsm_ctx* ctx, const float* a, const float* b, int64_t count, float* out) {
+    OpTimer timer(ctx, "Add", count);
     if (count == 0) return TSM_OK;
     add_kernel<<<(unsigned)((count + 255) / 256), 256, 0, ctx->stream>>>(a, b, count, out);
     count_launch(ctx);
@@ -469,6 +496,7 @@ __global__ void topk_kernel(const float* __restrict__ logits, int n, int count, 
 }
 
 int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, int* out_ids, float* out_values) {
+    OpTimer timer(ctx, "TopK", rows, n, count);
     if (count < 1 || count > n) return fail(ctx, TSM_ERR_ARG, "top " + std::to_string(count) + " of " + std::to_string(n));
     if (rows == 0) return TSM_OK;
     TSM_CUDA(ctx, launch_chained(ctx, topk_kernel, dim3(rows), dim3(1024), 0, logits, n, count, out_ids, out_values));
@@ -478,6 +506,7 @@ int launch_topk(tsm_ctx* ctx, const float* logits, int rows, int n, int count, i
 }
 
 int launch_argmax(tsm_ctx* ctx, const float* logits, int rows, int n, int* out) {
+    OpTimer timer(ctx, "ArgMax", rows, n);
     if (n < 1) return fail(ctx, TSM_ERR_ARG, "argmax of an empty row");
     return launch_topk(ctx, logits, rows, n, 1, out, nullptr);
 }

@@ -1,6 +1,8 @@
 // The context (device, stream, buffer pool, error record, counters) and the operator-level C ABI.
 #include <string.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace tsm {
@@ -106,6 +108,76 @@ void pool_release(tsm_ctx* ctx, void* p) {
     if (p) tsm_free(ctx, (tsm_dptr)(uintptr_t)p);
 }
 
+// ---- per-operator timing ------------------------------------------------------------------------
+
+static cudaEvent_t profile_event(tsm_ctx* ctx) {
+    Profile& pr = ctx->profile;
+    if (!pr.spare.empty()) {
+        cudaEvent_t e = pr.spare.back();
+        pr.spare.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return e;
+}
+
+OpTimer::OpTimer(tsm_ctx* c, const char* name, int64_t a, int64_t b, int64_t d) : ctx(c) {
+    Profile& pr = ctx->profile;
+    if (!pr.on) return;
+    if (pr.depth++ > 0) return;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(ctx->stream, &capturing);
+    if (capturing != cudaStreamCaptureStatusNone) return;
+    start = profile_event(ctx);
+    if (!start) return;
+    label = name;
+    if (pr.shapes && a >= 0) {
+        label += " [" + std::to_string(a);
+        if (b >= 0) label += "," + std::to_string(b);
+        if (d >= 0) label += "," + std::to_string(d);
+        label += "]";
+    }
+    cudaEventRecord(start, ctx->stream);
+    active = true;
+}
+
+OpTimer::~OpTimer() {
+    Profile& pr = ctx->profile;
+    if (!pr.on && !active) return;
+    if (pr.depth > 0) pr.depth--;
+    if (!active) return;
+    cudaEvent_t stop = profile_event(ctx);
+    if (!stop) {
+        pr.spare.push_back(start);
+        return;
+    }
+    cudaEventRecord(stop, ctx->stream);
+    pr.spans.push_back(ProfileSpan{label, start, stop});
+}
+
+// Waits for the stream, then moves every finished span into the totals.
+static int profile_collect(tsm_ctx* ctx) {
+    Profile& pr = ctx->profile;
+    if (pr.spans.empty()) return TSM_OK;
+    TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (ProfileSpan& span : pr.spans) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, span.start, span.stop) == cudaSuccess) {
+            auto& slot = pr.totals[span.label];
+            slot.first += 1, slot.second += (double)ms * 1e-3;
+        } else {
+            cudaGetLastError();
+        }
+        pr.spare.push_back(span.start), pr.spare.push_back(span.stop);
+    }
+    pr.spans.clear();
+    return TSM_OK;
+}
+
 }  // namespace tsm
 
 using namespace tsm;
@@ -179,6 +251,8 @@ int tsm_ctx_destroy(tsm_ctx* ctx) {
     if (ctx->quant.ptr) cudaFree(ctx->quant.ptr);
     if (ctx->attn.ptr) cudaFree(ctx->attn.ptr);
     if (ctx->order.ptr) cudaFree(ctx->order.ptr);
+    for (auto& span : ctx->profile.spans) cudaEventDestroy(span.start), cudaEventDestroy(span.stop);
+    for (cudaEvent_t e : ctx->profile.spare) cudaEventDestroy(e);
     cudaFree(ctx->errors);
     cudaFreeHost(ctx->errors_host);
     cudaStreamDestroy(ctx->stream);
@@ -244,7 +318,7 @@ int tsm_download(tsm_ctx* ctx, void* dst, tsm_dptr src, int64_t bytes) {
 int tsm_sync(tsm_ctx* ctx) {
     CTX_GUARD(ctx);
     TSM_CUDA(ctx, cudaMemcpyAsync(ctx->errors_host, ctx->errors, sizeof(ErrorRecord), cudaMemcpyDeviceToHost, ctx->stream));
-    TSM_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    TSM_TRY(tp_stream_wait(ctx));  // a plain stream wait on one GPU; bounded, with the communicator polled, in a group
     return check_error_record(ctx);
 }
 
@@ -253,13 +327,51 @@ int tsm_counters_read(tsm_ctx* ctx, tsm_counters* out) {
     *out = ctx->counters;
     std::lock_guard<std::mutex> guard(ctx->pool.lock);
     out->pool_held_bytes = ctx->pool.held_bytes;
-    out->host_ops = 0;
+    out->host_ops = 0;  // there is no host path to count
     return TSM_OK;
 }
 
 int tsm_counters_reset(tsm_ctx* ctx) {
     if (!ctx) return TSM_ERR_ARG;
     ctx->counters = tsm_counters{};
+    return TSM_OK;
+}
+
+int tsm_profile_begin(tsm_ctx* ctx, int shapes) {
+    CTX_GUARD(ctx);
+    TSM_TRY(profile_collect(ctx));
+    ctx->profile.totals.clear();
+    ctx->profile.on = true, ctx->profile.shapes = shapes != 0, ctx->profile.depth = 0;
+    return TSM_OK;
+}
+
+int tsm_profile_read(tsm_ctx* ctx, tsm_profile_entry* entries, int capacity, int* count) {
+    CTX_GUARD(ctx);
+    if (!count || capacity < 0 || (capacity > 0 && !entries)) return fail(ctx, TSM_ERR_ARG, "profile_read needs a place for its entries and their count");
+    TSM_TRY(profile_collect(ctx));
+    // longest total first, as the reference's report lists its operators (cuda/report.cr)
+    std::vector<std::pair<std::string, std::pair<int64_t, double>>> rows(ctx->profile.totals.begin(), ctx->profile.totals.end());
+    std::sort(rows.begin(), rows.end(), [](const auto& a, const auto& b) { return a.second.second > b.second.second; });
+    *count = (int)rows.size();
+    for (int i = 0; i < capacity && i < (int)rows.size(); i++) {
+        memset(&entries[i], 0, sizeof(tsm_profile_entry));
+        strncpy(entries[i].label, rows[i].first.c_str(), sizeof(entries[i].label) - 1);
+        entries[i].count = rows[i].second.first;
+        entries[i].seconds = rows[i].second.second;
+    }
+    return TSM_OK;
+}
+
+int tsm_profile_end(tsm_ctx* ctx) {
+    CTX_GUARD(ctx);
+    TSM_TRY(profile_collect(ctx));
+    ctx->profile.on = false, ctx->profile.depth = 0;
+    return TSM_OK;
+}
+
+int tsm_debug_wait_limit(tsm_ctx* ctx, unsigned spins, int starve_copies) {
+    if (!ctx) return TSM_ERR_ARG;
+    ctx->wait_spins = spins, ctx->starve_copies = starve_copies;
     return TSM_OK;
 }
 
@@ -354,6 +466,22 @@ int tsm_write_rows(tsm_ctx* ctx, tsm_dptr cache, int rows, int heads, int capaci
                    int tokens, tsm_dptr slots) {
     CTX_GUARD(ctx);
     return launch_write_rows(ctx, PF(cache), rows, heads, capacity, width, PCF(values), v_stride, tokens, PCI(slots));
+}
+
+int tsm_write(tsm_ctx* ctx, tsm_dptr dst, const int32_t* shape, int ndim, tsm_dptr value, int extent, int axis, int start) {
+    CTX_GUARD(ctx);
+    if (!shape || ndim < 1 || ndim > 8) return fail(ctx, TSM_ERR_ARG, "write takes tensors of 1 to 8 axes");
+    if (axis < 0) axis += ndim;
+    if (axis < 0 || axis >= ndim) return fail(ctx, TSM_ERR_ARG, "axis out of range");
+    int64_t outer = 1, inner = 1;
+    for (int i = 0; i < ndim; i++) {
+        if (shape[i] < 0) return fail(ctx, TSM_ERR_ARG, "negative size");
+        if (i < axis) outer *= shape[i];
+        if (i > axis) inner *= shape[i];
+    }
+    if (extent < 0 || start < 0 || (int64_t)start + extent > shape[axis])
+        return fail(ctx, TSM_ERR_ARG, "cannot write " + std::to_string(extent) + " at " + std::to_string(start) + " along an axis of " + std::to_string(shape[axis]));
+    return launch_write_region(ctx, PF(dst), PCF(value), outer, (int64_t)shape[axis] * inner, (int64_t)extent * inner, (int64_t)start * inner);
 }
 
 int tsm_ragged_attention(tsm_ctx* ctx, tsm_dptr q, int64_t q_stride, int tokens, int heads, int width, tsm_dptr k, tsm_dptr v,

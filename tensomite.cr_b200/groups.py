@@ -69,6 +69,53 @@ def join_tensor_parallel(device, dist, make_id=None):
     device.tp_init(rank, world, group_id)
 
 
+class StepGuard:
+    """Failure detection between steps, on the host.
+
+    A tensor-parallel step is a chain of kernels and exchanges that every rank must enter; a rank that has gone would leave
+    the others waiting inside a collective.  So the ranks talk on the host first: each one publishes the step it is about to
+    launch in a key-value store they share (a `torch.distributed` store, or anything with set / get / check), a rank that
+    leaves says so, and `before_step` refuses to launch, with `CommError`, once a peer has left or has not reached the step
+    within `patience` seconds.  The caller then drops its communicator (`device.tp_abort()`) and rebuilds the group; nothing
+    was in flight on the GPU, so nothing hangs there.  Ranks only ever leave between steps."""
+
+    def __init__(self, store, rank, world, patience=30.0, prefix="tsm/guard"):
+        self.store, self.rank, self.world, self.patience, self.prefix = store, rank, world, patience, prefix
+
+    def _key(self, what, rank):
+        return f"{self.prefix}/{what}/{rank}"
+
+    def leave(self):
+        """Tells the others that this rank will launch no more steps."""
+        self.store.set(self._key("gone", self.rank), b"1")
+
+    def gone(self):
+        """The ranks that have left."""
+        return [r for r in range(self.world) if r != self.rank and self.store.check([self._key("gone", r)])]
+
+    def before_step(self, step):
+        """Call on every rank before launching step `step`: returns once every peer is about to launch it too."""
+        import time
+        from . import binding
+        self.store.set(self._key("step", self.rank), str(step).encode())
+        deadline = time.monotonic() + self.patience
+        waiting = [r for r in range(self.world) if r != self.rank]
+        while waiting:
+            left = self.gone()
+            if left:
+                raise binding.CommError(f"rank {left[0]} left the group before step {step}")
+            still = []
+            for r in waiting:
+                key = self._key("step", r)
+                if not self.store.check([key]) or int(self.store.get(key)) < step:
+                    still.append(r)
+            waiting = still
+            if waiting:
+                if time.monotonic() > deadline:
+                    raise binding.CommError(f"rank {waiting[0]} did not reach step {step} within {self.patience:g} s")
+                time.sleep(0.002)
+
+
 def max_over_ranks(dist, seconds, device=None):
     """The slowest rank's time: what a multi-GPU number is quoted on."""
     import torch

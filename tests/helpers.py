@@ -180,22 +180,7 @@ def gpt2_tensors_from_hf(st, layers, quantize_kind=None, embeddings=False):
 
 def oracle_from_device_model(model, threads=1):
     """An oracle model over the very weights a device model holds (downloaded through the C ABI)."""
-    c = dict(model.config)
-    names = ["embed", "final_w"] + (["wpe", "final_b"] if c["arch"] == "gpt2" else [])
-    if not c["tied"]:
-        names.append("head")
-    for i in range(c["layers"]):
-        names += [f"{i}.{p}" for p in ("norm1_w", "norm2_w", "qkv", "o", "up", "down")]
-        if c["arch"] == "gpt2":
-            names += [f"{i}.{p}" for p in ("norm1_b", "norm2_b", "qkv_b", "o_b", "up_b", "down_b")]
-    t = {}
-    for name in names:
-        buf, kind, n, k = model.tensor(name)
-        if kind < 0:
-            t[name] = (-1, buf.numpy(np.float32).reshape(-1) if n == 1 else buf.numpy(np.float32).reshape(n, k))
-        else:
-            t[name] = (kind, buf.numpy(np.uint8).reshape(n, -1))
-    return oracle.Model(c, t, threads=threads)
+    return oracle.model_from_device(model, threads=threads)
 
 
 def write_gpt2_gguf(path, st, layers, heads, kind, embeddings=True):

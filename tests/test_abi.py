@@ -50,6 +50,53 @@ def test_gguf_round_trip(tmp_path):
     assert sorted(pkg.gguf.File(str(fixture)).entries) == ["q4_0", "q4_1", "q8_0"]
 
 
+def _gguf_bytes(tensors, metadata=None):
+    """A little GGUF v3 image: tensors = [(name, dims innermost first, kind, offset)], no payload beyond `tail` zeros."""
+    import struct
+
+    def text(s):
+        return struct.pack("<Q", len(s)) + s.encode()
+
+    metadata = metadata or {"general.architecture": "llama"}
+    out = struct.pack("<IIQQ", 0x46554747, 3, len(tensors), len(metadata))
+    for key, value in metadata.items():
+        out += text(key) + struct.pack("<I", 8) + text(value)
+    for name, dims, kind, offset in tensors:
+        out += text(name) + struct.pack("<I", len(dims)) + b"".join(struct.pack("<Q", d & (2 ** 64 - 1)) for d in dims)
+        out += struct.pack("<I", kind) + struct.pack("<Q", offset & (2 ** 64 - 1))
+    out += b"\0" * (-len(out) % 32)
+    return out
+
+
+def test_malformed_gguf_files_are_refused_not_read(tmp_path):
+    """gguf.cr:297-325 raises on files it cannot trust; here the same cases come back as TSM_ERR_IO with a reason, and no byte
+    outside the mapping is touched: a truncated file, an offset that is negative as a signed number, an offset past the end,
+    an empty axis, a count that overflows, a token table with one axis."""
+    lib = pkg.library()
+
+    def check(image):
+        path = tmp_path / "case.gguf"
+        path.write_bytes(image)
+        reason = C.create_string_buffer(512)
+        return lib.tsm_gguf_check(str(path).encode(), reason, 512), reason.value.decode()
+
+    good = _gguf_bytes([("token_embd.weight", [64, 4], 0, 0)]) + b"\0" * (64 * 4 * 4)
+    assert check(good) == (0, "")
+    rc, why = check(good[:-8])
+    assert rc == 5 and "do not fit" in why                                   # truncated payload
+    assert check(good[:40])[0] == 5                                          # truncated header
+    assert check(_gguf_bytes([("token_embd.weight", [64, 4], 0, -32)]) + b"\0" * 1024)[0] == 5       # "negative" offset
+    assert check(_gguf_bytes([("token_embd.weight", [64, 4], 0, 1 << 40)]) + b"\0" * 1024)[0] == 5   # far past the end
+    assert check(_gguf_bytes([("token_embd.weight", [0, 4], 0, 0)]) + b"\0" * 1024)[0] == 5          # an empty axis
+    assert check(_gguf_bytes([("token_embd.weight", [1 << 39, 1 << 39], 0, 0)]) + b"\0" * 1024)[0] == 5  # overflowing count
+    rc, why = check(_gguf_bytes([("token_embd.weight", [64], 0, 0)]) + b"\0" * 1024)
+    assert rc == 5 and "not a matrix" in why                                 # a 1-D token table
+    rc, why = check(_gguf_bytes([("wte.weight", [64], 0, 0), ("wpe.weight", [64, 4], 0, 256)], {"gpt2.heads": "2"}) + b"\0" * 2048)
+    assert rc == 5 and "wte.weight" in why
+    assert check(b"GGUF" + b"\0" * 8)[0] == 5                                # shorter than a header
+    assert lib.tsm_gguf_check(str(tmp_path / "absent.gguf").encode(), None, 0) == 5
+
+
 def test_unpermute_order_inverts_llama_cpps_rotary_layout():
     # models/llama.cr:226-235: loaded row head*hw + pair*(hw/2) + i = stored row head*hw + 2i + pair
     order = helpers.unpermute_order(16, 2)

@@ -89,6 +89,36 @@ def test_products_of_the_other_configurations(dev, name, rows, n, k, with_bias):
     wb.free()
 
 
+# The baseline's standalone sweep: every format x shape x column count, "bit-exact comparison against the reference"
+# (spec/block_matmul_spec.cr:103-123, 139-195 at these sizes).
+SWEEP_SHAPES = [(576, 1536), (2048, 8192), (4096, 14336), (14336, 4096), (128256, 4096)]
+
+
+@pytest.mark.parametrize("n,k", SWEEP_SHAPES)
+@pytest.mark.parametrize("name", ["Q4_0", "Q4_1", "Q8_0"])
+def test_sweep_of_formats_shapes_and_columns(dev, name, n, k):
+    """Activations of 1, 8, 64 and 256 columns (rows of x) over the same weights: a sample of 64 weight rows against the
+    oracle bit for bit at every column count, and each smaller product against the rows it shares with the 256-column
+    one, output for output (a row alone has the bits it has in the batch), which sets the streamed kernel (1 column), the
+    tensor-core kernels (8, 64) and their slabs of 64 activation rows (256) against one another."""
+    kind = oracle.KIND_NAMES[name]
+    rng = np.random.default_rng(n * 3 + k + kind)
+    w = random_blocks(rng, kind, n, k)
+    x = rng.normal(0, 1, (256, k)).astype(np.float32)
+    wb = dev.tensor(w)
+    sample = np.unique(np.concatenate([[0, 1, 15, 16, n - 17, n - 16, n - 1], rng.integers(0, n, 57)]))
+    want = oracle.matmul_reference(kind, x, np.ascontiguousarray(w[sample]), len(sample))
+    whole = dev.block_matmul(x, wb, kind, n)
+    assert np.array_equal(bits(whole[:, sample]), bits(want)), 256
+    for columns in (64, 8, 1):
+        got = dev.block_matmul(x[:columns], wb, kind, n)
+        assert np.array_equal(bits(got[:, sample]), bits(want[:columns])), columns
+        assert np.array_equal(bits(got), bits(whole[:columns])), columns
+    alone = dev.block_matmul(x[255:256], wb, kind, n)
+    assert np.array_equal(bits(alone[0]), bits(whole[255]))
+    wb.free()
+
+
 def uniform_fill(rng, shape):
     values = rng.random(shape, dtype=np.float32)
     values *= 2.0

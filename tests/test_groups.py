@@ -90,3 +90,64 @@ def test_two_gloo_ranks_agree_on_the_group_id_and_the_slowest_time():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert results == [(0, True, 2.0, True), (1, True, 2.0, True)]
+
+
+def _guarded_rank(rank, world, port, out):
+    """Two ranks step together; rank 1 leaves after step 2, between steps; rank 0 must learn of it on the host, before it
+    launches step 3, as a CommError, and not by waiting inside an exchange."""
+    import datetime
+    import torch.distributed as dist
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=rank == 0, timeout=datetime.timedelta(seconds=60))
+    guard = groups.StepGuard(store, rank, world, patience=20.0)
+    launched = []
+    try:
+        for step in range(5):
+            if rank == 1 and step == 3:
+                guard.leave()
+                break
+            guard.before_step(step)
+            launched.append(step)   # here the rank would call tsm_decode
+        out.put((rank, launched, None))
+    except pkg.CommError as problem:
+        out.put((rank, launched, str(problem)))
+    if rank == 0:
+        import time
+        time.sleep(0.5)  # the store lives in rank 0: let the peer finish talking to it
+
+
+def test_a_rank_that_leaves_between_steps_is_seen_on_the_host():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    procs = [ctx.Process(target=_guarded_rank, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = sorted(out.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results[1] == (1, [0, 1, 2], None)
+    rank0, launched, problem = results[0]
+    assert launched == [0, 1, 2] and problem is not None and "rank 1 left the group before step 3" in problem
+
+
+def test_a_rank_that_never_arrives_runs_the_patience_out():
+    class DictStore:
+        def __init__(self):
+            self.d = {}
+
+        def set(self, k, v):
+            self.d[k] = v
+
+        def get(self, k):
+            return self.d[k]
+
+        def check(self, keys):
+            return all(k in self.d for k in keys)
+
+    guard = groups.StepGuard(DictStore(), 0, 2, patience=0.05)
+    with pytest.raises(pkg.CommError, match="did not reach step 0"):
+        guard.before_step(0)
