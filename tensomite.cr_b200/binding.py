@@ -678,6 +678,6 @@ class GPT2(Model):
     pass
 
 
-__all__ = ["Q8_0", "Q4_0", "Q4_1", "F32", "BLOCK_BYTES", "FAST", "EXACT", "TP_GATHER", "TP_REDUCE", "Error", "DeviceError", "ShapeError", "ExecutionError",
+__all__ = ["tp_unique_id", "Q8_0", "Q4_0", "Q4_1", "F32", "BLOCK_BYTES", "FAST", "EXACT", "TP_GATHER", "TP_REDUCE", "Error", "DeviceError", "ShapeError", "ExecutionError",
            "DTypeError", "CommError", "TimeoutError_", "ModelConfig", "Counters", "declared_symbols", "library", "check_exports", "Buffer", "B200", "BatchCache",
            "Model", "Llama", "GPT2"]

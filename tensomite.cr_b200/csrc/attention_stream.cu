@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
     unsigned char* stages = smem + 8192;
     float* qs = (float*)(stages + kRing * STAGE_BYTES);    // [G][QP]
 
-    const int token = blockIdx.y;
+    const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;
     const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
     const int kvh = blockIdx.x / groups_per_kv;
     const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
@@ -493,7 +493,7 @@ __global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p) 
     __shared__ __align__(16) float ebuf[kEChunk];
     __shared__ float red[8];
     __shared__ float shared_total;
-    const int token = blockIdx.y, head = blockIdx.x;
+    const int token = p.order ? p.order[blockIdx.y] : blockIdx.y, head = blockIdx.x;
     const int row = p.table[3 * token], limit = p.table[3 * token + 1];
     if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) return;  // reported by the score kernel
     const int len = limit + 1;
@@ -648,6 +648,109 @@ __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, co
     }
 }
 
+// The value pass for launches with few (token, kv head) pairs, cut as finely as the ordered sums allow: every output column
+// of every head is its own chain over the positions, so a warp takes 8 columns x 4 heads (lane = head * 8 + column) and four
+// such warps share one 32-column box of every value tile.  A lane then carries ONE chain (two instructions per position
+// beside its two shared-memory loads), and a stream of 4096 positions is done in about as many times the add latency,
+// where the kernel above, with four chains per lane and one warp per box, takes four times as long on a quarter of the warps.
+template <int WIDTH>
+__global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
+    chained_kernel_entry();
+    constexpr int G = 4;
+    constexpr int BOX_BYTES = kTP * 128;
+    constexpr int kDeep = 6;
+    constexpr int kWarps = 4;
+    __shared__ __align__(1024) unsigned char stages[kDeep * BOX_BYTES];
+    __shared__ __align__(16) float wbuf[kWarps][2][kTP * G];
+    __shared__ uint64_t full[kDeep], empty[kDeep];
+    __shared__ int abort_words[2];
+    volatile int* abort_flag = abort_words;
+
+    const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;
+    const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
+    const int quarter = blockIdx.x & 3, group = blockIdx.x >> 2;
+    const int kvh = group / groups_per_kv;
+    const int head0 = kvh * per_kv + (group % groups_per_kv) * G;
+    const int row = p.table[3 * token], limit = p.table[3 * token + 1];
+    if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) return;   // reported by the score kernel
+    const int len = limit + 1;
+    const int tiles = (len + kTP - 1) / kTP;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int s = 0; s < kDeep; s++) s_mbar_init(&full[s], 1), s_mbar_init(&empty[s], kWarps);
+        abort_words[0] = 0, abort_words[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == kWarps) {
+        if (lane != 0) return;
+        const int plane = (row * p.kv_heads + kvh) * p.capacity;
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < tiles; j++) {
+            int s = j % kDeep;
+            if (j >= kDeep) ok = s_mbar_wait(&empty[s], (unsigned)((j / kDeep - 1) & 1), abort_flag);
+            if (!ok) break;
+            s_mbar_expect_tx(&full[s], BOX_BYTES);
+            s_tensor_load(stages + s * BOX_BYTES, &maps.v, 32 * quarter, plane + j * kTP, &full[s]);
+            issued = j + 1;
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int j = max(0, issued - kDeep); j < issued; j++) s_mbar_wait(&full[j % kDeep], (unsigned)((j / kDeep) & 1), abort_flag + 1);
+        }
+        return;
+    }
+    // consumer warp `warp`: columns 32 quarter + 8 warp + (lane & 7), head head0 + (lane >> 3)
+    const int h = lane >> 3, c8 = 8 * warp + (lane & 7);
+    const float* wrow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;   // weights [head][position]
+    const int piece = c8 >> 2, within = (c8 & 3) * 4;
+    float acc = 0.0f;
+    float w_next[G];   // as a loader, the lane is a position of the next tile: its four heads' weights
+#pragma unroll
+    for (int i = 0; i < G; i++) w_next[i] = lane < len ? wrow[(int64_t)i * p.capacity + lane] : 0.0f;
+    bool ok = true;
+    for (int tile = 0; tile < tiles; tile++) {
+        float* wt = wbuf[warp][tile & 1];
+        *(float4*)(wt + lane * G) = make_float4(w_next[0], w_next[1], w_next[2], w_next[3]);
+        int next = (tile + 1) * kTP + lane;
+#pragma unroll
+        for (int i = 0; i < G; i++) w_next[i] = next < len ? wrow[(int64_t)i * p.capacity + next] : 0.0f;
+        __syncwarp();
+        int s = tile % kDeep;
+        if (!s_mbar_wait(&full[s], (unsigned)((tile / kDeep) & 1), abort_flag)) ok = false, *abort_flag = 1;
+        const unsigned char* vt = stages + s * BOX_BYTES + within;
+        const float* wh = wt + h;
+        int count = min(kTP, len - tile * kTP);
+        if (count == kTP) {
+            float vv[kTP], ww[kTP];   // every load of the tile is issued before the chain starts
+#pragma unroll
+            for (int u = 0; u < kTP; u++) vv[u] = *(const float*)(vt + u * 128 + ((piece ^ (u & 7)) << 4)), ww[u] = wh[u * G];
+#pragma unroll
+            for (int u = 0; u < kTP; u++) acc = __fadd_rn(acc, __fmul_rn(ww[u], vv[u]));
+        } else {
+            for (int pos = 0; pos < count; pos++) {
+                float vv = *(const float*)(vt + pos * 128 + ((piece ^ (pos & 7)) << 4));
+                acc = __fadd_rn(acc, __fmul_rn(wh[pos * G], vv));
+            }
+        }
+        __syncwarp();
+        if (lane == 0) s_mbar_arrive(&empty[s]);
+    }
+    if (!ok && lane == 0) atomicExch(&p.errors->timeout, 1);
+    // a block of 32 columns lies across the CTA's four warps: the rows go out through shared memory so that the quantiser's
+    // warp-per-block arithmetic (quantize_block_q8) sees a block's 32 columns in one warp's lanes
+    __shared__ float rows_out[G][32];
+    rows_out[h][c8] = acc;
+    asm volatile("bar.sync 2, 128;" ::: "memory");   // the four consumer warps only; reached by all of them, gave up or not
+    if (*abort_flag) return;
+    const float mine = rows_out[warp][lane];          // warp = head, lane = column of the quarter
+    int64_t at = ((int64_t)token * p.heads + head0 + warp) * WIDTH + 32 * quarter + lane;
+    if (p.out) p.out[at] = mine;
+    if (p.sink.qs) quantize_block_q8(mine, lane, p.sink.scales + (at >> 5), p.sink.sums + (at >> 5), p.sink.totals + (at >> 5), p.sink.qs + at);
+}
+
 }  // namespace
 
 int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { return (int64_t)tokens * heads * capacity * 4 + 256; }
@@ -693,14 +796,18 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
             }
         }
         int64_t pairs = (int64_t)tokens * groups;
-        p.splits = (int)std::max<int64_t>(1, std::min<int64_t>(8, (2 * (int64_t)ctx->sm_count + pairs - 1) / pairs));
+        // enough position ranges for about four CTAs per SM, none shorter than 8 tiles
+        int64_t longest = ((int64_t)capacity + kTP - 1) / kTP;
+        p.splits = (int)std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(16, longest / 8), (4 * (int64_t)ctx->sm_count + pairs - 1) / pairs));
         TSM_CUDA(ctx, launch_chained(ctx, attention_scores_kernel<WIDTH>, dim3(groups, tokens, p.splits), dim3(kConsumers + 32), smem_scores, p, maps));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
         TSM_CUDA(ctx, launch_chained(ctx, attention_weights_kernel, dim3(heads, tokens), dim3(256), 0, p));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
-        TSM_CUDA(ctx, launch_chained(ctx, attention_values_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(64), 0, p, maps));
+        static const char* narrow = getenv("TSM_ATTN_VALUES_NARROW");   // the one-warp-per-box value pass, for timing it
+        if (narrow && narrow[0] == '1') TSM_CUDA(ctx, launch_chained(ctx, attention_values_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(64), 0, p, maps));
+        else TSM_CUDA(ctx, launch_chained(ctx, attention_values_wide_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(160), 0, p, maps));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
         return TSM_OK;

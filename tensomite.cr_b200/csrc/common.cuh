@@ -201,6 +201,9 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
 bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                              const float* bias, const float* residual, float* out);
+bool umma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
+int launch_block_matmul_umma(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
+                             const float* bias, const float* residual, float* out);
 int launch_block_matmul_mma(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                             const float* bias, const float* residual, float* out);
 int launch_quantize_blocks(tsm_ctx* ctx, const float* x, int64_t count, int kind, uint8_t* out);

@@ -497,6 +497,7 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
     else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, k, w, n, bias, residual, out, &taken)));
     else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, k, w, n, bias, residual, out, &taken)));
     if (taken) return TSM_OK;
+    if (rows > 4 && umma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_umma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     if (rows > 4 && pipe_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_pipe(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     if (rows > 4 && mma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_mma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     int nb = k / 32;

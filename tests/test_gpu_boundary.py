@@ -102,7 +102,7 @@ def test_profile_gives_gpu_time_per_operator(dev):
     assert got.tolist() == want.tolist()
     labels = {label: (count, seconds) for label, count, seconds in table}
     assert labels["RaggedAttention [2,4,64]"][0] == SMALL["layers"]
-    assert labels["BlockMatMul q4_0 [2,256,1024]"][0] == 2 * SMALL["layers"]   # gate/up of every layer, and the head: 1024 rows
+    assert labels["BlockMatMul q4_0 [2,256,1024]"][0] == SMALL["layers"] + 1   # gate/up of every layer, and the head: 1024 rows each
     assert labels["RMSNorm [2,256]"][0] == 2 * SMALL["layers"] + 1
     assert all(seconds > 0 for _, seconds in labels.values())
     assert [s for _, _, s in table] == sorted((s for _, _, s in table), reverse=True)

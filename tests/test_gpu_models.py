@@ -194,6 +194,34 @@ def test_tiny_gpt2_f32_safetensors_matches_pytorch_logits(dev, tmp_path):
     model.free()
 
 
+def test_an_f32_gpt2_saves_its_linears_as_the_module_holds_them(dev, tmp_path):
+    """GPT2.load("model.safetensors").save("model.gguf") without quantising: under tensomite's names an unquantised Linear
+    weight is [inputs, outputs] (modules.cr:1-20; Module#load reverses the shape for block formats only,
+    module.cr:217-228), so the file holds Hugging Face's Conv1D matrices as they are, and loads back to the same logits."""
+    g = golden()
+    path = tmp_path / "model.safetensors"
+    path.write_bytes(g["tiny_gpt2/safetensors"].tobytes())
+    st = helpers.read_safetensors(g["tiny_gpt2/safetensors"])
+    model = pkg.GPT2.load_safetensors(path, dev, dict(arch="gpt2", heads=4), pkg.F32)
+    saved = str(tmp_path / "saved.gguf")
+    model.save(saved)
+    f = helpers.gguf.File(saved)
+    for i in range(2):
+        for name in ("attn.c_attn", "attn.c_proj", "mlp.c_fc", "mlp.c_proj"):
+            hf = st[f"transformer.h.{i}.{name}.weight"]          # Conv1D: [inputs, outputs]
+            kind, shape, _ = f.raw(f"h.{i}.{name}.weight")
+            assert kind == helpers.gguf.F32 and list(shape) == list(hf.shape), (name, shape)
+            assert np.array_equal(bits(f.f32(f"h.{i}.{name}.weight").reshape(hf.shape)), bits(hf))
+    assert list(f.raw("wte.weight")[1]) == list(st["transformer.wte.weight"].shape)
+    again = pkg.GPT2.load(saved, dev)
+    prompt = g["tiny_gpt2/prompt_ids"].tolist()
+    want = model.forward([prompt], model.new_batch_cache(1, 64))
+    got = again.forward([prompt], again.new_batch_cache(1, 64))
+    assert np.array_equal(bits(got), bits(want))
+    assert np.max(np.abs(got - g["tiny_gpt2/logits"])) < 1e-4
+    model.free(), again.free()
+
+
 def test_tiny_gpt2_q8_0_with_f32_embeddings(dev, tmp_path):
     """Module#quantize(Q8_0) without embeddings: the tables stay F32, so the tied head is an F32 product fed by F32 rows
     while every layer reads quantised ones."""

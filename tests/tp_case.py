@@ -46,7 +46,7 @@ def main():
             got.append(logits)
             tokens_seen.append(tokens.tolist())
             ids = tokens.tolist()
-        run = model.decode_run(cache, ids, 5)
+        run = model.decode_run(cache, ids, 32)          # 32 greedy steps of every row, resident on the device
         text = model.generate(prompts[1], 12)
         # every rank holds the same results
         flat = np.concatenate([g.ravel() for g in got]).view(np.uint32).astype(np.int64)
@@ -64,15 +64,20 @@ def main():
                 want.append(logits)
                 assert tokens.tolist() == tokens_seen[step], (arch, "decode tokens", step)
                 ids = tokens.tolist()
-            assert np.array_equal(whole.decode_run(wcache, ids, 5), run), (arch, "device-resident run")
+            assert np.array_equal(whole.decode_run(wcache, ids, 32), run), (arch, "device-resident run: tokens differ from one GPU's")
             assert whole.generate(prompts[1], 12) == text, (arch, "generate")
             for step, (g, w) in enumerate(zip(got, want)):
                 assert np.array_equal(helpers.bits(g), helpers.bits(w)), (arch, "logits differ at", step)
             wcache.free(), whole.free()
         cache.free(), model.free()
         dist.barrier()
-    # ---- the all-reduce variant: o and down over each rank's own input columns.  Not the bits of one GPU: the reference's
-    #      budget for a GPU path, 0.001 nats KL per token and a few percent of the largest logit; every rank the same bits.
+    # ---- the all-reduce variant: o and down over each rank's own input columns.  Not the bits of one GPU: an output's
+    #      blocks are added in another order, so a sum can differ in its last bit, and one such bit can move an activation
+    #      across a rounding boundary of the 8-bit quantiser that feeds the next product, which alone moves a logit of
+    #      these small models by a few thousandths of the largest.  The 1e-3 relative bound on logits is therefore out of
+    #      reach for any reordered block sum (the measured figure is printed below); the variant is held to the reference's
+    #      own budget for a GPU path, 0.001 nats KL per token, and to 5e-2 of the largest logit; every rank has the same
+    #      bits; and its greedy tokens are compared with one GPU's over 32 steps and the agreement reported.
     def kl_per_token(want, got):
         def log_softmax(x):
             x = x.astype(np.float64)
@@ -97,7 +102,7 @@ def main():
             tokens, logits = model.decode(cache, ids, logits=True)
             got.append(logits)
             ids = tokens.tolist()
-        run = model.decode_run(cache, ids, 4)
+        run = model.decode_run(cache, ids, 32)
         flat = np.concatenate([g.ravel() for g in got]).view(np.uint32).astype(np.int64)
         mine = torch.tensor([int(flat.sum()), int(run.sum())], device=f"cuda:{local}")
         both = [torch.zeros_like(mine) for _ in range(world)]
@@ -108,7 +113,14 @@ def main():
             wcache = whole.new_batch_cache(4, 64)
             want = whole.forward_last(prompts, wcache)
             rel = float(np.abs(got[0] - want).max() / np.abs(want).max())
-            assert rel <= 5e-2 and kl_per_token(want, got[0]) <= 1e-3, (arch, "all-reduce variant too far from one GPU", rel)
+            kl = kl_per_token(want, got[0])
+            assert rel <= 5e-2 and kl <= 1e-3, (arch, "all-reduce variant too far from one GPU", rel, kl)
+            wids = [1, 2, 3, 4]
+            for _ in range(3):
+                wids = whole.decode(wcache, wids).tolist()
+            same = whole.decode_run(wcache, wids, 32) == run
+            print(f"all-reduce variant, {arch} {kind}: max relative logit error {rel:.2e}, KL {kl:.2e} nats, "
+                  f"{int(same.sum())} of {same.size} greedy tokens over 32 steps equal to one GPU's")
             wcache.free(), whole.free()
         cache.free(), model.free()
         dist.barrier()
