@@ -34,7 +34,19 @@ def stale():
 
 
 def build(verbose=False, force=False):
-    """Builds the shared library when a source is newer than it; returns its path."""
+    """Builds the shared library when a source is newer than it; returns its path.  Several processes may ask at once (one per
+    GPU under torch.distributed.run): a lock file lets one of them build while the others wait and then find it fresh."""
+    import fcntl
+    os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
+    with open(os.path.join(HERE, "build", ".lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(verbose, force)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose, force):
     if not force and not stale():
         return LIBRARY
     objects = []

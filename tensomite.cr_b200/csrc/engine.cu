@@ -178,6 +178,38 @@ static int launch_layer_reduced(tsm_model* m, tsm_cache* cache, int i, int total
     return TSM_OK;
 }
 
+// One layer of a TSM_TP_REDUCE step through the fused exchange (tp_exchange.cu).  On entry the exchange's activation buffer
+// holds the layer's first norm of every row, quantised; o and down write their partial products into the exchange region,
+// and each exchange kernel sums them over the ranks, adds the residual on the rows this rank owns, norms them with the NEXT
+// norm's weights and delivers the quantised rows to every rank.  Eight launches per layer, two of them exchanges.
+static int launch_layer_fused(tsm_model* m, tsm_cache* cache, int i, int total, const int* order, float scale) {
+    const tsm_model_config& c = m->cfg;
+    tsm_ctx* ctx = m->ctx;
+    Workspace& w = m->ws;
+    Layer& l = m->layers[i];
+    const int G = m->tp, hw = c.head_width;
+    const int heads_l = c.heads / G, kv_l = c.kv_heads / G, qn_l = heads_l * hw, qkvn_l = qn_l + 2 * kv_l * hw, hid_l = c.hidden / G;
+    const bool layer = c.arch == 1;
+    QuantizedActs qx = quant_scratch_layout(xchg_quantized(m), total, c.width);
+    QuantizedActs qb = quant_scratch_layout(w.qb, total, qn_l);
+    QuantizedActs qc = quant_scratch_layout(w.qc, total, hid_l);
+    TSM_TRY(product(m, qx, nullptr, total, l.qkv, nullptr, w.qkv));
+    TSM_TRY(launch_rope_append(ctx, w.qkv, total, heads_l, kv_l, hw, c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr,
+                               c.context, w.table, cache->keys[i], cache->values[i], cache->rows, cache->capacity));
+    TSM_TRY(launch_attention(ctx, w.qkv, qkvn_l, total, heads_l, hw, cache->keys[i], cache->values[i], cache->rows, kv_l, cache->capacity,
+                             w.table, scale, w.att, &qb, order));
+    TSM_TRY(product(m, qb, nullptr, total, l.o, nullptr, xchg_partial(m)));
+    TSM_TRY(launch_xchg_reduce_norm(m, total, w.x, nullptr, layer, l.norm2_w, l.norm2_b, c.eps));
+    TSM_TRY(product(m, qx, nullptr, total, l.up, nullptr, w.up));
+    if (c.arch == 0) TSM_TRY(launch_swiglu(ctx, w.up, w.up + hid_l, total, hid_l, 2 * (int64_t)hid_l, nullptr, &qc));
+    else TSM_TRY(launch_gelu(ctx, w.up, total, hid_l, nullptr, &qc));
+    TSM_TRY(product(m, qc, nullptr, total, l.down, nullptr, xchg_partial(m)));
+    const bool last = i + 1 == c.layers;
+    const float* next_w = last ? m->final_w : m->layers[i + 1].norm1_w;
+    const float* next_b = last ? m->final_b : m->layers[i + 1].norm1_b;
+    return launch_xchg_reduce_norm(m, total, w.x, nullptr, layer, next_w, next_b, c.eps);
+}
+
 // The head of a tensor-parallel step: this rank's vocabulary slice, the greedy pick across ranks, and (when asked) the
 // full logits in ws.logits.
 static int launch_head_sharded(tsm_model* m, const QuantizedActs& qh, int outputs, bool pick, bool full_logits) {
@@ -249,7 +281,19 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
         TSM_TRY(launch_length_order(ctx, w.table, total, w.order));
         order = w.order;
     }
+    // TSM_TP_REDUCE with mapped peer memory, every token an output (a decode step): the fused exchange; the first norm of the
+    // first layer is the only one computed on full rows
+    const bool fused = m->tp > 1 && m->tp_reduce && outputs == total && xchg_takes(m, total);
+    if (fused) {
+        QuantizedActs qx = quant_scratch_layout(xchg_quantized(m), total, c.width);
+        if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, m->layers[0].norm1_w, total, c.width, c.eps, nullptr, &qx));
+        else TSM_TRY(launch_layernorm(ctx, w.x, m->layers[0].norm1_w, m->layers[0].norm1_b, total, c.width, c.eps, nullptr, &qx));
+    }
     for (int i = 0; i < c.layers; i++) {
+        if (fused) {
+            TSM_TRY(launch_layer_fused(m, cache, i, total, order, scale));
+            continue;
+        }
         if (m->tp > 1) {
             if (m->tp_reduce) TSM_TRY(launch_layer_reduced(m, cache, i, total, order, qa, scale));
             else TSM_TRY(launch_layer_sharded(m, cache, i, total, order, qa, qb, qc, ordered, scale));
@@ -276,6 +320,8 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
         else TSM_TRY(launch_gelu(ctx, w.up, total, c.hidden, f.plain, f.quantized));
         TSM_TRY(product(m, qc, w.h, total, l.down, w.x, w.x));
     }
+    if (fused)   // the last exchange delivered the final norm of every row
+        return launch_head_sharded(m, quant_scratch_layout(xchg_quantized(m), total, c.width), outputs, pick, !pick);
     const float* xl = w.x;
     if (outputs < total) {
         TSM_TRY(launch_gather_f32(ctx, w.x, total, c.width, w.last, outputs, w.xl));
@@ -360,6 +406,7 @@ int tsm_model_free(tsm_model* model) {
     MODEL_GUARD(model);
     cudaStreamSynchronize(model->ctx->stream);
     free_workspace(model);
+    xchg_release(model);
     for (void* p : model->owned) pool_release(model->ctx, p);
     delete model;
     return TSM_OK;
@@ -379,6 +426,11 @@ int tsm_model_load_gguf(tsm_ctx* ctx, const char* path, tsm_model** out) {
     }
     set_head_local(m.get());
     register_names(m.get());
+    rc = xchg_setup(m.get());
+    if (rc != TSM_OK) {
+        tsm_model_free(m.release());
+        return rc;
+    }
     *out = m.release();
     return TSM_OK;
 }
@@ -408,6 +460,11 @@ int tsm_model_load_safetensors(tsm_ctx* ctx, const char* path, const tsm_model_c
     }
     set_head_local(m.get());
     register_names(m.get());
+    rc = xchg_setup(m.get());
+    if (rc != TSM_OK) {
+        tsm_model_free(m.release());
+        return rc;
+    }
     *out = m.release();
     return TSM_OK;
 }
@@ -429,6 +486,11 @@ int tsm_model_random(tsm_ctx* ctx, const tsm_model_config* config, int kind, uin
         return rc;
     }
     register_names(m.get());
+    rc = xchg_setup(m.get());
+    if (rc != TSM_OK) {
+        tsm_model_free(m.release());
+        return rc;
+    }
     *out = m.release();
     return TSM_OK;
 }
@@ -626,6 +688,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     if (!cache->graph) {
         // the step reads ids and positions from device memory, so one capture serves every later step
         cudaGraph_t graph = nullptr;
+        const int64_t exchanges_before = ctx->counters.collectives;
         TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         int rc = TSM_OK;
         cudaError_t e1 = cudaMemcpyAsync(w.ids, h_ids, (size_t)rows * 4, cudaMemcpyHostToDevice, ctx->stream);
@@ -641,6 +704,8 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
             if (e5 != cudaSuccess) rc = cuda_fail(ctx, e5, "cudaGraphInstantiate");
             cache->graph_kernels = kernel_nodes(graph);
             ctx->counters.launches -= cache->graph_kernels;  // captured, not launched; replays count below
+            cache->graph_collectives = (int)(ctx->counters.collectives - exchanges_before);
+            ctx->counters.collectives = exchanges_before;
         }
         if (graph) cudaGraphDestroy(graph);
         if (rc != TSM_OK) {
@@ -651,6 +716,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
     TSM_CUDA(ctx, cudaGraphLaunch(cache->graph, ctx->stream));
     ctx->counters.graph_replays++;
     ctx->counters.launches += cache->graph_kernels;
+    ctx->counters.collectives += cache->graph_collectives;
     ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
     ctx->counters.downloads += 1, ctx->counters.download_bytes += (int64_t)rows * 4;
     if (logits) {
@@ -713,6 +779,7 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
     ctx->counters.uploads += 2, ctx->counters.upload_bytes += (int64_t)rows * 16;
     if (!cache->run_graph) {
         cudaGraph_t graph = nullptr;
+        const int64_t exchanges_before = ctx->counters.collectives;
         TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         cudaError_t e0 = launch_chained(ctx, run_advance_kernel, dim3((rows + 255) / 256), dim3(256), 0, w.ids, w.table, w.picks, rows, cache->run_state);
         count_launch(ctx);
@@ -727,6 +794,8 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
             if (e3 != cudaSuccess) rc = cuda_fail(ctx, e3, "cudaGraphInstantiate");
             cache->run_kernels = kernel_nodes(graph);
             ctx->counters.launches -= cache->run_kernels;
+            cache->run_collectives = (int)(ctx->counters.collectives - exchanges_before);
+            ctx->counters.collectives = exchanges_before;
         }
         if (graph) cudaGraphDestroy(graph);
         if (rc != TSM_OK) {
@@ -742,6 +811,7 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
     }
     ctx->counters.graph_replays += steps;
     ctx->counters.launches += (int64_t)steps * cache->run_kernels;
+    ctx->counters.collectives += (int64_t)steps * cache->run_collectives;
     TSM_CUDA(ctx, cudaMemcpyAsync(tokens, cache->run_state + 1, (size_t)steps * rows * 4, cudaMemcpyDeviceToHost, ctx->stream));
     ctx->counters.downloads++, ctx->counters.download_bytes += (int64_t)steps * rows * 4;
     TSM_TRY(tsm_sync(ctx));

@@ -46,6 +46,15 @@ struct Workspace {
     int32_t* host = nullptr; // pinned: ids [T] + table [3T] + picks [T]
 };
 
+// The regions of the fused tensor-parallel exchange (tp_exchange.cu): this rank's and, mapped through CUDA IPC, the peers'.
+struct Exchange {
+    bool ready = false;
+    void* local = nullptr;
+    unsigned char* regions[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    int64_t bytes = 0, partial_at = 0, quant_at = 0;
+    int rows = 0, width = 0;
+};
+
 // Rows [start, start + count) of a matrix.
 struct RowRange {
     int64_t start, count;
@@ -67,6 +76,7 @@ struct tsm_model {
     int tp = 1, tp_rank = 0;     // tensor-parallel group of the context the model was built on
     bool tp_reduce = false;      // o and down split by input columns and all-reduced (TSM_TP_REDUCE), not by output rows
     tsm::Linear head_local;           // this rank's rows of the vocabulary head (a view when the head is the embedding table)
+    tsm::Exchange xchg;               // peer memory of the fused exchange (TSM_TP_REDUCE on GPUs that can map each other)
 };
 
 struct tsm_cache {
@@ -81,6 +91,7 @@ struct tsm_cache {
     int* run_state = nullptr;         // device: [0] steps done, then tokens [steps, rows]
     int64_t run_capacity = 0;         // ints in run_state
     int graph_kernels = 0, run_kernels = 0;  // kernel nodes per replay, for the launch counter
+    int graph_collectives = 0, run_collectives = 0;  // exchanges per replay
 };
 
 namespace tsm {
@@ -104,5 +115,12 @@ int check_gguf_file(const char* path, std::string* why);
 int save_gguf_model(tsm_model* m, const char* path);
 int load_safetensors_model(tsm_model* m, const char* path, const tsm_model_config& config, int kind);
 int build_random(tsm_model* m, int kind, uint64_t seed);
+// The fused exchange of a TSM_TP_REDUCE step (tp_exchange.cu).
+int xchg_setup(tsm_model* m);
+void xchg_release(tsm_model* m);
+bool xchg_takes(const tsm_model* m, int total);
+float* xchg_partial(tsm_model* m);
+void* xchg_quantized(tsm_model* m);
+int launch_xchg_reduce_norm(tsm_model* m, int total, float* x, const float* bias, bool layer, const float* w, const float* b, float eps);
 
 }  // namespace tsm

@@ -138,13 +138,16 @@ __device__ __forceinline__ void u_fence_before() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void u_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // J groups of 8 columns of 16 lanes in the accumulator-fragment shape: registers [4 j + e] = (lane g + 8 (e >> 1), column
-// 8 j + 2 t + (e & 1)) for thread 4 g + t.  The wait is part of the same statement, so nothing that reads the registers can be
-// scheduled before the data has arrived.
+// 8 j + 2 t + (e & 1)) for thread 4 g + t.  `load` only issues the read; `landed` waits for every read issued so far and
+// names the registers as its operands, so that nothing reading them can be scheduled before it.
 template <int J> struct UTmem;
 template <> struct UTmem<1> {
     static __device__ __forceinline__ void load(unsigned taddr, unsigned (&v)[4]) {
-        asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];\n\ttcgen05.wait::ld.sync.aligned;"
+        asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
                      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
+    }
+    static __device__ __forceinline__ void landed(unsigned (&v)[4]) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3])::"memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -152,8 +155,12 @@ template <> struct UTmem<1> {
 };
 template <> struct UTmem<2> {
     static __device__ __forceinline__ void load(unsigned taddr, unsigned (&v)[8]) {
-        asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n\ttcgen05.wait::ld.sync.aligned;"
+        asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
+    }
+    static __device__ __forceinline__ void landed(unsigned (&v)[8]) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])::"memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -162,10 +169,15 @@ template <> struct UTmem<2> {
 template <> struct UTmem<4> {
     static __device__ __forceinline__ void load(unsigned taddr, unsigned (&v)[16]) {
         asm volatile(
-            "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\ttcgen05.wait::ld.sync.aligned;"
+            "tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
               "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
             : "r"(taddr) : "memory");
+    }
+    static __device__ __forceinline__ void landed(unsigned (&v)[16]) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
+                       "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])::"memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -367,31 +379,62 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
 #pragma unroll
                 for (int e = 0; e < 4; e++) acc[h][j][e] = 0.0f;
         const int rloc = quarter * 32 + g;                         // rows rloc + 16 h + 8 hi of the tile
-        for (int chunk = 0; chunk < chunks && ok; chunk++) {
+        // One block's fold of one half (16 lanes) of this warp's part of the tile: rows rloc + 16 h + {0, 8}.
+        auto fold_half = [&](int h, const unsigned (&d)[4 * J], const float (&dwv)[2], const float (&mv)[2], const float (&dxv)[J][2],
+                             const float (&sxv)[J][2], bool fused) {
+#pragma unroll
+            for (int hi = 0; hi < 2; hi++) {
+                const float xw = __fmul_rn(-kUMagic, dwv[hi]);
+#pragma unroll
+                for (int j = 0; j < J; j++)
+#pragma unroll
+                    for (int lo = 0; lo < 2; lo++) {
+                        const float bits = __uint_as_float(d[4 * j + 2 * hi + lo]);
+                        float& a = acc[h][j][2 * hi + lo];
+                        if (KIND == TSM_Q8_0) {
+                            // float(dot) * (dw * dx), then the add
+                            a = __fadd_rn(a, __fmul_rn(__fsub_rn(bits, kUMagic), __fmul_rn(dwv[hi], dxv[j][lo])));
+                        } else if (KIND == TSM_Q4_0) {
+                            // (float(dot) * dw) * dx: fma(1.5 * 2^23 + dot, dw, -1.5 * 2^23 * dw) has exact products (dw has 11
+                            // significant bits), so it rounds once, like float(dot) * dw; a scale that is not finite takes the
+                            // subtract-then-multiply form, which gives the reference's infinities instead of NaN
+                            float scaled = fused ? __fmaf_rn(bits, dwv[hi], xw) : __fmul_rn(__fsub_rn(bits, kUMagic), dwv[hi]);
+                            a = __fadd_rn(a, __fmul_rn(scaled, dxv[j][lo]));
+                        } else {
+                            a = __fadd_rn(a, __fadd_rn(__fmul_rn(__fmul_rn(dwv[hi], dxv[j][lo]), __fsub_rn(bits, kUMagic)), __fmul_rn(mv[hi], sxv[j][lo])));
+                        }
+                    }
+            }
+        };
+        // The tile of block b is read in two halves, and one read is always in flight: while the first half of a block is
+        // folded the second is on its way, and while the second is folded the first half of the next block is.
+        unsigned d0[4 * J], d1[4 * J];
+        ok = u_mbar_wait(&t_full[0], 0u, abort_flag, p.spins);
+        u_fence_after();
+        UTmem<J>::load(lane_addr, d0);
+        for (int chunk = 0; chunk < chunks; chunk++) {
             int s = chunk % S;
-            ok = u_mbar_wait(&full[s], (unsigned)((chunk / S) & 1), abort_flag, p.spins) &&       // the scale boxes have landed
-                 u_mbar_wait(&a_ready[s], (unsigned)((chunk / S) & 1), abort_flag, p.spins);   // the block scales are in their table
-            if (!ok) break;
+            const unsigned parity = (unsigned)((chunk / S) & 1);
+            if (!u_mbar_wait(&full[s], parity, abort_flag, p.spins)) ok = false;      // the scale boxes have landed
+            if (!u_mbar_wait(&a_ready[s], parity, abort_flag, p.spins)) ok = false;   // the block scales are in their table
             const unsigned char* base = stages + (size_t)s * L::stage_bytes;
             const float* sc = (const float*)(base + L::scales_at);
             const float* sm = sc + NCOL * kUB;
-            const float* ws = (const float*)(base + L::wscale_at);
+            const float* ws = (const float*)(base + L::wscale_at) + rloc * kUB;
             const float* wm = ws + 128 * kUB;
 #pragma unroll 1
-            for (int sub = 0; sub < kUB / 4 && ok; sub++) {
-                float4 dw[2][2], mw[2][2];
-                bool plain = true;
+            for (int u = 0; u < kUB; u++) {
+                const int block = chunk * kUB + u, slot = block % kUSlots;
+                const unsigned t0 = lane_addr + slot * NCOL, t1 = t0 + (16u << 16);
+                // this block's scales: two weight rows per half, 2 J activation rows
+                float dwv[2][2], mv[2][2], dxv[J][2], sxv[J][2];
 #pragma unroll
                 for (int h = 0; h < 2; h++)
 #pragma unroll
                     for (int hi = 0; hi < 2; hi++) {
-                        const int row = rloc + 16 * h + 8 * hi;
-                        dw[h][hi] = *(const float4*)(ws + row * kUB + sub * 4);
-                        if (KIND == TSM_Q4_1) mw[h][hi] = *(const float4*)(wm + row * kUB + sub * 4);
-                        const float4& d4 = dw[h][hi];
-                        plain = plain && fabsf(d4.x) <= 65504.0f && fabsf(d4.y) <= 65504.0f && fabsf(d4.z) <= 65504.0f && fabsf(d4.w) <= 65504.0f;
+                        dwv[h][hi] = ws[(16 * h + 8 * hi) * kUB + u];
+                        mv[h][hi] = KIND == TSM_Q4_1 ? wm[(16 * h + 8 * hi) * kUB + u] : 0.0f;
                     }
-                float4 dx[J][2], sx[J][2];
 #pragma unroll
                 for (int j = 0; j < J; j++)
 #pragma unroll
@@ -399,70 +442,41 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
                         const int c = cbase + 8 * j + 2 * t + lo;
                         // the box is written with the 32-byte swizzle: the 16-byte half (blocks 0-3 or 4-7) of column c sits
                         // at half ^ bit 2 of c
-                        const int at = c * kUB + ((sub ^ ((c >> 2) & 1)) << 2);
-                        dx[j][lo] = *(const float4*)(sc + at);
-                        if (KIND == TSM_Q4_1) sx[j][lo] = *(const float4*)(sm + at);
+                        const int at = c * kUB + ((((u >> 2) ^ (c >> 2)) & 1) << 2) + (u & 3);
+                        dxv[j][lo] = sc[at];
+                        sxv[j][lo] = KIND == TSM_Q4_1 ? sm[at] : 0.0f;
                     }
+                bool plain = fabsf(dwv[0][0]) <= 65504.0f && fabsf(dwv[0][1]) <= 65504.0f && fabsf(dwv[1][0]) <= 65504.0f && fabsf(dwv[1][1]) <= 65504.0f;
                 const bool fused = KIND != TSM_Q4_0 || __all_sync(0xffffffffu, plain);
-#pragma unroll
-                for (int u4 = 0; u4 < 4; u4++) {
-                    const int block = chunk * kUB + sub * 4 + u4, slot = block % kUSlots;
-                    if (!u_mbar_wait(&t_full[slot], (unsigned)((block / kUSlots) & 1), abort_flag, p.spins)) {
-                        ok = false;
-                        break;
-                    }
-                    u_fence_after();
-                    unsigned d[2][4 * J];
-                    UTmem<J>::load(lane_addr + slot * NCOL, d[0]);
-                    UTmem<J>::load(lane_addr + slot * NCOL + (16u << 16), d[1]);
-                    // the tile goes back to 1.5 * 2^23 for the block that will use it next
-                    UTmem<J>::store(lane_addr + slot * NCOL, 0x4b400000u);
-                    UTmem<J>::store(lane_addr + slot * NCOL + (16u << 16), 0x4b400000u);
-#pragma unroll
-                    for (int h = 0; h < 2; h++)
-#pragma unroll
-                        for (int hi = 0; hi < 2; hi++) {
-                            const float4& d4 = dw[h][hi];
-                            const float dwv = u4 == 0 ? d4.x : u4 == 1 ? d4.y : u4 == 2 ? d4.z : d4.w;
-                            const float xw = __fmul_rn(-kUMagic, dwv);
-                            float mv = 0.0f;
-                            if (KIND == TSM_Q4_1) {
-                                const float4& m4 = mw[h][hi];
-                                mv = u4 == 0 ? m4.x : u4 == 1 ? m4.y : u4 == 2 ? m4.z : m4.w;
-                            }
-#pragma unroll
-                            for (int j = 0; j < J; j++)
-#pragma unroll
-                                for (int lo = 0; lo < 2; lo++) {
-                                    const float4& x4 = dx[j][lo];
-                                    const float dxv = u4 == 0 ? x4.x : u4 == 1 ? x4.y : u4 == 2 ? x4.z : x4.w;
-                                    const float bits = __uint_as_float(d[h][4 * j + 2 * hi + lo]);
-                                    float& a = acc[h][j][2 * hi + lo];
-                                    if (KIND == TSM_Q8_0) {
-                                        // float(dot) * (dw * dx), then the add
-                                        a = __fadd_rn(a, __fmul_rn(__fsub_rn(bits, kUMagic), __fmul_rn(dwv, dxv)));
-                                    } else if (KIND == TSM_Q4_0) {
-                                        // (float(dot) * dw) * dx: fma(1.5 * 2^23 + dot, dw, -1.5 * 2^23 * dw) has exact products (dw has 11
-                                        // significant bits), so it rounds once, like float(dot) * dw; a scale that is not finite takes
-                                        // the subtract-then-multiply form, which gives the reference's infinities instead of NaN
-                                        float scaled = fused ? __fmaf_rn(bits, dwv, xw) : __fmul_rn(__fsub_rn(bits, kUMagic), dwv);
-                                        a = __fadd_rn(a, __fmul_rn(scaled, dxv));
-                                    } else {
-                                        const float4& s4 = sx[j][lo];
-                                        const float sxv = u4 == 0 ? s4.x : u4 == 1 ? s4.y : u4 == 2 ? s4.z : s4.w;
-                                        a = __fadd_rn(a, __fadd_rn(__fmul_rn(__fmul_rn(dwv, dxv), __fsub_rn(bits, kUMagic)), __fmul_rn(mv, sxv)));
-                                    }
-                                }
-                        }
+                UTmem<J>::landed(d0);
+                if (block > 0) {
+                    // the block before this one: its tile was reset a whole fold ago, so this wait costs nothing by now
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     u_fence_before();
                     __syncwarp();
-                    if (lane == 0) u_mbar_arrive(&t_empty[slot]);
+                    if (lane == 0) u_mbar_arrive(&t_empty[(block - 1) % kUSlots]);
                 }
+                UTmem<J>::load(t1, d1);
+                UTmem<J>::store(t0, 0x4b400000u);   // the tile goes back to 1.5 * 2^23 for the block that uses it next
+                fold_half(0, d0, dwv[0], mv[0], dxv, sxv, fused);
+                UTmem<J>::landed(d1);
+                UTmem<J>::store(t1, 0x4b400000u);
+                if (block + 1 < nb) {
+                    const int next = (block + 1) % kUSlots;
+                    if (!u_mbar_wait(&t_full[next], (unsigned)(((block + 1) / kUSlots) & 1), abort_flag, p.spins)) ok = false;
+                    u_fence_after();
+                    UTmem<J>::load(lane_addr + next * NCOL, d0);
+                }
+                fold_half(1, d1, dwv[1], mv[1], dxv, sxv, fused);
             }
             __syncwarp();
-            if (ok && lane == 0) u_mbar_arrive(&empty[s]);   // the stage's scales have been read
+            if (lane == 0) u_mbar_arrive(&empty[s]);   // the stage's scales have been read
+            if (!ok) break;
         }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");   // the last block's tile
+        u_fence_before();
+        __syncwarp();
+        if (lane == 0 && nb > 0) u_mbar_arrive(&t_empty[(nb - 1) % kUSlots]);
         if (!ok) {
             *abort_flag = 1;
             if (lane == 0) atomicExch(&p.errors->timeout, 1);

@@ -1,0 +1,44 @@
+// Device helpers shared by the kernels that fold a row's sum in the host's order (the norms, and the tensor-parallel
+// exchange that ends in one).
+#pragma once
+#include "common.cuh"
+
+namespace tsm {
+
+// Σ f(row[j]) in index order from 0f, each step rounded (the host's fold, devices/host.cr:391-403,
+// 348-361); every thread receives the result.  All threads first write the terms ((row[j] - shift)² or
+// row[j]) to `terms`, padded to a multiple of 16 with +0 (adding +0 to a sum that started at +0 and only ever
+// had such terms added never changes it: the running sum is never -0); one thread then folds them with
+// 16-byte loads running ahead of the dependent adds, so a step costs the latency of one add.
+template <bool SQUARE>
+__device__ __forceinline__ float ordered_sum(const float* row, float* terms, int n, float shift, float* scratch) {
+    const int padded = (n + 15) & ~15;
+    for (int j = threadIdx.x; j < padded; j += blockDim.x) {
+        float v = 0.0f;
+        if (j < n) {
+            v = SQUARE ? __fsub_rn(row[j], shift) : row[j];
+            if (SQUARE) v = __fmul_rn(v, v);
+        }
+        terms[j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float acc = 0.0f;
+        const float4* t4 = (const float4*)terms;
+        float4 a = t4[0], b = t4[1], c = t4[2], d = t4[3];
+        for (int j = 0; j < padded; j += 16) {
+            float4 na = a, nb = b, nc = c, nd = d;
+            if (j + 16 < padded) na = t4[(j >> 2) + 4], nb = t4[(j >> 2) + 5], nc = t4[(j >> 2) + 6], nd = t4[(j >> 2) + 7];
+            acc = __fadd_rn(acc, a.x), acc = __fadd_rn(acc, a.y), acc = __fadd_rn(acc, a.z), acc = __fadd_rn(acc, a.w);
+            acc = __fadd_rn(acc, b.x), acc = __fadd_rn(acc, b.y), acc = __fadd_rn(acc, b.z), acc = __fadd_rn(acc, b.w);
+            acc = __fadd_rn(acc, c.x), acc = __fadd_rn(acc, c.y), acc = __fadd_rn(acc, c.z), acc = __fadd_rn(acc, c.w);
+            acc = __fadd_rn(acc, d.x), acc = __fadd_rn(acc, d.y), acc = __fadd_rn(acc, d.z), acc = __fadd_rn(acc, d.w);
+            a = na, b = nb, c = nc, d = nd;
+        }
+        scratch[0] = acc;
+    }
+    __syncthreads();
+    return scratch[0];
+}
+
+}  // namespace tsm

@@ -103,6 +103,18 @@ def main():
             got.append(logits)
             ids = tokens.tolist()
         run = model.decode_run(cache, ids, 32)
+        # which exchange a decode step used: the fused kernel over peer memory where the GPUs can map each other's memory,
+        # NCCL's all-reduce otherwise; either way two exchanges per layer
+        probe = model.new_batch_cache(4, 8)
+        model.forward_last([[1], [2], [3], [4]], probe)
+        rdev.profile()
+        model.decode(probe, [1, 2, 3, 4])
+        labels = {label: count for label, count, _ in rdev.profile_read(end=True)}
+        probe.free()
+        exchanges = sum(count for label, count in labels.items() if label.startswith("Exchange reduce") or label == "AllReduce")
+        assert exchanges == 2 * config["layers"], labels
+        if rank == 0:
+            print("all-reduce variant exchanges through", "the fused peer-memory kernel" if any(k.startswith("Exchange") for k in labels) else "NCCL", flush=True)
         flat = np.concatenate([g.ravel() for g in got]).view(np.uint32).astype(np.int64)
         mine = torch.tensor([int(flat.sum()), int(run.sum())], device=f"cuda:{local}")
         both = [torch.zeros_like(mine) for _ in range(world)]
