@@ -27,6 +27,7 @@ constexpr int kRing = 3;           // stages (5 measured no faster)
 constexpr int kEChunk = 1024;     // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
+constexpr int kWideDeep = 6;       // stages of 4 KB in attention_values_wide_kernel's ring
 
 struct StreamParams {
     const float* q;
@@ -40,6 +41,7 @@ struct StreamParams {
     float* scratch;  // [tokens][heads][capacity]: scores, then exp values (split path: then weights)
     int splits;      // split path: CTAs that share one (token, kv head)'s key positions
     QuantSink sink;  // where the output rows also go quantised (or nulls)
+    unsigned wait_hint;  // nanoseconds a waiting thread may sleep per poll (0: plain polling)
 };
 
 struct StreamMaps {
@@ -65,13 +67,27 @@ __device__ __forceinline__ bool s_mbar_try_wait(uint64_t* bar, unsigned parity) 
         : "memory");
     return ok != 0;
 }
-// Bounded: gives up after kSpinLimit polls, or soon after another warp has raised the CTA's abort flag.
+// The same poll, but the thread may be suspended for up to `hint_ns` while the phase has not completed: a waiting warp then
+// leaves its issue slots to the warps that have work.
+__device__ __forceinline__ bool s_mbar_try_wait_sleeping(uint64_t* bar, unsigned parity, unsigned hint_ns) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(s_smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after kSpinLimit polls, or soon after another warp has raised the CTA's abort flag.  abort_flag[2] holds
+// the suspend hint in nanoseconds (0: plain polling).
 __device__ __forceinline__ bool s_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag) {
+    if (s_mbar_try_wait(bar, parity)) return true;
+    const unsigned hint = (unsigned)abort_flag[2];
     for (unsigned spin = 0; spin < kSpinLimit; spin++) {
-        if (s_mbar_try_wait(bar, parity)) return true;
-        if (spin > 256) {
+        if (hint ? s_mbar_try_wait_sleeping(bar, parity, hint) : s_mbar_try_wait(bar, parity)) return true;
+        if (hint || spin > 256) {
             if (*abort_flag) return false;
-            __nanosleep(64);
+            if (!hint) __nanosleep(64);
         }
     }
     return false;
@@ -94,7 +110,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     constexpr int QP = WIDTH + 4;                  // query row pitch: the four heads' 16-byte reads fall in distinct banks
     static_assert(WIDTH == kConsumers, "one folding thread per column");
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (s_smem_u32(smem_raw) & 1023u)) & 1023u);  // an offset from the shared array: the address space stays known
     static_assert(kRing <= 8 && 512 + 3 * kRing * 512 <= 8192, "the header holds the barriers and the hand-over slots of at most 8 stages");
     uint64_t* full = (uint64_t*)smem;              // [kRing], bytes 0..63
     uint64_t* empty = (uint64_t*)(smem + 64);      // [kRing], bytes 64..127
@@ -127,7 +143,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             s_mbar_init(&empty[s], kConsumers / 32);
             for (int w2 = 0; w2 < 3; w2++) s_mbar_init(&ready[w2 * kRing + s], 1);
         }
-        abort_flag[0] = 0, abort_flag[1] = 0;
+        abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = tid; i < G * WIDTH; i += blockDim.x)
@@ -379,7 +395,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
     constexpr int STAGE_BYTES = BOXES * BOX_BYTES;
     constexpr int QP = WIDTH + 4;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (s_smem_u32(smem_raw) & 1023u)) & 1023u);  // an offset from the shared array: the address space stays known
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = (uint64_t*)(smem + 64);
     uint64_t* ready = (uint64_t*)(smem + 128);
@@ -410,7 +426,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
             s_mbar_init(&empty[s], kConsumers / 32);
             for (int w2 = 0; w2 < 3; w2++) s_mbar_init(&ready[w2 * kRing + s], 1);
         }
-        abort_flag[0] = 0, abort_flag[1] = 0;
+        abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = tid; i < G * WIDTH; i += blockDim.x)
@@ -550,7 +566,7 @@ __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, co
     __shared__ __align__(1024) unsigned char stages[kDeep * BOX_BYTES];
     __shared__ __align__(16) float wbuf[2][kTP * G];
     __shared__ uint64_t full[kDeep], empty[kDeep];
-    __shared__ int abort_words[2];
+    __shared__ int abort_words[4];
     volatile int* abort_flag = abort_words;
 
     const int token = blockIdx.y;
@@ -565,7 +581,7 @@ __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, co
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < kDeep; s++) s_mbar_init(&full[s], 1), s_mbar_init(&empty[s], 1);
-        abort_words[0] = 0, abort_words[1] = 0;
+        abort_words[0] = 0, abort_words[1] = 0, abort_words[2] = (int)p.wait_hint, abort_words[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -658,12 +674,13 @@ __global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams
     chained_kernel_entry();
     constexpr int G = 4;
     constexpr int BOX_BYTES = kTP * 128;
-    constexpr int kDeep = 6;
+    constexpr int kDeep = kWideDeep;   // (12 stages were tried: the larger CTAs lost more in residency than the depth gained)
     constexpr int kWarps = 4;
-    __shared__ __align__(1024) unsigned char stages[kDeep * BOX_BYTES];
+    extern __shared__ unsigned char wide_raw[];
+    unsigned char* stages = wide_raw + ((1024u - (s_smem_u32(wide_raw) & 1023u)) & 1023u);   // [kDeep][BOX_BYTES], swizzled boxes
     __shared__ __align__(16) float wbuf[kWarps][2][kTP * G];
     __shared__ uint64_t full[kDeep], empty[kDeep];
-    __shared__ int abort_words[2];
+    __shared__ int abort_words[4];
     volatile int* abort_flag = abort_words;
 
     const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;
@@ -678,7 +695,7 @@ __global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) {
         for (int s = 0; s < kDeep; s++) s_mbar_init(&full[s], 1), s_mbar_init(&empty[s], kWarps);
-        abort_words[0] = 0, abort_words[1] = 0;
+        abort_words[0] = 0, abort_words[1] = 0, abort_words[2] = (int)p.wait_hint, abort_words[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -771,7 +788,7 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
                             float* scratch, QuantSink sink) {
     constexpr int WIDTH = 128;
-    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch, 1, sink};
+    StreamParams p{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, order, scratch, 1, sink, ctx->wait_hint};
     StreamMaps maps;
     uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
@@ -807,7 +824,19 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         TSM_LAUNCH_CHECK(ctx);
         static const char* narrow = getenv("TSM_ATTN_VALUES_NARROW");   // the one-warp-per-box value pass, for timing it
         if (narrow && narrow[0] == '1') TSM_CUDA(ctx, launch_chained(ctx, attention_values_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(64), 0, p, maps));
-        else TSM_CUDA(ctx, launch_chained(ctx, attention_values_wide_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(160), 0, p, maps));
+        else {
+            const size_t smem_wide = 1024 + (size_t)kWideDeep * kTP * 128;
+            static std::mutex wide_lock;
+            static std::map<int, bool> wide_done;
+            {
+                std::lock_guard<std::mutex> guard(wide_lock);
+                if (!wide_done.count(ctx->ordinal)) {
+                    TSM_CUDA(ctx, cudaFuncSetAttribute(attention_values_wide_kernel<WIDTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wide));
+                    wide_done[ctx->ordinal] = true;
+                }
+            }
+            TSM_CUDA(ctx, launch_chained(ctx, attention_values_wide_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(160), smem_wide, p, maps));
+        }
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
         return TSM_OK;

@@ -77,6 +77,7 @@ struct tsm_ctx {
     tsm_counters counters{};
     std::mutex counter_lock;
     tsm::Profile profile;
+    unsigned wait_hint = 0;                   // TSM_WAIT_HINT_NS: nanoseconds a thread waiting on an mbarrier may sleep per poll
     unsigned wait_spins = 0;                  // tsm_debug_wait_limit: a shorter limit for the kernels' bounded waits (0: theirs)
     int starve_copies = 0;                    //                       and a stage the next product's producer leaves out
 };

@@ -75,9 +75,12 @@ __device__ __forceinline__ void g_bulk_load(void* dst, const void* src, unsigned
 
 // The 4 bytes at p (2-byte aligned, in shared memory) as a little-endian word.
 __device__ __forceinline__ unsigned lds_u32_at2(const unsigned char* p) {
-    uintptr_t a = (uintptr_t)p;
-    const unsigned* q = (const unsigned*)(a & ~(uintptr_t)3);
-    return __funnelshift_r(q[0], q[1], (unsigned)(a & 3) * 8);
+    // through the 32-bit shared address: a pointer rebuilt from an integer would be a generic one, and its loads generic loads
+    const unsigned a = g_smem_u32(p);
+    unsigned lo, hi;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(lo) : "r"(a & ~3u));
+    asm volatile("ld.shared.u32 %0, [%1 + 4];" : "=r"(hi) : "r"(a & ~3u));
+    return __funnelshift_r(lo, hi, (a & 3u) * 8);
 }
 __device__ __forceinline__ unsigned lds_u16_at2(const unsigned char* p) { return *(const unsigned short*)p; }
 

@@ -54,6 +54,7 @@ struct PipeParams {
     ErrorRecord* errors;
     unsigned spins;        // polls after which a wait gives up
     int skip_chunks;       // stages the producer leaves out at the end (0 but for tsm_debug_wait_limit's test of the waits)
+    unsigned wait_hint;    // nanoseconds a waiting thread may sleep per poll (0: plain polling)
 };
 
 __device__ __forceinline__ unsigned p_smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -77,12 +78,25 @@ __device__ __forceinline__ bool p_mbar_try_wait(uint64_t* bar, unsigned parity) 
 }
 // Bounded: gives up after `limit` polls (kPipeSpins unless a test lowered it), or as soon as another warp has raised the
 // CTA's abort flag.
+__device__ __forceinline__ bool p_mbar_try_wait_sleeping(uint64_t* bar, unsigned parity, unsigned hint_ns) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(p_smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+// abort_flag[2] holds the suspend hint in nanoseconds: with one, a poll may sleep until the phase completes, which leaves
+// the waiting warp's issue slots to the warps that have work (0: plain polling).
 __device__ __forceinline__ bool p_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned limit) {
+    if (p_mbar_try_wait(bar, parity)) return true;
+    const unsigned hint = (unsigned)abort_flag[2];
     for (unsigned spin = 0; spin < limit; spin++) {
-        if (p_mbar_try_wait(bar, parity)) return true;
-        if (spin > 1024) {
+        if (hint ? p_mbar_try_wait_sleeping(bar, parity, hint) : p_mbar_try_wait(bar, parity)) return true;
+        if (hint || spin > 1024) {
             if (*abort_flag) return false;
-            __nanosleep(64);
+            if (!hint) __nanosleep(64);
         }
     }
     return false;
@@ -96,9 +110,12 @@ __device__ __forceinline__ void p_tensor_load(void* dst, const CUtensorMap* map,
 
 // The 4 bytes at p (2-byte aligned, in shared memory) as a little-endian word.
 __device__ __forceinline__ unsigned p_lds_u32_at2(const unsigned char* p) {
-    uintptr_t a = (uintptr_t)p;
-    const unsigned* q = (const unsigned*)(a & ~(uintptr_t)3);
-    return __funnelshift_r(q[0], q[1], (unsigned)(a & 3) * 8);
+    // through the 32-bit shared address: a pointer rebuilt from an integer would be a generic one, and its loads generic loads
+    const unsigned a = p_smem_u32(p);
+    unsigned lo, hi;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(lo) : "r"(a & ~3u));
+    asm volatile("ld.shared.u32 %0, [%1 + 4];" : "=r"(hi) : "r"(a & ~3u));
+    return __funnelshift_r(lo, hi, (a & 3u) * 8);
 }
 __device__ __forceinline__ unsigned p_lds_u16(const unsigned char* p) { return *(const unsigned short*)p; }
 
@@ -154,7 +171,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
     constexpr int B = L::B, WP = L::WP;
     extern __shared__ unsigned char smem_raw[];
     // the swizzled boxes need 1024-byte alignment: barriers sit in the first 128 bytes, stages start at the next 1024
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (p_smem_u32(smem_raw) & 1023u)) & 1023u);  // an offset from the shared array: the address space stays known
     uint64_t* full = (uint64_t*)smem;                 // [kPipeStages]
     uint64_t* empty = full + kPipeStages;             // [kPipeStages]
     volatile int* abort_flag = (volatile int*)(smem + 96);
@@ -177,7 +194,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_kernel(PipeParams p, int w
             p_mbar_init(&full[s], 1);
             p_mbar_init(&empty[s], group_count * active_wc);
         }
-        abort_flag[0] = 0, abort_flag[1] = 0;  // [1] stays 0: a wait that must not be cut short polls it
+        abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;  // [1] stays 0: a wait that must not be cut short polls it
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -377,7 +394,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
     using L = PipeLayout<KIND, COLS>;
     constexpr int B = L::B, WP = L::WP;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* smem = smem_raw + ((1024u - (p_smem_u32(smem_raw) & 1023u)) & 1023u);  // an offset from the shared array: the address space stays known
     uint64_t* full = (uint64_t*)smem;
     uint64_t* empty = full + kPipeStages;
     volatile int* abort_flag = (volatile int*)(smem + 96);
@@ -401,7 +418,7 @@ __global__ void __launch_bounds__(512, 1) matmul_pipe_t_kernel(PipeParams p, int
             p_mbar_init(&full[s], 1);
             p_mbar_init(&empty[s], group_count * active_wc);
         }
-        abort_flag[0] = 0, abort_flag[1] = 0;
+        abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -731,6 +748,7 @@ int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int
     p.errors = ctx->errors;
     p.spins = ctx->wait_spins ? ctx->wait_spins : kPipeSpins;
     p.skip_chunks = ctx->starve_copies ? 1 : 0;
+    p.wait_hint = ctx->wait_hint;
     switch (kind) {
         case TSM_Q8_0: return launch_pipe_kind<TSM_Q8_0>(ctx, p);
         case TSM_Q4_0: return launch_pipe_kind<TSM_Q4_0>(ctx, p);

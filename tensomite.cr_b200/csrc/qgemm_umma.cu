@@ -87,23 +87,24 @@ __device__ __forceinline__ void u_mbar_expect_tx(uint64_t* bar, unsigned bytes) 
 __device__ __forceinline__ void u_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(u_smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ bool u_mbar_try_wait(uint64_t* bar, unsigned parity) {
+// One poll that may sleep: the thread is suspended until the barrier's phase completes or about `hint_ns` have passed,
+// whichever comes first, so a warp that waits does not spend the issue slots the folding warps need.
+__device__ __forceinline__ bool u_mbar_try_wait(uint64_t* bar, unsigned parity, unsigned hint_ns) {
     unsigned ok;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(ok)
-        : "r"(u_smem_u32(bar)), "r"(parity)
+        : "r"(u_smem_u32(bar)), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
-// Bounded: gives up after `limit` polls, or soon after another role has raised the CTA's abort flag.
+// Bounded: gives up after `limit` polls (each may sleep up to two microseconds), or soon after another role has raised the
+// CTA's abort flag.
 __device__ __forceinline__ bool u_mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, unsigned limit) {
+    if (u_mbar_try_wait(bar, parity, 0u)) return true;
     for (unsigned spin = 0; spin < limit; spin++) {
-        if (u_mbar_try_wait(bar, parity)) return true;
-        if (spin > 512) {
-            if (*abort_flag) return false;
-            __nanosleep(64);
-        }
+        if (u_mbar_try_wait(bar, parity, 2000u)) return true;
+        if (*abort_flag) return false;
     }
     return false;
 }
@@ -138,8 +139,9 @@ __device__ __forceinline__ void u_fence_before() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void u_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // J groups of 8 columns of 16 lanes in the accumulator-fragment shape: registers [4 j + e] = (lane g + 8 (e >> 1), column
-// 8 j + 2 t + (e & 1)) for thread 4 g + t.  `load` only issues the read; `landed` waits for every read issued so far and
-// names the registers as its operands, so that nothing reading them can be scheduled before it.
+// 8 j + 2 t + (e & 1)) for thread 4 g + t.  `load` only issues the read; `landed` waits for every read issued so far (the
+// registers themselves are guarded by the hardware's scoreboard like those of any load; naming them as operands of the wait
+// cost a register copy each).
 template <int J> struct UTmem;
 template <> struct UTmem<1> {
     static __device__ __forceinline__ void load(unsigned taddr, unsigned (&v)[4]) {
@@ -147,7 +149,8 @@ template <> struct UTmem<1> {
                      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(taddr) : "memory");
     }
     static __device__ __forceinline__ void landed(unsigned (&v)[4]) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3])::"memory");
+        (void)v;
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x1.b32 [%0], {%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -159,8 +162,8 @@ template <> struct UTmem<2> {
                      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
     }
     static __device__ __forceinline__ void landed(unsigned (&v)[8]) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7])::"memory");
+        (void)v;
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -175,9 +178,8 @@ template <> struct UTmem<4> {
             : "r"(taddr) : "memory");
     }
     static __device__ __forceinline__ void landed(unsigned (&v)[16]) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]),
-                       "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])::"memory");
+        (void)v;
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
     }
     static __device__ __forceinline__ void store(unsigned taddr, unsigned x) {
         asm volatile("tcgen05.st.sync.aligned.16x256b.x4.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(x) : "memory");
@@ -193,6 +195,37 @@ __device__ __forceinline__ unsigned u_word_at(const unsigned (&raw)[WORDS], int 
     return (at & 3) ? __funnelshift_r(raw[at >> 2], raw[(at >> 2) + 1 < WORDS ? (at >> 2) + 1 : at >> 2], 16) : raw[at >> 2];
 }
 
+// One block's fold of one half (16 lanes) of a fold warp's part of the tile: two weight rows by 2 J activation rows.  FUSED is
+// a template argument so that the two forms of the Q4_0 product are two bodies behind one real branch: as one body with the
+// choice inside, both forms were computed for every output and one of them dropped.
+template <int KIND, int J, bool FUSED>
+__device__ __forceinline__ void u_fold_half(float (&acc)[J][4], const unsigned (&d)[4 * J], const float (&dwv)[2], const float (&mv)[2],
+                                            const float (&dxv)[J][2], const float (&sxv)[J][2]) {
+#pragma unroll
+    for (int hi = 0; hi < 2; hi++) {
+        const float xw = __fmul_rn(-kUMagic, dwv[hi]);
+#pragma unroll
+        for (int j = 0; j < J; j++)
+#pragma unroll
+            for (int lo = 0; lo < 2; lo++) {
+                const float bits = __uint_as_float(d[4 * j + 2 * hi + lo]);
+                float& a = acc[j][2 * hi + lo];
+                if (KIND == TSM_Q8_0) {
+                    // float(dot) * (dw * dx), then the add
+                    a = __fadd_rn(a, __fmul_rn(__fsub_rn(bits, kUMagic), __fmul_rn(dwv[hi], dxv[j][lo])));
+                } else if (KIND == TSM_Q4_0) {
+                    // (float(dot) * dw) * dx: fma(1.5 * 2^23 + dot, dw, -1.5 * 2^23 * dw) has exact products (dw has 11
+                    // significant bits), so it rounds once, like float(dot) * dw; a scale that is not finite takes the
+                    // subtract-then-multiply form, which gives the reference's infinities instead of NaN
+                    float scaled = FUSED ? __fmaf_rn(bits, dwv[hi], xw) : __fmul_rn(__fsub_rn(bits, kUMagic), dwv[hi]);
+                    a = __fadd_rn(a, __fmul_rn(scaled, dxv[j][lo]));
+                } else {
+                    a = __fadd_rn(a, __fadd_rn(__fmul_rn(__fmul_rn(dwv[hi], dxv[j][lo]), __fsub_rn(bits, kUMagic)), __fmul_rn(mv[hi], sxv[j][lo])));
+                }
+            }
+    }
+}
+
 // Roles by warp: 0-7 fold (tensor-memory lanes 32 (warp & 3) .., columns of half warp >> 2), 8-11 repack, 12 copies, 13 multiplies.
 template <int KIND, int NCOL>
 __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p, const __grid_constant__ UmmaMaps maps) {
@@ -202,7 +235,8 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
     constexpr int J = NCOL / 16;                       // 8-column groups per fold warp (each takes half the columns)
     constexpr int TCOLS = NCOL * kUSlots < 32 ? 32 : NCOL * kUSlots;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // aligned by an offset from the shared array itself, so that the compiler still knows these are shared-memory addresses
+    unsigned char* smem = smem_raw + ((1024u - (u_smem_u32(smem_raw) & 1023u)) & 1023u);
     uint64_t* full = (uint64_t*)smem;                  // [S]      a stage's copies have landed
     uint64_t* empty = full + 4;                        // [S]      repack, fold and multiply are done with the stage
     uint64_t* a_ready = empty + 4;                     // [S]      the stage's blocks are repacked
@@ -379,33 +413,6 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
 #pragma unroll
                 for (int e = 0; e < 4; e++) acc[h][j][e] = 0.0f;
         const int rloc = quarter * 32 + g;                         // rows rloc + 16 h + 8 hi of the tile
-        // One block's fold of one half (16 lanes) of this warp's part of the tile: rows rloc + 16 h + {0, 8}.
-        auto fold_half = [&](int h, const unsigned (&d)[4 * J], const float (&dwv)[2], const float (&mv)[2], const float (&dxv)[J][2],
-                             const float (&sxv)[J][2], bool fused) {
-#pragma unroll
-            for (int hi = 0; hi < 2; hi++) {
-                const float xw = __fmul_rn(-kUMagic, dwv[hi]);
-#pragma unroll
-                for (int j = 0; j < J; j++)
-#pragma unroll
-                    for (int lo = 0; lo < 2; lo++) {
-                        const float bits = __uint_as_float(d[4 * j + 2 * hi + lo]);
-                        float& a = acc[h][j][2 * hi + lo];
-                        if (KIND == TSM_Q8_0) {
-                            // float(dot) * (dw * dx), then the add
-                            a = __fadd_rn(a, __fmul_rn(__fsub_rn(bits, kUMagic), __fmul_rn(dwv[hi], dxv[j][lo])));
-                        } else if (KIND == TSM_Q4_0) {
-                            // (float(dot) * dw) * dx: fma(1.5 * 2^23 + dot, dw, -1.5 * 2^23 * dw) has exact products (dw has 11
-                            // significant bits), so it rounds once, like float(dot) * dw; a scale that is not finite takes the
-                            // subtract-then-multiply form, which gives the reference's infinities instead of NaN
-                            float scaled = fused ? __fmaf_rn(bits, dwv[hi], xw) : __fmul_rn(__fsub_rn(bits, kUMagic), dwv[hi]);
-                            a = __fadd_rn(a, __fmul_rn(scaled, dxv[j][lo]));
-                        } else {
-                            a = __fadd_rn(a, __fadd_rn(__fmul_rn(__fmul_rn(dwv[hi], dxv[j][lo]), __fsub_rn(bits, kUMagic)), __fmul_rn(mv[hi], sxv[j][lo])));
-                        }
-                    }
-            }
-        };
         // The tile of block b is read in two halves, and one read is always in flight: while the first half of a block is
         // folded the second is on its way, and while the second is folded the first half of the next block is.
         unsigned d0[4 * J], d1[4 * J];
@@ -422,6 +429,9 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
             const float* sm = sc + NCOL * kUB;
             const float* ws = (const float*)(base + L::wscale_at) + rloc * kUB;
             const float* wm = ws + 128 * kUB;
+            const float* sc_mine = sc + (cbase + 2 * t) * kUB;
+            const float* sm_mine = sm + (cbase + 2 * t) * kUB;
+            const int flip = ((t >> 1) & 1) << 2;
 #pragma unroll 1
             for (int u = 0; u < kUB; u++) {
                 const int block = chunk * kUB + u, slot = block % kUSlots;
@@ -435,16 +445,17 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
                         dwv[h][hi] = ws[(16 * h + 8 * hi) * kUB + u];
                         mv[h][hi] = KIND == TSM_Q4_1 ? wm[(16 * h + 8 * hi) * kUB + u] : 0.0f;
                     }
+                // The scale box is written with the 32-byte swizzle: the 16-byte half (blocks 0-3 or 4-7) of column c sits at
+                // half ^ bit 2 of c.  This thread's columns are cbase + 8 j + 2 t + lo, whose bit 2 is bit 1 of t for every
+                // j and lo, so block u is found at index u ^ flip of each of its columns' eight floats.
+                const float* su = sc_mine + (u ^ flip);
+                const float* mu = sm_mine + (u ^ flip);
 #pragma unroll
                 for (int j = 0; j < J; j++)
 #pragma unroll
                     for (int lo = 0; lo < 2; lo++) {
-                        const int c = cbase + 8 * j + 2 * t + lo;
-                        // the box is written with the 32-byte swizzle: the 16-byte half (blocks 0-3 or 4-7) of column c sits
-                        // at half ^ bit 2 of c
-                        const int at = c * kUB + ((((u >> 2) ^ (c >> 2)) & 1) << 2) + (u & 3);
-                        dxv[j][lo] = sc[at];
-                        sxv[j][lo] = KIND == TSM_Q4_1 ? sm[at] : 0.0f;
+                        dxv[j][lo] = su[(8 * j + lo) * kUB];
+                        sxv[j][lo] = KIND == TSM_Q4_1 ? mu[(8 * j + lo) * kUB] : 0.0f;
                     }
                 bool plain = fabsf(dwv[0][0]) <= 65504.0f && fabsf(dwv[0][1]) <= 65504.0f && fabsf(dwv[1][0]) <= 65504.0f && fabsf(dwv[1][1]) <= 65504.0f;
                 const bool fused = KIND != TSM_Q4_0 || __all_sync(0xffffffffu, plain);
@@ -458,7 +469,8 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
                 }
                 UTmem<J>::load(t1, d1);
                 UTmem<J>::store(t0, 0x4b400000u);   // the tile goes back to 1.5 * 2^23 for the block that uses it next
-                fold_half(0, d0, dwv[0], mv[0], dxv, sxv, fused);
+                if (fused) u_fold_half<KIND, J, true>(acc[0], d0, dwv[0], mv[0], dxv, sxv);
+                else u_fold_half<KIND, J, false>(acc[0], d0, dwv[0], mv[0], dxv, sxv);
                 UTmem<J>::landed(d1);
                 UTmem<J>::store(t1, 0x4b400000u);
                 if (block + 1 < nb) {
@@ -467,7 +479,8 @@ __global__ void __launch_bounds__(kUThreads, 1) matmul_umma_kernel(UmmaParams p,
                     u_fence_after();
                     UTmem<J>::load(lane_addr + next * NCOL, d0);
                 }
-                fold_half(1, d1, dwv[1], mv[1], dxv, sxv, fused);
+                if (fused) u_fold_half<KIND, J, true>(acc[1], d1, dwv[1], mv[1], dxv, sxv);
+                else u_fold_half<KIND, J, false>(acc[1], d1, dwv[1], mv[1], dxv, sxv);
             }
             __syncwarp();
             if (lane == 0) u_mbar_arrive(&empty[s]);   // the stage's scales have been read

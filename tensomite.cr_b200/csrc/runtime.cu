@@ -236,6 +236,7 @@ int tsm_ctx_create(int ordinal, tsm_ctx** out) {
         return TSM_ERR_CUDA;
     }
     ctx->sm_count = prop.multiProcessorCount;
+    ctx->wait_hint = getenv("TSM_WAIT_HINT_NS") ? (unsigned)atoi(getenv("TSM_WAIT_HINT_NS")) : 0u;
     // what the pool may keep: max(1 GiB, a quarter of the device), as the reference's pool (cuda.cr:339-353)
     int64_t quarter = (int64_t)(prop.totalGlobalMem / 4);
     ctx->pool.limit_bytes = quarter > (1ll << 30) ? quarter : (1ll << 30);
