@@ -62,8 +62,11 @@ struct RowRange {
 
 }  // namespace tsm
 
+namespace tsm { struct Stager; }
+
 struct tsm_model {
     tsm_ctx* ctx = nullptr;
+    tsm::Stager* stager = nullptr;    // the pinned staging buffers of a load in progress (model_gguf.cu)
     tsm_model_config cfg{};
     tsm::Linear embed, wpe, head;
     float *final_w = nullptr, *final_b = nullptr;

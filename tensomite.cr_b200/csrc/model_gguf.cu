@@ -7,6 +7,9 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
+#include <thread>
+
 #include "model.cuh"
 
 namespace tsm {
@@ -190,6 +193,66 @@ static int upload_f32(tsm_model* m, GgufFile& f, const std::string& name, int64_
     return tsm_upload(m->ctx, (tsm_dptr)(uintptr_t)*out, src, count * 4);
 }
 
+// Weights travel from the mapped file to the device through two pinned buffers: while one is being copied to the device
+// (cudaMemcpyAsync on the context's stream), the host fills the other from the file, on a few threads.  The reference's
+// loader hands each tensor to Device#upload as one pageable block (gguf.cr:112-136, cuda.cr:389-391); for files of
+// several gigabytes the pageable copy and the wait after every tensor were most of the load time.
+struct Stager {
+    static constexpr size_t kBytes = 48u << 20;
+    tsm_ctx* ctx = nullptr;
+    uint8_t* buffer[2] = {nullptr, nullptr};
+    cudaEvent_t sent[2] = {nullptr, nullptr};
+    bool busy[2] = {false, false};
+    int turn = 0;
+    int64_t bytes_sent = 0;
+    int begin(tsm_ctx* c) {
+        ctx = c;
+        for (int i = 0; i < 2; i++) {
+            TSM_CUDA(ctx, cudaMallocHost((void**)&buffer[i], kBytes));
+            TSM_CUDA(ctx, cudaEventCreateWithFlags(&sent[i], cudaEventDisableTiming));
+        }
+        return TSM_OK;
+    }
+    // a pinned buffer that no copy is reading any more
+    int acquire(uint8_t** out) {
+        if (busy[turn]) {
+            TSM_CUDA(ctx, cudaEventSynchronize(sent[turn]));
+            busy[turn] = false;
+        }
+        *out = buffer[turn];
+        return TSM_OK;
+    }
+    int send(void* dst, size_t bytes) {
+        TSM_CUDA(ctx, cudaMemcpyAsync(dst, buffer[turn], bytes, cudaMemcpyHostToDevice, ctx->stream));
+        TSM_CUDA(ctx, cudaEventRecord(sent[turn], ctx->stream));
+        busy[turn] = true, turn ^= 1, bytes_sent += (int64_t)bytes;
+        ctx->counters.uploads++, ctx->counters.upload_bytes += (int64_t)bytes;
+        return TSM_OK;
+    }
+    ~Stager() {
+        if (!ctx) return;
+        cudaStreamSynchronize(ctx->stream);
+        for (int i = 0; i < 2; i++) {
+            if (sent[i]) cudaEventDestroy(sent[i]);
+            if (buffer[i]) cudaFreeHost(buffer[i]);
+        }
+    }
+};
+
+// Copies rows[first .. first + count) (row_bytes each) into dst back to back, on up to four threads.
+static void gather_rows(uint8_t* dst, const std::vector<const uint8_t*>& rows, int64_t first, int64_t count, int64_t row_bytes) {
+    const int workers = (int)std::min<int64_t>(4, std::max<int64_t>(1, count * row_bytes >> 22));
+    auto part = [&](int w) {
+        int64_t a = first + count * w / workers, b = first + count * (w + 1) / workers;
+        for (int64_t r = a; r < b; r++) memcpy(dst + (r - first) * row_bytes, rows[(size_t)r], (size_t)row_bytes);
+    };
+    if (workers == 1) return part(0);
+    std::vector<std::thread> pool;
+    for (int w = 1; w < workers; w++) pool.emplace_back(part, w);
+    part(0);
+    for (auto& t : pool) t.join();
+}
+
 struct RowSource {
     std::string name;
     int heads;  // > 0: undo llama.cpp's rotary row order for this many heads (llama.cr:226-235)
@@ -219,6 +282,47 @@ static int upload_rows(tsm_model* m, GgufFile& f, const std::vector<RowSource>& 
     }
     if (total_rows != expect_n) return fail(m->ctx, TSM_ERR_ARG, parts[0].name + ": the file holds " + std::to_string(total_rows) + " rows, the model " + std::to_string(expect_n));
     int64_t row_bytes = weight_bytes(kind, 1, k);
+    // Rows that are in the file as the device wants them (block formats, F32): streamed through the pinned buffers, row
+    // order (joined parts, rotary order undone, a rank's share) applied while the buffer is filled.
+    bool as_stored = m->stager != nullptr;
+    for (auto& part : parts) {
+        const GgufEntry& e = f.entries[part.name];
+        if (e.kind == 1 || e.kind == 30 || (part.linear_of_module && e.kind == 0)) as_stored = false;
+    }
+    if (as_stored) {
+        std::vector<const uint8_t*> rows;
+        rows.reserve((size_t)total_rows);
+        for (auto& part : parts) {
+            const GgufEntry& e = f.entries[part.name];
+            const uint8_t* src = f.data + e.offset;
+            int64_t count = e.shape[0];
+            if (part.heads > 0) {
+                int64_t half = count / part.heads / 2;
+                for (int head = 0; head < part.heads; head++)
+                    for (int pair = 0; pair < 2; pair++)
+                        for (int64_t i = 0; i < half; i++) rows.push_back(src + (head * 2 * half + 2 * i + pair) * row_bytes);
+            } else {
+                for (int64_t r = 0; r < count; r++) rows.push_back(src + r * row_bytes);
+            }
+        }
+        if (!ranges.empty()) {  // a tensor-parallel rank keeps its rows only
+            std::vector<const uint8_t*> kept;
+            for (auto& range : ranges) kept.insert(kept.end(), rows.begin() + range.start, rows.begin() + range.start + range.count);
+            rows.swap(kept);
+        }
+        const int64_t held = (int64_t)rows.size();
+        out->kind = kind, out->n = (int)held, out->k = k;
+        TSM_TRY(dev_alloc(m, held * row_bytes, (void**)&out->w));
+        const int64_t per_chunk = std::max<int64_t>(1, (int64_t)Stager::kBytes / row_bytes);
+        for (int64_t first = 0; first < held; first += per_chunk) {
+            int64_t count = std::min(per_chunk, held - first);
+            uint8_t* pinned = nullptr;
+            TSM_TRY(m->stager->acquire(&pinned));
+            gather_rows(pinned, rows, first, count, row_bytes);
+            TSM_TRY(m->stager->send(out->w + first * row_bytes, (size_t)(count * row_bytes)));
+        }
+        return TSM_OK;
+    }
     std::vector<uint8_t> staging((size_t)(total_rows * row_bytes));
     int64_t at = 0;
     for (auto& part : parts) {
@@ -409,9 +513,19 @@ int load_gguf_model(tsm_model* m, const char* path) {
     GgufFile f;
     TSM_TRY(gguf_open(m->ctx, path, f));
     std::string arch = f.strings.count("general.architecture") ? f.strings["general.architecture"] : "";
-    if (arch == "llama") return load_llama(m, f);
-    if (f.strings.count("gpt2.heads")) return load_gpt2(m, f);
-    return fail(m->ctx, TSM_ERR_IO, std::string(path) + " holds a " + arch + " model, not a Llama or GPT-2");
+    Stager stager;   // two pinned buffers for the length of the load; the destructor waits for the last copy
+    static const bool pageable = getenv("TSM_LOAD_PAGEABLE") != nullptr;   // the one-block-per-tensor path, for timing it
+    if (!pageable) {
+        TSM_TRY(stager.begin(m->ctx));
+        m->stager = &stager;
+    }
+    int rc;
+    if (arch == "llama") rc = load_llama(m, f);
+    else if (f.strings.count("gpt2.heads")) rc = load_gpt2(m, f);
+    else rc = fail(m->ctx, TSM_ERR_IO, std::string(path) + " holds a " + arch + " model, not a Llama or GPT-2");
+    m->stager = nullptr;
+    if (rc == TSM_OK) rc = tsm_sync(m->ctx);   // every copy has landed before the file is unmapped
+    return rc;
 }
 
 // ---- Module#save to a .gguf file (module.cr:148-164; GGUF.write, gguf.cr:156-191) ---------------------------------
