@@ -547,6 +547,10 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     const QuantSink sink = quant_sink(quantized);  // the kernels for widths 64 and 128 quantise their rows themselves
     if (attention_stream_fits(ctx, tokens, heads, width, kv_heads, q, q_stride, k, v)) {
         TSM_TRY(ensure_scratch(ctx, ctx->attn, attention_stream_scratch_bytes(tokens, heads, capacity)));
+        static const bool no_prefill = getenv("TSM_NO_PREFILL_KERNEL") != nullptr;   // prompts through the decode kernels, for timing
+        if (ctx->prefill_tiles && ctx->prefill_tile_count > 0 && !no_prefill)   // a step that holds prompts: keys and values once per 16 tokens
+            return launch_attention_prefill(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out,
+                                            (float*)ctx->attn.ptr, sink, ctx->prefill_tiles, ctx->prefill_tile_count);
         return launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
                                        (float*)ctx->attn.ptr, sink);
     }

@@ -669,16 +669,18 @@ __global__ void __launch_bounds__(64) attention_values_kernel(StreamParams p, co
 // such warps share one 32-column box of every value tile.  A lane then carries ONE chain (two instructions per position
 // beside its two shared-memory loads), and a stream of 4096 positions is done in about as many times the add latency,
 // where the kernel above, with four chains per lane and one warp per box, takes four times as long on a quarter of the warps.
-template <int WIDTH>
+template <int WIDTH, int DEEP>
 __global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
     chained_kernel_entry();
     constexpr int G = 4;
     constexpr int BOX_BYTES = kTP * 128;
-    constexpr int kDeep = kWideDeep;   // (12 stages were tried: the larger CTAs lost more in residency than the depth gained)
+    // The ring's depth bounds how fast one CTA's stream arrives (a copy takes about a microsecond to land): 6 stages when
+    // the launch has CTAs enough to fill every SM several times over, 16 when it has few and long streams.
+    constexpr int kDeep = DEEP;
     constexpr int kWarps = 4;
     extern __shared__ unsigned char wide_raw[];
     unsigned char* stages = wide_raw + ((1024u - (s_smem_u32(wide_raw) & 1023u)) & 1023u);   // [kDeep][BOX_BYTES], swizzled boxes
-    __shared__ __align__(16) float wbuf[kWarps][2][kTP * G];
+    float* wbuf_all = (float*)(stages + kDeep * BOX_BYTES);   // [kWarps][2 chunks][256 positions][G]: each warp's weights
     __shared__ uint64_t full[kDeep], empty[kDeep];
     __shared__ int abort_words[4];
     volatile int* abort_flag = abort_words;
@@ -724,17 +726,42 @@ __global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams
     const float* wrow = p.scratch + ((int64_t)token * p.heads + head0) * p.capacity;   // weights [head][position]
     const int piece = c8 >> 2, within = (c8 & 3) * 4;
     float acc = 0.0f;
-    float w_next[G];   // as a loader, the lane is a position of the next tile: its four heads' weights
+    // The weights of kWChunk positions at a time, fetched a whole chunk ahead: they come from L2, whose latency is several
+    // times what a warp needs to fold a tile, so a fetch one tile ahead left every tile waiting for its weights.
+    // Each warp keeps its own copy ([2 chunks][position][head]), so the warps need no barrier among themselves.
+    constexpr int kWChunk = 256;
+    constexpr int kPerLane = kWChunk / 32;
+    float4* wchunk = (float4*)wbuf_all + (size_t)warp * 2 * kWChunk;
+    auto fetch = [&](int chunk, float (&w4)[kPerLane][G]) {
 #pragma unroll
-    for (int i = 0; i < G; i++) w_next[i] = lane < len ? wrow[(int64_t)i * p.capacity + lane] : 0.0f;
+        for (int u = 0; u < kPerLane; u++) {
+            int pos = chunk * kWChunk + u * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < G; i++) w4[u][i] = pos < len ? wrow[(int64_t)i * p.capacity + pos] : 0.0f;
+        }
+    };
+    auto stash = [&](int chunk, const float (&w4)[kPerLane][G]) {
+        float4* dst = wchunk + (size_t)(chunk & 1) * kWChunk;
+#pragma unroll
+        for (int u = 0; u < kPerLane; u++) dst[u * 32 + lane] = make_float4(w4[u][0], w4[u][1], w4[u][2], w4[u][3]);
+    };
+    float w_next[kPerLane][G];
+    fetch(0, w_next);
+    stash(0, w_next);
+    const int chunks = (len + kWChunk - 1) / kWChunk;
+    if (chunks > 1) fetch(1, w_next);
+    __syncwarp();
     bool ok = true;
     for (int tile = 0; tile < tiles; tile++) {
-        float* wt = wbuf[warp][tile & 1];
-        *(float4*)(wt + lane * G) = make_float4(w_next[0], w_next[1], w_next[2], w_next[3]);
-        int next = (tile + 1) * kTP + lane;
-#pragma unroll
-        for (int i = 0; i < G; i++) w_next[i] = next < len ? wrow[(int64_t)i * p.capacity + next] : 0.0f;
-        __syncwarp();
+        const int chunk = tile / (kWChunk / kTP);
+        if (tile % (kWChunk / kTP) == 0 && tile > 0) {
+            // entering chunk `chunk`: its weights were fetched while the chunk before it was folded; store them and start
+            // fetching the chunk after it
+            stash(chunk, w_next);
+            if (chunk + 1 < chunks) fetch(chunk + 1, w_next);
+            __syncwarp();
+        }
+        const float* wt = (const float*)(wchunk + (size_t)(chunk & 1) * kWChunk + (tile % (kWChunk / kTP)) * kTP);
         int s = tile % kDeep;
         if (!s_mbar_wait(&full[s], (unsigned)((tile / kDeep) & 1), abort_flag)) ok = false, *abort_flag = 1;
         const unsigned char* vt = stages + s * BOX_BYTES + within;
@@ -768,6 +795,284 @@ __global__ void __launch_bounds__(160) attention_values_wide_kernel(StreamParams
     if (p.sink.qs) quantize_block_q8(mine, lane, p.sink.scales + (at >> 5), p.sink.sums + (at >> 5), p.sink.totals + (at >> 5), p.sink.qs + at);
 }
 
+// ---- prefill: many consecutive tokens of one stream --------------------------------------------------------------
+// A prompt's tokens attend over the same keys and values, each up to its own position.  The kernels above take one query
+// token per CTA, so a prompt of n tokens reads its keys and values n times.  Here a CTA takes a tile of 16 consecutive tokens
+// of one stream (x 4 query heads of one key/value head = 64 query rows) and streams the keys, then the values, ONCE for all
+// of them, through the same ring of tiled tensor copies.  Every sum keeps the host's order, so a token's bits are those of
+// the decode kernels (prefill == decode, spec/block_matmul_spec.cr:253-260):
+//   scores   register tiles of 4 query rows x 4 positions per thread over a tile of 32 positions, the 128 products of a score
+//            added in column order; the two halves of the CTA take alternate key tiles.  Scores go to the scratch array
+//            (which stays in L2), masked by each row's own last position;
+//   softmax  maximum per row, exp in place by all threads, then one thread per row folds its denominator in position order;
+//   values   register tiles of 4 query rows x 8 columns per thread; a position's weights (exp / denominator) are made once per
+//            tile into shared memory.  Positions a row must not see have weight +0, and +-0 never changes a running sum
+//            that started at +0, so they cost nothing but the issue slots.
+constexpr int kQT = 16;                // query tokens per CTA
+constexpr int kQRows = kQT * 4;        // query rows: token-major, head-minor
+constexpr int kPrefillConsumers = 256;
+
+struct PrefillParams {
+    StreamParams s;
+    const int* qtiles;   // [tiles][2]: first token of the tile (in packed order), tokens in it (<= kQT)
+};
+
+template <int WIDTH>
+__global__ void __launch_bounds__(kPrefillConsumers + 32, 2) attention_prefill_kernel(PrefillParams pp, const __grid_constant__ StreamMaps maps) {
+    chained_kernel_entry();
+    const StreamParams& p = pp.s;
+    constexpr int G = 4;
+    constexpr int BOXES = WIDTH / 32;
+    constexpr int BOX_BYTES = kTP * 128;
+    constexpr int STAGE_BYTES = BOXES * BOX_BYTES;
+    constexpr int QP = WIDTH + 4;                  // pitch of a query row, and of an output row staged for the quantiser
+    static_assert(WIDTH == 128, "the thread tiles below are laid out for 128 columns");
+    extern __shared__ unsigned char prefill_raw[];
+    unsigned char* smem = prefill_raw + ((1024u - (s_smem_u32(prefill_raw) & 1023u)) & 1023u);
+    uint64_t* full = (uint64_t*)smem;              // [kRing]
+    uint64_t* empty = (uint64_t*)(smem + 64);      // [kRing]
+    volatile int* abort_flag = (volatile int*)(smem + 128);
+    int* limits = (int*)(smem + 256);              // [kQRows] last visible position of each query row, -1: no such row
+    float* tops = (float*)(smem + 512);            // [kQRows]
+    float* tots = (float*)(smem + 768);            // [kQRows]
+    unsigned char* stages = smem + 1024;           // [kRing][BOXES][kTP][128 bytes], swizzled
+    float* qs = (float*)(stages + kRing * STAGE_BYTES);     // [kQRows][QP]; later the outputs
+    float* wbuf = qs + kQRows * QP;                // [kQRows][kTP + 1] weights of one value tile; first the partial maxima
+
+    const int tile_first = pp.qtiles[2 * blockIdx.y], tile_count = pp.qtiles[2 * blockIdx.y + 1];
+    const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
+    const int kvh = blockIdx.x / groups_per_kv;
+    const int head0 = kvh * per_kv + (blockIdx.x % groups_per_kv) * G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int row = p.table[3 * tile_first];
+    const int last_limit = p.table[3 * (tile_first + tile_count - 1) + 1];
+    if (row < 0 || row >= p.rows || last_limit < 0 || last_limit >= p.capacity || tile_count < 1 || tile_count > kQT) {
+        if (tid == 0 && blockIdx.x == 0) report_bad_index(p.errors, last_limit, p.capacity);
+        return;
+    }
+    const int len = last_limit + 1;                // positions the tile's last token sees
+    const int tiles = (len + kTP - 1) / kTP;
+
+    if (tid == 0) {
+        for (int s = 0; s < kRing; s++) {
+            s_mbar_init(&full[s], 1);
+            s_mbar_init(&empty[s], kPrefillConsumers / 32);
+        }
+        abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    for (int i = tid; i < kQRows * WIDTH; i += blockDim.x) {
+        int r = i / WIDTH, d = i % WIDTH, t = r >> 2, h = r & 3;
+        qs[r * QP + d] = t < tile_count ? p.q[(int64_t)(tile_first + t) * p.q_stride + (int64_t)(head0 + h) * WIDTH + d] : 0.0f;
+    }
+    for (int r = tid; r < kQRows; r += blockDim.x) {
+        int t = r >> 2;
+        // a token of another stream, or out of order, would break the tile: such a row is left out
+        bool mine = t < tile_count && p.table[3 * (tile_first + t)] == row;
+        int limit = mine ? p.table[3 * (tile_first + t) + 1] : -1;
+        limits[r] = limit >= 0 && limit <= last_limit ? limit : -1;
+    }
+    __syncthreads();
+
+    if (warp == kPrefillConsumers / 32) {
+        // ------------------------------------------------------------ producer: keys, then values, one ring
+        if (lane != 0) return;
+        const int plane = (row * p.kv_heads + kvh) * p.capacity;
+        int issued = 0;
+        bool ok = true;
+        for (int j = 0; j < 2 * tiles; j++) {
+            int s = j % kRing;
+            if (j >= kRing) ok = s_mbar_wait(&empty[s], (unsigned)((j / kRing - 1) & 1), abort_flag);
+            if (!ok) break;
+            const CUtensorMap* map = j < tiles ? &maps.k : &maps.v;
+            int y = plane + (j < tiles ? j : j - tiles) * kTP;
+            unsigned char* dst = stages + (size_t)s * STAGE_BYTES;
+            s_mbar_expect_tx(&full[s], STAGE_BYTES);
+#pragma unroll
+            for (int b = 0; b < BOXES; b++) s_tensor_load(dst + b * BOX_BYTES, map, 32 * b, y, &full[s]);
+            issued = j + 1;
+        }
+        if (!ok) {
+            *abort_flag = 1;
+            atomicExch(&p.errors->timeout, 1);
+            for (int j = max(0, issued - kRing); j < issued; j++) s_mbar_wait(&full[j % kRing], (unsigned)((j / kRing) & 1), abort_flag + 1);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers (256 threads; every named barrier below is
+    // reached by all of them, whether a wait gave up or not)
+    auto consumers_barrier = [] { asm volatile("bar.sync 3, %0;" ::"n"(kPrefillConsumers) : "memory"); };
+    bool ok = true;
+    float* srow0 = p.scratch + ((int64_t)tile_first * p.heads + head0) * p.capacity;   // row r = 4 t + h: + (t * heads + h) * capacity
+    auto score_row = [&](int r) { return srow0 + ((int64_t)(r >> 2) * p.heads + (r & 3)) * p.capacity; };
+
+    // ---- 1. scores ----
+    {
+        const int half = warp >> 2;                // which key tiles this half of the CTA takes
+        const int u = tid & 127, rg = u >> 3, pg = u & 7;   // rows 4 rg .. 4 rg + 3, positions pg + 8 j of the tile
+        float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        int lim[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) lim[i] = limits[4 * rg + i];
+        for (int tile = 0; tile < tiles; tile++) {
+            const int s = tile % kRing;
+            if (!s_mbar_wait(&full[s], (unsigned)((tile / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+            if ((tile & 1) == half) {
+                float acc[4][4];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+                const unsigned char* st = stages + (size_t)s * STAGE_BYTES;
+#pragma unroll 4
+                for (int c = 0; c < WIDTH / 4; c++) {   // four columns at a time, in column order
+                    float4 kq[4], qq[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int pos = pg + 8 * j;   // pos & 7 == pg: the eight lanes of a load's phase hit eight different banks
+                        kq[j] = *(const float4*)(st + (c >> 3) * BOX_BYTES + pos * 128 + (((c & 7) ^ pg) << 4));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) qq[i] = *(const float4*)(qs + (4 * rg + i) * QP + 4 * c);
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(qq[i].x, kq[j].x));
+                            acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(qq[i].y, kq[j].y));
+                            acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(qq[i].z, kq[j].z));
+                            acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(qq[i].w, kq[j].w));
+                        }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float* sr = score_row(4 * rg + i);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int pos = tile * kTP + pg + 8 * j;
+                        if (pos <= lim[i]) {
+                            float sc = __fadd_rn(__fmul_rn(acc[i][j], p.scale), 0.0f);
+                            sr[pos] = sc;
+                            top[i] = fmaxf(top[i], sc);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) s_mbar_arrive(&empty[s]);
+        }
+        // a row's maximum: 16 threads hold a part of it (8 position groups x 2 halves)
+#pragma unroll
+        for (int i = 0; i < 4; i++) wbuf[(4 * rg + i) * 16 + half * 8 + pg] = top[i];
+    }
+    consumers_barrier();
+    if (tid < kQRows) {
+        float top = wbuf[tid * 16];
+#pragma unroll
+        for (int i = 1; i < 16; i++) top = fmaxf(top, wbuf[tid * 16 + i]);
+        tops[tid] = top;
+    }
+    consumers_barrier();
+    // ---- 2. softmax: exp in place by everyone, then one thread per row folds the denominator in position order ----
+    for (int r = warp; r < kQRows; r += kPrefillConsumers / 32) {
+        const int limit = limits[r];
+        float* sr = score_row(r);
+        const float top = tops[r];
+        for (int pos = lane; pos <= limit; pos += 32) sr[pos] = exact_exp(__fsub_rn(sr[pos], top));
+    }
+    consumers_barrier();
+    if (tid < kQRows) {
+        const int limit = limits[tid];
+        const float* sr = score_row(tid);
+        float total = 0.0f;
+        int pos = 0;
+        // a row starts on a 16-byte boundary when the capacity is a multiple of 4; otherwise plain loads
+        if ((((uintptr_t)sr) & 15) == 0) {
+            for (; pos + 8 <= limit + 1; pos += 8) {
+                float4 a = *(const float4*)(sr + pos), b = *(const float4*)(sr + pos + 4);
+                total = __fadd_rn(total, a.x), total = __fadd_rn(total, a.y), total = __fadd_rn(total, a.z), total = __fadd_rn(total, a.w);
+                total = __fadd_rn(total, b.x), total = __fadd_rn(total, b.y), total = __fadd_rn(total, b.z), total = __fadd_rn(total, b.w);
+            }
+        }
+        for (; pos <= limit; pos++) total = __fadd_rn(total, sr[pos]);
+        tots[tid] = total;
+    }
+    consumers_barrier();
+    // ---- 3. outputs ----
+    {
+        const int rg = tid >> 4, cg = tid & 15;    // rows 4 rg .. + 3, columns 8 cg .. + 7
+        float acc[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int c = 0; c < 8; c++) acc[i][c] = 0.0f;
+        // as a maker of weights, the thread takes position `lane` of each tile for the eight rows warp + 8 e: a warp's loads
+        // of exp values are then 128 consecutive bytes of one row of the scratch array
+        constexpr int WP = kTP + 1;                 // pitch of a row's weights in shared memory: [row][position]
+        int wlimit[8];
+        float wtot[8];
+        const float* wsr[8];
+        float e_next[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int wr = warp + 8 * e;
+            wlimit[e] = limits[wr], wtot[e] = tots[wr], wsr[e] = score_row(wr);
+            e_next[e] = lane <= wlimit[e] ? wsr[e][lane] : 0.0f;
+        }
+        const int box = cg >> 2, piece0 = (cg & 3) * 2;   // the thread's 8 columns are two 16-byte pieces of box `box`
+        for (int tile = 0; tile < tiles; tile++) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int pos = tile * kTP + lane;
+                // a position the row must not see weighs +0 (the host masks it to -inf before the softmax: exp gives 0f)
+                wbuf[(warp + 8 * e) * WP + lane] = pos <= wlimit[e] ? __fdiv_rn(e_next[e], wtot[e]) : 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int pos = (tile + 1) * kTP + lane;
+                e_next[e] = pos <= wlimit[e] ? wsr[e][pos] : 0.0f;
+            }
+            consumers_barrier();   // the tile's weights are in place
+            const int j = tiles + tile, s = j % kRing;
+            if (!s_mbar_wait(&full[s], (unsigned)((j / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+            const unsigned char* vt = stages + (size_t)s * STAGE_BYTES + box * BOX_BYTES;
+            const int count = min(kTP, len - tile * kTP);
+            for (int pos = 0; pos < count; pos++) {
+                const float ws[4] = {wbuf[(4 * rg) * WP + pos], wbuf[(4 * rg + 1) * WP + pos], wbuf[(4 * rg + 2) * WP + pos], wbuf[(4 * rg + 3) * WP + pos]};
+                const float4 va = *(const float4*)(vt + pos * 128 + ((piece0 ^ (pos & 7)) << 4));
+                const float4 vb = *(const float4*)(vt + pos * 128 + (((piece0 + 1) ^ (pos & 7)) << 4));
+                const float vs[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int c = 0; c < 8; c++) acc[i][c] = __fadd_rn(acc[i][c], __fmul_rn(ws[i], vs[c]));
+            }
+            __syncwarp();
+            if (lane == 0) s_mbar_arrive(&empty[s]);
+            consumers_barrier();   // everyone is done with the weights before the next tile's overwrite them
+        }
+        // the rows go out through shared memory (over the queries), so that a warp holds one 32-column block for the quantiser
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int c = 0; c < 8; c++) qs[(4 * rg + i) * QP + 8 * cg + c] = acc[i][c];
+    }
+    consumers_barrier();
+    if (!ok || *abort_flag) {
+        if (tid == 0) atomicExch(&p.errors->timeout, 1);
+        return;
+    }
+    for (int item = warp; item < kQRows * (WIDTH / 32); item += kPrefillConsumers / 32) {
+        const int r = item / (WIDTH / 32), blk = item % (WIDTH / 32);
+        if (limits[r] < 0) continue;
+        const float v = qs[r * QP + 32 * blk + lane];
+        const int64_t at = ((int64_t)(tile_first + (r >> 2)) * p.heads + head0 + (r & 3)) * WIDTH + 32 * blk + lane;
+        if (p.out) p.out[at] = v;
+        if (p.sink.qs) quantize_block_q8(v, lane, p.sink.scales + (at >> 5), p.sink.sums + (at >> 5), p.sink.totals + (at >> 5), p.sink.qs + at);
+    }
+}
+
 }  // namespace
 
 int64_t attention_stream_scratch_bytes(int tokens, int heads, int capacity) { return (int64_t)tokens * heads * capacity * 4 + 256; }
@@ -782,6 +1087,35 @@ bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int k
     (void)ctx, (void)tokens;
     bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
     return width == 128 && kv_heads > 0 && heads % kv_heads == 0 && (heads / kv_heads) % 4 == 0 && aligned && tensor_maps_available();
+}
+
+// The prefill kernel over `tile_count` query tiles (pairs first token, count in device memory, longest first).
+int launch_attention_prefill(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v, int rows,
+                             int kv_heads, int capacity, const int* table, float scale, float* out, float* scratch, QuantSink sink,
+                             const int* qtiles, int tile_count) {
+    constexpr int WIDTH = 128;
+    (void)tokens;
+    PrefillParams pp{StreamParams{q, q_stride, heads, rows, kv_heads, capacity, table, scale, out, ctx->errors, nullptr, scratch, 1, sink, ctx->wait_hint}, qtiles};
+    StreamMaps maps;
+    uint64_t plane_rows = (uint64_t)rows * kv_heads * capacity;
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
+    TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
+    const size_t smem = 1024 + 1024 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)kQRows * (WIDTH + 4) * 4 + (size_t)kQRows * (kTP + 1) * 4;
+    auto kernel = attention_prefill_kernel<WIDTH>;
+    {
+        static std::mutex lock;
+        static std::map<int, bool> done;
+        std::lock_guard<std::mutex> guard(lock);
+        if (!done.count(ctx->ordinal)) {
+            TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            done[ctx->ordinal] = true;
+        }
+    }
+    const int groups = kv_heads * (heads / kv_heads / 4);
+    TSM_CUDA(ctx, launch_chained(ctx, kernel, dim3(groups, tile_count), dim3(kPrefillConsumers + 32), smem, pp, maps));
+    count_launch(ctx);
+    TSM_LAUNCH_CHECK(ctx);
+    return TSM_OK;
 }
 
 int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
@@ -825,17 +1159,19 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         static const char* narrow = getenv("TSM_ATTN_VALUES_NARROW");   // the one-warp-per-box value pass, for timing it
         if (narrow && narrow[0] == '1') TSM_CUDA(ctx, launch_chained(ctx, attention_values_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(64), 0, p, maps));
         else {
-            const size_t smem_wide = 1024 + (size_t)kWideDeep * kTP * 128;
+            const bool deep = (int64_t)groups * 4 * tokens <= 3 * (int64_t)ctx->sm_count;
+            const size_t smem_wide = 1024 + (size_t)(deep ? 16 : kWideDeep) * kTP * 128 + (size_t)4 * 2 * 256 * 4 * 4;   // the ring, then the warps' weights
+            auto wide = deep ? attention_values_wide_kernel<WIDTH, 16> : attention_values_wide_kernel<WIDTH, kWideDeep>;
             static std::mutex wide_lock;
-            static std::map<int, bool> wide_done;
+            static std::map<std::pair<int, bool>, bool> wide_done;
             {
                 std::lock_guard<std::mutex> guard(wide_lock);
-                if (!wide_done.count(ctx->ordinal)) {
-                    TSM_CUDA(ctx, cudaFuncSetAttribute(attention_values_wide_kernel<WIDTH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wide));
-                    wide_done[ctx->ordinal] = true;
+                if (!wide_done.count({ctx->ordinal, deep})) {
+                    TSM_CUDA(ctx, cudaFuncSetAttribute(wide, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_wide));
+                    wide_done[{ctx->ordinal, deep}] = true;
                 }
             }
-            TSM_CUDA(ctx, launch_chained(ctx, attention_values_wide_kernel<WIDTH>, dim3(groups * 4, tokens), dim3(160), smem_wide, p, maps));
+            TSM_CUDA(ctx, launch_chained(ctx, wide, dim3(groups * 4, tokens), dim3(160), smem_wide, p, maps));
         }
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);

@@ -69,6 +69,8 @@ struct tsm_ctx {
     uint64_t scratch_generation = 1;          // bumped whenever a scratch buffer moves
     int tp_rank = 0, tp_world = 1;            // this context's place in a tensor-parallel group
     bool chain_launches = false;              // the engine sets it around steps of a few rows (see launch_chained)
+    const int* prefill_tiles = nullptr;       // set by the engine around a step that holds prompts: query tiles of 16 consecutive
+    int prefill_tile_count = 0;               //   tokens of one stream (first token, count), longest first, in device memory
     void* comm = nullptr;                     // its NCCL communicator
     bool comm_failed = false;                 // an exchange failed or the group was aborted: every later one is refused
     int tp_variant = 0;                       // TSM_TP_GATHER or TSM_TP_REDUCE: how models built on this context are split
@@ -199,6 +201,9 @@ bool attention_stream_fits(tsm_ctx* ctx, int tokens, int heads, int width, int k
 int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v,
                             int rows, int kv_heads, int capacity, const int* table, float scale, float* out, const int* order,
                             float* scratch, QuantSink sink);
+int launch_attention_prefill(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, const float* k, const float* v, int rows,
+                             int kv_heads, int capacity, const int* table, float scale, float* out, float* scratch, QuantSink sink,
+                             const int* qtiles, int tile_count);
 bool pipe_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 int launch_block_matmul_pipe(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                              const float* bias, const float* residual, float* out);

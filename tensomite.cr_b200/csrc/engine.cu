@@ -25,7 +25,7 @@ static bool has_f32_matrix(const tsm_model* m) {
 
 static void free_workspace(tsm_model* m) {
     Workspace& w = m->ws;
-    void* bufs[] = {w.ids, w.table, w.last, w.order, w.x, w.xl, w.qkv, w.att, w.up, w.h, w.logits, w.picks, w.qa, w.qb, w.qc, w.tp_parts, w.tp_rows, w.tp_best};
+    void* bufs[] = {w.ids, w.table, w.last, w.order, w.qtiles, w.x, w.xl, w.qkv, w.att, w.up, w.h, w.logits, w.picks, w.qa, w.qb, w.qc, w.tp_parts, w.tp_rows, w.tp_best};
     for (void* b : bufs) pool_release(m->ctx, b);
     if (w.host) cudaFreeHost(w.host);
     w = Workspace{};
@@ -45,6 +45,7 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     TSM_TRY(pool_alloc(ctx, T * 12, (void**)&w.table));
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.last));
     TSM_TRY(pool_alloc(ctx, T * 4, (void**)&w.order));
+    TSM_TRY(pool_alloc(ctx, T * 8, (void**)&w.qtiles));
     TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.x));
     TSM_TRY(pool_alloc(ctx, T * c.width * 4, (void**)&w.xl));
     TSM_TRY(pool_alloc(ctx, T * (qn + 2 * kvn) * 4, (void**)&w.qkv));
@@ -62,7 +63,7 @@ static int ensure_workspace(tsm_model* m, int tokens) {
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.width), &w.qa));
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, qn), &w.qb));
     TSM_TRY(pool_alloc(ctx, quant_scratch_bytes(tokens, c.hidden), &w.qc));
-    TSM_CUDA(ctx, cudaMallocHost((void**)&w.host, (size_t)T * 5 * 4));
+    TSM_CUDA(ctx, cudaMallocHost((void**)&w.host, (size_t)T * 7 * 4));
     w.tokens = tokens;
     m->ws_generation++;
     return TSM_OK;
@@ -630,7 +631,30 @@ static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* count
     TSM_CUDA(ctx, cudaMemcpyAsync(w.last, h_last, (size_t)outputs * 4, cudaMemcpyHostToDevice, ctx->stream));
     ctx->counters.uploads += 3;
     ctx->counters.upload_bytes += (int64_t)total * 16 + (int64_t)outputs * 4;
-    TSM_TRY(launch_step(model, cache, total, outputs, picks != nullptr));
+    // A step that holds a prompt (a row with 8 new tokens or more): attention takes the tokens in tiles of 16 consecutive
+    // tokens of one row, the tiles that see the most positions first.
+    int longest = 0;
+    for (int row = 0; row < cache->rows; row++) longest = std::max(longest, (int)counts[row]);
+    ctx->prefill_tiles = nullptr, ctx->prefill_tile_count = 0;
+    if (longest >= 8) {
+        int32_t* h_tiles = w.host + 5 * (int64_t)w.tokens;
+        std::vector<std::pair<int, std::pair<int, int>>> tiles;   // (last position, (first token, count))
+        int first = 0;
+        for (int row = 0; row < cache->rows; row++) {
+            for (int j = 0; j < counts[row]; j += 16) {
+                int n = std::min(16, (int)counts[row] - j);
+                tiles.push_back({cache->lengths[row] + j + n - 1, {first + j, n}});
+            }
+            first += counts[row];
+        }
+        std::stable_sort(tiles.begin(), tiles.end(), [](const auto& a, const auto& b) { return a.first > b.first; });
+        for (size_t i = 0; i < tiles.size(); i++) h_tiles[2 * i] = tiles[i].second.first, h_tiles[2 * i + 1] = tiles[i].second.second;
+        TSM_CUDA(ctx, cudaMemcpyAsync(w.qtiles, h_tiles, tiles.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
+        ctx->prefill_tiles = w.qtiles, ctx->prefill_tile_count = (int)tiles.size();
+    }
+    int step_rc = launch_step(model, cache, total, outputs, picks != nullptr);
+    ctx->prefill_tiles = nullptr, ctx->prefill_tile_count = 0;
+    TSM_TRY(step_rc);
     if (logits && picks && model->tp > 1) TSM_TRY(gather_full_logits(model, outputs));
     if (keep_on_device) {  // the caller reads ws.logits itself, after its own kernels
         for (int row = 0; row < cache->rows; row++) cache->lengths[row] += counts[row];

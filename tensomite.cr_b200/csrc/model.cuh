@@ -29,6 +29,7 @@ struct Workspace {
     int* table = nullptr;    // [T,3] row, position, positions held
     int* last = nullptr;     // [T] indices of the rows whose logits are wanted
     int* order = nullptr;    // [T] tokens by visible positions, most first (attention's launch order)
+    int* qtiles = nullptr;   // [T, 2] query tiles of a step that holds prompts: first token, tokens (attention's prefill kernel)
     float* x = nullptr;      // [T, width]
     float* xl = nullptr;     // [T, width] gathered last rows
     float* qkv = nullptr;    // [T, (heads + 2 kv) * hw]
@@ -43,7 +44,7 @@ struct Workspace {
     void* qa = nullptr;      // quantised activations, K = width
     void* qb = nullptr;      // K = heads * hw
     void* qc = nullptr;      // K = hidden
-    int32_t* host = nullptr; // pinned: ids [T] + table [3T] + picks [T]
+    int32_t* host = nullptr; // pinned: ids [T] + table [3T] + picks [T] + query tiles [2T]
 };
 
 // The regions of the fused tensor-parallel exchange (tp_exchange.cu): this rank's and, mapped through CUDA IPC, the peers'.

@@ -411,3 +411,34 @@ def test_errors_are_raised_not_trapped(dev, tmp_path):
     with pytest.raises(pkg.Error):
         pkg.Llama.load(str(bad), dev)
     model.free()
+
+
+def test_prompts_through_the_prefill_attention_kernel_have_the_decode_bits(dev):
+    """spec/block_matmul_spec.cr:253-260 at a shape the prefill attention kernel takes (heads of width 128, four query heads
+    per key/value head, eight layers): prompts of 150 and 37 tokens in one packed step (tiles of 16 tokens, a last tile
+    that is not full, a row that stays idle), then a second chunk of 40 tokens on top of the first row's cache, give every
+    position the logits it has when the tokens are fed one by one, bit for bit, and the oracle's."""
+    config = dict(arch="llama", layers=8, width=1024, heads=8, kv_heads=2, head_width=128, hidden=2048, vocab=2048, context=512,
+                  eps=1e-5, rope_theta=500000.0, tied=False)
+    model = pkg.Model.random(dev, config, pkg.Q4_0, seed=77)
+    rng = np.random.default_rng(8)
+    first = rng.integers(0, config["vocab"], size=150).tolist()
+    other = rng.integers(0, config["vocab"], size=37).tolist()
+    more = rng.integers(0, config["vocab"], size=40).tolist()
+    cache = model.new_batch_cache(3, 256)
+    got = model.forward([first, [], other], cache)                 # 187 tokens, one step
+    got_more = model.forward([more, [], []], cache)                # 40 more on a cache that already holds 150
+    step = model.new_batch_cache(3, 256)
+    rows = []
+    for t in first:
+        rows.append(model.forward_last([[t], [], []], step)[0])
+    for t in other:
+        rows.append(model.forward_last([[], [], [t]], step)[0])
+    assert np.array_equal(bits(got), bits(np.stack(rows)))
+    rows = [model.forward_last([[t], [], []], step)[0] for t in more]
+    assert np.array_equal(bits(got_more), bits(np.stack(rows)))
+    ref = oracle.model_from_device(model, threads=8)
+    rcache = ref.new_cache(1, 256)
+    want = ref.forward(rcache, [first], last=False)
+    assert np.array_equal(bits(got[:150]), bits(want))
+    cache.free(), step.free(), model.free()
