@@ -291,7 +291,7 @@ def kernel_case(pkg, dev, torch, stream, spec, repeats, peak):
     else:
         raise SystemExit(f"unknown case {spec!r}")
     dev.sync()
-    if what == "matvec" and algorithmic < (256 << 20):
+    if what in ("matvec", "product") and rows <= 4 and algorithmic < (256 << 20):
         # weights smaller than L2: a 512 MB buffer is rewritten before every launch and its time taken out, as in the sweep
         flush = dev.alloc(512 << 20)
 

@@ -17,6 +17,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "row_helpers.cuh"
 
 namespace tsm {
 
@@ -296,7 +297,8 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
                                                                   const float* __restrict__ k, const float* __restrict__ v,
                                                                   int rows, int kv_heads, int capacity,
                                                                   const int* __restrict__ table, float scale, float* out,
-                                                                  ErrorRecord* errors, const int* __restrict__ order, QuantSink sink) {
+                                                                  ErrorRecord* errors, const int* __restrict__ order, QuantSink sink,
+                                                                  int fresh, FreshRows fresh_rows) {
     chained_kernel_entry();
     constexpr int GS = G == 3 ? 4 : G;          // interleave stride of the scores
     constexpr int PITCH = WIDTH + 4;            // floats per staged key row
@@ -309,6 +311,7 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     float* sc = kt + STAGES * TP * PITCH;   // [capacity * GS]
     __shared__ float wred[WARPS][4];
     __shared__ float totals[4];
+    __shared__ __align__(16) float fresh_k[WIDTH], fresh_v[WIDTH];  // the token's own key and value (FreshRows)
 
     const int token = order ? order[blockIdx.y] : blockIdx.y;  // longest tokens first when an order is given
     const int per_kv = heads / kv_heads, groups_per_kv = per_kv / G;
@@ -324,8 +327,38 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
     const float* kb = k + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
     const float* vb = v + ((int64_t)row * kv_heads + kvh) * capacity * WIDTH;
 
-    for (int i = tid; i < G * WIDTH; i += THREADS)
-        qs[(i / WIDTH) * PITCH + i % WIDTH] = q[(int64_t)token * q_stride + (int64_t)head0 * WIDTH + i];
+    if (fresh) {
+        // q is the token's joined [q; k; v] row as the projection left it: rotate this CTA's query heads and the kv head's key
+        // on the way in (rope_append_kernel's arithmetic), keep key and value for position `limit`, and let the first CTA of
+        // the kv head append them to the cache
+        constexpr int HALF = WIDTH / 2;
+        const float* joined = q + (int64_t)token * q_stride;
+        const float* cs = fresh_rows.cos_table ? fresh_rows.cos_table + (int64_t)limit * WIDTH : nullptr;
+        const float* sn = fresh_rows.cos_table ? fresh_rows.sin_table + (int64_t)limit * WIDTH : nullptr;
+        if (cs && limit >= fresh_rows.context) {
+            if (threadIdx.x == 0 && blockIdx.x == 0) report_bad_index(errors, limit, fresh_rows.context);
+            return;
+        }
+        for (int i = tid; i < (G + 2) * HALF; i += THREADS) {
+            int h = i / HALF, col = i % HALF;  // h < G: a query head; G: the key; G + 1: the value
+            const float* src = joined + (int64_t)(h < G ? head0 + h : h == G ? heads + kvh : heads + kv_heads + kvh) * WIDTH;
+            float a = src[col], b = src[col + HALF];
+            if (cs && h <= G) {
+                float ra, rb;
+                rotate_pair(a, b, cs, sn, col, HALF, &ra, &rb);
+                a = ra, b = rb;
+            }
+            float* dst = h < G ? qs + h * PITCH : h == G ? fresh_k : fresh_v;
+            dst[col] = a, dst[col + HALF] = b;
+            if (h >= G && blockIdx.x % groups_per_kv == 0) {
+                float* cache_row = const_cast<float*>(h == G ? kb : vb) + (int64_t)limit * WIDTH;
+                cache_row[col] = a, cache_row[col + HALF] = b;
+            }
+        }
+    } else {
+        for (int i = tid; i < G * WIDTH; i += THREADS)
+            qs[(i / WIDTH) * PITCH + i % WIDTH] = q[(int64_t)token * q_stride + (int64_t)head0 * WIDTH + i];
+    }
 
     const int tiles = (len + TP - 1) / TP;
     // Tile loads: thread tid always copies 16-byte piece (tid % CHUNKS) of rows (tid / CHUNKS) + n * (THREADS / CHUNKS),
@@ -356,6 +389,10 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
         load_tile(tile + STAGES - 1);  // into the stage read in the previous iteration (a barrier ended it)
         cp_async_wait<STAGES - 1>();
         __syncthreads();
+        if (fresh && tile == tiles - 1) {  // the last position is this token's own key: whatever the cache held there is replaced
+            if (tid < WIDTH) kt[((tile % STAGES) * TP + (limit - tile * TP)) * PITCH + tid] = fresh_k[tid];
+            __syncthreads();
+        }
         int p = tile * TP + sp;
         if (sp < TP && shd < G && p < len) {
             const float4* kr = (const float4*)(kt + ((tile % STAGES) * TP + sp) * PITCH);
@@ -425,6 +462,10 @@ __global__ void __launch_bounds__(THREADS) attention_exact_kernel(const float* _
         load_values(tile + STAGES - 1);
         cp_async_wait<STAGES - 1>();
         __syncthreads();
+        if (fresh && tile == tiles - 1) {
+            if (tid < WIDTH) kt[((tile % STAGES) * TP + (limit - tile * TP)) * PITCH + tid] = fresh_v[tid];
+            __syncthreads();
+        }
         if (folds) {
             const float* vt = kt + (tile % STAGES) * TP * PITCH + col;
             const float* wt = sc + (int64_t)tile * TP * GS;
@@ -532,12 +573,22 @@ static int launch_fast(tsm_ctx* ctx, const float* q, int64_t q_stride, int token
 
 int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
                      const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
-                     const QuantizedActs* quantized, const int* order) {
-    OpTimer timer(ctx, "RaggedAttention", tokens, heads, width);
+                     const QuantizedActs* quantized, const int* order, const FreshRows* fresh) {
+    OpTimer timer(ctx, fresh ? "Rope+WriteRows+RaggedAttention" : "RaggedAttention", tokens, heads, width);
     if (kv_heads <= 0 || heads % kv_heads != 0)
         return fail(ctx, TSM_ERR_ARG, std::to_string(heads) + " query heads do not group into " + std::to_string(kv_heads) + " key and value heads");
     if (tokens == 0) return TSM_OK;
     bool aligned = (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) == 0 && q_stride % 4 == 0;
+    // FreshRows is served by attention_exact_kernel alone; every other kernel gets the separate rope + append launch first
+    static const bool no_fresh = getenv("TSM_NO_FRESH_ROWS") != nullptr;  // time the separate launch instead
+    auto settle_fresh = [&]() -> int {
+        if (!fresh) return TSM_OK;
+        const FreshRows* f = fresh;
+        fresh = nullptr;
+        return launch_rope_append(ctx, const_cast<float*>(q), tokens, heads, kv_heads, width, f->cos_table, f->sin_table, f->context, table,
+                                  const_cast<float*>(k), const_cast<float*>(v), rows, capacity);
+    };
+    if (no_fresh || (ctx->mode == TSM_FAST && aligned && (width == 64 || width == 128))) TSM_TRY(settle_fresh());
     if (ctx->mode == TSM_FAST && aligned && width == 64)
         return launch_fast<64>(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, quantized);
     if (ctx->mode == TSM_FAST && aligned && width == 128)
@@ -546,6 +597,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     bool launched = false;
     const QuantSink sink = quant_sink(quantized);  // the kernels for widths 64 and 128 quantise their rows themselves
     if (attention_stream_fits(ctx, tokens, heads, width, kv_heads, q, q_stride, k, v)) {
+        TSM_TRY(settle_fresh());
         TSM_TRY(ensure_scratch(ctx, ctx->attn, attention_stream_scratch_bytes(tokens, heads, capacity)));
         static const bool no_prefill = getenv("TSM_NO_PREFILL_KERNEL") != nullptr;   // prompts through the decode kernels, for timing
         if (ctx->prefill_tiles && ctx->prefill_tile_count > 0 && !no_prefill)   // a step that holds prompts: keys and values once per 16 tokens
@@ -554,6 +606,8 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         return launch_attention_stream(ctx, q, q_stride, tokens, heads, k, v, rows, kv_heads, capacity, table, scale, out, order,
                                        (float*)ctx->attn.ptr, sink);
     }
+    const int fresh_on = fresh ? 1 : 0;
+    const FreshRows fresh_rows = fresh ? *fresh : FreshRows{nullptr, nullptr, 0};
     if (aligned && (width == 64 || width == 128)) {
         int per_kv = heads / kv_heads;
         int pitch = width + 4;
@@ -571,7 +625,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
         auto kernel = attention_exact_kernel<W, G, T, TP, S, U>;                                                          \
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
         TSM_CUDA(ctx, launch_chained(ctx, kernel, grid, dim3(T), smem, q, q_stride, heads, k, v, rows, kv_heads, capacity, table, scale, \
-                                     out, ctx->errors, order, sink));                                                     \
+                                     out, ctx->errors, order, sink, fresh_on, fresh_rows));                               \
     } while (0)
 #define TSM_EXACT_STAGES(W, G, T, TP, U)          \
     do {                                          \
@@ -603,6 +657,7 @@ int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens,
     }
     const bool fused_quantiser = launched;
     if (!launched) {
+        TSM_TRY(settle_fresh());
         size_t smem = (size_t)(width + capacity) * 4;
         if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "ordered attention over more than 51000 positions");
         if (smem > 48 * 1024)

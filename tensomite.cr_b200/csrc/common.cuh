@@ -102,6 +102,7 @@ inline void count_launch(tsm_ctx* ctx, int n = 1) { ctx->counters.launches += n;
 struct OpTimer {
     tsm_ctx* ctx;
     bool active = false;
+    bool dropped = false;  // set by a launcher that queued nothing after all: the span is not recorded
     cudaEvent_t start = nullptr;
     std::string label;
     OpTimer(tsm_ctx* c, const char* name, int64_t a = -1, int64_t b = -1, int64_t d = -1);
@@ -110,9 +111,10 @@ struct OpTimer {
 
 // A launch that may begin while the kernel before it on the stream is still draining (programmatic dependent launch): the
 // kernel's blocks are scheduled as soon as every block of its predecessor has started, run nothing but
-// `chained_kernel_entry()` until the predecessor has finished and its writes are visible, and only then touch memory.  Every
-// kernel launched through here calls chained_kernel_entry() as its first statement.  The attribute is set only while the
-// context's `chain_launches` is on, which the engine does for steps of at most 4 rows: measured, a batch-1 step of ~300
+// `chained_kernel_entry()` until the predecessor has finished and its writes are visible, and only then touch memory that a
+// kernel writes (the streamed matvec starts the copies of its first weights before it waits: weights are written by no kernel
+// of a step).  Every kernel launched through here calls chained_kernel_entry(), or its two halves, before anything else.
+// The attribute is set only while the context's `chain_launches` is on, which the engine does for steps of at most 4 rows: measured, a batch-1 step of ~300
 // very short kernels gains 5 %, while steps of 16 and 64 rows lose 9 % and 1 % (early blocks hold SM resources while they
 // wait).  TSM_CHAINED_LAUNCH=0 turns it off everywhere.
 bool chained_launch_enabled();
@@ -183,6 +185,11 @@ int launch_quantize_rows(tsm_ctx* ctx, const float* x, int rows, int k, int64_t 
                          int* totals, int8_t* qs);
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,
                         const float* bias, const float* residual, float* out);
+// A product of at most 4 F32 rows that quantises them itself, in every CTA of the streamed kernel (the quantiser's arithmetic,
+// so the same bits): one launch instead of two.  `taken` false: the shape is not one the streamed kernel serves, nothing
+// was launched.
+int launch_block_matvec_plain(tsm_ctx* ctx, const float* x, int64_t x_stride, int rows, int k, const uint8_t* w, int kind, int n,
+                              const float* bias, const float* residual, float* out, bool* taken);
 bool mma_product_fits(const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n);
 // Tensor-parallel exchanges (collective.cu).
 int tp_all_gather(tsm_ctx* ctx, void* buffer, int64_t bytes);
@@ -237,9 +244,19 @@ int launch_write_rows(tsm_ctx* ctx, float* cache, int rows, int heads, int capac
 int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_heads, int width, const float* cos_table,
                        const float* sin_table, int context, const int* table, float* keys, float* values, int rows,
                        int capacity);
+// A decode step's rope + cache append done by the attention kernel itself (modules.cr:434-452 then 194-217): `q` is then the
+// joined [q; k; v] row of each token, un-rotated; every CTA rotates its query heads and its kv head's new key as it loads
+// them, the first CTA of a kv head writes key and value to the cache at the token's position, and every CTA uses its own
+// copy of them for that position.  Only for steps in which each cache row receives ONE token (a token's CTAs never read what
+// another token's CTAs write).  Kernels that do not serve it get the separate rope + append launch first.
+struct FreshRows {
+    const float* cos_table;  // null: no rotation (GPT-2)
+    const float* sin_table;
+    int context;             // positions the tables hold
+};
 int launch_attention(tsm_ctx* ctx, const float* q, int64_t q_stride, int tokens, int heads, int width, const float* k,
                      const float* v, int rows, int kv_heads, int capacity, const int* table, float scale, float* out,
-                     const QuantizedActs* quantized, const int* order = nullptr);
+                     const QuantizedActs* quantized, const int* order, const FreshRows* fresh = nullptr);
 // order[r] = the token with the r-th most visible positions (ties by index), so that attention can start its
 // longest tokens first; null means token order.
 int launch_length_order(tsm_ctx* ctx, const int* table, int tokens, int* order);
@@ -268,8 +285,15 @@ __device__ __forceinline__ float half_bits_to_float(unsigned int bits) {
 
 // The reference's own exp (maths.cr:36-54), operation for operation; no contraction.
 // First statement of every kernel launched with launch_chained: waits for the kernel before it (complete, writes visible),
-// then lets the kernel after it be scheduled.  A no-op under an ordinary launch.
+// then lets the kernel after it be scheduled.  A no-op under an ordinary launch.  (Letting the successor in BEFORE the wait,
+// so that several kernels' blocks queue up on the SMs, measured 8 % slower on a batch-1 step of 300 kernels.)
 __device__ __forceinline__ void chained_kernel_entry() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// The same with room before the wait for work that reads nothing a kernel writes (the streamed matvec starts the copies of
+// its first weights there).
+__device__ __forceinline__ void chained_kernel_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

@@ -305,12 +305,17 @@ static int launch_step_kernels(tsm_model* m, tsm_cache* cache, int total, int ou
         if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm1_w, total, c.width, c.eps, f.plain, f.quantized));
         else TSM_TRY(launch_layernorm(ctx, w.x, l.norm1_w, l.norm1_b, total, c.width, c.eps, f.plain, f.quantized));
         TSM_TRY(product(m, qa, w.h, total, l.qkv, nullptr, w.qkv));
-        TSM_TRY(launch_rope_append(ctx, w.qkv, total, c.heads, c.kv_heads, hw, c.arch == 0 ? m->rope_cos : nullptr,
-                                   c.arch == 0 ? m->rope_sin : nullptr, c.context, w.table, cache->keys[i], cache->values[i],
-                                   cache->rows, cache->capacity));
+        // a decode step of a few rows: rope and the cache append happen inside the attention kernel
+        const bool fresh_rows = total <= 4 && m->one_token_per_row;
+        FreshRows fresh{c.arch == 0 ? m->rope_cos : nullptr, c.arch == 0 ? m->rope_sin : nullptr, c.context};
+        if (!fresh_rows)
+            TSM_TRY(launch_rope_append(ctx, w.qkv, total, c.heads, c.kv_heads, hw, c.arch == 0 ? m->rope_cos : nullptr,
+                                       c.arch == 0 ? m->rope_sin : nullptr, c.context, w.table, cache->keys[i], cache->values[i],
+                                       cache->rows, cache->capacity));
         f = feeds(l.o, w.att, &qb);
         TSM_TRY(launch_attention(ctx, w.qkv, qkvn, total, c.heads, hw, cache->keys[i], cache->values[i], cache->rows, c.kv_heads,
-                                 cache->capacity, w.table, scale, ordered || f.plain ? w.att : nullptr, f.quantized, order));
+                                 cache->capacity, w.table, scale, ordered || f.plain ? w.att : nullptr, f.quantized, order,
+                                 fresh_rows ? &fresh : nullptr));
         TSM_TRY(product(m, qb, w.att, total, l.o, w.x, w.x));
         f = feeds(l.up, w.h, &qa);
         if (c.arch == 0) TSM_TRY(launch_rmsnorm(ctx, w.x, l.norm2_w, total, c.width, c.eps, f.plain, f.quantized));
@@ -652,6 +657,7 @@ static int forward_impl(tsm_model* model, tsm_cache* cache, const int32_t* count
         TSM_CUDA(ctx, cudaMemcpyAsync(w.qtiles, h_tiles, tiles.size() * 8, cudaMemcpyHostToDevice, ctx->stream));
         ctx->prefill_tiles = w.qtiles, ctx->prefill_tile_count = (int)tiles.size();
     }
+    model->one_token_per_row = longest <= 1;
     int step_rc = launch_step(model, cache, total, outputs, picks != nullptr);
     ctx->prefill_tiles = nullptr, ctx->prefill_tile_count = 0;
     TSM_TRY(step_rc);
@@ -718,6 +724,7 @@ int tsm_decode(tsm_model* model, tsm_cache* cache, const int32_t* ids, int32_t* 
         cudaError_t e1 = cudaMemcpyAsync(w.ids, h_ids, (size_t)rows * 4, cudaMemcpyHostToDevice, ctx->stream);
         cudaError_t e2 = cudaMemcpyAsync(w.table, h_table, (size_t)rows * 12, cudaMemcpyHostToDevice, ctx->stream);
         if (e1 != cudaSuccess || e2 != cudaSuccess) rc = cuda_fail(ctx, e1 != cudaSuccess ? e1 : e2, "cudaMemcpyAsync");
+        model->one_token_per_row = true;
         if (rc == TSM_OK) rc = launch_step(model, cache, rows, rows, true);
         cudaError_t e3 = cudaMemcpyAsync(h_picks, w.picks, (size_t)rows * 4, cudaMemcpyDeviceToHost, ctx->stream);
         if (e3 == cudaSuccess) e3 = cudaMemcpyAsync(ctx->errors_host, ctx->errors, sizeof(ErrorRecord), cudaMemcpyDeviceToHost, ctx->stream);
@@ -807,6 +814,7 @@ int tsm_decode_run(tsm_model* model, tsm_cache* cache, const int32_t* ids, int s
         TSM_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
         cudaError_t e0 = launch_chained(ctx, run_advance_kernel, dim3((rows + 255) / 256), dim3(256), 0, w.ids, w.table, w.picks, rows, cache->run_state);
         count_launch(ctx);
+        model->one_token_per_row = true;
         int rc = launch_step(model, cache, rows, rows, true);
         if (e0 == cudaSuccess) e0 = launch_chained(ctx, run_record_kernel, dim3(1), dim3(1024), 0, w.picks, rows, cache->run_state);
         count_launch(ctx);

@@ -77,6 +77,7 @@ struct tsm_model {
     std::map<std::string, tsm::Named> named;
     tsm::Workspace ws;
     uint64_t ws_generation = 1;
+    bool one_token_per_row = false;   // the step being queued gives every cache row at most one token (a decode step)
     int tp = 1, tp_rank = 0;     // tensor-parallel group of the context the model was built on
     bool tp_reduce = false;      // o and down split by input columns and all-reduced (TSM_TP_REDUCE), not by output rows
     tsm::Linear head_local;           // this rank's rows of the vocabulary head (a view when the head is the embedding table)

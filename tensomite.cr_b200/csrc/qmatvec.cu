@@ -45,6 +45,9 @@ struct MatvecParams {
     int cap, stages;    // groups a stage holds, stages in the ring
     unsigned nb_magic;  // floor(2^32 / nb) + 1: x / nb = umulhi(x, nb_magic) for the small x used here
     ErrorRecord* errors;
+    const float* plain;   // not null: the rows come as F32, `plain_stride` apart, and every CTA quantises them itself
+    int64_t plain_stride;
+    int plain_vector;     // they may be read in 16-byte loads
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -93,7 +96,6 @@ __host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (k
 
 template <int KIND, int C, bool ALIGNED>
 __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
-    chained_kernel_entry();
     using F = Fmt<KIND>;
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = p.nb;
@@ -143,6 +145,52 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     if (producer)
         for (int it = 0; it < kStages; it++) issue(it);
 
+    // The weights' first stages are on their way; everything below reads what the kernel before this one wrote.
+    chained_kernel_wait();
+    if (p.plain) {
+        // F32 rows: one thread per block of 32 with the quantiser's arithmetic (quantize_block_q8: amax, d = amax / 127,
+        // id = 1 / d, round half away, f16 scale)
+        for (int c = 0; c < C; c++) {
+            const float* xr = p.plain + (int64_t)c * p.plain_stride;
+            for (int blk = tid; blk < nb; blk += kThreads) {
+                float v[32];
+                if (p.plain_vector) {
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        float4 t = ((const float4*)(xr + blk * 32))[u];
+                        v[4 * u] = t.x, v[4 * u + 1] = t.y, v[4 * u + 2] = t.z, v[4 * u + 3] = t.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 32; u++) v[u] = xr[blk * 32 + u];
+                }
+                float amax = fabsf(v[0]);
+#pragma unroll
+                for (int u = 1; u < 32; u++) amax = fmaxf(amax, fabsf(v[u]));
+                float d = __fdiv_rn(amax, 127.0f);
+                float id = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+                int total = 0;
+                unsigned words[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    unsigned word = 0;
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        int q = (int)(signed char)(int)roundf(__fmul_rn(v[4 * u + e], id));
+                        total += q;
+                        word |= (unsigned)(q & 0xff) << (8 * e);
+                    }
+                    words[u] = word;
+                }
+                unsigned char* dst = acts_q + c * act_bytes + act_offset(blk);
+                *(uint4*)dst = make_uint4(words[0], words[1], words[2], words[3]);
+                *(uint4*)(dst + 16) = make_uint4(words[4], words[5], words[6], words[7]);
+                acts_scale[c * nb + blk] = round_to_half(d);
+                if (KIND == TSM_Q4_0) ((int*)acts_aux)[c * nb + blk] = total;
+                if (KIND == TSM_Q4_1) acts_aux[c * nb + blk] = round_to_half(__fmul_rn((float)total, d));
+            }
+        }
+    } else {
     // quantised activations -> shared memory (every CTA reads them once; they stay in L2)
     for (int c = 0; c < C; c++) {
         const int4* src = (const int4*)(p.acts.qs + (int64_t)c * nb * 32);
@@ -162,6 +210,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
             }
             if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = p.acts.sums[(int64_t)c * nb + i];
         }
+    }
     }
     __syncthreads();
 
@@ -423,12 +472,13 @@ static size_t stream_smem_bytes(int nb, int cap, int stages) {
 }
 
 template <int KIND, int C>
-static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint8_t* w, int n, const float* bias,
+static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plain, int64_t plain_stride, int k, const uint8_t* w, int n, const float* bias,
                          const float* residual, float* out, bool* taken) {
     using F = Fmt<KIND>;
     *taken = false;
     int nb = k / 32;
-    if (((uintptr_t)w & 15) != 0 || ((int64_t)n * nb) % F::G != 0 || ((uintptr_t)a.qs & 15) != 0) return TSM_OK;
+    if (((uintptr_t)w & 15) != 0 || ((int64_t)n * nb) % F::G != 0) return TSM_OK;
+    if (!plain && ((uintptr_t)a.qs & 15) != 0) return TSM_OK;
     if (nb < F::G) return TSM_OK;  // rows shorter than a group: the generic kernel takes them
     // A stage holds `cap` groups.  Short rows: 128 groups (one per compute thread).  Long rows: 256 groups, so
     // that a tile still holds several rows for the fold warp to fold side by side.
@@ -481,6 +531,8 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, int k, const uint
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
     p.cap = cap, p.stages = stages;
     p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
+    p.plain = plain, p.plain_stride = plain_stride;
+    p.plain_vector = plain && ((uintptr_t)plain & 15) == 0 && plain_stride % 4 == 0;
     TSM_CUDA(ctx, launch_chained(ctx, kernel, dim3(grid), dim3(kThreads), smem, p));
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
@@ -492,10 +544,10 @@ template <int KIND>
 static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int n, const float* bias,
                        const float* residual, float* out) {
     bool taken = false;
-    if (rows == 1) TSM_TRY((launch_stream<KIND, 1>(ctx, a, k, w, n, bias, residual, out, &taken)));
-    else if (rows == 2) TSM_TRY((launch_stream<KIND, 2>(ctx, a, k, w, n, bias, residual, out, &taken)));
-    else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, k, w, n, bias, residual, out, &taken)));
-    else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, k, w, n, bias, residual, out, &taken)));
+    if (rows == 1) TSM_TRY((launch_stream<KIND, 1>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 2) TSM_TRY((launch_stream<KIND, 2>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
+    else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
     if (taken) return TSM_OK;
     if (rows > 4 && umma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_umma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     if (rows > 4 && pipe_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_pipe(ctx, a, rows, k, w, KIND, n, bias, residual, out);
@@ -506,6 +558,35 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);
     return TSM_OK;
+}
+
+template <int KIND>
+static int launch_plain_kind(tsm_ctx* ctx, const float* x, int64_t x_stride, int rows, int k, const uint8_t* w, int n, const float* bias,
+                             const float* residual, float* out, bool* taken) {
+    QuantizedActs none{nullptr, nullptr, nullptr, nullptr};
+    switch (rows) {
+        case 1: return launch_stream<KIND, 1>(ctx, none, x, x_stride, k, w, n, bias, residual, out, taken);
+        case 2: return launch_stream<KIND, 2>(ctx, none, x, x_stride, k, w, n, bias, residual, out, taken);
+        case 3: return launch_stream<KIND, 3>(ctx, none, x, x_stride, k, w, n, bias, residual, out, taken);
+        case 4: return launch_stream<KIND, 4>(ctx, none, x, x_stride, k, w, n, bias, residual, out, taken);
+    }
+    return TSM_OK;
+}
+
+int launch_block_matvec_plain(tsm_ctx* ctx, const float* x, int64_t x_stride, int rows, int k, const uint8_t* w, int kind, int n,
+                              const float* bias, const float* residual, float* out, bool* taken) {
+    *taken = false;
+    static const bool off = getenv("TSM_SEPARATE_QUANTISER") != nullptr;  // time the two launches instead
+    if (off || rows < 1 || rows > 4 || n == 0 || k <= 0 || k % 32 != 0 || ((uintptr_t)w & 1) != 0) return TSM_OK;
+    OpTimer timer(ctx, kind == TSM_Q8_0 ? "BlockMatMul q8_0" : kind == TSM_Q4_0 ? "BlockMatMul q4_0" : "BlockMatMul q4_1", rows, k, n);
+    int rc = TSM_OK;
+    switch (kind) {
+        case TSM_Q8_0: rc = launch_plain_kind<TSM_Q8_0>(ctx, x, x_stride, rows, k, w, n, bias, residual, out, taken); break;
+        case TSM_Q4_0: rc = launch_plain_kind<TSM_Q4_0>(ctx, x, x_stride, rows, k, w, n, bias, residual, out, taken); break;
+        case TSM_Q4_1: rc = launch_plain_kind<TSM_Q4_1>(ctx, x, x_stride, rows, k, w, n, bias, residual, out, taken); break;
+    }
+    timer.dropped = !*taken;
+    return rc;
 }
 
 int launch_block_matmul(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, const uint8_t* w, int kind, int n,

@@ -41,4 +41,33 @@ __device__ __forceinline__ float ordered_sum(const float* row, float* terms, int
     return scratch[0];
 }
 
+// One rotary pair (host.cr:448-466): x*cos + rotate_half(x)*sin, three roundings per element.
+__device__ __forceinline__ void rotate_pair(float a, float b, const float* c, const float* s, int i, int half, float* oa,
+                                            float* ob) {
+    // a = x[i] (first half), b = x[i + half]
+    *oa = __fadd_rn(__fmul_rn(a, c[i]), __fmul_rn(__fmul_rn(b, -1.0f), s[i]));
+    *ob = __fadd_rn(__fmul_rn(b, c[i + half]), __fmul_rn(a, s[i + half]));
+}
+
+// kernels.cr:4,18 through the tape of kernel.cr:259-300: every step rounded on its own.
+__device__ __forceinline__ float swiglu_value(float gate, float up) {
+    float t1 = exact_exp(-gate);
+    float t2 = __fadd_rn(t1, 1.0f);
+    float t3 = __fdiv_rn(gate, t2);
+    return __fmul_rn(t3, up);
+}
+
+__device__ __forceinline__ float gelu_value(float x) {
+    const float c = 0.7978845608028654f;  // f32(sqrt(2 / pi))
+    float t0 = __fmul_rn(x, 0.5f);
+    float t1 = __fmul_rn(x, x);
+    float t2 = __fmul_rn(t1, x);
+    float t3 = __fmul_rn(t2, 0.044715f);
+    float t4 = __fadd_rn(x, t3);
+    float t5 = __fmul_rn(t4, c);
+    float t6 = exact_tanh(t5);
+    float t7 = __fadd_rn(t6, 1.0f);
+    return __fmul_rn(t0, t7);
+}
+
 }  // namespace tsm

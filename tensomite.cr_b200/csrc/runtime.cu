@@ -150,7 +150,7 @@ OpTimer::~OpTimer() {
     if (!pr.on && !active) return;
     if (pr.depth > 0) pr.depth--;
     if (!active) return;
-    cudaEvent_t stop = profile_event(ctx);
+    cudaEvent_t stop = dropped ? nullptr : profile_event(ctx);
     if (!stop) {
         pr.spare.push_back(start);
         return;
@@ -415,6 +415,11 @@ int tsm_block_matmul(tsm_ctx* ctx, tsm_dptr x, int rows, int k, int64_t x_stride
     if (k <= 0 || k % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(k) + " do not split into blocks of 32");
     if (rows < 0 || n < 0) return fail(ctx, TSM_ERR_ARG, "negative size");
     if (rows == 0 || n == 0) return TSM_OK;
+    if (rows <= 4) {  // the streamed kernel quantises a few rows itself: one launch
+        bool taken = false;
+        TSM_TRY(launch_block_matvec_plain(ctx, PCF(x), x_stride, rows, k, PCB(w), kind, n, PCF(bias), nullptr, PF(out), &taken));
+        if (taken) return TSM_OK;
+    }
     TSM_TRY(ensure_scratch(ctx, ctx->quant, quant_scratch_bytes(rows, k)));
     QuantizedActs a = quant_scratch_layout(ctx->quant.ptr, rows, k);
     TSM_TRY(launch_quantize_rows(ctx, PCF(x), rows, k, x_stride, (float*)a.scales, (float*)a.sums, (int*)a.totals, (int8_t*)a.qs));

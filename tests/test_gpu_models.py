@@ -442,3 +442,36 @@ def test_prompts_through_the_prefill_attention_kernel_have_the_decode_bits(dev):
     want = ref.forward(rcache, [first], last=False)
     assert np.array_equal(bits(got[:150]), bits(want))
     cache.free(), step.free(), model.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("arch", ["llama", "gpt2"])
+def test_decode_steps_that_rotate_and_append_inside_attention_have_the_prompt_bits(dev, arch):
+    """A step of at most four rows with one token each leaves RoPE and the cache append (modules.cr:434-452, 194-217) to the
+    attention kernel: every CTA rotates its query heads and its key as it loads them, one CTA per key/value head writes the
+    cache, the others (here two groups of four query heads share the one key/value head) use their own copy.  Tokens fed that
+    way, three rows at a time, must give the logits of the same tokens fed as packed prompts (separate rope + append launch),
+    bit for bit, and the oracle's; and the cache they leave must serve a later packed step."""
+    config = dict(arch=arch, layers=3, width=512, heads=8, kv_heads=1 if arch == "llama" else 8, head_width=64, hidden=1024, vocab=512,
+                  context=128, eps=1e-5, rope_theta=10000.0, tied=True)
+    model = pkg.Model.random(dev, config, pkg.Q8_0, seed=5)
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, config["vocab"], size=n).tolist() for n in (9, 1, 6)]
+    steps = [rng.integers(0, config["vocab"], size=3).tolist() for _ in range(5)]
+    tail = [rng.integers(0, config["vocab"], size=7).tolist() for _ in range(3)]
+    packed = model.new_batch_cache(5, 64)                                      # two more rows: steps of 5 tokens take the separate launch
+    model.forward_last(prompts + [[1], [2]], packed)
+    want = [model.forward_last([[t] for t in step] + [[3], [4]], packed)[:3] for step in steps]
+    want_tail = model.forward(tail + [[], []], packed)
+    fed = model.new_batch_cache(3, 64)
+    model.forward_last(prompts, fed)
+    got = [model.forward_last([[t] for t in step], fed) for step in steps]     # one token per row: the fused path
+    for a, b in zip(got, want):
+        assert np.array_equal(bits(a), bits(b))
+    assert np.array_equal(bits(model.forward(tail, fed)), bits(want_tail))     # 21 tokens over the cache the fused steps wrote
+    ref = oracle.model_from_device(model, threads=4)
+    rcache = ref.new_cache(1, 64)
+    row0 = prompts[0] + [step[0] for step in steps]
+    logits = ref.forward(rcache, [row0], last=False)
+    assert np.array_equal(bits(got[-1][0]), bits(logits[-1]))
+    packed.free(), fed.free(), model.free()
