@@ -23,7 +23,7 @@ namespace tsm {
 namespace {
 
 constexpr int kTP = 32;            // positions per tile
-constexpr int kRing = 3;           // stages (5 measured no faster)
+constexpr int kRing = 3;           // stages of the split-path and prefill kernels' rings
 constexpr int kEChunk = 1024;     // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
@@ -100,7 +100,13 @@ __device__ __forceinline__ void s_tensor_load(void* dst, const CUtensorMap* map,
 }
 __device__ __forceinline__ void consumers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
 
-template <int WIDTH>
+// attention_stream_kernel's shared memory before the ring: 1 KB of barriers and flags, then 12 KB that hold the score
+// pipeline's hand-over slots (3 warps x RING x 512 bytes) and, once all scores are made, the exp values of a chunk and the
+// weights of the tiles being folded.
+constexpr int kSEChunk = 512;          // positions whose exp values are staged at once for the denominator's chain
+constexpr int kStreamHeader = 1024 + 12288;
+
+template <int WIDTH, int RING>
 __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(StreamParams p, const __grid_constant__ StreamMaps maps) {
     chained_kernel_entry();
     constexpr int G = 4;
@@ -108,21 +114,25 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     constexpr int BOX_BYTES = kTP * 128;
     constexpr int STAGE_BYTES = BOXES * BOX_BYTES;
     constexpr int QP = WIDTH + 4;                  // query row pitch: the four heads' 16-byte reads fall in distinct banks
-    static_assert(WIDTH == kConsumers, "one folding thread per column");
+    static_assert(WIDTH == kConsumers && BOXES == kConsumers / 32, "one folding thread per column, one box per warp");
+    static_assert(RING >= 2 && RING <= 6, "the header is laid out for at most 6 stages");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (s_smem_u32(smem_raw) & 1023u)) & 1023u);  // an offset from the shared array: the address space stays known
-    static_assert(kRing <= 8 && 512 + 3 * kRing * 512 <= 8192, "the header holds the barriers and the hand-over slots of at most 8 stages");
-    uint64_t* full = (uint64_t*)smem;              // [kRing], bytes 0..63
-    uint64_t* empty = (uint64_t*)(smem + 64);      // [kRing], bytes 64..127
-    uint64_t* ready = (uint64_t*)(smem + 128);     // [3 warps][kRing], bytes 128..319: a tile's running sums are in `hand`
-    volatile int* abort_flag = (volatile int*)(smem + 320);   // [1] stays 0
-    float* maxes = (float*)(smem + 336);           // [4]
-    float* totals = (float*)(smem + 352);          // [4]
-    float* hand = (float*)(smem + 512);            // [3 warps][kRing][32 positions][4 heads]
-    unsigned char* stages = smem + 8192;           // [kRing][BOXES][kTP][128 bytes], swizzled
-    float* ebuf = (float*)(stages + kRing * STAGE_BYTES);    // [G][kEChunk]
-    float* wbuf = ebuf + G * kEChunk;              // [2][4 tiles][kTP][G]
-    float* qs = wbuf + 2 * 4 * kTP * G;            // [G][QP]
+    // RING stages of 16 KB: measured 262, 239 and 233 us for 3, 4 and 5 stages at the headline shape (two CTAs still fit an
+    // SM at 5).  A ring per box (each warp's quarter refilled as soon as that warp is done with it, since the last warp of the
+    // score pipeline runs three tiles behind the first) measured 3 % slower at every depth than one barrier pair per stage.
+    uint64_t* full = (uint64_t*)smem;              // [RING], bytes 0..63
+    uint64_t* empty = (uint64_t*)(smem + 64);      // [RING], bytes 64..127
+    uint64_t* ready = (uint64_t*)(smem + 512);     // [3 warps][RING], bytes 512..703: a tile's running sums are in `hand`
+    volatile int* abort_flag = (volatile int*)(smem + 896);   // [1] stays 0
+    float* maxes = (float*)(smem + 912);           // [4]
+    float* totals = (float*)(smem + 928);          // [4]
+    float* hand = (float*)(smem + 1024);           // [3 warps][RING][32 positions][4 heads]: the score phase only
+    float* ebuf = (float*)(smem + 1024);           // [G][kSEChunk]: after the score phase (a barrier of all consumers lies between)
+    float* wbuf = ebuf + G * kSEChunk;             // [2][4 tiles][kTP][G]
+    static_assert(3 * RING * 512 <= 12288 && (G * kSEChunk + 2 * 4 * kTP * G) * 4 <= 12288, "both uses fit the 12 KB");
+    unsigned char* stages = smem + kStreamHeader;  // [RING][BOXES][kTP][128 bytes], swizzled
+    float* qs = (float*)(stages + RING * STAGE_BYTES);   // [G][QP]
 
     const int token = p.order ? p.order[blockIdx.y] : blockIdx.y;  // longest tokens first when an order is given
     const int per_kv = p.heads / p.kv_heads, groups_per_kv = per_kv / G;
@@ -138,11 +148,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (tid == 0) {
-        for (int s = 0; s < kRing; s++) {
-            s_mbar_init(&full[s], 1);
-            s_mbar_init(&empty[s], kConsumers / 32);
-            for (int w2 = 0; w2 < 3; w2++) s_mbar_init(&ready[w2 * kRing + s], 1);
-        }
+        for (int i = 0; i < RING; i++) s_mbar_init(&full[i], 1), s_mbar_init(&empty[i], BOXES);
+        for (int i = 0; i < 3 * RING; i++) s_mbar_init(&ready[i], 1);
         abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -157,8 +164,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
         int issued = 0;
         bool ok = true;
         for (int j = 0; j < 2 * tiles; j++) {
-            int s = j % kRing;
-            if (j >= kRing) ok = s_mbar_wait(&empty[s], (unsigned)((j / kRing - 1) & 1), abort_flag);
+            int s = j % RING;
+            if (j >= RING) ok = s_mbar_wait(&empty[s], (unsigned)((j / RING - 1) & 1), abort_flag);
             if (!ok) break;
             const CUtensorMap* map = j < tiles ? &maps.k : &maps.v;
             int y = plane + (j < tiles ? j : j - tiles) * kTP;
@@ -172,7 +179,7 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             // the consumers stopped arriving: say so, then see the copies already issued land before leaving
             *abort_flag = 1;
             atomicExch(&p.errors->timeout, 1);
-            for (int j = max(0, issued - kRing); j < issued; j++) s_mbar_wait(&full[j % kRing], (unsigned)((j / kRing) & 1), abort_flag + 1);
+            for (int j = max(0, issued - RING); j < issued; j++) s_mbar_wait(&full[j % RING], (unsigned)((j / RING) & 1), abort_flag + 1);
         }
         return;
     }
@@ -199,13 +206,13 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             for (int j = 0; j < 32; j++) qreg[h][j] = qs[h * QP + 32 * warp + j];
         const int sw = lane & 7;
         for (int tile = 0; tile < tiles; tile++) {
-            const int s = tile % kRing;
-            const unsigned parity = (unsigned)((tile / kRing) & 1);
+            const int s = tile % RING;
+            const unsigned parity = (unsigned)((tile / RING) & 1);
             if (!s_mbar_wait(&full[s], parity, abort_flag)) ok = false, *abort_flag = 1;
             float acc[G] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (warp > 0) {
-                if (!s_mbar_wait(&ready[(warp - 1) * kRing + s], parity, abort_flag)) ok = false, *abort_flag = 1;
-                float4 in = *(const float4*)(hand + (((warp - 1) * kRing + s) * 32 + lane) * 4);
+                if (!s_mbar_wait(&ready[(warp - 1) * RING + s], parity, abort_flag)) ok = false, *abort_flag = 1;
+                float4 in = *(const float4*)(hand + (((warp - 1) * RING + s) * 32 + lane) * 4);
                 acc[0] = in.x, acc[1] = in.y, acc[2] = in.z, acc[3] = in.w;
             }
             const unsigned char* rowp = stages + (size_t)s * STAGE_BYTES + warp * BOX_BYTES + lane * 128;
@@ -223,9 +230,9 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             __syncwarp();
             if (lane == 0) s_mbar_arrive(&empty[s]);
             if (warp < 3) {
-                *(float4*)(hand + ((warp * kRing + s) * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *(float4*)(hand + ((warp * RING + s) * 32 + lane) * 4) = make_float4(acc[0], acc[1], acc[2], acc[3]);
                 __syncwarp();
-                if (lane == 0) s_mbar_arrive(&ready[warp * kRing + s]);
+                if (lane == 0) s_mbar_arrive(&ready[warp * RING + s]);
             } else {
                 int pos = tile * kTP + lane;
                 if (pos < len) {
@@ -251,8 +258,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
     consumers_sync();
     {
         float total = 0.0f;  // lane 0 of warp h folds head h
-        for (int e0 = 0; e0 < len; e0 += kEChunk) {
-            int count = min(kEChunk, len - e0);
+        for (int e0 = 0; e0 < len; e0 += kSEChunk) {
+            int count = min(kSEChunk, len - e0);
             // eight loads in flight per thread: the scores come back from L2
             for (int i0 = 0; i0 < count; i0 += 2 * kConsumers) {
                 float sv[2][G];
@@ -271,13 +278,13 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
                         if (i < count) {
                             float e = exact_exp(__fsub_rn(sv[u][h], maxes[h]));
                             srow[(int64_t)h * p.capacity + e0 + i] = e;
-                            ebuf[h * kEChunk + i] = e;
+                            ebuf[h * kSEChunk + i] = e;
                         }
                     }
             }
             consumers_sync();
             if (lane == 0) {
-                const float* eh = ebuf + warp * kEChunk;
+                const float* eh = ebuf + warp * kSEChunk;
                 int i = 0;
                 for (; i + 8 <= count; i += 8) {
                     float4 a = *(const float4*)(eh + i), b = *(const float4*)(eh + i + 4);
@@ -321,8 +328,8 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
             const int last = min(tiles, tile0 + kBatch);
             for (int tile = tile0; tile < last; tile++) {
                 const float* wt = wb + (tile - tile0) * kTP * G;
-                int j = tiles + tile, s = j % kRing;
-                if (!s_mbar_wait(&full[s], (unsigned)((j / kRing) & 1), abort_flag)) ok = false, *abort_flag = 1;
+                int j = tiles + tile, s = j % RING;
+                if (!s_mbar_wait(&full[s], (unsigned)((j / RING) & 1), abort_flag)) ok = false, *abort_flag = 1;
                 const unsigned char* vt = colp + (size_t)s * STAGE_BYTES;
                 int count = min(kTP, len - tile * kTP);
                 int pos = 0;
@@ -1177,8 +1184,12 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         TSM_LAUNCH_CHECK(ctx);
         return TSM_OK;
     }
-    size_t smem = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + (size_t)4 * kEChunk * 4 + 2 * 4 * kTP * 4 * 4 + 4 * (WIDTH + 4) * 4;
-    auto kernel = attention_stream_kernel<WIDTH>;
+    // TSM_ATTN_RING = 3 .. 6 stages (of 16 KB) per CTA, for timing one depth against another; two CTAs fit an SM up to 6
+    static const int ring = getenv("TSM_ATTN_RING") ? atoi(getenv("TSM_ATTN_RING")) : 5;
+    const int depth = ring >= 3 && ring <= 6 ? ring : 5;
+    size_t smem = 1024 + (size_t)kStreamHeader + (size_t)depth * kTP * WIDTH * 4 + 4 * (WIDTH + 4) * 4;
+    auto kernel = depth == 3 ? attention_stream_kernel<WIDTH, 3> : depth == 4 ? attention_stream_kernel<WIDTH, 4>
+                : depth == 6 ? attention_stream_kernel<WIDTH, 6> : attention_stream_kernel<WIDTH, 5>;
     {
         static std::mutex lock;
         static std::map<int, bool> done;
