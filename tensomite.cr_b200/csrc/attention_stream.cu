@@ -23,7 +23,7 @@ namespace tsm {
 namespace {
 
 constexpr int kTP = 32;            // positions per tile
-constexpr int kRing = 3;           // stages of the split-path and prefill kernels' rings
+constexpr int kRing = 4;           // stages of the split-path and prefill kernels' rings
 constexpr int kEChunk = 1024;     // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
