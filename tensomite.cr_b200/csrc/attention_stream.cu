@@ -1135,12 +1135,13 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
     TSM_TRY(make_tensor_map_2d(ctx, &maps.k, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, k, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
     TSM_TRY(make_tensor_map_2d(ctx, &maps.v, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, v, WIDTH, plane_rows, WIDTH * 4, 32, kTP, CU_TENSOR_MAP_SWIZZLE_128B));
     const int groups = kv_heads * (heads / kv_heads / 4);
-    // At most two (token, kv head) pairs per SM and long caches (measured: 102 against 181 us for 8 streams of up to 4096
-    // positions, 156 against 209 for 16, 236 against 253 for 32; 433 against 307 for 64, where the single launch stays): three launches that cut the score pass by positions and the
-    // value pass by quarters of the width, so that the longest stream does not set the time alone.  TSM_ATTN_SPLIT=0 / 1
-    // forces the choice.
+    // At most one (token, kv head) pair per SM and long caches: three launches that cut the score pass by positions and the
+    // value pass by quarters of the width, so that the longest stream does not set the time alone (the single launch lasts
+    // as long as one CTA takes for the longest stream: 163 us for 4224 positions).  Measured, 64 streams of up to 4224
+    // positions on 1, 2, 4 and 8 kv heads (64 to 512 pairs): 106 against 163 us, 130 against 166, 195 against 184, and 433
+    // against 231, where the single launch stays.  TSM_ATTN_SPLIT=0 / 1 forces the choice.
     static const char* forced = getenv("TSM_ATTN_SPLIT");
-    bool split = (int64_t)tokens * groups <= 2 * (int64_t)ctx->sm_count && capacity >= 1024;
+    bool split = (int64_t)tokens * groups <= (int64_t)ctx->sm_count && capacity >= 1024;
     if (forced) split = forced[0] == '1';
     if (split) {
         size_t smem_scores = 1024 + 8192 + (size_t)kRing * kTP * WIDTH * 4 + 4 * (WIDTH + 4) * 4;

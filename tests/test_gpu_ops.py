@@ -86,6 +86,36 @@ def test_block_product_is_bit_exact(dev, name):
         assert np.array_equal(bits(got), bits(want)), (name, count, n, k)
 
 
+@pytest.mark.parametrize("name", list(KINDS))
+def test_a_few_rows_quantised_inside_the_product_have_the_quantisers_bits(dev, name):
+    """tsm_block_matmul of at most four rows quantises them inside the streamed kernel (one thread per block) instead of
+    launching the quantiser first.  Rows that are views (a stride that is no multiple of four floats, so the 16-byte loads
+    are off), blocks of zeros, a block whose largest value is negative, values that round half away from zero and a tiny
+    block must give the oracle's product over Quant.quantize_activations' blocks (quant.cr:428-442), bit for bit."""
+    import ctypes as C
+    rng = np.random.default_rng(21)
+    kind = KINDS[name]
+    n, k = 1000, 2048
+    w = oracle.quantize(kind, rng.normal(0, 0.02, n * k).astype(np.float32))
+    wb = dev.tensor(w)
+    for rows, stride in ((1, k), (3, k + 5), (4, k + 8), (2, 3 * k)):
+        x = rng.normal(0, 1, (rows, stride)).astype(np.float32)
+        x[0, 0:32] = 0.0                                     # a block of zeros: scale 0, inverse 0
+        x[0, 32:64] = -np.abs(x[0, 32:64]) - 1.0             # the largest magnitude is negative
+        x[0, 64:96] = np.arange(32, dtype=np.float32) * (127.0 / 62.0) - 63.5   # multiples of half a step
+        x[rows - 1, 96:128] = 1e-20                          # a tiny block
+        xb = dev.tensor(x)
+        out = dev.alloc(rows * n * 4)
+        dev.check(dev.lib.tsm_block_matmul(dev.ctx, C.c_uint64(xb.ptr), rows, k, C.c_int64(stride), C.c_uint64(wb.ptr), kind, n,
+                                           C.c_uint64(0), C.c_uint64(out.ptr)), "tsm_block_matmul")
+        dev.sync()
+        got = out.numpy(np.float32)[:rows * n].reshape(rows, n)
+        want = oracle.matmul_reference(kind, np.ascontiguousarray(x[:, :k]), w, n)
+        xb.free(), out.free()
+        assert np.array_equal(bits(got), bits(want)), (name, rows, stride)
+    wb.free()
+
+
 def test_block_product_with_a_scale_that_is_not_finite(dev):
     """A Q4_0 block whose scale is infinite: the outputs it reaches are the reference's infinities and NaNs."""
     rng = np.random.default_rng(12)
