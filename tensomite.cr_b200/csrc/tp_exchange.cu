@@ -15,6 +15,9 @@
 // peers' regions; the counters only grow, and the targets are kept beside them on the device, so a captured graph replays
 // the kernel unchanged.  Every wait is bounded: when it runs out the kernel sets the error record's timeout word and
 // returns; nothing traps and no GPU is left spinning.  Plain peer loads and stores only: no multimem, no multicast.
+// Where a row's 26 us go on two GPUs (clock64 around the phases): waiting for the peers' arrival 3-4, the peers' partial rows
+// 2.7 (every rank's loads issued before the first add), the ordered sum of 4096 squares 9.3, norm and quantiser 3.2 (the
+// norm's weights fetched before the sum), stores 0.8, the releasing arrival 3.5, waiting for the other rows 1.5-2.
 //
 // The regions are cudaMalloc'ed, exported with cudaIpcGetMemHandle, carried between the processes by an NCCL all-gather and
 // opened with cudaIpcOpenMemHandle.  Where that is not possible (no peer access) the step keeps using NCCL's all-reduce.
@@ -90,9 +93,23 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
     const unsigned ready_target = mine->ready_target + (unsigned)p.ranks, delivered_target = mine->delivered_target + (unsigned)p.total;
 
     // "my partial product is complete": the kernel before this one on the stream wrote it
-    if (blockIdx.x == 0 && threadIdx.x < p.ranks) {
-        __threadfence_system();
-        red_release_sys(&((XchgHeader*)p.regions[threadIdx.x])->ready, 1u);
+    // (the release of the add itself orders everything the kernel before this one wrote: a separate system fence in front
+    // of it cost a second 3.7 us)
+    if (blockIdx.x == 0 && threadIdx.x < p.ranks) red_release_sys(&((XchgHeader*)p.regions[threadIdx.x])->ready, 1u);
+    // what phase 3 needs of the norm's weight (and bias): fetched now, so that the loads are long back when the ordered
+    // sums end (fetched after them they cost a trip to L2 per block of the row)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int blocks = n >> 5;
+    constexpr int kKeep = 8;
+    const bool kept = blocks <= kKeep * warps;
+    float wv[kKeep], bv[kKeep];
+    if (kept) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) {
+            const int j = (warp + i * warps) * 32 + lane;
+            wv[i] = j < n && p.norm_w ? p.norm_w[j] : 1.0f;
+            bv[i] = LAYER && j < n ? p.norm_b[j] : 0.0f;
+        }
     }
     if (threadIdx.x == 0) {
         bool ok = wait_counter(&mine->ready, ready_target, p.spins);
@@ -105,20 +122,47 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
     if (ok && t < p.total) {
         // 1. the row of every rank's partial product, added in rank order; 2. the residual
         float* xr = p.x + (int64_t)t * n;
-        for (int j = threadIdx.x * 4; j < n; j += blockDim.x * 4) {
-            float4 sum = *(const float4*)((const float*)(p.regions[0] + p.partial_at) + (int64_t)t * n + j);
-            for (int q = 1; q < p.ranks; q++) {
-                float4 part = *(const float4*)((const float*)(p.regions[q] + p.partial_at) + (int64_t)t * n + j);
-                sum.x = __fadd_rn(sum.x, part.x), sum.y = __fadd_rn(sum.y, part.y), sum.z = __fadd_rn(sum.z, part.z), sum.w = __fadd_rn(sum.w, part.w);
+        // two 16-byte pieces per thread and pass, every rank's loads of both issued before the first add: one trip over
+        // NVLink per pass instead of one per piece
+        const int step = blockDim.x * 4;
+        for (int j0 = threadIdx.x * 4; j0 < n; j0 += 2 * step) {
+            const int j1 = j0 + step;
+            const bool two = j1 < n;
+            float4 part[2][8], x4[2], b4[2];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                if (q < p.ranks) {
+                    const float* src = (const float*)(p.regions[q] + p.partial_at) + (int64_t)t * n;
+                    part[0][q] = *(const float4*)(src + j0);
+                    part[1][q] = two ? *(const float4*)(src + j1) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
+            x4[0] = *(const float4*)(xr + j0);
+            x4[1] = two ? *(const float4*)(xr + j1) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (p.bias) {
-                float4 b = *(const float4*)(p.bias + j);
-                sum.x = __fadd_rn(sum.x, b.x), sum.y = __fadd_rn(sum.y, b.y), sum.z = __fadd_rn(sum.z, b.z), sum.w = __fadd_rn(sum.w, b.w);
+                b4[0] = *(const float4*)(p.bias + j0);
+                b4[1] = two ? *(const float4*)(p.bias + j1) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            float4 x4 = *(const float4*)(xr + j);
-            x4.x = __fadd_rn(x4.x, sum.x), x4.y = __fadd_rn(x4.y, sum.y), x4.z = __fadd_rn(x4.z, sum.z), x4.w = __fadd_rn(x4.w, sum.w);
-            *(float4*)(xr + j) = x4;
-            *(float4*)(row + j) = x4;
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                if (k == 1 && !two) break;
+                float4 sum = part[k][0];
+#pragma unroll
+                for (int q = 1; q < 8; q++) {
+                    if (q < p.ranks) {
+                        sum.x = __fadd_rn(sum.x, part[k][q].x), sum.y = __fadd_rn(sum.y, part[k][q].y);
+                        sum.z = __fadd_rn(sum.z, part[k][q].z), sum.w = __fadd_rn(sum.w, part[k][q].w);
+                    }
+                }
+                if (p.bias) {
+                    sum.x = __fadd_rn(sum.x, b4[k].x), sum.y = __fadd_rn(sum.y, b4[k].y), sum.z = __fadd_rn(sum.z, b4[k].z), sum.w = __fadd_rn(sum.w, b4[k].w);
+                }
+                float4 v = x4[k];
+                v.x = __fadd_rn(v.x, sum.x), v.y = __fadd_rn(v.y, sum.y), v.z = __fadd_rn(v.z, sum.z), v.w = __fadd_rn(v.w, sum.w);
+                const int j = k == 0 ? j0 : j1;
+                *(float4*)(xr + j) = v;
+                *(float4*)(row + j) = v;
+            }
         }
         __syncthreads();
         // the norm, in the host's order of addition (rmsnorm_row / the LayerNorm rows branch, devices/host.cr:348-403)
@@ -129,17 +173,30 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
         const float denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, count), p.eps));
         // 3. quantised (staged in shared memory, over the terms, which are no longer needed), then stored to every rank in
         //    16-byte pieces
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-        const int blocks = n >> 5;
         int8_t* q8 = (int8_t*)terms;                       // [n]
         float* head = (float*)(q8 + n);                    // [3][blocks]: scales, sums, totals (as bits)
-        for (int blk = warp; blk < blocks; blk += warps) {
-            const int j = blk * 32 + lane;
-            float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
-            float y = __fdiv_rn(c, denom);
-            if (p.norm_w) y = __fmul_rn(y, p.norm_w[j]);
-            if (LAYER) y = __fadd_rn(y, p.norm_b[j]);
-            quantize_block_q8(y, lane, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + j);
+        if (kept) {
+#pragma unroll
+            for (int i = 0; i < kKeep; i++) {
+                const int blk = warp + i * warps;
+                if (blk < blocks) {
+                    const int j = blk * 32 + lane;
+                    float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
+                    float y = __fdiv_rn(c, denom);
+                    if (p.norm_w) y = __fmul_rn(y, wv[i]);
+                    if (LAYER) y = __fadd_rn(y, bv[i]);
+                    quantize_block_q8(y, lane, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + j);
+                }
+            }
+        } else {
+            for (int blk = warp; blk < blocks; blk += warps) {
+                const int j = blk * 32 + lane;
+                float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
+                float y = __fdiv_rn(c, denom);
+                if (p.norm_w) y = __fmul_rn(y, p.norm_w[j]);
+                if (LAYER) y = __fadd_rn(y, p.norm_b[j]);
+                quantize_block_q8(y, lane, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + j);
+            }
         }
         __syncthreads();
         const int64_t all_blocks = (int64_t)p.total * blocks;
@@ -155,10 +212,8 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
         }
         __syncthreads();
         // "row delivered", on every rank
-        if (threadIdx.x < p.ranks) {
-            __threadfence_system();
-            red_release_sys(&((XchgHeader*)p.regions[threadIdx.x])->delivered, 1u);
-        }
+        // (the barrier above makes the CTA's stores this thread's to release; no fence of its own in front of the add)
+        if (threadIdx.x < p.ranks) red_release_sys(&((XchgHeader*)p.regions[threadIdx.x])->delivered, 1u);
     }
     // the kernel ends when every row of the step has arrived here
     if (threadIdx.x == 0) {
