@@ -41,6 +41,48 @@ __device__ __forceinline__ float ordered_sum(const float* row, float* terms, int
     return scratch[0];
 }
 
+// One THREAD quantises one block of 32 values that lie in shared memory (16-byte aligned; rows there are stored with 4 pad
+// floats per block, so that threads on consecutive blocks read distinct banks), with quantize_block_q8's arithmetic: the
+// maximum of 32 magnitudes in any order is the same number, the rest is element by element.  A row of 128 blocks costs the
+// 128 threads about 600 cycles this way; one warp per block, eight blocks per warp one after the other, each with two chains
+// of five shuffles, cost 3.2 us.  `vector`: q_out may be written in two 16-byte pieces.
+__device__ __forceinline__ void quantize_block_by_thread(const float* y, float* scale, float* sum, int* total, int8_t* q_out, bool vector) {
+    float v[32];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        float4 t = ((const float4*)y)[u];
+        v[4 * u] = t.x, v[4 * u + 1] = t.y, v[4 * u + 2] = t.z, v[4 * u + 3] = t.w;
+    }
+    float amax = fabsf(v[0]);
+#pragma unroll
+    for (int u = 1; u < 32; u++) amax = fmaxf(amax, fabsf(v[u]));
+    float d = __fdiv_rn(amax, 127.0f);
+    float id = d == 0.0f ? 0.0f : __fdiv_rn(1.0f, d);
+    int t = 0;
+    unsigned words[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+        unsigned word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            int q = (int)(signed char)(int)roundf(__fmul_rn(v[4 * u + e], id));
+            t += q;
+            word |= (unsigned)(q & 0xff) << (8 * e);
+        }
+        words[u] = word;
+    }
+    if (vector) {
+        ((uint4*)q_out)[0] = make_uint4(words[0], words[1], words[2], words[3]);
+        ((uint4*)q_out)[1] = make_uint4(words[4], words[5], words[6], words[7]);
+    } else {
+#pragma unroll
+        for (int u = 0; u < 32; u++) q_out[u] = (int8_t)(words[u >> 2] >> (8 * (u & 3)));
+    }
+    *scale = round_to_half(d);
+    *sum = round_to_half(__fmul_rn((float)t, d));
+    *total = t;
+}
+
 // One rotary pair (host.cr:448-466): x*cos + rotate_half(x)*sin, three roundings per element.
 __device__ __forceinline__ void rotate_pair(float a, float b, const float* c, const float* s, int i, int half, float* oa,
                                             float* ob) {

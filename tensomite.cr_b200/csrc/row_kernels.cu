@@ -90,24 +90,27 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     int blocks = (n + 31) >> 5;
     if (kept) {
+        // the normed values go to shared memory (over the sums' terms, which are done with), then one thread per block
+        // quantises them
+        float* ybuf = terms;   // 36 floats per block of 32
 #pragma unroll
         for (int i = 0; i < kKeep; i++) {
-            int blk = warp + i * warps;  // block blk's element `lane` is this thread's value i
-            if (blk < blocks) {
-                int j = blk * 32 + lane;
-                float y = 0.0f;
-                if (j < n) {
-                    float c = LAYER ? __fsub_rn(xv[i], mean) : xv[i];
-                    y = __fdiv_rn(c, denom);
-                    if (w) y = __fmul_rn(y, wv[i]);
-                    if (LAYER) y = __fadd_rn(y, bv[i]);
-                    if (out) out[(int64_t)r * n + j] = y;
-                }
-                if (q.qs) {
-                    int64_t at = (int64_t)r * (n >> 5) + blk;
-                    quantize_block_q8(y, lane, q.scales + at, q.sums + at, q.totals + at, q.qs + (int64_t)r * n + j);
-                }
+            int j = threadIdx.x + i * blockDim.x;
+            if (j < n) {
+                float c = LAYER ? __fsub_rn(xv[i], mean) : xv[i];
+                float y = __fdiv_rn(c, denom);
+                if (w) y = __fmul_rn(y, wv[i]);
+                if (LAYER) y = __fadd_rn(y, bv[i]);
+                if (out) out[(int64_t)r * n + j] = y;
+                if (q.qs) ybuf[j + (j >> 5) * 4] = y;
             }
+        }
+        if (!q.qs) return;
+        __syncthreads();
+        const bool vector = (((uintptr_t)q.qs | (uintptr_t)n) & 15) == 0;
+        for (int blk = threadIdx.x; blk < blocks; blk += blockDim.x) {
+            int64_t at = (int64_t)r * (n >> 5) + blk;
+            quantize_block_by_thread(ybuf + blk * 36, q.scales + at, q.sums + at, q.totals + at, q.qs + (int64_t)r * n + blk * 32, vector);
         }
         return;
     }
@@ -135,7 +138,8 @@ static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w,
     if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
     if ((size_t)n * 4 > 100 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "norm rows over 25600 values");
     int threads = n >= 2048 ? 512 : n >= 512 ? 256 : 128;
-    size_t smem = (size_t)(((n + 3) & ~3) + ((n + 15) & ~15)) * 4;  // the row and the terms of its ordered sums
+    // the row, then the terms of its ordered sums or, after them, the normed values with 4 pad floats per block
+    size_t smem = (size_t)(((n + 3) & ~3) + std::max((n + 15) & ~15, n + (n >> 5) * 4 + 4)) * 4;
     QuantOut q = quant_out(quantized);
     int exact = ctx->mode == TSM_EXACT;
     if (layer) {

@@ -173,31 +173,35 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
         const float denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, count), p.eps));
         // 3. quantised (staged in shared memory, over the terms, which are no longer needed), then stored to every rank in
         //    16-byte pieces
-        int8_t* q8 = (int8_t*)terms;                       // [n]
+        // the normed values go to shared memory (over the sums' terms, 4 pad floats per block), then one thread per block
+        // quantises them into the staging rows behind
+        float* ybuf = terms;
+        int8_t* q8 = (int8_t*)(terms + (n + (n >> 5) * 4 + 4));   // [n]
         float* head = (float*)(q8 + n);                    // [3][blocks]: scales, sums, totals (as bits)
         if (kept) {
 #pragma unroll
             for (int i = 0; i < kKeep; i++) {
-                const int blk = warp + i * warps;
-                if (blk < blocks) {
-                    const int j = blk * 32 + lane;
+                const int j = (warp + i * warps) * 32 + lane;
+                if (j < n) {
                     float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
                     float y = __fdiv_rn(c, denom);
                     if (p.norm_w) y = __fmul_rn(y, wv[i]);
                     if (LAYER) y = __fadd_rn(y, bv[i]);
-                    quantize_block_q8(y, lane, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + j);
+                    ybuf[j + (j >> 5) * 4] = y;
                 }
             }
         } else {
-            for (int blk = warp; blk < blocks; blk += warps) {
-                const int j = blk * 32 + lane;
+            for (int j = threadIdx.x; j < n; j += blockDim.x) {
                 float c = LAYER ? __fsub_rn(row[j], mean) : row[j];
                 float y = __fdiv_rn(c, denom);
                 if (p.norm_w) y = __fmul_rn(y, p.norm_w[j]);
                 if (LAYER) y = __fadd_rn(y, p.norm_b[j]);
-                quantize_block_q8(y, lane, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + j);
+                ybuf[j + (j >> 5) * 4] = y;
             }
         }
+        __syncthreads();
+        for (int blk = threadIdx.x; blk < blocks; blk += blockDim.x)
+            quantize_block_by_thread(ybuf + blk * 36, head + blk, head + blocks + blk, (int*)head + 2 * blocks + blk, q8 + blk * 32, true);
         __syncthreads();
         const int64_t all_blocks = (int64_t)p.total * blocks;
         const int64_t qs_at = (all_blocks * 12 + 255) / 256 * 256;   // quant_scratch_layout
@@ -364,7 +368,8 @@ int launch_xchg_reduce_norm(tsm_model* m, int total, float* x, const float* bias
     const int n = e.width;
     const int ctas = std::max(1, (total - m->tp_rank + m->tp - 1) / m->tp);
     const int threads = n >= 2048 ? 512 : n >= 512 ? 256 : 128;
-    const size_t smem = (size_t)(((n + 3) & ~3) + ((n + 15) & ~15)) * 4;
+    // the row; the terms of its ordered sums, later the normed values (36 floats per block); the quantised row and its scales
+    const size_t smem = (size_t)(((n + 3) & ~3) + std::max((n + 15) & ~15, n + (n >> 5) * 4 + 4)) * 4 + (size_t)n + (size_t)(n >> 5) * 12 + 16;
     if (smem > 200 * 1024) return fail(ctx, TSM_ERR_UNSUPPORTED, "rows too wide for the fused exchange");
     if (layer) {
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(tp_reduce_norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
