@@ -464,12 +464,13 @@ def main():
     dev.sync()
     draw_seconds = time.perf_counter() - load_start
     rows = w["rows"]
-    config = dict(workload=w["name"], streams_per_gpu=rows if tp == 1 else f"{rows} shared by the {world} ranks",
+    tp_named = world if parallelism != "dp" else 1   # what the job's own arm runs at this N: the reference arm names the same configuration
+    config = dict(workload=w["name"], streams_per_gpu=rows if tp_named == 1 else f"{rows} shared by the {world} ranks",
                   kv_lengths=f"uniform {w['len_lo']}..{w['len_hi']} (seed 11)",
                   kv_dtype="f32", weights=w["kind"], mode=args.mode, l2="per-step working set (weights + KV) far exceeds the 126 MB L2",
                   parallelism=((f"tp{world}: projections split by output rows, NCCL all-gathers between them (the bits of one GPU)" if parallelism == "tp" else
                                 f"tp{world}: q/k/v, gate/up and the head split by output rows, o and down by input columns with their partial "
-                                f"sums exchanged over NVLink (not bit-exact)") if tp > 1 else
+                                f"sums exchanged over NVLink (not bit-exact)") if tp_named > 1 else
                                f"dp{world}: a replica and {rows} streams per GPU, no collective") if world > 1 else "single gpu")
     sample = pick_sample(lengths, 2)
     sample_note = f"streams {sample} of {rows} (cached lengths {[int(lengths[r]) for r in sample]}, workload mean {float(np.mean(lengths)):.0f})"
