@@ -36,10 +36,11 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // LAYER = true: mean, centred, variance, c / std * w + b (host.cr:348-361).
 template <bool LAYER>
 __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, int n,
-                            float eps, float* out, QuantOut q, int exact) {
+                            float eps, float* out, QuantOut q, int exact, int chunked_sum) {
     chained_kernel_entry();
     extern __shared__ __align__(16) float row[];  // [n], then the terms of the ordered sums, 16-byte aligned
     __shared__ float scratch[32];
+    __shared__ SumScratch sum_scratch;
     float* terms = row + ((n + 3) & ~3);
     int r = blockIdx.x;
     const float* xr = x + (int64_t)r * n;
@@ -77,7 +78,7 @@ __global__ void norm_kernel(const float* __restrict__ x, const float* __restrict
     }
     float squares;
     if (exact) {
-        squares = ordered_sum<true>(row, terms, n, mean, scratch);
+        squares = ordered_sum_squares(row, terms, n, mean, scratch, &sum_scratch, chunked_sum != 0);
     } else {
         float part = 0.0f;
         for (int j = threadIdx.x; j < n; j += blockDim.x) {
@@ -142,12 +143,13 @@ static int launch_norm(tsm_ctx* ctx, bool layer, const float* x, const float* w,
     size_t smem = (size_t)(((n + 3) & ~3) + std::max((n + 15) & ~15, n + (n >> 5) * 4 + 4)) * 4;
     QuantOut q = quant_out(quantized);
     int exact = ctx->mode == TSM_EXACT;
+    static const int chunked = getenv("TSM_PLAIN_ORDERED_SUM") ? 0 : 1;   // the term-by-term sum instead, for timing it
     if (layer) {
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
-        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<true>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact));
+        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<true>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact, chunked));
     } else {
         if (smem > 48 * 1024) TSM_CUDA(ctx, cudaFuncSetAttribute(norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024));
-        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<false>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact));
+        TSM_CUDA(ctx, launch_chained(ctx, norm_kernel<false>, dim3(rows), dim3(threads), smem, x, w, b, n, eps, out, q, exact, chunked));
     }
     count_launch(ctx);
     TSM_LAUNCH_CHECK(ctx);

@@ -58,6 +58,7 @@ struct XchgParams {
     float eps;
     ErrorRecord* errors;
     unsigned long long spins;
+    int chunked_sum;             // the norm's sum of squares chunk by chunk (ordered_sum_squares_fast)
 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
@@ -84,6 +85,7 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
     chained_kernel_entry();
     extern __shared__ __align__(16) float row[];   // [width], then the terms of the ordered sums
     __shared__ float scratch[32];
+    __shared__ SumScratch sum_scratch;
     __shared__ int proceed;
     const int n = p.width;
     float* terms = row + ((n + 3) & ~3);
@@ -169,7 +171,7 @@ __global__ void tp_reduce_norm_kernel(XchgParams p) {
         const float count = (float)n;
         float mean = 0.0f;
         if (LAYER) mean = __fdiv_rn(ordered_sum<false>(row, terms, n, 0.0f, scratch), count);
-        const float squares = ordered_sum<true>(row, terms, n, mean, scratch);
+        const float squares = ordered_sum_squares(row, terms, n, mean, scratch, &sum_scratch, p.chunked_sum != 0);
         const float denom = __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, count), p.eps));
         // 3. quantised (staged in shared memory, over the terms, which are no longer needed), then stored to every rank in
         //    16-byte pieces
@@ -365,6 +367,8 @@ int launch_xchg_reduce_norm(tsm_model* m, int total, float* x, const float* bias
     p.partial_at = e.partial_at, p.quant_at = e.quant_at;
     p.x = x, p.bias = bias, p.norm_w = w, p.norm_b = b, p.eps = eps, p.errors = ctx->errors;
     p.spins = ctx->wait_spins ? ctx->wait_spins : kXchgSpins;
+    static const int chunked = getenv("TSM_PLAIN_ORDERED_SUM") ? 0 : 1;
+    p.chunked_sum = chunked;
     const int n = e.width;
     const int ctas = std::max(1, (total - m->tp_rank + m->tp - 1) / m->tp);
     const int threads = n >= 2048 ? 512 : n >= 512 ? 256 : 128;

@@ -196,6 +196,46 @@ def test_norms(dev, n):
     assert np.array_equal(bits(dev.layernorm(x, w, b)), bits(oracle.layernorm(x, w, b)))
 
 
+@pytest.mark.parametrize("n", [512, 2048, 4096, 8192])
+def test_the_chunked_sum_of_squares_is_the_sequential_sum(dev, n):
+    """The norms add their squares chunk by chunk with integer arithmetic wherever the running sum stays in one binade, and
+    term by term elsewhere; the result must be the host's sequential sum (rmsnorm_row, devices/host.cr:391-403) for rows built
+    to defeat the shortcut: terms that are exact ties (powers of two, small integers), outliers a thousand times the rest,
+    zeros, subnormal squares, a sum that overflows to infinity, and ordinary rows at several scales."""
+    rng = np.random.default_rng(31)
+    rows = []
+    for scale in (1e-3, 0.02, 1.0, 30.0, 1e4):
+        rows.append(rng.normal(0, scale, n))
+    outliers = rng.normal(0, 1, n)
+    outliers[rng.integers(0, n, 5)] *= 1000
+    rows.append(outliers)
+    holes = rng.normal(0, 1, n)
+    holes[rng.integers(0, n, n // 2)] = 0
+    rows.append(holes)
+    rows.append(np.ones(n))                                              # every add a tie candidate
+    rows.append(2.0 ** rng.integers(-12, 4, n))                          # powers of two: ties whenever the sum is large
+    rows.append(rng.integers(0, 8, n) * 2.0 ** -3)                       # small integers
+    rows.append(np.tile([1024.0, 2.0 ** -7, 2.0 ** -6.5, 0.75 * 2.0 ** -6], n // 4))
+    rows.append(np.full(n, 1e-20))                                       # squares are subnormal or zero
+    rows.append(np.concatenate([np.full(n // 2, 3e-20), rng.normal(0, 1, n - n // 2)]))
+    rows.append(np.full(n, 1.5e19))                                      # the sum of squares overflows
+    rows.append(np.concatenate([np.zeros(n - 1), [5.0]]))
+    x = np.stack(rows).astype(np.float32)
+    w = rng.normal(1, 0.2, n).astype(np.float32)
+    b = rng.normal(0, 0.2, n).astype(np.float32)
+    with np.errstate(all="ignore"):
+        want = oracle.rmsnorm(x, w)
+        want_layer = oracle.layernorm(x, w, b)
+    got = dev.rmsnorm(x, w)
+    assert np.array_equal(bits(got), bits(want)), [i for i in range(len(rows)) if not np.array_equal(bits(got[i]), bits(want[i]))]
+    finite = np.isfinite(want_layer).all(axis=1)
+    got_layer = dev.layernorm(x, w, b)
+    assert np.array_equal(bits(got_layer[finite]), bits(want_layer[finite]))
+    for seed in range(40):                                               # many ordinary rows: every chunk pattern
+        y = np.random.default_rng(seed).normal(0, 2.0 ** (seed % 9 - 4), (8, n)).astype(np.float32)
+        assert np.array_equal(bits(dev.rmsnorm(y, w)), bits(oracle.rmsnorm(y, w))), seed
+
+
 def test_rope_is_bit_exact(dev):
     rng = np.random.default_rng(7)
     cos, sin = oracle.rope_tables(64, 300, 10000.0)
