@@ -59,14 +59,11 @@ struct SumScratch {
     int2 step[kSumMaxChunks];        // (predicted exponent or -1 when the chunk must be replayed, increment in ulps)
 };
 
-__device__ __forceinline__ float ordered_sum_squares_fast(const float* row, float* terms, int n, float shift, float* scratch, SumScratch* ss) {
+// `terms` [n] lie in shared memory, n a multiple of kSumChunk up to kSumChunk * kSumMaxChunks, every term >= 0 (or a NaN); the
+// sum continues from `start` (the same in every thread); every thread of the CTA calls and receives the result.
+__device__ __forceinline__ float chunked_sum_of_terms(const float* terms, int n, float start, float* scratch, SumScratch* ss) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int chunks = n / kSumChunk;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        float v = __fsub_rn(row[j], shift);
-        terms[j] = __fmul_rn(v, v);
-    }
-    __syncthreads();
     // 1. a tree sum per chunk (any order: it only predicts an exponent)
     for (int c = warp; c < chunks; c += warps) {
         float2 t2 = ((const float2*)(terms + c * kSumChunk))[lane];
@@ -91,7 +88,7 @@ __device__ __forceinline__ float ordered_sum_squares_fast(const float* row, floa
             float up = __shfl_up_sync(0xffffffffu, before, off);
             if (lane >= off) before += up;
         }
-        before -= total;   // the sum of the lanes before this one
+        before = before - total + start;   // what precedes this lane's chunks
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             int c = lane * 4 + i;
@@ -128,7 +125,7 @@ __device__ __forceinline__ float ordered_sum_squares_fast(const float* row, floa
     __syncthreads();
     // 4. one thread, the exact running sum
     if (threadIdx.x == 0) {
-        unsigned ab = 0u;   // bits of the running sum, +0
+        unsigned ab = __float_as_uint(start);   // bits of the running sum
         int2 next = ss->step[0];
         for (int c = 0; c < chunks; c++) {
             const int2 st = next;
@@ -158,8 +155,14 @@ __device__ __forceinline__ float ordered_sum_squares_fast(const float* row, floa
 
 // The sum of squares of a norm: the chunked form where it applies (`fast`, whole chunks, a block of at least four warps).
 __device__ __forceinline__ float ordered_sum_squares(const float* row, float* terms, int n, float shift, float* scratch, SumScratch* ss, bool fast) {
-    if (fast && n % kSumChunk == 0 && n >= 8 * kSumChunk && n <= kSumChunk * kSumMaxChunks && blockDim.x >= 128)
-        return ordered_sum_squares_fast(row, terms, n, shift, scratch, ss);
+    if (fast && n % kSumChunk == 0 && n >= 8 * kSumChunk && n <= kSumChunk * kSumMaxChunks && blockDim.x >= 128) {
+        for (int j = threadIdx.x; j < n; j += blockDim.x) {
+            float v = __fsub_rn(row[j], shift);
+            terms[j] = __fmul_rn(v, v);
+        }
+        __syncthreads();
+        return chunked_sum_of_terms(terms, n, 0.0f, scratch, ss);
+    }
     return ordered_sum<true>(row, terms, n, shift, scratch);
 }
 

@@ -58,7 +58,7 @@ struct XchgParams {
     float eps;
     ErrorRecord* errors;
     unsigned long long spins;
-    int chunked_sum;             // the norm's sum of squares chunk by chunk (ordered_sum_squares_fast)
+    int chunked_sum;             // the norm's sum of squares chunk by chunk (chunked_sum_of_terms)
 };
 
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {

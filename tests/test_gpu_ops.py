@@ -321,6 +321,23 @@ def test_long_caches_with_few_streams_take_the_three_launch_path(dev):
     assert np.array_equal(bits(dev.ragged_attention(q[2:3], k, v, table[2:3], scale)[0]), bits(got[2]))
 
 
+def test_softmax_denominators_of_degenerate_streams(dev):
+    """Long streams through the three-launch path whose keys repeat (every score equal, every exp value 1: each add of the
+    denominator a rounding tie), whose scores take a few values only, whose last key dominates, and whose scores are all near
+    zero: the oracle's bits."""
+    rng = np.random.default_rng(13)
+    lengths = [(0, 2000), (1, 1536), (2, 1900), (3, 1100)]
+    q, k, v, table, heads = attention_case(rng, 4, 1, 4, 2048, 128, lengths)
+    k[0, :, :, :] = k[0, :, 0:1, :]                                  # one key repeated: all weights equal
+    k[1, 0] = k[1, 0][rng.integers(0, 3, 2048)]                     # three distinct keys
+    k[2, :, 1899, :] = 40.0 * q[2, 0]                               # one position takes nearly all the weight
+    k[3] *= 1e-3                                                     # scores near zero: exp values near 1
+    scale = np.float32(1.0 / np.sqrt(128))
+    want = oracle_attention(q, k, v, table, scale)
+    got = dev.ragged_attention(q, k, v, table, scale)
+    assert np.array_equal(bits(got), bits(want))
+
+
 def test_sampler_picks(dev):
     logits = np.array([[0.5, 2.0, 2.0, -1.0, 2.0, 1.5], [3.0, 1.0, 3.0, 0.0, 0.0, 0.0]], dtype=np.float32)
     assert dev.argmax(logits).tolist() == [1, 0]
