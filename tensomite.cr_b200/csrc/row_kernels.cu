@@ -328,11 +328,58 @@ __global__ void activation_kernel(const float* __restrict__ a, const float* __re
     }
 }
 
+// The same for rows that go out quantised and can be read in 16-byte pieces: a CTA takes 32 consecutive blocks; every thread
+// makes four consecutive values of one block (four independent chains of the exp polynomial), the values pass through
+// shared memory, and one thread per block quantises them (quantize_block_by_thread).  12.6 -> about 7 us for 64 rows of
+// 14336, where one warp per block went through load, exp and two chains of shuffles one after the other.
+template <bool GELU>
+__global__ void __launch_bounds__(256) activation_blocks_kernel(const float* __restrict__ a, const float* __restrict__ b, int64_t blocks,
+                                                                int blocks_per_row, int64_t in_stride, float* out, QuantOut q) {
+    chained_kernel_entry();
+    __shared__ __align__(16) float ybuf[32 * 36];
+    const int tid = threadIdx.x;
+    const int64_t first = (int64_t)blockIdx.x * 32;
+    {
+        const int64_t B = first + (tid >> 3);
+        if (B < blocks) {
+            const int r = (int)(B / blocks_per_row), blk = (int)(B % blocks_per_row);
+            const int j = blk * 32 + (tid & 7) * 4;
+            const float4 g4 = *(const float4*)(a + (int64_t)r * in_stride + j);
+            float4 y;
+            if (GELU) {
+                y.x = gelu_value(g4.x), y.y = gelu_value(g4.y), y.z = gelu_value(g4.z), y.w = gelu_value(g4.w);
+            } else {
+                const float4 u4 = *(const float4*)(b + (int64_t)r * in_stride + j);
+                y.x = swiglu_value(g4.x, u4.x), y.y = swiglu_value(g4.y, u4.y), y.z = swiglu_value(g4.z, u4.z), y.w = swiglu_value(g4.w, u4.w);
+            }
+            if (out) *(float4*)(out + (int64_t)r * blocks_per_row * 32 + j) = y;
+            *(float4*)(ybuf + (tid >> 3) * 36 + (tid & 7) * 4) = y;
+        }
+    }
+    __syncthreads();
+    if (tid < 32) {
+        const int64_t B = first + tid;
+        if (B < blocks) quantize_block_by_thread(ybuf + tid * 36, q.scales + B, q.sums + B, q.totals + B, q.qs + B * 32, true);
+    }
+}
+
 static int launch_activation(tsm_ctx* ctx, bool gelu, const float* a, const float* b, int rows, int n, int64_t in_stride,
                              float* out, const QuantizedActs* quantized) {
     OpTimer timer(ctx, gelu ? "Kernel gelu" : "Kernel swiglu", rows, n);
     if (rows == 0 || n == 0) return TSM_OK;
     if (quantized && n % 32 != 0) return fail(ctx, TSM_ERR_ARG, "rows of " + std::to_string(n) + " do not split into blocks of 32");
+    const bool pieces = quantized && in_stride % 4 == 0 &&
+                        (((uintptr_t)a | (uintptr_t)(b ? b : a) | (uintptr_t)(out ? out : a) | (uintptr_t)quantized->qs) & 15) == 0;
+    if (pieces) {
+        QuantOut qb = quant_out(quantized);
+        const int64_t blocks = (int64_t)rows * (n / 32);
+        const unsigned ctas = (unsigned)((blocks + 31) / 32);
+        if (gelu) TSM_CUDA(ctx, launch_chained(ctx, activation_blocks_kernel<true>, dim3(ctas), dim3(256), 0, a, b, blocks, n / 32, in_stride, out, qb));
+        else TSM_CUDA(ctx, launch_chained(ctx, activation_blocks_kernel<false>, dim3(ctas), dim3(256), 0, a, b, blocks, n / 32, in_stride, out, qb));
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        return TSM_OK;
+    }
     int64_t items = (int64_t)rows * ((n + 31) / 32);
     unsigned grid = (unsigned)((items + 7) / 8);
     QuantOut q = quant_out(quantized);
