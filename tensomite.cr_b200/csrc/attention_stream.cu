@@ -17,6 +17,7 @@
 // quantised for the product that follows (QuantSink).  Further down: the same arithmetic as three launches
 // (attention_scores_kernel, attention_weights_kernel, attention_values_kernel) for calls that cannot fill the GPU.
 #include "common.cuh"
+#include "row_helpers.cuh"
 
 namespace tsm {
 
@@ -24,7 +25,6 @@ namespace {
 
 constexpr int kTP = 32;            // positions per tile
 constexpr int kRing = 4;           // stages of the split-path and prefill kernels' rings
-constexpr int kEChunk = 1024;     // positions whose exp values are staged at once for the denominator's chain
 constexpr int kConsumers = 128;
 constexpr unsigned kSpinLimit = 4u << 20;
 constexpr int kWideDeep = 6;       // stages of 4 KB in attention_values_wide_kernel's ring
@@ -511,55 +511,116 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
 }
 
 // One (token, head): maximum, exp, the denominator folded in position order, weights = exp / denominator in place.
-__global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p) {
+// A stream of up to kWeightKeep * 256 positions stays in registers from its one read to its one write (as three passes
+// over the scratch array, each thread waiting for one load per pass and step, the kernel took 18 us); the exp values are
+// staged in shared memory and summed chunk by chunk (chunked_sum_of_terms: the sequential sum's bits).  Longer streams go
+// segment by segment through the scratch array, every segment's loads issued before their first use.
+constexpr int kWeightSegment = kSumChunk * kSumMaxChunks;   // positions staged at once
+constexpr int kWeightKeep = 20;
+
+__device__ __forceinline__ float weights_sum(float* ebuf, int count, int padded, float start, float* sum_out, SumScratch* ss, int chunked) {
+    // ebuf[0, padded) holds `count` exp values and +0 behind them; all threads call
+    if (chunked && padded >= 8 * kSumChunk) return chunked_sum_of_terms(ebuf, padded, start, sum_out, ss);
+    if (threadIdx.x == 0) {
+        float acc = start;
+        int i = 0;
+        for (; i + 8 <= count; i += 8) {
+            float4 a = *(const float4*)(ebuf + i), b = *(const float4*)(ebuf + i + 4);
+            acc = __fadd_rn(acc, a.x), acc = __fadd_rn(acc, a.y), acc = __fadd_rn(acc, a.z), acc = __fadd_rn(acc, a.w);
+            acc = __fadd_rn(acc, b.x), acc = __fadd_rn(acc, b.y), acc = __fadd_rn(acc, b.z), acc = __fadd_rn(acc, b.w);
+        }
+        for (; i < count; i++) acc = __fadd_rn(acc, ebuf[i]);
+        sum_out[0] = acc;
+    }
+    __syncthreads();
+    return sum_out[0];
+}
+
+__global__ void __launch_bounds__(256) attention_weights_kernel(StreamParams p, int chunked) {
     chained_kernel_entry();
-    __shared__ __align__(16) float ebuf[kEChunk];
+    extern __shared__ __align__(16) float ebuf[];   // min(kWeightSegment, the capacity rounded up to whole chunks)
     __shared__ float red[8];
-    __shared__ float shared_total;
+    __shared__ float sum_out[1];
+    __shared__ SumScratch sum_scratch;
     const int token = p.order ? p.order[blockIdx.y] : blockIdx.y, head = blockIdx.x;
     const int row = p.table[3 * token], limit = p.table[3 * token + 1];
     if (row < 0 || row >= p.rows || limit < 0 || limit >= p.capacity) return;  // reported by the score kernel
     const int len = limit + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float* sr = p.scratch + ((int64_t)token * p.heads + head) * p.capacity;
-    float top = -INFINITY;
-    for (int i = tid; i < len; i += 256) top = fmaxf(top, sr[i]);
+    auto block_max = [&](float top) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
-    if (lane == 0) red[warp] = top;
-    __syncthreads();
-    top = red[0];
-#pragma unroll
-    for (int w2 = 1; w2 < 8; w2++) top = fmaxf(top, red[w2]);
-    float total = 0.0f;
-    for (int e0 = 0; e0 < len; e0 += kEChunk) {
-        int count = min(kEChunk, len - e0);
-        float sv[kEChunk / 256];
-#pragma unroll
-        for (int u = 0; u < kEChunk / 256; u++) sv[u] = u * 256 + tid < count ? sr[e0 + u * 256 + tid] : 0.0f;
-#pragma unroll
-        for (int u = 0; u < kEChunk / 256; u++)
-            if (u * 256 + tid < count) {
-                float e = exact_exp(__fsub_rn(sv[u], top));
-                sr[e0 + u * 256 + tid] = e;
-                ebuf[u * 256 + tid] = e;
-            }
+        for (int off = 16; off > 0; off >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, off));
+        if (lane == 0) red[warp] = top;
         __syncthreads();
-        if (tid == 0) {
-            int i = 0;
-            for (; i + 8 <= count; i += 8) {
-                float4 a = *(const float4*)(ebuf + i), b = *(const float4*)(ebuf + i + 4);
-                total = __fadd_rn(total, a.x), total = __fadd_rn(total, a.y), total = __fadd_rn(total, a.z), total = __fadd_rn(total, a.w);
-                total = __fadd_rn(total, b.x), total = __fadd_rn(total, b.y), total = __fadd_rn(total, b.z), total = __fadd_rn(total, b.w);
-            }
-            for (; i < count; i++) total = __fadd_rn(total, ebuf[i]);
+        top = red[0];
+#pragma unroll
+        for (int w2 = 1; w2 < 8; w2++) top = fmaxf(top, red[w2]);
+        return top;
+    };
+    if (len <= kWeightKeep * 256) {
+        float sv[kWeightKeep];
+#pragma unroll
+        for (int u = 0; u < kWeightKeep; u++) sv[u] = u * 256 + tid < len ? sr[u * 256 + tid] : -INFINITY;
+        float top = sv[0];
+#pragma unroll
+        for (int u = 1; u < kWeightKeep; u++) top = fmaxf(top, sv[u]);
+        top = block_max(top);
+        const int padded = (len + kSumChunk - 1) / kSumChunk * kSumChunk;   // +0 behind the last value: it changes no sum
+#pragma unroll
+        for (int u = 0; u < kWeightKeep; u++) {
+            const int i = u * 256 + tid;
+            sv[u] = i < len ? exact_exp(__fsub_rn(sv[u], top)) : 0.0f;
+            if (i < padded) ebuf[i] = sv[u];
         }
         __syncthreads();
+        const float total = weights_sum(ebuf, len, padded, 0.0f, sum_out, &sum_scratch, chunked);
+#pragma unroll
+        for (int u = 0; u < kWeightKeep; u++)
+            if (u * 256 + tid < len) sr[u * 256 + tid] = __fdiv_rn(sv[u], total);
+        return;
     }
-    if (tid == 0) shared_total = total;
-    __syncthreads();
-    total = shared_total;
-    for (int i = tid; i < len; i += 256) sr[i] = __fdiv_rn(sr[i], total);
+    // long streams: eight loads in flight per thread in every pass
+    float top = -INFINITY;
+    for (int i0 = 0; i0 < len; i0 += 8 * 256) {
+        float sv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) sv[u] = i0 + u * 256 + tid < len ? sr[i0 + u * 256 + tid] : -INFINITY;
+#pragma unroll
+        for (int u = 0; u < 8; u++) top = fmaxf(top, sv[u]);
+    }
+    top = block_max(top);
+    float total = 0.0f;
+    for (int e0 = 0; e0 < len; e0 += kWeightSegment) {
+        const int count = min(kWeightSegment, len - e0);
+        const int padded = (count + kSumChunk - 1) / kSumChunk * kSumChunk;
+        for (int i0 = 0; i0 < padded; i0 += 8 * 256) {
+            float sv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) sv[u] = i0 + u * 256 + tid < count ? sr[e0 + i0 + u * 256 + tid] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * 256 + tid;
+                float e = 0.0f;
+                if (i < count) {
+                    e = exact_exp(__fsub_rn(sv[u], top));
+                    sr[e0 + i] = e;
+                }
+                if (i < padded) ebuf[i] = e;
+            }
+        }
+        __syncthreads();
+        total = weights_sum(ebuf, count, padded, total, sum_out, &sum_scratch, chunked);
+        __syncthreads();   // the next segment overwrites ebuf
+    }
+    for (int i0 = 0; i0 < len; i0 += 8 * 256) {
+        float sv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) sv[u] = i0 + u * 256 + tid < len ? sr[i0 + u * 256 + tid] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (i0 + u * 256 + tid < len) sr[i0 + u * 256 + tid] = __fdiv_rn(sv[u], total);
+    }
 }
 
 // Outputs of one quarter of the width (32 columns) of one (token, kv head): one consumer warp folds weight * value over all
@@ -1161,7 +1222,9 @@ int launch_attention_stream(tsm_ctx* ctx, const float* q, int64_t q_stride, int 
         TSM_CUDA(ctx, launch_chained(ctx, attention_scores_kernel<WIDTH>, dim3(groups, tokens, p.splits), dim3(kConsumers + 32), smem_scores, p, maps));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
-        TSM_CUDA(ctx, launch_chained(ctx, attention_weights_kernel, dim3(heads, tokens), dim3(256), 0, p));
+        static const int chunked = getenv("TSM_PLAIN_ORDERED_SUM") ? 0 : 1;   // the term-by-term sum instead, for timing it
+        const size_t smem_weights = (size_t)std::min(kWeightSegment, (capacity + kSumChunk - 1) / kSumChunk * kSumChunk) * 4;
+        TSM_CUDA(ctx, launch_chained(ctx, attention_weights_kernel, dim3(heads, tokens), dim3(256), smem_weights, p, chunked));
         count_launch(ctx);
         TSM_LAUNCH_CHECK(ctx);
         static const char* narrow = getenv("TSM_ATTN_VALUES_NARROW");   // the one-warp-per-box value pass, for timing it

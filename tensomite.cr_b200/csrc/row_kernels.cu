@@ -290,6 +290,49 @@ __global__ void rope_append_kernel(float* qkv, int tokens, int heads, int kv_hea
     }
 }
 
+// The same with four pairs per thread in 16-byte pieces (head widths that are multiples of 8, 16-byte aligned buffers): a
+// thread's loads are all in flight at once, where one pair per thread left most of the launch waiting for its two.
+__global__ void rope_append4_kernel(float* qkv, int tokens, int heads, int kv_heads, int width, const float* __restrict__ cos_table,
+                                    const float* __restrict__ sin_table, int context, const int* __restrict__ table,
+                                    float* keys, float* values, int rows, int capacity, ErrorRecord* errors) {
+    chained_kernel_entry();
+    const int half = width >> 1, quads = half >> 2;
+    const int all = heads + 2 * kv_heads;
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t total = (int64_t)tokens * all * quads;
+    if (i >= total) return;
+    const int col = (int)(i % quads) * 4;
+    const int head = (int)((i / quads) % all);
+    const int token = (int)(i / ((int64_t)quads * all));
+    const int row = table[3 * token], pos = table[3 * token + 1];
+    if (row < 0 || row >= rows || pos < 0 || pos >= capacity || (cos_table && pos >= context)) {
+        if (col == 0 && head == 0) report_bad_index(errors, pos, capacity);
+        return;
+    }
+    float* xr = qkv + (int64_t)token * all * width + (int64_t)head * width;
+    float4 a = *(const float4*)(xr + col), b = *(const float4*)(xr + col + half);
+    if (head < heads + kv_heads && cos_table) {
+        const float* c = cos_table + (int64_t)pos * width;
+        const float* sn = sin_table + (int64_t)pos * width;
+        const float4 ca = *(const float4*)(c + col), cb = *(const float4*)(c + col + half);
+        const float4 sa = *(const float4*)(sn + col), sb = *(const float4*)(sn + col + half);
+        // rotate_pair, element by element: a' = a cos_i + (b * -1) sin_i, b' = b cos_(i+half) + a sin_(i+half)
+        float4 ra, rb;
+        ra.x = __fadd_rn(__fmul_rn(a.x, ca.x), __fmul_rn(__fmul_rn(b.x, -1.0f), sa.x)), rb.x = __fadd_rn(__fmul_rn(b.x, cb.x), __fmul_rn(a.x, sb.x));
+        ra.y = __fadd_rn(__fmul_rn(a.y, ca.y), __fmul_rn(__fmul_rn(b.y, -1.0f), sa.y)), rb.y = __fadd_rn(__fmul_rn(b.y, cb.y), __fmul_rn(a.y, sb.y));
+        ra.z = __fadd_rn(__fmul_rn(a.z, ca.z), __fmul_rn(__fmul_rn(b.z, -1.0f), sa.z)), rb.z = __fadd_rn(__fmul_rn(b.z, cb.z), __fmul_rn(a.z, sb.z));
+        ra.w = __fadd_rn(__fmul_rn(a.w, ca.w), __fmul_rn(__fmul_rn(b.w, -1.0f), sa.w)), rb.w = __fadd_rn(__fmul_rn(b.w, cb.w), __fmul_rn(a.w, sb.w));
+        a = ra, b = rb;
+        *(float4*)(xr + col) = a, *(float4*)(xr + col + half) = b;
+    }
+    if (head >= heads) {
+        const bool is_key = head < heads + kv_heads;
+        const int kh = is_key ? head - heads : head - heads - kv_heads;
+        float* dst = (is_key ? keys : values) + (((int64_t)row * kv_heads + kh) * capacity + pos) * width;
+        *(float4*)(dst + col) = a, *(float4*)(dst + col + half) = b;
+    }
+}
+
 int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_heads, int width, const float* cos_table,
                        const float* sin_table, int context, const int* table, float* keys, float* values, int rows,
                        int capacity) {
@@ -297,6 +340,15 @@ int launch_rope_append(tsm_ctx* ctx, float* qkv, int tokens, int heads, int kv_h
     if (width % 2 != 0) return fail(ctx, TSM_ERR_ARG, "head width must be even, not " + std::to_string(width));
     int64_t total = (int64_t)tokens * (heads + 2 * kv_heads) * (width / 2);
     if (total == 0) return TSM_OK;
+    const bool pieces = width % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)keys | (uintptr_t)values | (uintptr_t)(cos_table ? cos_table : (const float*)qkv) |
+                                            (uintptr_t)(sin_table ? sin_table : (const float*)qkv)) & 15) == 0;
+    if (pieces) {
+        TSM_CUDA(ctx, launch_chained(ctx, rope_append4_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, qkv, tokens, heads, kv_heads,
+                                     width, cos_table, sin_table, context, table, keys, values, rows, capacity, ctx->errors));
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        return TSM_OK;
+    }
     TSM_CUDA(ctx, launch_chained(ctx, rope_append_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, qkv, tokens, heads, kv_heads, width,
                                  cos_table, sin_table, context, table, keys, values, rows, capacity, ctx->errors));
     count_launch(ctx);
