@@ -155,7 +155,8 @@ __device__ __forceinline__ float chunked_sum_of_terms(const float* terms, int n,
 
 // The sum of squares of a norm: the chunked form where it applies (`fast`, whole chunks, a block of at least four warps).
 __device__ __forceinline__ float ordered_sum_squares(const float* row, float* terms, int n, float shift, float* scratch, SumScratch* ss, bool fast) {
-    if (fast && n % kSumChunk == 0 && n >= 8 * kSumChunk && n <= kSumChunk * kSumMaxChunks && blockDim.x >= 128) {
+    // (rows under 1024 terms are quicker term by term: the chunked form's four barriers cost more than the short chain)
+    if (fast && n % kSumChunk == 0 && n >= 16 * kSumChunk && n <= kSumChunk * kSumMaxChunks && blockDim.x >= 128) {
         for (int j = threadIdx.x; j < n; j += blockDim.x) {
             float v = __fsub_rn(row[j], shift);
             terms[j] = __fmul_rn(v, v);
