@@ -43,6 +43,7 @@ struct MatvecParams {
     float* out;
     int rows_per_tile, num_tiles;
     int cap, stages;    // groups a stage holds, stages in the ring
+    int segments;       // > 1: long rows, a tile is `rows_per_tile` rows x one of `segments` equal pieces of a row (see below)
     unsigned nb_magic;  // floor(2^32 / nb) + 1: x / nb = umulhi(x, nb_magic) for the small x used here
     ErrorRecord* errors;
     const float* plain;   // not null: the rows come as F32, `plain_stride` apart, and every CTA quantises them itself
@@ -124,7 +125,26 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
         g0 = fb0 / F::G;
         groups = (int)((fb1 + F::G - 1) / F::G - g0);
     };
+    // Long rows (p.segments > 1): a whole row fills most of a stage, so whole-row tiles hold 4 rows and the fold warp adds with
+    // 4 of its lanes while the rest of the CTA waits for it.  A tile is then `rows_per_tile` rows x ONE of `segments` equal
+    // pieces of a row: one copy per row, each row's piece contiguous in the stage; pass `it` of a CTA is piece it % segments
+    // of its row tile it / segments, and the fold warp's lanes (one per row, up to 32) keep their running sums from piece to
+    // piece, so every output still adds its blocks in order.
+    const int S = p.segments;
+    const int nbs = nb / S;                 // blocks of a piece
+    const int gps = nbs / F::G;             // groups of a piece
     auto issue = [&](int it) {
+        if (S > 1) {
+            int tile = blockIdx.x + (it / S) * gridDim.x, seg = it % S;
+            if (tile >= p.num_tiles) return;
+            int r0 = tile * p.rows_per_tile, rows = min(p.n, r0 + p.rows_per_tile) - r0;
+            int s = it % kStages;
+            const unsigned piece = (unsigned)gps * F::GB;
+            mbar_expect_tx(&full[s], piece * (unsigned)rows);
+            for (int i = 0; i < rows; i++)
+                bulk_load(stages + (size_t)s * kStageBytes + (size_t)i * piece, p.w + ((int64_t)(r0 + i) * nb + (int64_t)seg * nbs) * F::B, piece, &full[s]);
+            return;
+        }
         int tile = blockIdx.x + it * gridDim.x;
         if (tile >= p.num_tiles) return;
         int r0, r1, groups;
@@ -191,37 +211,76 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
             }
         }
     } else {
-    // quantised activations -> shared memory (every CTA reads them once; they stay in L2)
+    // quantised activations -> shared memory (every CTA reads them once; they stay in L2).  Up to eight loads per thread are
+    // issued before the first store: one load per pass, each waited for, cost a trip to L2 per 160 pieces (six trips for rows of
+    // 14336 values)
     for (int c = 0; c < C; c++) {
         const int4* src = (const int4*)(p.acts.qs + (int64_t)c * nb * 32);
-        for (int i = tid; i < nb * 2; i += kThreads) {
-            int kb = i >> 1;
-            *(int4*)(acts_q + c * act_bytes + act_offset(kb) + (i & 1) * 16) = src[i];
-        }
-        for (int i = tid; i < nb; i += kThreads) {
-            acts_scale[c * nb + i] = p.acts.scales[(int64_t)c * nb + i];
-            if (KIND == TSM_Q4_0) {
-                // the block's integer sum of quantised activations, for the -8 offset of Q4_0's nibbles
-                const int* words = (const int*)(p.acts.qs + ((int64_t)c * nb + i) * 32);
-                int total = 0;
+        for (int i0 = tid; i0 < nb * 2; i0 += kThreads * 8) {
+            int4 v[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) total = __dp4a(0x01010101, words[u], total);
+            for (int u = 0; u < 8; u++)
+                if (i0 + u * kThreads < nb * 2) v[u] = src[i0 + u * kThreads];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * kThreads;
+                if (i < nb * 2) *(int4*)(acts_q + c * act_bytes + act_offset(i >> 1) + (i & 1) * 16) = v[u];
+            }
+        }
+        for (int i0 = tid; i0 < nb; i0 += kThreads * 4) {
+            float sc[4], au[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * kThreads;
+                sc[u] = i < nb ? p.acts.scales[(int64_t)c * nb + i] : 0.0f;
+                au[u] = KIND == TSM_Q4_1 && i < nb ? p.acts.sums[(int64_t)c * nb + i] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int i = i0 + u * kThreads;
+                if (i < nb) {
+                    acts_scale[c * nb + i] = sc[u];
+                    if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = au[u];
+                }
+            }
+        }
+    }
+    if (KIND == TSM_Q4_0) {
+        // the block's integer sum of quantised activations, for the -8 offset of Q4_0's nibbles: from the copy just made
+        __syncthreads();
+        for (int c = 0; c < C; c++)
+            for (int i = tid; i < nb; i += kThreads) {
+                const int4* words = (const int4*)(acts_q + c * act_bytes + act_offset(i));
+                const int4 lo = words[0], hi = words[1];
+                int total = __dp4a(0x01010101, lo.x, 0);
+                total = __dp4a(0x01010101, lo.y, total), total = __dp4a(0x01010101, lo.z, total), total = __dp4a(0x01010101, lo.w, total);
+                total = __dp4a(0x01010101, hi.x, total), total = __dp4a(0x01010101, hi.y, total);
+                total = __dp4a(0x01010101, hi.z, total), total = __dp4a(0x01010101, hi.w, total);
                 ((int*)acts_aux)[c * nb + i] = total;
             }
-            if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = p.acts.sums[(int64_t)c * nb + i];
-        }
     }
     }
     __syncthreads();
 
-    int prev_r0 = 0, prev_r1 = 0, prev_base = 0;  // the tile whose contributions wait to be folded
+    int prev_r0 = 0, prev_r1 = 0, prev_base = 0, prev_seg = 0;  // the tile whose contributions wait to be folded
     bool have_prev = false;
+    float run[C];                                 // segmented tiles: the fold lane's running sums of its row
+#pragma unroll
+    for (int c = 0; c < C; c++) run[c] = 0.0f;
     for (int it = 0;; it++) {
-        int tile = blockIdx.x + it * gridDim.x;
+        int tile = S > 1 ? blockIdx.x + (it / S) * gridDim.x : blockIdx.x + it * gridDim.x;
+        const int seg = S > 1 ? it % S : 0;
         bool valid = tile < p.num_tiles;
         int r0 = 0, r1 = 0, groups = 0;
         int64_t g0 = 0;
-        if (valid) tile_span(tile, r0, r1, g0, groups);
+        if (valid) {
+            if (S > 1) {
+                r0 = tile * p.rows_per_tile, r1 = min(p.n, r0 + p.rows_per_tile);
+                groups = (r1 - r0) * gps;
+            } else {
+                tile_span(tile, r0, r1, g0, groups);
+            }
+        }
         float* cur = parts + (it & 1) * C * pcap;
         if (warp < 4) {
             if (valid) {
@@ -244,6 +303,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                     // first activation block of the group: (kb_first + gi * G) mod nb by a reciprocal multiply
                     unsigned x = (unsigned)(kb_first + gi * F::G);
                     int kb = (int)(x - __umulhi(x, p.nb_magic) * (unsigned)nb);
+                    if (S > 1) kb = seg * nbs + (gi % gps) * F::G;   // group gi is group gi % gps of row gi / gps's piece
                     float* dst = cur + gi * F::G + ((gi * F::G) >> 5);  // part_index(gi * G), then + j within the same 32
                     // the group's activation scales (and totals or sums) in 16-byte loads when the group lies in one row
                     float dxs[C][F::G], auxs[C][F::G];
@@ -341,6 +401,38 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                     }
                 }
             }
+        } else if (have_prev && S > 1) {
+            // the previous pass's piece: lane i adds row i's nbs contributions onto its running sums
+            const float* old = parts + ((it - 1) & 1) * C * pcap;
+            const int r = prev_r0 + lane;
+            if (r < prev_r1) {
+                if (prev_seg == 0) {
+#pragma unroll
+                    for (int c = 0; c < C; c++) run[c] = 0.0f;
+                }
+                const int at = lane * nbs;
+                for (int b = 0; b < nbs; b += 8) {   // nbs is a multiple of 8: 8 consecutive blocks never straddle a pad word
+                    float v[C][8];
+                    const float* src = old + part_index(at + b);
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+#pragma unroll
+                        for (int c = 0; c < C; c++) v[c][u] = src[c * pcap + u];
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+#pragma unroll
+                        for (int c = 0; c < C; c++) run[c] = __fadd_rn(run[c], v[c][u]);
+                }
+                if (prev_seg == S - 1) {
+#pragma unroll
+                    for (int c = 0; c < C; c++) {
+                        float v = run[c];
+                        if (p.bias) v = __fadd_rn(v, p.bias[r]);
+                        if (p.residual) v = __fadd_rn(p.residual[(int64_t)c * p.n + r], v);
+                        p.out[(int64_t)c * p.n + r] = v;
+                    }
+                }
+            }
         } else if (have_prev) {
             // fold the previous tile: lane per row, each row's blocks in order from 0f
             const float* old = parts + ((it - 1) & 1) * C * pcap;
@@ -384,7 +476,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
         if (*abort_flag) break;
         if (!valid) break;
         have_prev = true;
-        prev_r0 = r0, prev_r1 = r1;
+        prev_r0 = r0, prev_r1 = r1, prev_seg = seg;
         prev_base = (int)((int64_t)r0 * nb - g0 * F::G);
         if (producer) issue(it + kStages);
     }
@@ -512,6 +604,35 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     TSM_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem));
     if (per_sm < 1) return TSM_OK;
     int slots = per_sm * ctx->sm_count;
+    // Long rows in pieces (see the kernel): the fewest pieces of at most 128 blocks that are whole groups and multiples of 8
+    // blocks, as many rows per tile as give every CTA slot one row tile, at most 32 (a fold lane per row) and a stage's worth.
+    static const bool whole_rows = getenv("TSM_MATVEC_WHOLE_ROWS") != nullptr;   // whole-row tiles for long rows too, for timing them
+    int segments = 1;
+    if (long_rows && aligned && !whole_rows) {
+        for (int pieces = 2; pieces <= 16 && segments == 1; pieces *= 2) {
+            int nbs = nb / pieces;
+            if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= 128) segments = pieces;
+        }
+    }
+    if (segments > 1) {
+        const int gps = nb / segments / F::G;
+        const int most = std::min(32, cap / gps);
+        int rows_per_tile = std::max(1, std::min(most, (n + slots - 1) / slots));
+        int tiles = (n + rows_per_tile - 1) / rows_per_tile;
+        int grid = std::min(tiles, slots);
+        MatvecParams p;
+        p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
+        p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
+        p.cap = cap, p.stages = stages, p.segments = segments;
+        p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
+        p.plain = plain, p.plain_stride = plain_stride;
+        p.plain_vector = plain && ((uintptr_t)plain & 15) == 0 && plain_stride % 4 == 0;
+        TSM_CUDA(ctx, launch_chained(ctx, kernel, dim3(grid), dim3(kThreads), smem, p));
+        count_launch(ctx);
+        TSM_LAUNCH_CHECK(ctx);
+        *taken = true;
+        return TSM_OK;
+    }
     int tiles = (n + max_rows - 1) / max_rows;
     if (tiles < ctx->sm_count) {
         // a small matrix: full tiles would leave most SMs without work, and the kernel's time is then one CTA's latency
@@ -529,7 +650,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     MatvecParams p;
     p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
-    p.cap = cap, p.stages = stages;
+    p.cap = cap, p.stages = stages, p.segments = 1;
     p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
     p.plain = plain, p.plain_stride = plain_stride;
     p.plain_vector = plain && ((uintptr_t)plain & 15) == 0 && plain_stride % 4 == 0;
