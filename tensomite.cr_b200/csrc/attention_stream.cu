@@ -153,8 +153,23 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_stream_kernel(St
         abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < G * WIDTH; i += blockDim.x)
-        qs[(i / WIDTH) * QP + i % WIDTH] = p.q[(int64_t)token * p.q_stride + (int64_t)head0 * WIDTH + i];
+    {
+        // the four heads' queries: every thread's loads issued before its first store (one per pass, each waited for, cost a
+        // trip to L2 per pass)
+        const float* qsrc = p.q + (int64_t)token * p.q_stride + (int64_t)head0 * WIDTH;
+        constexpr int kPasses = (G * WIDTH + kConsumers + 31) / (kConsumers + 32);
+        float qv[kPasses];
+#pragma unroll
+        for (int u = 0; u < kPasses; u++) {
+            const int i = tid + u * (kConsumers + 32);
+            qv[u] = i < G * WIDTH ? qsrc[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kPasses; u++) {
+            const int i = tid + u * (kConsumers + 32);
+            if (i < G * WIDTH) qs[(i / WIDTH) * QP + i % WIDTH] = qv[u];
+        }
+    }
     __syncthreads();
 
     if (warp == kConsumers / 32) {
@@ -436,8 +451,23 @@ __global__ void __launch_bounds__(kConsumers + 32, 2) attention_scores_kernel(St
         abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < G * WIDTH; i += blockDim.x)
-        qs[(i / WIDTH) * QP + i % WIDTH] = p.q[(int64_t)token * p.q_stride + (int64_t)head0 * WIDTH + i];
+    {
+        // the four heads' queries: every thread's loads issued before its first store (one per pass, each waited for, cost a
+        // trip to L2 per pass)
+        const float* qsrc = p.q + (int64_t)token * p.q_stride + (int64_t)head0 * WIDTH;
+        constexpr int kPasses = (G * WIDTH + kConsumers + 31) / (kConsumers + 32);
+        float qv[kPasses];
+#pragma unroll
+        for (int u = 0; u < kPasses; u++) {
+            const int i = tid + u * (kConsumers + 32);
+            qv[u] = i < G * WIDTH ? qsrc[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < kPasses; u++) {
+            const int i = tid + u * (kConsumers + 32);
+            if (i < G * WIDTH) qs[(i / WIDTH) * QP + i % WIDTH] = qv[u];
+        }
+    }
     __syncthreads();
 
     if (warp == kConsumers / 32) {
