@@ -959,9 +959,19 @@ __global__ void __launch_bounds__(kPrefillConsumers + 32, 2) attention_prefill_k
         abort_flag[0] = 0, abort_flag[1] = 0, abort_flag[2] = (int)p.wait_hint, abort_flag[3] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = tid; i < kQRows * WIDTH; i += blockDim.x) {
-        int r = i / WIDTH, d = i % WIDTH, t = r >> 2, h = r & 3;
-        qs[r * QP + d] = t < tile_count ? p.q[(int64_t)(tile_first + t) * p.q_stride + (int64_t)(head0 + h) * WIDTH + d] : 0.0f;
+    for (int i0 = tid; i0 < kQRows * WIDTH; i0 += 8 * blockDim.x) {   // eight loads per thread in flight, then their stores
+        float qv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int i = i0 + u * blockDim.x;
+            const int r = i / WIDTH, d = i % WIDTH, t = r >> 2, h = r & 3;
+            qv[u] = i < kQRows * WIDTH && t < tile_count ? p.q[(int64_t)(tile_first + t) * p.q_stride + (int64_t)(head0 + h) * WIDTH + d] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int i = i0 + u * blockDim.x;
+            if (i < kQRows * WIDTH) qs[(i / WIDTH) * QP + i % WIDTH] = qv[u];
+        }
     }
     for (int r = tid; r < kQRows; r += blockDim.x) {
         int t = r >> 2;
@@ -1077,7 +1087,15 @@ __global__ void __launch_bounds__(kPrefillConsumers + 32, 2) attention_prefill_k
         const int limit = limits[r];
         float* sr = score_row(r);
         const float top = tops[r];
-        for (int pos = lane; pos <= limit; pos += 32) sr[pos] = exact_exp(__fsub_rn(sr[pos], top));
+        // eight loads per lane in flight: one per pass, each waited for before its exp, cost a trip to L2 per 32 positions
+        for (int p0 = lane; p0 <= limit; p0 += 8 * 32) {
+            float sv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) sv[u] = p0 + 32 * u <= limit ? sr[p0 + 32 * u] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (p0 + 32 * u <= limit) sr[p0 + 32 * u] = exact_exp(__fsub_rn(sv[u], top));
+        }
     }
     consumers_barrier();
     if (tid < kQRows) {
@@ -1087,11 +1105,30 @@ __global__ void __launch_bounds__(kPrefillConsumers + 32, 2) attention_prefill_k
         int pos = 0;
         // a row starts on a 16-byte boundary when the capacity is a multiple of 4; otherwise plain loads
         if ((((uintptr_t)sr) & 15) == 0) {
-            for (; pos + 8 <= limit + 1; pos += 8) {
-                float4 a = *(const float4*)(sr + pos), b = *(const float4*)(sr + pos + 4);
-                total = __fadd_rn(total, a.x), total = __fadd_rn(total, a.y), total = __fadd_rn(total, a.z), total = __fadd_rn(total, a.w);
-                total = __fadd_rn(total, b.x), total = __fadd_rn(total, b.y), total = __fadd_rn(total, b.z), total = __fadd_rn(total, b.w);
+            // the exp values come back from L2: 32 positions are on their way while the 32 before them are added
+            constexpr int kAhead = 8;   // 16-byte pieces per step
+            const int whole = (limit + 1) / (4 * kAhead);
+            float4 cur[kAhead], nxt[kAhead];
+            if (whole > 0) {
+#pragma unroll
+                for (int u = 0; u < kAhead; u++) cur[u] = *(const float4*)(sr + 4 * u);
             }
+            for (int g = 0; g < whole; g++) {
+                if (g + 1 < whole) {
+#pragma unroll
+                    for (int u = 0; u < kAhead; u++) nxt[u] = *(const float4*)(sr + (g + 1) * 4 * kAhead + 4 * u);
+                }
+#pragma unroll
+                for (int u = 0; u < kAhead; u++) {
+                    total = __fadd_rn(total, cur[u].x), total = __fadd_rn(total, cur[u].y);
+                    total = __fadd_rn(total, cur[u].z), total = __fadd_rn(total, cur[u].w);
+                }
+                if (g + 1 < whole) {
+#pragma unroll
+                    for (int u = 0; u < kAhead; u++) cur[u] = nxt[u];
+                }
+            }
+            pos = whole * 4 * kAhead;
         }
         for (; pos <= limit; pos++) total = __fadd_rn(total, sr[pos]);
         tots[tid] = total;
