@@ -44,6 +44,7 @@ struct MatvecParams {
     int rows_per_tile, num_tiles;
     int cap, stages;    // groups a stage holds, stages in the ring
     int segments;       // > 1: long rows, a tile is `rows_per_tile` rows x one of `segments` equal pieces of a row (see below)
+    int seg_blocks, seg_groups;   // blocks and groups of a piece (the host divides, once)
     unsigned nb_magic;  // floor(2^32 / nb) + 1: x / nb = umulhi(x, nb_magic) for the small x used here
     ErrorRecord* errors;
     const float* plain;   // not null: the rows come as F32, `plain_stride` apart, and every CTA quantises them itself
@@ -95,8 +96,9 @@ __host__ __device__ __forceinline__ int part_index(int p) { return p + (p >> 5);
 // consecutive groups (256 bytes apart) read different banks.
 __host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (kb >> 3) * 16; }
 
-template <int KIND, int C, bool ALIGNED>
+template <int KIND, int C, int MODE>   // MODE 0: rows that are not whole groups; 1: whole groups; 2: whole groups, long rows in pieces
 __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
+    constexpr bool ALIGNED = MODE >= 1;
     using F = Fmt<KIND>;
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = p.nb;
@@ -130,9 +132,9 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     // pieces of a row: one copy per row, each row's piece contiguous in the stage; pass `it` of a CTA is piece it % segments
     // of its row tile it / segments, and the fold warp's lanes (one per row, up to 32) keep their running sums from piece to
     // piece, so every output still adds its blocks in order.
-    const int S = p.segments;
-    const int nbs = nb / S;                 // blocks of a piece
-    const int gps = nbs / F::G;             // groups of a piece
+    const int S = MODE == 2 ? p.segments : 1;   // a constant 1 in the other modes: the pieces' code and registers drop out
+    const int nbs = p.seg_blocks;           // blocks of a piece
+    const int gps = p.seg_groups;           // groups of a piece
     auto issue = [&](int it) {
         if (S > 1) {
             int tile = blockIdx.x + (it / S) * gridDim.x, seg = it % S;
@@ -211,9 +213,32 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
             }
         }
     } else {
-    // quantised activations -> shared memory (every CTA reads them once; they stay in L2).  Up to eight loads per thread are
-    // issued before the first store: one load per pass, each waited for, cost a trip to L2 per 160 pieces (six trips for rows of
-    // 14336 values)
+    // quantised activations -> shared memory (every CTA reads them once; they stay in L2).
+    if (nb <= kThreads) {
+    // short rows: a thread has at most two pieces and one block's scale to fetch, and Q4_0's totals come from the same global
+    // words, so everything is one round of independent loads and one barrier
+    for (int c = 0; c < C; c++) {
+        const int4* src = (const int4*)(p.acts.qs + (int64_t)c * nb * 32);
+        for (int i = tid; i < nb * 2; i += kThreads) {
+            int kb = i >> 1;
+            *(int4*)(acts_q + c * act_bytes + act_offset(kb) + (i & 1) * 16) = src[i];
+        }
+        for (int i = tid; i < nb; i += kThreads) {
+            acts_scale[c * nb + i] = p.acts.scales[(int64_t)c * nb + i];
+            if (KIND == TSM_Q4_0) {
+                // the block's integer sum of quantised activations, for the -8 offset of Q4_0's nibbles
+                const int* words = (const int*)(p.acts.qs + ((int64_t)c * nb + i) * 32);
+                int total = 0;
+#pragma unroll
+                for (int u = 0; u < 8; u++) total = __dp4a(0x01010101, words[u], total);
+                ((int*)acts_aux)[c * nb + i] = total;
+            }
+            if (KIND == TSM_Q4_1) acts_aux[c * nb + i] = p.acts.sums[(int64_t)c * nb + i];
+        }
+    }
+    } else {
+    // long rows: up to eight loads per thread are issued before the first store: one load per pass, each waited for, cost a
+    // trip to L2 per 160 pieces (six trips for rows of 14336 values)
     for (int c = 0; c < C; c++) {
         const int4* src = (const int4*)(p.acts.qs + (int64_t)c * nb * 32);
         for (int i0 = tid; i0 < nb * 2; i0 += kThreads * 8) {
@@ -260,6 +285,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
             }
     }
     }
+    }
     __syncthreads();
 
     int prev_r0 = 0, prev_r1 = 0, prev_base = 0, prev_seg = 0;  // the tile whose contributions wait to be folded
@@ -267,9 +293,9 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     float run[C];                                 // segmented tiles: the fold lane's running sums of its row
 #pragma unroll
     for (int c = 0; c < C; c++) run[c] = 0.0f;
+    int seg = 0, row_tile = blockIdx.x;           // segmented tiles: the piece and the row tile of pass `it`, counted up
     for (int it = 0;; it++) {
-        int tile = S > 1 ? blockIdx.x + (it / S) * gridDim.x : blockIdx.x + it * gridDim.x;
-        const int seg = S > 1 ? it % S : 0;
+        const int tile = S > 1 ? row_tile : blockIdx.x + it * gridDim.x;
         bool valid = tile < p.num_tiles;
         int r0 = 0, r1 = 0, groups = 0;
         int64_t g0 = 0;
@@ -477,6 +503,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
         if (!valid) break;
         have_prev = true;
         prev_r0 = r0, prev_r1 = r1, prev_seg = seg;
+        if (S > 1 && ++seg == S) seg = 0, row_tile += gridDim.x;
         prev_base = (int)((int64_t)r0 * nb - g0 * F::G);
         if (producer) issue(it + kStages);
     }
@@ -588,7 +615,17 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     size_t smem = stream_smem_bytes<KIND, C>(nb, cap, stages);
     if (smem > 200 * 1024) return TSM_OK;
     bool aligned = nb % F::G == 0;
-    auto kernel = aligned ? matvec_stream_kernel<KIND, C, true> : matvec_stream_kernel<KIND, C, false>;
+    // Long rows in pieces (see the kernel): the fewest pieces of at most 128 blocks that are whole groups and multiples of 8
+    // blocks, as many rows per tile as give every CTA slot one row tile, at most 32 (a fold lane per row) and a stage's worth.
+    static const bool whole_rows = getenv("TSM_MATVEC_WHOLE_ROWS") != nullptr;   // whole-row tiles for long rows too, for timing them
+    int segments = 1;
+    if (long_rows && aligned && !whole_rows) {
+        for (int pieces = 2; pieces <= 16 && segments == 1; pieces *= 2) {
+            int nbs = nb / pieces;
+            if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= 128) segments = pieces;
+        }
+    }
+    auto kernel = segments > 1 ? matvec_stream_kernel<KIND, C, 2> : aligned ? matvec_stream_kernel<KIND, C, 1> : matvec_stream_kernel<KIND, C, 0>;
     static std::mutex attr_lock;  // the attribute is per device and per function
     static std::map<std::pair<int, const void*>, size_t> attr_set;
     {
@@ -604,16 +641,6 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     TSM_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem));
     if (per_sm < 1) return TSM_OK;
     int slots = per_sm * ctx->sm_count;
-    // Long rows in pieces (see the kernel): the fewest pieces of at most 128 blocks that are whole groups and multiples of 8
-    // blocks, as many rows per tile as give every CTA slot one row tile, at most 32 (a fold lane per row) and a stage's worth.
-    static const bool whole_rows = getenv("TSM_MATVEC_WHOLE_ROWS") != nullptr;   // whole-row tiles for long rows too, for timing them
-    int segments = 1;
-    if (long_rows && aligned && !whole_rows) {
-        for (int pieces = 2; pieces <= 16 && segments == 1; pieces *= 2) {
-            int nbs = nb / pieces;
-            if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= 128) segments = pieces;
-        }
-    }
     if (segments > 1) {
         const int gps = nb / segments / F::G;
         const int most = std::min(32, cap / gps);
@@ -623,7 +650,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
         MatvecParams p;
         p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
         p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
-        p.cap = cap, p.stages = stages, p.segments = segments;
+        p.cap = cap, p.stages = stages, p.segments = segments, p.seg_blocks = nb / segments, p.seg_groups = gps;
         p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
         p.plain = plain, p.plain_stride = plain_stride;
         p.plain_vector = plain && ((uintptr_t)plain & 15) == 0 && plain_stride % 4 == 0;
@@ -650,7 +677,7 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     MatvecParams p;
     p.w = w, p.n = n, p.nb = nb, p.acts = a, p.bias = bias, p.residual = residual, p.out = out;
     p.rows_per_tile = rows_per_tile, p.num_tiles = tiles, p.errors = ctx->errors;
-    p.cap = cap, p.stages = stages, p.segments = 1;
+    p.cap = cap, p.stages = stages, p.segments = 1, p.seg_blocks = nb, p.seg_groups = nb / F::G;
     p.nb_magic = (unsigned)((1ull << 32) / (unsigned)nb) + 1u;
     p.plain = plain, p.plain_stride = plain_stride;
     p.plain_vector = plain && ((uintptr_t)plain & 15) == 0 && plain_stride % 4 == 0;
