@@ -116,7 +116,7 @@ def test_the_crystal_stub_binds_every_entry_point():
     assert set(declared) == set(pkg.declared_symbols())
     for name, args in declared.items():
         found = re.search(r"fun \w+ = " + name + r"\(([^)]*)\)", stub)
-        assert found, f"{name} has no fun line in INTEGRATION.md"
+        assert found, f"{name} has no fun line in the integration notes"
         want = 0 if args.strip() in ("", "void") else args.count(",") + 1
         got = 0 if not found.group(1).strip() else found.group(1).count(",") + 1
         assert want == got, (name, want, got)
