@@ -96,9 +96,18 @@ __host__ __device__ __forceinline__ int part_index(int p) { return p + (p >> 5);
 // consecutive groups (256 bytes apart) read different banks.
 __host__ __device__ __forceinline__ int act_offset(int kb) { return kb * 32 + (kb >> 3) * 16; }
 
-template <int KIND, int C, int MODE>   // MODE 0: rows that are not whole groups; 1: whole groups; 2: whole groups, long rows in pieces
+// MODE 0: rows that are not whole groups; 1: whole groups; 2: whole groups, long rows in pieces; 3: whole groups, one row of
+// activations, and a row length that divides the blocks one sweep of the compute threads covers: a thread then meets the same
+// G activation blocks in every group it takes, and keeps them (values, scales, totals) in registers
+template <int KIND, int C, int MODE>
 __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p) {
     constexpr bool ALIGNED = MODE >= 1;
+    constexpr bool KEPT = MODE == 3;
+    // Q4_0 with kept activations: a thread takes HALF a group (4 blocks, 72 bytes, read in 8-byte loads), so that it keeps 32
+    // activation registers and not 64 (with 64 the kernel needed 121 registers and a CTA less fitted an SM)
+    constexpr bool HALVES = KEPT && KIND == TSM_Q4_0;
+    constexpr int GG = HALVES ? 4 : Fmt<KIND>::G;   // blocks a thread takes at a time
+    static_assert(!KEPT || C == 1, "kept activations: one row");
     using F = Fmt<KIND>;
     extern __shared__ __align__(128) unsigned char smem[];
     const int nb = p.nb;
@@ -288,6 +297,25 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
     }
     __syncthreads();
 
+    // Kept activations: the shared-memory copy is read once.  Read per block instead, the activations are 32 of the 50-odd
+    // bytes a 4-bit block moves through shared memory, and that data path, not HBM, was what the kernel filled.
+    unsigned kept_q[KEPT ? GG * 8 : 1];
+    float kept_dx[KEPT ? GG : 1], kept_aux[KEPT ? GG : 1];
+    if (KEPT && tid < kComputeThreads) {
+        const int kb = (tid * GG) % nb;
+        const uint4* ap = (const uint4*)(acts_q + act_offset(kb));
+#pragma unroll
+        for (int i = 0; i < GG * 2; i++) {
+            const uint4 v = ap[i];
+            kept_q[4 * i] = v.x, kept_q[4 * i + 1] = v.y, kept_q[4 * i + 2] = v.z, kept_q[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int j = 0; j < GG; j++) {
+            kept_dx[j] = acts_scale[kb + j];
+            kept_aux[j] = KIND != TSM_Q8_0 ? acts_aux[kb + j] : 0.0f;
+        }
+    }
+
     int prev_r0 = 0, prev_r1 = 0, prev_base = 0, prev_seg = 0;  // the tile whose contributions wait to be folded
     bool have_prev = false;
     float run[C];                                 // segmented tiles: the fold lane's running sums of its row
@@ -318,22 +346,35 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                 // the row's block 0 starts (r0 * nb) mod G blocks earlier, i.e. inside the previous row
                 int lead = (int)(((int64_t)r0 * nb) & (F::G - 1));
                 int kb_first = ALIGNED || lead == 0 ? 0 : nb - lead;
-                for (int gi = tid; gi < groups && arrived; gi += kComputeThreads) {
-                    unsigned W[F::WORDS];
-                    const uint4* gp = (const uint4*)(stage + (size_t)gi * F::GB);
+                // gi counts groups, or half groups (HALVES)
+                for (int gi = tid; gi < (HALVES ? 2 * groups : groups) && arrived; gi += kComputeThreads) {
+                    unsigned W[HALVES ? F::WORDS / 2 : F::WORDS];
+                    if (HALVES) {
+                        const uint2* gp = (const uint2*)(stage + (size_t)gi * (F::GB / 2));
 #pragma unroll
-                    for (int i = 0; i < F::WORDS / 4; i++) {
-                        uint4 v = gp[i];
-                        W[4 * i] = v.x, W[4 * i + 1] = v.y, W[4 * i + 2] = v.z, W[4 * i + 3] = v.w;
+                        for (int i = 0; i < F::WORDS / 4; i++) {
+                            uint2 v = gp[i];
+                            W[2 * i] = v.x, W[2 * i + 1] = v.y;
+                        }
+                    } else {
+                        const uint4* gp = (const uint4*)(stage + (size_t)gi * F::GB);
+#pragma unroll
+                        for (int i = 0; i < F::WORDS / 4; i++) {
+                            uint4 v = gp[i];
+                            W[4 * i] = v.x, W[4 * i + 1] = v.y, W[4 * i + 2] = v.z, W[4 * i + 3] = v.w;
+                        }
                     }
                     // first activation block of the group: (kb_first + gi * G) mod nb by a reciprocal multiply
                     unsigned x = (unsigned)(kb_first + gi * F::G);
                     int kb = (int)(x - __umulhi(x, p.nb_magic) * (unsigned)nb);
                     if (S > 1) kb = seg * nbs + (gi % gps) * F::G;   // group gi is group gi % gps of row gi / gps's piece
-                    float* dst = cur + gi * F::G + ((gi * F::G) >> 5);  // part_index(gi * G), then + j within the same 32
+                    float* dst = cur + gi * GG + ((gi * GG) >> 5);  // part_index(gi * GG), then + j within the same 32
                     // the group's activation scales (and totals or sums) in 16-byte loads when the group lies in one row
                     float dxs[C][F::G], auxs[C][F::G];
-                    if (ALIGNED) {
+                    if (KEPT) {
+#pragma unroll
+                        for (int j = 0; j < GG; j++) dxs[0][j] = kept_dx[j], auxs[0][j] = kept_aux[j];
+                    } else if (ALIGNED) {
 #pragma unroll
                         for (int c = 0; c < C; c++)
 #pragma unroll
@@ -347,7 +388,7 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                             }
                     }
 #pragma unroll
-                    for (int j = 0; j < F::G; j++) {
+                    for (int j = 0; j < GG; j++) {
                         int kbj = kb + j;
                         if (!ALIGNED && kbj >= nb) kbj -= nb;  // a group may run over the end of a row (rows hold >= G blocks)
                         float dw, mw = 0.0f;
@@ -388,7 +429,13 @@ __global__ void __launch_bounds__(kThreads) matvec_stream_kernel(MatvecParams p)
                         for (int c = 0; c < C; c++) {
                             const uint4* ap = ALIGNED ? (const uint4*)(acts_q + c * act_bytes + act_offset(kb)) + 2 * j
                                                       : (const uint4*)(acts_q + c * act_bytes + act_offset(kbj));
-                            uint4 a0 = ap[0], a1 = ap[1];
+                            uint4 a0, a1;
+                            if (KEPT) {
+                                a0 = make_uint4(kept_q[8 * j], kept_q[8 * j + 1], kept_q[8 * j + 2], kept_q[8 * j + 3]);
+                                a1 = make_uint4(kept_q[8 * j + 4], kept_q[8 * j + 5], kept_q[8 * j + 6], kept_q[8 * j + 7]);
+                            } else {
+                                a0 = ap[0], a1 = ap[1];
+                            }
                             int total;
                             if (KIND == TSM_Q8_0) {
                                 total = __dp4a((int)q[0], (int)a0.x, 0);
@@ -603,17 +650,6 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     // that a tile still holds several rows for the fold warp to fold side by side.
     int per_thread = F::CAP / 128;  // groups per thread of the small configuration (Q4_1's groups are half as large)
     bool long_rows = nb / F::G > 32 * per_thread;
-    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = 2;  // two stages measured faster than three: more CTAs fit an SM
-    // TSM_MATVEC_CAP / TSM_MATVEC_STAGES override the tile size (in units of the format's default) and ring depth, so
-    // that variants can be timed without rebuilding (as TENSOMITE_BLOCK_MATMUL does in the reference, quant.cr:36-41)
-    static const int env_cap = getenv("TSM_MATVEC_CAP") ? atoi(getenv("TSM_MATVEC_CAP")) : 0;
-    static const int env_stages = getenv("TSM_MATVEC_STAGES") ? atoi(getenv("TSM_MATVEC_STAGES")) : 0;
-    if (env_cap > 0 && !long_rows) cap = F::CAP * env_cap / 4;  // quarters of the default
-    if (env_stages >= 1 && env_stages <= 4) stages = env_stages;
-    int max_rows = ((cap - 2) * F::G) / nb;
-    if (max_rows < 1) return TSM_OK;
-    size_t smem = stream_smem_bytes<KIND, C>(nb, cap, stages);
-    if (smem > 200 * 1024) return TSM_OK;
     bool aligned = nb % F::G == 0;
     // Long rows in pieces (see the kernel): the fewest pieces of at most 128 blocks that are whole groups and multiples of 8
     // blocks, as many rows per tile as give every CTA slot one row tile, at most 32 (a fold lane per row) and a stage's worth.
@@ -625,7 +661,27 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
             if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= 128) segments = pieces;
         }
     }
+    // One row of activations whose length divides a sweep of the compute threads: the activations stay in registers (mode 3 of
+    // the kernel).  TSM_MATVEC_KEPT=0 turns the mode off, for timing the two against each other.
+    static const bool kept_on = !(getenv("TSM_MATVEC_KEPT") && atoi(getenv("TSM_MATVEC_KEPT")) == 0);
+    const int sweep = kComputeThreads * (KIND == TSM_Q4_0 ? 4 : F::G);   // Q4_0: a thread takes half a group there
+    const bool kept = C == 1 && kept_on && aligned && segments == 1 && sweep % nb == 0;
+    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = 2;  // two stages measured faster than three: more CTAs fit an SM
+    if (kept && KIND == TSM_Q4_0 && !long_rows) cap = F::CAP * 6 / 4;   // three half-group sweeps per stage measured fastest (49 against 54 us for 128256 x 4096)
+    // TSM_MATVEC_CAP / TSM_MATVEC_STAGES override the tile size (in units of the format's default) and ring depth, so
+    // that variants can be timed without rebuilding (as TENSOMITE_BLOCK_MATMUL does in the reference, quant.cr:36-41)
+    static const int env_cap = getenv("TSM_MATVEC_CAP") ? atoi(getenv("TSM_MATVEC_CAP")) : 0;
+    static const int env_stages = getenv("TSM_MATVEC_STAGES") ? atoi(getenv("TSM_MATVEC_STAGES")) : 0;
+    if (env_cap > 0 && !long_rows) cap = F::CAP * env_cap / 4;  // quarters of the default
+    if (env_stages >= 1 && env_stages <= 4) stages = env_stages;
+    int max_rows = ((cap - 2) * F::G) / nb;   // (filling a stage to the last group with rows of whole groups measured no faster)
+    if (max_rows < 1) return TSM_OK;
+    size_t smem = stream_smem_bytes<KIND, C>(nb, cap, stages);
+    if (smem > 200 * 1024) return TSM_OK;
     auto kernel = segments > 1 ? matvec_stream_kernel<KIND, C, 2> : aligned ? matvec_stream_kernel<KIND, C, 1> : matvec_stream_kernel<KIND, C, 0>;
+    if constexpr (C == 1) {
+        if (kept) kernel = matvec_stream_kernel<KIND, C, 3>;
+    }
     static std::mutex attr_lock;  // the attribute is per device and per function
     static std::map<std::pair<int, const void*>, size_t> attr_set;
     {
