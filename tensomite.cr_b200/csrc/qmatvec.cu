@@ -655,10 +655,25 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     // blocks, as many rows per tile as give every CTA slot one row tile, at most 32 (a fold lane per row) and a stage's worth.
     static const bool whole_rows = getenv("TSM_MATVEC_WHOLE_ROWS") != nullptr;   // whole-row tiles for long rows too, for timing them
     int segments = 1;
+    // Pieces of at most 128 blocks; for Q8_0 and Q4_1 of at most 64 when no more than 8 (Q4_1: 16) such pieces make a row.
+    // Measured on 4096 x 14336: eight pieces of 56 blocks instead of four of 112 took Q8_0 from 25.7 to 21.6 us and Q4_1 from
+    // 23.6 to 19.8, Q4_0 from 17.6 to 19.7; on 4096 x 28672 sixteen pieces of 56 took Q4_1 from 42.3 to 34.2 and Q8_0 from
+    // 42.8 to 58.8.
+    static const int env_pieces = getenv("TSM_MATVEC_PIECES") ? atoi(getenv("TSM_MATVEC_PIECES")) : 0;   // start the search at this many pieces
+    bool small_pieces = false;
     if (long_rows && aligned && !whole_rows) {
-        for (int pieces = 2; pieces <= 16 && segments == 1; pieces *= 2) {
-            int nbs = nb / pieces;
-            if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= 128) segments = pieces;
+        auto search = [&](int first, int last, int piece_most) {
+            for (int pieces = first; pieces <= last && segments == 1; pieces *= 2) {
+                int nbs = nb / pieces;
+                if (nb % pieces == 0 && nbs % 8 == 0 && nbs % F::G == 0 && nbs <= piece_most) segments = pieces;
+            }
+        };
+        if (env_pieces > 0) {
+            search(env_pieces, 16, 128);
+        } else {
+            if (KIND != TSM_Q4_0) search(2, KIND == TSM_Q8_0 ? 8 : 16, 64);
+            small_pieces = segments > 1;
+            search(2, 16, 128);
         }
     }
     // One row of activations whose length divides a sweep of the compute threads: the activations stay in registers (mode 3 of
@@ -666,7 +681,10 @@ static int launch_stream(tsm_ctx* ctx, const QuantizedActs& a, const float* plai
     static const bool kept_on = !(getenv("TSM_MATVEC_KEPT") && atoi(getenv("TSM_MATVEC_KEPT")) == 0);
     const int sweep = kComputeThreads * (KIND == TSM_Q4_0 ? 4 : F::G);   // Q4_0: a thread takes half a group there
     const bool kept = C == 1 && kept_on && aligned && segments == 1 && sweep % nb == 0;
-    int cap = long_rows ? 2 * F::CAP : F::CAP, stages = 2;  // two stages measured faster than three: more CTAs fit an SM
+    static const int env_long_cap = getenv("TSM_MATVEC_LONG_CAP") ? atoi(getenv("TSM_MATVEC_LONG_CAP")) : 0;   // long rows' stage, in halves of the default short one
+    // rows in pieces: the stage that measured fastest with them (same shape): the short rows' for Q8_0, half as much again for Q4_1
+    const int long_cap = !small_pieces ? 2 * F::CAP : KIND == TSM_Q8_0 ? F::CAP : F::CAP * 3 / 2;
+    int cap = long_rows ? (env_long_cap >= 2 && env_long_cap <= 6 ? F::CAP * env_long_cap / 2 : long_cap) : F::CAP, stages = 2;  // two stages measured faster than three: more CTAs fit an SM
     if (kept && KIND == TSM_Q4_0 && !long_rows) cap = F::CAP * 6 / 4;   // three half-group sweeps per stage measured fastest (49 against 54 us for 128256 x 4096)
     // TSM_MATVEC_CAP / TSM_MATVEC_STAGES override the tile size (in units of the format's default) and ring depth, so
     // that variants can be timed without rebuilding (as TENSOMITE_BLOCK_MATMUL does in the reference, quant.cr:36-41)
