@@ -88,6 +88,31 @@ def test_block_product_is_bit_exact(dev, name):
 
 
 @pytest.mark.parametrize("name", list(KINDS))
+def test_one_row_with_its_activations_kept_in_registers(dev, name):
+    """One row of activations whose length divides a sweep of the streamed kernel's compute threads (8 .. 256 blocks; for
+    Q4_0 and Q4_1 up to 512 blocks' worth of a sweep) keeps each thread's activation blocks in registers.  Row counts that
+    leave a last tile short or a single row, a bias, a block of zero activations, one whose largest value is the first and a
+    tiny one: the oracle's product (Quant.block_matmul over quantize_activations' blocks, quant.cr:45-60, 428-442), bit
+    for bit."""
+    rng = np.random.default_rng(31)
+    kind = KINDS[name]
+    for n, k in [(1, 256), (129, 512), (1000, 1024), (515, 4096), (300, 8192), (2501, 256), (64, 2048)]:
+        values = rng.uniform(-2, 2, n * k).astype(np.float32)
+        values[:32] = 0
+        x = rng.uniform(-3, 3, (1, k)).astype(np.float32)
+        x[0, 32:64] = 0
+        x[0, 64:96] = [127.0 if j == 0 else j - 15.5 for j in range(32)]
+        x[0, k - 32:] *= 1e-20
+        bias = rng.normal(0, 1, n).astype(np.float32) if n % 2 else None
+        w = oracle.quantize(kind, values)
+        wb = dev.tensor(w)
+        got = dev.block_matmul(x, wb, kind, n, bias=bias)
+        want = oracle.matmul_reference(kind, x, w, n, bias=bias)
+        wb.free()
+        assert np.array_equal(bits(got), bits(want)), (name, n, k)
+
+
+@pytest.mark.parametrize("name", list(KINDS))
 def test_a_few_rows_quantised_inside_the_product_have_the_quantisers_bits(dev, name):
     """tsm_block_matmul of at most four rows quantises them inside the streamed kernel (one thread per block) instead of
     launching the quantiser first.  Rows that are views (a stride that is no multiple of four floats, so the 16-byte loads
