@@ -15,6 +15,10 @@
 //   against the quantised activations held in shared memory, and writes the group's float
 //   contributions to a staging array.  A fifth warp folds each row's contributions in block order
 //   (one lane per row) while the compute warps work on the next tile, and issues the copies.
+//   Two variants of the tile: rows too long for several to fit a stage are taken in pieces (the fold
+//   lanes carry their running sums from piece to piece), and with a single row of activations whose
+//   length divides what one sweep of the compute threads covers, every thread keeps its activation
+//   blocks in registers instead of re-reading them from shared memory for every weight block.
 //
 // generic kernel (any row count, any alignment down to 2 bytes)
 //   One warp per output; lane l takes blocks l, l+32, ...; contributions are folded in block order
