@@ -775,6 +775,29 @@ static int launch_kind(tsm_ctx* ctx, const QuantizedActs& a, int rows, int k, co
     else if (rows == 3) TSM_TRY((launch_stream<KIND, 3>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
     else if (rows == 4) TSM_TRY((launch_stream<KIND, 4>(ctx, a, nullptr, 0, k, w, n, bias, residual, out, &taken)));
     if (taken) return TSM_OK;
+    if (rows == 1 && k >= 32) {
+        // One row of activations and a matrix that is not a whole number of groups (GPT-2's 50257 x 1600 vocabulary head): the
+        // streamed kernel takes the rows up to the last whole group, the generic kernel the few that are left (it alone took
+        // 49 us for that head, the streamed kernel 20 us for 50256 of its rows).
+        using F = Fmt<KIND>;
+        const int nb = k / 32;
+        int unit = F::G;   // rows that make a whole number of groups: G / gcd(nb, G)
+        for (int d = F::G; d >= 1; d /= 2)
+            if (nb % d == 0) { unit = F::G / d; break; }
+        const int main = n - n % unit;
+        if (main >= 1024 && main < n) {
+            TSM_TRY((launch_stream<KIND, 1>(ctx, a, nullptr, 0, k, w, main, bias, residual, out, &taken)));
+            if (taken) {
+                const int left = n - main;
+                TSM_CUDA(ctx, launch_chained(ctx, matvec_generic_kernel<KIND>, dim3((unsigned)((left + 3) / 4)), dim3(128), 0,
+                                             w + (int64_t)main * nb * F::B, left, nb, a, 1, bias ? bias + main : (const float*)nullptr,
+                                             residual ? residual + main : (const float*)nullptr, out + main));
+                count_launch(ctx);
+                TSM_LAUNCH_CHECK(ctx);
+                return TSM_OK;
+            }
+        }
+    }
     if (rows > 4 && umma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_umma(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     if (rows > 4 && pipe_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_pipe(ctx, a, rows, k, w, KIND, n, bias, residual, out);
     if (rows > 4 && mma_product_fits(a, rows, k, w, KIND, n)) return launch_block_matmul_mma(ctx, a, rows, k, w, KIND, n, bias, residual, out);

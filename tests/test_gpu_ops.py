@@ -66,6 +66,7 @@ SHAPES = [(1, 37, 64), (3, 5, 1280), (2, 9, 4096),            # the reference's 
           (1, 2048, 2048), (3, 1024, 4096), (1, 256, 14336),  # aligned rows, long rows
           (1, 4096, 14336), (3, 300, 14336), (4, 77, 28672), (2, 130, 16384), (1, 50, 10240), (4, 33, 12288),  # long rows in pieces: row tiles of up to 32 rows, a last tile that is short
           (8, 128, 2048), (16, 64, 576), (1, 7, 4096), (1, 4097, 256),
+          (1, 2051, 1600), (1, 1027, 576), (1, 1025, 96),     # one row, not a whole number of groups: the streamed kernel and the generic one share the rows
           (5, 40, 1536), (33, 48, 4096), (64, 200, 1600), (100, 96, 576), (64, 1024, 2048), (17, 72, 14336),  # tensor-core kernels
           (64, 304, 4096), (70, 100, 1024), (12, 2400, 512), (24, 48, 2048), (64, 5000, 256), (40, 2500, 1024),  # odd group counts, two slabs of activation rows, several groups per CTA
           (64, 19008, 256), (9, 20000, 512), (70, 19200, 256),  # many rows: 16-row groups, one warp per group
