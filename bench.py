@@ -183,6 +183,12 @@ def time_kernel(torch, stream, fn, repeats):
 L2_TURNOVER = 256 << 20   # bytes of other weights read between two uses of one copy: twice the 126 MB L2
 
 
+def weight_copies(size):
+    """Copies of a weight matrix of `size` bytes that time_rotating cycles through: between two uses of one copy the others
+    bring at least L2_TURNOVER bytes through L2."""
+    return 1 + -(-L2_TURNOVER // size)
+
+
 def rotating_weights(dev, kind, n, k):
     """Copies of one quantised n x k weight matrix (normal(0, 0.02), quantised on the device in slabs of at most 4096 rows),
     enough of them that a launch reading the copies in turn never finds its weights in L2: L2_TURNOVER bytes of other copies
@@ -191,7 +197,7 @@ def rotating_weights(dev, kind, n, k):
     import ctypes as C
     size = n * (k // 32) * BLOCK[kind]
     stride = (size + 255) & ~255
-    copies = 1 + -(-L2_TURNOVER // size)
+    copies = weight_copies(size)
     wbuf = dev.alloc(stride * copies)
     src = dev.alloc(min(n, 4096) * k * 4)
     for r0 in range(0, n, 4096):

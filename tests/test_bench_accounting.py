@@ -29,3 +29,13 @@ def test_ragged_lengths_are_the_configured_range_and_reproducible():
     a, b = bench.draw_lengths(w, 0), bench.draw_lengths(w, 0)
     assert a.tolist() == b.tolist() and len(a) == 64
     assert a.min() >= 128 and a.max() <= 4096
+
+
+def test_rotating_weight_copies_put_twice_l2_between_two_uses_of_a_copy():
+    """The sweep's launches read copies of the weights in turn (bench.rotating_weights); between two uses of one copy the
+    others must bring at least 256 MB, twice the 126 MB L2, through the cache, whatever the matrix's size."""
+    for n, k, block in [(576, 1536, 18), (2048, 8192, 34), (4096, 14336, 20), (14336, 4096, 18), (128256, 4096, 34), (128256, 4096, 18)]:
+        size = n * (k // 32) * block
+        copies = bench.weight_copies(size)
+        assert copies >= 2 and (copies - 1) * size >= 256 << 20
+        assert (copies - 2) * size < 256 << 20          # and no more copies than that takes
